@@ -1,0 +1,128 @@
+"""ctypes binding of libgear_b200.so (the C ABI declared in include/gear_b200.h).
+
+The library is the product: if it is missing the import fails loudly -- there is
+no Python or CPU fallback for any device operation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "lib" / "libgear_b200.so"
+
+OK = 0
+ERR_INVALID, ERR_CUDA, ERR_NOMEM, ERR_STATE, ERR_TIMEOUT, ERR_NCCL, ERR_UNSUPPORTED = range(1, 8)
+
+ST_LOOKBACK_TIMEOUT = 0x1
+ST_L1_RESUMMED = 0x2
+ST_BAD_PRIORITY = 0x4
+ST_BAD_REQUEST = 0x8
+ST_LEN_CLAMPED = 0x10
+ST_SCAN_ABORTED = 0x20
+STATUS_WORDS = 4
+
+PART = 4096
+RES_HOST, RES_HBM = 1, 2
+PAD_INACTIVE, PAD_HEAD, PAD_TAIL = 0, 1, 2
+MAX_COLUMNS = 16
+SEARCH_SCALE = 1
+
+FILL_U32, FILL_F32_NORMAL, FILL_F32_UNIFORM, FILL_F32_LOGNORMAL, FILL_I32_RANGE, FILL_U8, FILL_U01_F64 = range(7)
+
+
+class GearError(RuntimeError):
+    """A C-ABI call returned a non-zero status (the reference raises RuntimeError
+    for argument/state errors, include/gear_errors.h:3-8)."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[gear_b200 status {code}] {msg}")
+        self.code = code
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        if os.environ.get("GEAR_B200_AUTOBUILD", "1") != "0":
+            from . import build as _b
+            _b.build()
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m gear_b200.build` "
+                "(gear_b200 has no fallback path)")
+    return C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
+
+
+lib = _load()
+
+vp, i32, i64, u64, f64 = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_double
+pi64 = C.POINTER(C.c_int64)
+pi32 = C.POINTER(C.c_int32)
+
+_SIGS = {
+    "gearb_last_error": (C.c_char_p, []),
+    "gearb_version": (C.c_int, []),
+    "gearb_init": (C.c_int, [C.c_int]),
+    "gearb_device_count": (C.c_int, [C.POINTER(C.c_int)]),
+    "gearb_table_create": (C.c_int, [pi64, C.c_int, i64, i64, C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
+    "gearb_table_connect": (C.c_int, [vp, pi64]),
+    "gearb_table_destroy": (C.c_int, [vp]),
+    "gearb_table_layout": (C.c_int, [vp, pi64, pi64, pi64]),
+    "gearb_table_host_ptr": (vp, [vp]),
+    "gearb_table_device_ptr": (vp, [vp]),
+    "gearb_table_upload": (C.c_int, [vp, vp]),
+    "gearb_table_write": (C.c_int, [vp, i64, vp, i64, vp]),
+    "gearb_table_read": (C.c_int, [vp, i64, vp, i64]),
+    "gearb_handler_create": (C.c_int, [vp, i64, i64, i64, i64, i64, C.POINTER(vp)]),
+    "gearb_handler_destroy": (C.c_int, [vp]),
+    "gearb_handler_set": (C.c_int, [vp, pi64, C.c_int, pi32, pi64, pi32]),
+    "gearb_handler_sub": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, vp, vp, vp, pi64]),
+    "gearb_handler_subcopy": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, vp, vp, vp]),
+    "gearb_handler_gather": (C.c_int, [vp, pi32, C.c_int, vp, vp, vp, i64, C.POINTER(vp), C.c_int, vp, vp]),
+    "gearb_handler_view": (C.c_int, [vp, i64, C.c_int, C.POINTER(vp), pi64]),
+    "gearb_vcopy": (C.c_int, [vp, vp, vp, vp, vp, i64, i64, vp]),
+    "gearb_copy": (C.c_int, [vp, vp, vp, vp, i64, i64, vp]),
+    "gearb_indexset_create": (C.c_int, [i64, i64, i64, C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
+    "gearb_indexset_destroy": (C.c_int, [vp]),
+    "gearb_indexset_timesteps": (vp, [vp]),
+    "gearb_indexset_weights": (vp, [vp]),
+    "gearb_scan_scratch_bytes": (i64, [i64]),
+    "gearb_scan": (C.c_int, [vp, i64, vp, vp, vp, i64, vp, vp]),
+    "gearb_search": (C.c_int, [vp, vp, i64, vp, i64, C.c_int, vp, vp, vp]),
+    "gearb_sample_uniform": (C.c_int, [i64, vp, i64, vp, vp]),
+    "gearb_decode": (C.c_int, [vp, i64, i64, vp, i64, vp, vp, vp, vp]),
+    "gearb_sampler_create": (C.c_int, [i64, C.POINTER(vp)]),
+    "gearb_sampler_destroy": (C.c_int, [vp]),
+    "gearb_sampler_scan": (C.c_int, [vp, vp, vp]),
+    "gearb_sampler_search": (C.c_int, [vp, vp, i64, C.c_int, vp, vp]),
+    "gearb_sampler_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
+    "gearb_sampler_result": (C.c_int, [vp, vp, C.POINTER(f64), pi32]),
+    "gearb_fill": (C.c_int, [vp, i64, C.c_int, u64, u64, f64, f64, vp]),
+}
+
+# Entry points added after the first slice are optional at bind time so that the
+# symbol test can report exactly which declared names are missing.
+for _name, (_res, _args) in _SIGS.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return lib.gearb_last_error().decode("utf-8", "replace")
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise GearError(code, last_error())
+
+
+def call(name: str, *args):
+    check(getattr(lib, name)(*args))
+
+
+def declared_symbols() -> list[str]:
+    """Names declared in include/gear_b200.h (parsed from the header text)."""
+    import re
+    text = (PKG.parent / "include" / "gear_b200.h").read_text()
+    return sorted(set(re.findall(r"\b(gearb_[a-z0-9_]+)\s*\(", text)))

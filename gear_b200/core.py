@@ -1,0 +1,417 @@
+"""Object layer over the C ABI: table, handler, index set, sampler.
+
+torch tensors appear here only as owners of device memory and as the source of
+the current CUDA stream; every operation is one call into libgear_b200.so.
+Names follow the reference's host classes (TrajectoryTable, SubscribePattern,
+CpuTrajectoryStorageHandler, Indexset; src/storage, include/index/set.h).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _native as N
+from ._native import GearError, call, lib
+
+__all__ = [
+    "GearError", "SubscribePattern", "TrajectoryTable", "StorageHandler", "Indexset",
+    "PrioritySampler", "scan", "search", "sample_uniform", "decode", "fill", "vcopy", "copy",
+    "init", "device_count",
+]
+
+
+def _stream(stream=None) -> C.c_void_p:
+    if stream is None:
+        if not torch.cuda.is_available():
+            return C.c_void_p(0)
+        stream = torch.cuda.current_stream()
+    return C.c_void_p(stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream))
+
+
+def _dev_i64(t: torch.Tensor, what: str) -> C.c_void_p:
+    if t.dtype != torch.int64 or not t.is_cuda or not t.is_contiguous():
+        raise GearError(N.ERR_INVALID, f"{what} must be a contiguous int64 CUDA tensor")
+    return C.c_void_p(t.data_ptr())
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+_TYPESTR = {torch.float32: "<f4", torch.float64: "<f8", torch.int32: "<i4", torch.int64: "<i8",
+            torch.uint8: "|u1"}
+
+
+class _DevArray:
+    def __init__(self, ptr: int, n: int, dtype: torch.dtype):
+        self.__cuda_array_interface__ = {"shape": (int(n),), "typestr": _TYPESTR[dtype],
+                                         "data": (int(ptr), False), "version": 2}
+
+
+def device_view(ptr: int, n: int, dtype: torch.dtype) -> torch.Tensor:
+    """Zero-copy tensor over device memory owned by the native library."""
+    return torch.as_tensor(_DevArray(ptr, n, dtype), device="cuda")
+
+
+def init(device: int = 0) -> None:
+    """gear::cuda::init (src/cuda/init.cu:6-13)."""
+    call("gearb_init", int(device))
+
+
+def device_count() -> int:
+    n = C.c_int(0)
+    call("gearb_device_count", C.byref(n))
+    return n.value
+
+
+@dataclass(frozen=True)
+class SubscribePattern:
+    """SubscribePattern (include/storage/handler.h:17-31): which timesteps of a
+    column a request takes, relative to its timestep, and where padding goes."""
+    offset: int = 0
+    length: int = 1
+    pad: int = N.PAD_TAIL
+
+
+class TrajectoryTable:
+    """TrajectoryTable (src/storage/table.cc): layout [trajectory][column][t][elem]."""
+
+    def __init__(self, row_bytes: Sequence[int], trajectory_length: int, capacity: int,
+                 residency: int = N.RES_HOST, key: int = 0, create: bool = True):
+        self.row_bytes = [int(r) for r in row_bytes]
+        self.trajectory_length = int(trajectory_length)
+        self.capacity = int(capacity)
+        self._h = C.c_void_p(0)
+        rb = (C.c_int64 * len(self.row_bytes))(*self.row_bytes)
+        call("gearb_table_create", rb, len(self.row_bytes), self.trajectory_length, self.capacity,
+             int(residency), int(key), int(bool(create)), C.byref(self._h))
+        stride, nbytes = C.c_int64(0), C.c_int64(0)
+        accu = (C.c_int64 * (len(self.row_bytes) + 1))()
+        call("gearb_table_layout", self._h, C.byref(stride), C.byref(nbytes), accu)
+        self.trajectory_stride, self.nbytes, self.accu = stride.value, nbytes.value, list(accu)
+        self.connected = False
+
+    def connect(self) -> int:
+        n = C.c_int64(0)
+        call("gearb_table_connect", self._h, C.byref(n))
+        self.connected = True
+        return n.value
+
+    @property
+    def ncolumns(self) -> int:
+        return len(self.row_bytes)
+
+    @property
+    def host_ptr(self) -> int:
+        return lib.gearb_table_host_ptr(self._h) or 0
+
+    @property
+    def device_ptr(self) -> int:
+        return lib.gearb_table_device_ptr(self._h) or 0
+
+    def host_view(self) -> np.ndarray:
+        """uint8 view of the host image (no copy)."""
+        p = self.host_ptr
+        if not p:
+            raise GearError(N.ERR_STATE, "the table has no host copy")
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(self.nbytes,))
+
+    def upload(self, stream=None) -> None:
+        call("gearb_table_upload", self._h, _stream(stream))
+
+    def write(self, offset: int, data: np.ndarray, stream=None) -> None:
+        data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        call("gearb_table_write", self._h, int(offset), data.ctypes.data_as(C.c_void_p), data.nbytes,
+             _stream(stream))
+        if torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()  # `data` may be freed by the caller
+
+    def read(self, offset: int, nbytes: int) -> np.ndarray:
+        out = np.empty(int(nbytes), np.uint8)
+        call("gearb_table_read", self._h, int(offset), out.ctypes.data_as(C.c_void_p), int(nbytes))
+        return out
+
+    def column_offset(self, column: int) -> int:
+        return self.accu[column] * self.trajectory_length
+
+    def close(self) -> None:
+        if self._h:
+            lib.gearb_table_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class StorageHandler:
+    """CpuTrajectoryStorageHandler (src/storage/handler.cc) over either residency."""
+
+    def __init__(self, table: TrajectoryTable, global_capacity: Optional[int] = None,
+                 wregion=(0, 0), rregion: Optional[tuple] = None):
+        self.table = table  # keeps the table alive: the native handler only borrows it
+        gc = table.capacity if global_capacity is None else int(global_capacity)
+        rregion = (0, table.capacity) if rregion is None else rregion
+        self._h = C.c_void_p(0)
+        call("gearb_handler_create", table._h, gc, int(wregion[0]), int(wregion[1]),
+             int(rregion[0]), int(rregion[1]), C.byref(self._h))
+        self.patterns: dict[int, SubscribePattern] = {}
+        self._status: Optional[torch.Tensor] = None
+
+    def set(self, cids: Sequence[int], patterns: Sequence[SubscribePattern]) -> None:
+        n = len(cids)
+        call("gearb_handler_set", self._h, (C.c_int64 * n)(*[int(c) for c in cids]), n,
+             (C.c_int32 * n)(*[int(p.offset) for p in patterns]),
+             (C.c_int64 * n)(*[int(p.length) for p in patterns]),
+             (C.c_int32 * n)(*[int(p.pad) for p in patterns]))
+        for c, p in zip(cids, patterns):
+            self.patterns[int(c)] = p
+
+    def sub(self, idx, ts, ln, column: int):
+        """(src_off, dst_off, copy_len, slot_bytes) on the host (handler.cc:78-131)."""
+        idx = np.ascontiguousarray(idx, np.int64); ts = np.ascontiguousarray(ts, np.int64)
+        ln = np.ascontiguousarray(ln, np.int64)
+        if not (len(idx) == len(ts) == len(ln)):
+            raise GearError(N.ERR_INVALID, "Spans describing target properties have inconsistent size")
+        n = len(idx)
+        s = np.zeros(n, np.int64); d = np.zeros(n, np.int64); b = np.zeros(n, np.int64)
+        slot = C.c_int64(0)
+        vp = lambda a: a.ctypes.data_as(C.c_void_p)
+        call("gearb_handler_sub", self._h, vp(idx), vp(ts), vp(ln), n, int(column), vp(s), vp(d), vp(b),
+             C.byref(slot))
+        return s, d, b, slot.value
+
+    def status_tensor(self, device) -> torch.Tensor:
+        if self._status is None or self._status.device != torch.device(device):
+            self._status = torch.zeros(N.STATUS_WORDS, dtype=torch.int32, device=device)
+        return self._status
+
+    def subcopy(self, idx: torch.Tensor, ts: torch.Tensor, ln: torch.Tensor, column: int,
+                dst: torch.Tensor, stream=None) -> None:
+        """handler.subcopy (src/storage/pybind.cc:140-146)."""
+        self.gather([column], idx, ts, ln, [dst], zero_fill=False, stream=stream)
+
+    def gather(self, columns: Sequence[int], idx: torch.Tensor, ts: torch.Tensor, ln: torch.Tensor,
+               dsts: Sequence[torch.Tensor], zero_fill: bool = True, stream=None) -> None:
+        n = idx.numel()
+        if not (ts.numel() == n and ln.numel() == n):
+            raise GearError(N.ERR_INVALID, "idx, ts and len must have the same number of entries")
+        if len(dsts) != len(columns):
+            raise GearError(N.ERR_INVALID, "one destination per column is required")
+        for c, d in zip(columns, dsts):
+            p = self.patterns.get(int(c))
+            if p is not None:
+                need = n * p.length * self.table.row_bytes[int(c)]
+                if not d.is_cuda or not d.is_contiguous() or d.numel() * d.element_size() < need:
+                    raise GearError(N.ERR_INVALID,
+                                    f"destination of column {c} must be a contiguous CUDA tensor of >= {need} bytes")
+        if n == 0 or not columns:
+            return
+        nc = len(columns)
+        st = self.status_tensor(idx.device)
+        call("gearb_handler_gather", self._h, (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
+             _dev_i64(idx, "idx"), _dev_i64(ts, "ts"), _dev_i64(ln, "len"), n,
+             (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)), _ptr(st),
+             _stream(stream))
+
+    def view(self, index: int, column: int) -> np.ndarray:
+        """Host bytes of one column of one trajectory (handler.cc:223-233)."""
+        p, b = C.c_void_p(0), C.c_int64(0)
+        call("gearb_handler_view", self._h, int(index), int(column), C.byref(p), C.byref(b))
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(b.value,))
+
+    def status(self) -> int:
+        return 0 if self._status is None else int(self._status[0].item())
+
+    def close(self) -> None:
+        if self._h:
+            lib.gearb_handler_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Indexset:
+    """Indexset (include/index/set.h:191-251): float32 weights + int64 timesteps."""
+
+    def __init__(self, global_capacity: int, local_capacity: int, index_offset: int,
+                 shared: bool = False, key: int = 0, create: bool = False):
+        self.global_capacity, self.local_capacity = int(global_capacity), int(local_capacity)
+        self.index_offset, self.is_sharing, self.shm_key = int(index_offset), bool(shared), int(key)
+        self._h = C.c_void_p(0)
+        call("gearb_indexset_create", self.global_capacity, self.local_capacity, self.index_offset,
+             int(bool(shared)), int(key), int(bool(create)), C.byref(self._h))
+        tp = lib.gearb_indexset_timesteps(self._h)
+        wp = lib.gearb_indexset_weights(self._h)
+        self.timesteps_np = np.ctypeslib.as_array(C.cast(tp, C.POINTER(C.c_int64)), shape=(self.local_capacity,))
+        self.weights_np = np.ctypeslib.as_array(C.cast(wp, C.POINTER(C.c_float)), shape=(self.local_capacity,))
+
+    @property
+    def timesteps(self) -> torch.Tensor:
+        return torch.from_numpy(self.timesteps_np)
+
+    @property
+    def weights(self) -> torch.Tensor:
+        return torch.from_numpy(self.weights_np)
+
+    def close(self) -> None:
+        if self._h:
+            self.timesteps_np = self.weights_np = None
+            lib.gearb_indexset_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# --------------------------------------------------------------------------- #
+# sampling
+# --------------------------------------------------------------------------- #
+def _nparts(n: int) -> int:
+    return (n + N.PART - 1) // N.PART
+
+
+def scan(priorities: torch.Tensor, stream=None):
+    """Functional scan: returns (cdf f32[n], l1 f64[nparts+1], status i32[4])."""
+    if priorities.dtype != torch.float32 or not priorities.is_cuda or not priorities.is_contiguous():
+        raise GearError(N.ERR_INVALID, "priorities must be a contiguous float32 CUDA tensor")
+    n = priorities.numel()
+    dev = priorities.device
+    cdf = torch.empty(n, dtype=torch.float32, device=dev)
+    l1 = torch.empty(_nparts(max(n, 1)) + 1, dtype=torch.float64, device=dev)
+    sb = lib.gearb_scan_scratch_bytes(max(n, 1))
+    scratch = torch.empty(sb, dtype=torch.uint8, device=dev)
+    status = torch.zeros(N.STATUS_WORDS, dtype=torch.int32, device=dev)
+    call("gearb_scan", _ptr(priorities), n, _ptr(cdf), _ptr(l1), _ptr(scratch), sb, _ptr(status),
+         _stream(stream))
+    return cdf, l1, status
+
+
+def search(cdf: torch.Tensor, l1: torch.Tensor, variates: torch.Tensor, scale: bool = False,
+           status: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
+        raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
+    out = torch.empty(variates.numel(), dtype=torch.int64, device=variates.device)
+    call("gearb_search", _ptr(cdf), _ptr(l1), cdf.numel(), _ptr(variates), variates.numel(),
+         N.SEARCH_SCALE if scale else 0, _ptr(out), _ptr(status), _stream(stream))
+    return out
+
+
+def sample_uniform(n: int, u01: torch.Tensor, stream=None) -> torch.Tensor:
+    if u01.dtype != torch.float64 or not u01.is_cuda or not u01.is_contiguous():
+        raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
+    out = torch.empty(u01.numel(), dtype=torch.int64, device=u01.device)
+    call("gearb_sample_uniform", int(n), _ptr(u01), u01.numel(), _ptr(out), _stream(stream))
+    return out
+
+
+def decode(flat: torch.Tensor, trajectory_length: int, lengths: Optional[torch.Tensor] = None,
+           index_offset: int = 0, stream=None):
+    b = flat.numel()
+    idx = torch.empty(b, dtype=torch.int64, device=flat.device)
+    ts = torch.empty_like(idx); ln = torch.empty_like(idx)
+    call("gearb_decode", _dev_i64(flat, "flat"), b, int(trajectory_length), _ptr(lengths),
+         int(index_offset), _ptr(idx), _ptr(ts), _ptr(ln), _stream(stream))
+    return idx, ts, ln
+
+
+class PrioritySampler:
+    """Owns the cumulative table of n priorities on the current device."""
+
+    def __init__(self, n: int):
+        self.n = int(n)
+        self._h = C.c_void_p(0)
+        call("gearb_sampler_create", self.n, C.byref(self._h))
+        c, l, s = C.c_void_p(0), C.c_void_p(0), C.c_void_p(0)
+        call("gearb_sampler_buffers", self._h, C.byref(c), C.byref(l), C.byref(s))
+        self.cdf_ptr, self.l1_ptr, self.status_ptr = c.value, l.value, s.value
+
+    def scan(self, priorities: torch.Tensor, stream=None) -> None:
+        if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
+            raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
+        call("gearb_sampler_scan", self._h, _ptr(priorities), _stream(stream))
+
+    def search(self, variates: torch.Tensor, scale: bool = False, out: Optional[torch.Tensor] = None,
+               stream=None) -> torch.Tensor:
+        if variates.dtype != torch.float64 or not variates.is_cuda:
+            raise GearError(N.ERR_INVALID, "variates must be a float64 CUDA tensor")
+        if out is None:
+            out = torch.empty(variates.numel(), dtype=torch.int64, device=variates.device)
+        call("gearb_sampler_search", self._h, _ptr(variates), variates.numel(),
+             N.SEARCH_SCALE if scale else 0, _ptr(out), _stream(stream))
+        return out
+
+    def result(self, stream=None):
+        """(total, status words) after synchronising the stream."""
+        total = C.c_double(0.0)
+        st = (C.c_int32 * N.STATUS_WORDS)()
+        call("gearb_sampler_result", self._h, _stream(stream), C.byref(total), st)
+        return total.value, list(st)
+
+    @property
+    def cdf(self) -> torch.Tensor:
+        """Level-2 table as a tensor view of the sampler's own memory."""
+        return device_view(self.cdf_ptr, self.n, torch.float32)
+
+    @property
+    def l1(self) -> torch.Tensor:
+        return device_view(self.l1_ptr, _nparts(self.n) + 1, torch.float64)
+
+    @property
+    def status(self) -> torch.Tensor:
+        return device_view(self.status_ptr, N.STATUS_WORDS, torch.int32)
+
+    def close(self) -> None:
+        if self._h:
+            lib.gearb_sampler_destroy(self._h)
+            self._h = C.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def fill(dst: torch.Tensor, kind: int, seed: int, stream_id: int = 0, a: float = 0.0, b: float = 1.0,
+         count: Optional[int] = None, stream=None) -> None:
+    """Seeded synthetic data written on the device (benchmark tables)."""
+    cnt = dst.numel() if count is None else int(count)
+    call("gearb_fill", _ptr(dst), cnt, int(kind), C.c_uint64(seed), C.c_uint64(stream_id), float(a),
+         float(b), _stream(stream))
+
+
+def fill_ptr(ptr: int, count: int, kind: int, seed: int, stream_id: int = 0, a: float = 0.0,
+             b: float = 1.0, stream=None) -> None:
+    call("gearb_fill", C.c_void_p(ptr), int(count), int(kind), C.c_uint64(seed), C.c_uint64(stream_id),
+         float(a), float(b), _stream(stream))
+
+
+def vcopy(src_ptr: int, dst: torch.Tensor, src_off: torch.Tensor, dst_off: torch.Tensor,
+          lengths: torch.Tensor, max_length: int, stream=None) -> None:
+    """libgear.core.vcopy (src/cuda/copy.cu:175-215)."""
+    n = min(src_off.numel(), dst_off.numel(), lengths.numel())
+    call("gearb_vcopy", C.c_void_p(src_ptr), _ptr(dst), _dev_i64(src_off, "src_offsets"),
+         _dev_i64(dst_off, "dst_offsets"), _dev_i64(lengths, "strides"), n, int(max_length),
+         _stream(stream))
+
+
+def copy(src_ptr: int, dst: torch.Tensor, src_off: torch.Tensor, dst_off: torch.Tensor, length: int,
+         stream=None) -> None:
+    """libgear.core.copy (src/cuda/copy.cu:138-173)."""
+    n = min(src_off.numel(), dst_off.numel())
+    call("gearb_copy", C.c_void_p(src_ptr), _ptr(dst), _dev_i64(src_off, "src_offsets"),
+         _dev_i64(dst_off, "dst_offsets"), n, int(length), _stream(stream))

@@ -1,0 +1,624 @@
+// Host side of libgear_b200: the objects behind the C ABI (trajectory table,
+// storage handler, index set, sampler) and the extern "C" entry points.
+//
+// These mirror, in behaviour and not in code, the reference's host classes:
+//   TrajectoryTable             src/storage/table.cc
+//   CpuTrajectoryStorageHandler src/storage/handler.cc
+//   SharedMemory / CudaUVMemory src/memory/shared_memory.cc, cuda_uvm.cc
+//   CudaMemory                  src/memory/cuda_memory.cc
+//   Indexset / StatusTableShard include/index/set.h
+// with 64-bit sizes everywhere and status codes instead of assert/exit.
+#include <errno.h>
+#include <sys/ipc.h>
+#include <sys/shm.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <optional>
+#include <vector>
+
+#include "common.h"
+
+namespace gearb {
+
+std::string &last_error() {
+  static thread_local std::string e;
+  return e;
+}
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  last_error() = buf;
+  return code;
+}
+
+int sm_count() {
+  static std::mutex mu;
+  static std::map<int, int> cache;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 1;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(dev);
+  if (it != cache.end()) return it->second;
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+  cache[dev] = n;
+  return n;
+}
+
+static bool have_cuda_device() {
+  static int state = -1;
+  if (state < 0) {
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    state = (e == cudaSuccess && n > 0) ? 1 : 0;
+  }
+  return state == 1;
+}
+
+static inline int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+// A block of host memory the GPU can read in place: a System-V segment that is
+// registered with CUDA (SharedMemory, shared_memory.cc:35-63), or
+// cudaHostAlloc(Mapped|Portable) memory (CudaUVMemory, cuda_uvm.cc:29-32).
+// Without a CUDA device (CPU-only hosts) it degrades to plain memory so that
+// the host-side logic stays usable.
+struct HostBlock {
+  void *addr = nullptr;
+  void *dev_alias = nullptr;
+  int64_t size = 0;
+  int shmid = -1;
+  bool is_shm = false, creator = false, registered = false, cuda_alloc = false;
+
+  int alloc(int64_t bytes, int key, bool create) {
+    if (addr) return GEARB_OK;
+    size = bytes;
+    const size_t sz = static_cast<size_t>(bytes > 0 ? bytes : 1);
+    if (key != 0) {
+      shmid = create ? shmget(key, sz, IPC_CREAT | 0777) : shmget(key, sz, 0666);
+      if (shmid == -1)
+        return fail(GEARB_ERR_STATE, "shmget(key=%d, size=%zu, create=%d) failed: errno %d", key, sz,
+                    (int)create, errno);
+      void *p = shmat(shmid, nullptr, 0);
+      if (p == reinterpret_cast<void *>(-1))
+        return fail(GEARB_ERR_STATE, "shmat(key=%d) failed: errno %d", key, errno);
+      addr = p;
+      is_shm = true;
+      creator = create;
+      if (have_cuda_device()) {
+        cudaError_t e = cudaHostRegister(addr, sz, cudaHostRegisterMapped | cudaHostRegisterPortable);
+        if (e != cudaSuccess) {
+          (void)cudaGetLastError();
+          release();
+          return fail(GEARB_ERR_CUDA, "cudaHostRegister(%zu bytes) failed: %s", sz,
+                      cudaGetErrorString(e));
+        }
+        registered = true;
+      }
+    } else if (have_cuda_device()) {
+      cudaError_t e = cudaHostAlloc(&addr, sz, cudaHostAllocMapped | cudaHostAllocPortable);
+      if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        addr = nullptr;
+        return fail(GEARB_ERR_NOMEM, "cudaHostAlloc(%zu bytes) failed: %s", sz, cudaGetErrorString(e));
+      }
+      cuda_alloc = true;
+      std::memset(addr, 0, sz);
+    } else {
+      if (posix_memalign(&addr, 256, round_up(static_cast<int64_t>(sz), 256)) != 0) {
+        addr = nullptr;
+        return fail(GEARB_ERR_NOMEM, "host allocation of %zu bytes failed", sz);
+      }
+      std::memset(addr, 0, sz);
+    }
+    if (registered || cuda_alloc) {
+      if (cudaHostGetDevicePointer(&dev_alias, addr, 0) != cudaSuccess) {
+        (void)cudaGetLastError();
+        dev_alias = nullptr;
+      }
+    }
+    return GEARB_OK;
+  }
+
+  void release() {
+    if (!addr) return;
+    if (registered) (void)cudaHostUnregister(addr);
+    if (is_shm) {
+      shmdt(addr);
+      if (creator && shmid != -1) shmctl(shmid, IPC_RMID, nullptr);
+    } else if (cuda_alloc) {
+      (void)cudaFreeHost(addr);
+    } else {
+      std::free(addr);
+    }
+    addr = dev_alias = nullptr;
+    registered = cuda_alloc = is_shm = false;
+  }
+  ~HostBlock() { release(); }
+};
+
+struct Pattern {
+  int32_t offset;
+  int64_t length;
+  int32_t pad;
+};
+
+}  // namespace gearb
+
+using namespace gearb;
+
+struct gearb_table {
+  std::vector<int64_t> row_bytes, accu;
+  int64_t T = 0, capacity = 0, traj_stride = 0, nbytes = 0;
+  int residency = 0, shm_key = 0;
+  bool create = true, connected = false;
+  HostBlock host;
+  void *hbm = nullptr;
+  int hbm_device = -1;
+
+  const uint8_t *device_base() const {
+    if (hbm) return static_cast<const uint8_t *>(hbm);
+    return static_cast<const uint8_t *>(host.dev_alias);
+  }
+};
+
+struct gearb_handler {
+  gearb_table *table = nullptr;
+  int64_t global_capacity = 0, w_lb = 0, w_hb = 0, r_lb = 0, r_hb = 0;
+  std::vector<std::optional<Pattern>> patterns;
+};
+
+struct gearb_indexset {
+  int64_t global_capacity = 0, local_capacity = 0, index_offset = 0;
+  HostBlock mem;
+  int64_t *timesteps = nullptr;
+  float *weights = nullptr;
+};
+
+struct gearb_sampler {
+  int64_t n = 0, nparts = 0, scratch_bytes = 0;
+  int device = 0;
+  float *cdf = nullptr;
+  double *l1 = nullptr;
+  void *scratch = nullptr;
+  int32_t *status = nullptr;
+};
+
+extern "C" {
+
+const char *gearb_last_error(void) { return last_error().c_str(); }
+int gearb_version(void) { return 100; }
+
+int gearb_init(int device) {
+  GEARB_CUDA(cudaSetDevice(device));
+  GEARB_CUDA(cudaFree(nullptr));  // force context creation, like the first runtime call would
+  return GEARB_OK;
+}
+
+int gearb_device_count(int *count) {
+  GEARB_REQUIRE(count, "device_count: null argument");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  *count = n;
+  return GEARB_OK;
+}
+
+/* ------------------------------ table ---------------------------------- */
+int gearb_table_create(const int64_t *row_bytes, int ncols, int64_t trajectory_length,
+                       int64_t capacity, int residency, int shm_key, int create,
+                       gearb_table **out) {
+  GEARB_REQUIRE(out && row_bytes, "table_create: null argument");
+  GEARB_REQUIRE(ncols > 0 && ncols <= GEARB_MAX_COLUMNS, "table_create: %d columns (1..%d supported)",
+                ncols, GEARB_MAX_COLUMNS);
+  GEARB_REQUIRE(trajectory_length > 0 && capacity > 0,
+                "table_create: trajectory_length and capacity must be positive");
+  GEARB_REQUIRE((residency & (GEARB_RES_HOST | GEARB_RES_HBM)) != 0 &&
+                    (residency & ~(GEARB_RES_HOST | GEARB_RES_HBM)) == 0,
+                "table_create: residency must combine GEARB_RES_HOST / GEARB_RES_HBM");
+  auto *t = new gearb_table();
+  t->row_bytes.assign(row_bytes, row_bytes + ncols);
+  t->accu.resize(ncols + 1);
+  int64_t sum = 0;
+  for (int c = 0; c < ncols; ++c) {
+    if (row_bytes[c] <= 0 || row_bytes[c] > (int64_t(1) << 30)) {
+      delete t;
+      return fail(GEARB_ERR_INVALID, "table_create: column %d has row size %lld", c,
+                  (long long)row_bytes[c]);
+    }
+    t->accu[c] = sum;
+    sum += row_bytes[c];
+  }
+  t->accu[ncols] = sum;
+  t->T = trajectory_length;
+  t->capacity = capacity;
+  t->traj_stride = sum * trajectory_length;
+  t->nbytes = t->traj_stride * capacity;
+  t->residency = residency;
+  t->shm_key = shm_key;
+  t->create = create != 0;
+  *out = t;
+  return GEARB_OK;
+}
+
+int gearb_table_connect(gearb_table *t, int64_t *nbytes) {
+  GEARB_REQUIRE(t, "table_connect: null table");
+  if (!t->connected) {
+    if (t->residency & GEARB_RES_HOST) {
+      int rc = t->host.alloc(t->nbytes, t->shm_key, t->create);
+      if (rc != GEARB_OK) return rc;
+    }
+    if ((t->residency & GEARB_RES_HBM) && !t->hbm) {
+      GEARB_CUDA(cudaGetDevice(&t->hbm_device));
+      cudaError_t e = cudaMalloc(&t->hbm, static_cast<size_t>(round_up(t->nbytes, 256)));
+      if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        t->hbm = nullptr;
+        return fail(GEARB_ERR_NOMEM, "cudaMalloc(%lld bytes) for the HBM table failed: %s",
+                    (long long)t->nbytes, cudaGetErrorString(e));
+      }
+      if (!(t->residency & GEARB_RES_HOST)) GEARB_CUDA(cudaMemset(t->hbm, 0, static_cast<size_t>(t->nbytes)));
+    }
+    t->connected = true;
+  }
+  if (nbytes) *nbytes = t->nbytes;
+  return GEARB_OK;
+}
+
+int gearb_table_destroy(gearb_table *t) {
+  if (!t) return GEARB_OK;
+  if (t->hbm) (void)cudaFree(t->hbm);
+  delete t;
+  return GEARB_OK;
+}
+
+int gearb_table_layout(const gearb_table *t, int64_t *trajectory_stride, int64_t *nbytes,
+                       int64_t *accu) {
+  GEARB_REQUIRE(t, "table_layout: null table");
+  if (trajectory_stride) *trajectory_stride = t->traj_stride;
+  if (nbytes) *nbytes = t->nbytes;
+  if (accu) std::memcpy(accu, t->accu.data(), t->accu.size() * sizeof(int64_t));
+  return GEARB_OK;
+}
+
+void *gearb_table_host_ptr(const gearb_table *t) { return t ? t->host.addr : nullptr; }
+void *gearb_table_device_ptr(const gearb_table *t) {
+  return t ? const_cast<uint8_t *>(t->device_base()) : nullptr;
+}
+
+int gearb_table_upload(gearb_table *t, void *stream) {
+  GEARB_REQUIRE(t && t->connected, "table_upload: table is not connected");
+  GEARB_REQUIRE(t->host.addr, "table_upload: table has no host copy");
+  if (!t->hbm) {
+    GEARB_CUDA(cudaGetDevice(&t->hbm_device));
+    cudaError_t e = cudaMalloc(&t->hbm, static_cast<size_t>(round_up(t->nbytes, 256)));
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      t->hbm = nullptr;
+      return fail(GEARB_ERR_NOMEM, "cudaMalloc(%lld bytes) for the HBM table failed: %s",
+                  (long long)t->nbytes, cudaGetErrorString(e));
+    }
+    t->residency |= GEARB_RES_HBM;
+  }
+  GEARB_CUDA(cudaMemcpyAsync(t->hbm, t->host.addr, static_cast<size_t>(t->nbytes),
+                             cudaMemcpyHostToDevice, as_stream(stream)));
+  return GEARB_OK;
+}
+
+int gearb_table_write(gearb_table *t, int64_t offset, const void *src, int64_t bytes, void *stream) {
+  GEARB_REQUIRE(t && t->connected, "table_write: table is not connected");
+  GEARB_REQUIRE(offset >= 0 && bytes >= 0 && offset + bytes <= t->nbytes,
+                "table_write: range [%lld, +%lld) outside the table (%lld bytes)", (long long)offset,
+                (long long)bytes, (long long)t->nbytes);
+  if (bytes == 0) return GEARB_OK;
+  GEARB_REQUIRE(src, "table_write: null source");
+  if (t->host.addr) std::memcpy(static_cast<char *>(t->host.addr) + offset, src, static_cast<size_t>(bytes));
+  if (t->hbm)
+    GEARB_CUDA(cudaMemcpyAsync(static_cast<char *>(t->hbm) + offset, src, static_cast<size_t>(bytes),
+                               cudaMemcpyDefault, as_stream(stream)));
+  return GEARB_OK;
+}
+
+int gearb_table_read(const gearb_table *t, int64_t offset, void *dst, int64_t bytes) {
+  GEARB_REQUIRE(t && t->connected, "table_read: table is not connected");
+  GEARB_REQUIRE(offset >= 0 && bytes >= 0 && offset + bytes <= t->nbytes,
+                "table_read: range outside the table");
+  if (bytes == 0) return GEARB_OK;
+  GEARB_REQUIRE(dst, "table_read: null destination");
+  if (t->hbm) {
+    GEARB_CUDA(cudaMemcpy(dst, static_cast<const char *>(t->hbm) + offset, static_cast<size_t>(bytes),
+                          cudaMemcpyDefault));
+  } else {
+    std::memcpy(dst, static_cast<const char *>(t->host.addr) + offset, static_cast<size_t>(bytes));
+  }
+  return GEARB_OK;
+}
+
+/* ------------------------------ handler -------------------------------- */
+int gearb_handler_create(gearb_table *t, int64_t global_capacity, int64_t w_lb, int64_t w_hb,
+                         int64_t r_lb, int64_t r_hb, gearb_handler **out) {
+  GEARB_REQUIRE(t && out, "handler_create: null argument");
+  auto *h = new gearb_handler();
+  h->table = t;
+  h->global_capacity = global_capacity;
+  h->w_lb = w_lb; h->w_hb = w_hb; h->r_lb = r_lb; h->r_hb = r_hb;
+  h->patterns.resize(t->row_bytes.size());
+  *out = h;
+  return GEARB_OK;
+}
+
+int gearb_handler_destroy(gearb_handler *h) {
+  delete h;
+  return GEARB_OK;
+}
+
+int gearb_handler_set(gearb_handler *h, const int64_t *cids, int n, const int32_t *offsets,
+                      const int64_t *lengths, const int32_t *pads) {
+  GEARB_REQUIRE(h && (n == 0 || (cids && offsets && lengths && pads)), "handler_set: null argument");
+  for (int i = 0; i < n; ++i) {
+    GEARB_REQUIRE(cids[i] >= 0 && cids[i] < (int64_t)h->patterns.size(),
+                  "handler_set: column id %lld out of range", (long long)cids[i]);
+    GEARB_REQUIRE(lengths[i] >= 0 && lengths[i] < (int64_t(1) << 31),
+                  "handler_set: pattern length %lld out of range", (long long)lengths[i]);
+    GEARB_REQUIRE(pads[i] >= GEARB_PAD_INACTIVE && pads[i] <= GEARB_PAD_TAIL,
+                  "handler_set: unknown pad option %d", pads[i]);
+  }
+  for (int i = 0; i < n; ++i) h->patterns[cids[i]] = Pattern{offsets[i], lengths[i], pads[i]};
+  return GEARB_OK;
+}
+
+static int pattern_of(const gearb_handler *h, int column, const Pattern **out) {
+  GEARB_REQUIRE(h, "null handler");
+  GEARB_REQUIRE(column >= 0 && column < (int)h->patterns.size(), "column id %d out of range", column);
+  if (!h->patterns[column].has_value())
+    return fail(GEARB_ERR_STATE, "Subscribing a column without setting its SubscribePattern.");
+  *out = &*h->patterns[column];
+  return GEARB_OK;
+}
+
+int gearb_handler_sub(const gearb_handler *h, const int64_t *idx, const int64_t *ts,
+                      const int64_t *len, int64_t n, int column, int64_t *src_off,
+                      int64_t *dst_off, int64_t *copy_len, int64_t *slot_bytes) {
+  const Pattern *pat = nullptr;
+  int rc = pattern_of(h, column, &pat);
+  if (rc != GEARB_OK) return rc;
+  GEARB_REQUIRE(n == 0 || (idx && ts && len && src_off && dst_off && copy_len),
+                "handler_sub: null argument");
+  const gearb_table *t = h->table;
+  const int64_t row = t->row_bytes[column];
+  const int64_t column_ofst = t->accu[column] * t->T;
+  const int64_t slot = pat->length * row;
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t start = ts[i] + pat->offset;
+    if (start < 0) start = 0;
+    int64_t end = start + pat->length;
+    if (end > len[i]) end = len[i];
+    int64_t bytes = (end - start) * row;
+    if (bytes < 0) bytes = 0;
+    copy_len[i] = bytes;
+    src_off[i] = idx[i] * t->traj_stride + column_ofst + start * row;
+    dst_off[i] = slot * i + (pat->pad == GEARB_PAD_HEAD ? slot - bytes : 0);
+  }
+  if (slot_bytes) *slot_bytes = slot;
+  return GEARB_OK;
+}
+
+int gearb_handler_gather(gearb_handler *h, const int32_t *columns, int ncols, const int64_t *idx,
+                         const int64_t *ts, const int64_t *len, int64_t n, void *const *dst,
+                         int zero_fill, int32_t *status, void *stream) {
+  GEARB_REQUIRE(h && h->table, "handler_gather: null handler");
+  GEARB_REQUIRE(ncols >= 0 && ncols <= GEARB_MAX_COLUMNS, "handler_gather: %d columns", ncols);
+  GEARB_REQUIRE(n >= 0, "handler_gather: negative request count");
+  if (n == 0 || ncols == 0) return GEARB_OK;
+  GEARB_REQUIRE(columns && idx && ts && len && dst, "handler_gather: null argument");
+  const gearb_table *t = h->table;
+  if (!t->connected || !t->device_base())
+    return fail(GEARB_ERR_STATE, "handler_gather: the table has no device-visible copy (connect it first)");
+  GatherParams p{};
+  p.table = t->device_base();
+  p.idx = idx; p.ts = ts; p.len = len;
+  p.n = n;
+  p.traj_stride = t->traj_stride;
+  p.capacity = t->capacity;
+  p.T = t->T;
+  p.status = status;
+  p.zero_fill = zero_fill ? 1 : 0;
+  p.chunk_bytes = 2048;
+  int64_t chunks = 0;
+  int used = 0;
+  for (int i = 0; i < ncols; ++i) {
+    const Pattern *pat = nullptr;
+    int rc = pattern_of(h, columns[i], &pat);
+    if (rc != GEARB_OK) return rc;
+    GEARB_REQUIRE(dst[i], "handler_gather: null destination for column %d", columns[i]);
+    const int64_t row = t->row_bytes[columns[i]];
+    const int64_t slot = row * pat->length;
+    if (slot == 0) continue;
+    GatherColumn &c = p.cols[used++];
+    c.col_offset = t->accu[columns[i]] * t->T;
+    c.dst = static_cast<uint8_t *>(dst[i]);
+    c.row = static_cast<int32_t>(row);
+    c.pat_offset = pat->offset;
+    c.pat_length = static_cast<int32_t>(pat->length);
+    c.pad_head = pat->pad == GEARB_PAD_HEAD;
+    c.chunk_first = static_cast<int32_t>(chunks);
+    const int64_t cc = (slot + p.chunk_bytes - 1) / p.chunk_bytes;
+    c.chunk_count = static_cast<int32_t>(cc);
+    chunks += cc;
+    GEARB_REQUIRE(chunks < (int64_t(1) << 30), "handler_gather: request too large");
+  }
+  p.ncols = used;
+  p.chunks_per_request = static_cast<int32_t>(chunks);
+  if (used == 0) return GEARB_OK;
+  return launch_gather(p, as_stream(stream));
+}
+
+int gearb_handler_subcopy(gearb_handler *h, const int64_t *idx, const int64_t *ts,
+                          const int64_t *len, int64_t n, int column, void *dst, int32_t *status,
+                          void *stream) {
+  const int32_t col = column;
+  void *d = dst;
+  return gearb_handler_gather(h, &col, 1, idx, ts, len, n, &d, 0, status, stream);
+}
+
+int gearb_handler_view(const gearb_handler *h, int64_t index, int column, void **host_ptr,
+                       int64_t *bytes) {
+  GEARB_REQUIRE(h && h->table && host_ptr && bytes, "handler_view: null argument");
+  const gearb_table *t = h->table;
+  GEARB_REQUIRE(column >= 0 && column < (int)t->row_bytes.size(), "handler_view: column %d out of range",
+                column);
+  GEARB_REQUIRE(index >= 0 && index < t->capacity, "handler_view: trajectory %lld out of range",
+                (long long)index);
+  if (!t->host.addr) return fail(GEARB_ERR_STATE, "handler_view: the table has no host copy");
+  *host_ptr = static_cast<char *>(t->host.addr) + index * t->traj_stride + t->accu[column] * t->T;
+  *bytes = t->row_bytes[column] * t->T;
+  return GEARB_OK;
+}
+
+int gearb_vcopy(const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off,
+                const int64_t *lengths, int64_t n, int64_t max_length, void *stream) {
+  GEARB_REQUIRE(lengths || n == 0, "vcopy: null lengths");
+  return launch_vcopy(static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), src_off, dst_off,
+                      lengths, 0, n, max_length, as_stream(stream));
+}
+
+int gearb_copy(const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off, int64_t n,
+               int64_t length, void *stream) {
+  return launch_vcopy(static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), src_off, dst_off,
+                      nullptr, length, n, length, as_stream(stream));
+}
+
+/* ------------------------------ index set ------------------------------ */
+int gearb_indexset_create(int64_t global_capacity, int64_t local_capacity, int64_t index_offset,
+                          int shared, int shm_key, int create, gearb_indexset **out) {
+  GEARB_REQUIRE(out, "indexset_create: null argument");
+  GEARB_REQUIRE(local_capacity > 0 && global_capacity >= local_capacity && index_offset >= 0,
+                "indexset_create: bad capacities");
+  auto *s = new gearb_indexset();
+  s->global_capacity = global_capacity;
+  s->local_capacity = local_capacity;
+  s->index_offset = index_offset;
+  const int64_t ts_bytes = round_up(local_capacity * 8, 128);
+  const int64_t w_bytes = round_up(local_capacity * 4, 128);
+  int rc = s->mem.alloc(ts_bytes + w_bytes, shared ? shm_key : 0, create != 0);
+  if (rc != GEARB_OK) {
+    delete s;
+    return rc;
+  }
+  s->timesteps = static_cast<int64_t *>(s->mem.addr);
+  s->weights = reinterpret_cast<float *>(static_cast<char *>(s->mem.addr) + ts_bytes);
+  *out = s;
+  return GEARB_OK;
+}
+
+int gearb_indexset_destroy(gearb_indexset *s) {
+  delete s;
+  return GEARB_OK;
+}
+int64_t *gearb_indexset_timesteps(const gearb_indexset *s) { return s ? s->timesteps : nullptr; }
+float *gearb_indexset_weights(const gearb_indexset *s) { return s ? s->weights : nullptr; }
+
+/* ------------------------------ sampling ------------------------------- */
+int64_t gearb_scan_scratch_bytes(int64_t n) { return n > 0 ? scan_scratch_bytes(n) : 0; }
+
+int gearb_scan(const float *priorities, int64_t n, float *cdf, double *l1, void *scratch,
+               int64_t scratch_bytes, int32_t *status, void *stream) {
+  return launch_scan(priorities, n, cdf, l1, scratch, scratch_bytes, status, 1, as_stream(stream));
+}
+
+int gearb_search(const float *cdf, const double *l1, int64_t n, const double *variates, int64_t b,
+                 int flags, int64_t *out_index, int32_t *status, void *stream) {
+  return launch_search(cdf, l1, n, variates, b, flags, out_index, status, as_stream(stream));
+}
+
+int gearb_sample_uniform(int64_t n, const double *u01, int64_t b, int64_t *out_index, void *stream) {
+  return launch_uniform(n, u01, b, out_index, as_stream(stream));
+}
+
+int gearb_decode(const int64_t *flat, int64_t b, int64_t trajectory_length, const int64_t *lengths,
+                 int64_t index_offset, int64_t *idx, int64_t *ts, int64_t *len, void *stream) {
+  return launch_decode(flat, b, trajectory_length, lengths, index_offset, idx, ts, len,
+                       as_stream(stream));
+}
+
+int gearb_sampler_create(int64_t n, gearb_sampler **out) {
+  GEARB_REQUIRE(out && n > 0, "sampler_create: n must be positive");
+  auto *s = new gearb_sampler();
+  s->n = n;
+  s->nparts = (n + GEARB_PART - 1) / GEARB_PART;
+  s->scratch_bytes = scan_scratch_bytes(n);
+  cudaError_t e = cudaGetDevice(&s->device);
+  if (e == cudaSuccess) e = cudaMalloc(&s->cdf, static_cast<size_t>(round_up(n * 4, 256)));
+  if (e == cudaSuccess) e = cudaMalloc(&s->l1, static_cast<size_t>(round_up((s->nparts + 1) * 8, 256)));
+  if (e == cudaSuccess) e = cudaMalloc(&s->scratch, static_cast<size_t>(s->scratch_bytes));
+  if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
+  if (e == cudaSuccess) e = cudaMemset(s->scratch, 0, static_cast<size_t>(s->scratch_bytes));
+  if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    gearb_sampler_destroy(s);
+    return fail(GEARB_ERR_NOMEM, "sampler_create(%lld): %s", (long long)n, cudaGetErrorString(e));
+  }
+  *out = s;
+  return GEARB_OK;
+}
+
+int gearb_sampler_destroy(gearb_sampler *s) {
+  if (!s) return GEARB_OK;
+  if (s->cdf) (void)cudaFree(s->cdf);
+  if (s->l1) (void)cudaFree(s->l1);
+  if (s->scratch) (void)cudaFree(s->scratch);
+  if (s->status) (void)cudaFree(s->status);
+  delete s;
+  return GEARB_OK;
+}
+
+int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) {
+  GEARB_REQUIRE(s, "sampler_scan: null sampler");
+  return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
+                     as_stream(stream));
+}
+
+int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, int flags,
+                         int64_t *out_index, void *stream) {
+  GEARB_REQUIRE(s, "sampler_search: null sampler");
+  return launch_search(s->cdf, s->l1, s->n, variates, b, flags, out_index, s->status,
+                       as_stream(stream));
+}
+
+int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status) {
+  GEARB_REQUIRE(s, "sampler_buffers: null sampler");
+  if (cdf) *cdf = s->cdf;
+  if (l1) *l1 = s->l1;
+  if (status) *status = s->status;
+  return GEARB_OK;
+}
+
+int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t *status) {
+  GEARB_REQUIRE(s, "sampler_result: null sampler");
+  GEARB_CUDA(cudaStreamSynchronize(as_stream(stream)));
+  if (total)
+    GEARB_CUDA(cudaMemcpy(total, s->l1 + s->nparts, sizeof(double), cudaMemcpyDeviceToHost));
+  if (status)
+    GEARB_CUDA(cudaMemcpy(status, s->status, sizeof(int32_t) * GEARB_STATUS_WORDS,
+                          cudaMemcpyDeviceToHost));
+  return GEARB_OK;
+}
+
+/* ------------------------------ fill ----------------------------------- */
+int gearb_fill(void *dst, int64_t count, int kind, uint64_t seed, uint64_t stream_id, double a,
+               double b, void *stream) {
+  return launch_fill(dst, count, kind, seed, stream_id, a, b, as_stream(stream));
+}
+
+}  // extern "C"

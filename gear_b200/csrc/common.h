@@ -1,0 +1,97 @@
+// Shared host-side helpers of libgear_b200: error text, CUDA checks, launch
+// parameter structs exchanged between the C ABI layer and the kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+
+#include "gear_b200.h"
+
+namespace gearb {
+
+// Thread-local text of the last failure; returned by gearb_last_error().
+std::string &last_error();
+int fail(int code, const char *fmt, ...);
+
+#define GEARB_CUDA(expr)                                                              \
+  do {                                                                                \
+    cudaError_t e__ = (expr);                                                         \
+    if (e__ != cudaSuccess)                                                           \
+      return ::gearb::fail(GEARB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,            \
+                           cudaGetErrorString(e__), __FILE__, __LINE__);              \
+  } while (0)
+
+#define GEARB_REQUIRE(cond, ...)                                                      \
+  do {                                                                                \
+    if (!(cond)) return ::gearb::fail(GEARB_ERR_INVALID, __VA_ARGS__);                \
+  } while (0)
+
+inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// ---- scan ------------------------------------------------------------------
+// Layout of the scan scratch block (all offsets 256-byte aligned):
+//   header   : ScanHeader
+//   state[P] : uint32  (epoch << 2) | {0 none, 1 aggregate published, 2 prefix published}
+//   agg[P]   : float64 partition aggregates
+struct ScanHeader {
+  unsigned int ticket;  // next partition to hand out
+  unsigned int done;    // CTAs that have finished
+  unsigned int epoch;   // launch counter; state words of other epochs read as "none"
+  unsigned int pad[61];
+};
+static_assert(sizeof(ScanHeader) == 256, "header is one 256-byte block");
+
+int64_t scan_scratch_bytes(int64_t n);
+// fresh != 0: scratch contents are unknown, clear them first (one memset).
+int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
+                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream);
+int launch_search(const float *cdf, const double *l1, int64_t n, const double *u, int64_t b,
+                  int flags, int64_t *out, int32_t *status, cudaStream_t stream);
+int launch_uniform(int64_t n, const double *u01, int64_t b, int64_t *out, cudaStream_t stream);
+int launch_decode(const int64_t *flat, int64_t b, int64_t T, const int64_t *lengths,
+                  int64_t index_offset, int64_t *idx, int64_t *ts, int64_t *len,
+                  cudaStream_t stream);
+
+// ---- gather ----------------------------------------------------------------
+struct GatherColumn {
+  int64_t col_offset;  // byte offset of the column inside one trajectory (accu * T)
+  uint8_t *dst;        // [n, pat_length * row] bytes
+  int32_t row;         // bytes per timestep
+  int32_t pat_offset;  // SubscribePattern::offset
+  int32_t pat_length;  // SubscribePattern::length
+  int32_t pad_head;    // 1 when PadOption::kHead
+  int32_t chunk_first; // first chunk id of this column inside a request
+  int32_t chunk_count; // chunks this column's slot is cut into
+};
+
+struct GatherParams {
+  const uint8_t *table;
+  const int64_t *idx, *ts, *len;
+  int64_t n;
+  int64_t traj_stride;
+  int64_t capacity;  // trajectories in the table (bounds check)
+  int64_t T;         // trajectory_length (length clamp)
+  int32_t *status;   // may be null
+  int32_t ncols;
+  int32_t chunks_per_request;
+  int32_t chunk_bytes;
+  int32_t zero_fill;
+  GatherColumn cols[GEARB_MAX_COLUMNS];
+};
+
+int launch_gather(const GatherParams &p, cudaStream_t stream);
+int launch_vcopy(const uint8_t *src, uint8_t *dst, const int64_t *src_off,
+                 const int64_t *dst_off, const int64_t *lengths, int64_t fixed_length,
+                 int64_t n, int64_t max_length, cudaStream_t stream);
+
+int launch_fill(void *dst, int64_t count, int kind, uint64_t seed, uint64_t stream_id, double a,
+                double b, cudaStream_t stream);
+
+}  // namespace gearb

@@ -1,0 +1,611 @@
+// Single-pass construction of the two-level cumulative priority table.
+//
+// Stands where the reference's launch_prefix_sum / launch_sum would be
+// (src/cuda/one_dim_prefix_sum.cu:125-273, src/cuda/one_dim_sum.cu:22-99).
+// The reference kernel is unfinished and has no caller; what is kept from it is
+// the shape of the addition tree (four values per thread in sequence, :40-49; a
+// Hillis-Steele shuffle scan over the lanes of a warp, :23-28; a second scan
+// over warp totals, :192-201; partition descriptors with a status word for the
+// look-back, one_dim_prefix_sum.cuh:5-10).
+//
+// Level 2 (cdf): each 4096-entry partition is scanned on its own, in float32,
+// with a fixed tree, so the stored values do not depend on scheduling:
+//   tile  = 128 values, lane l owns 4l..4l+3: s0=x0, s1=s0+x1, s2=s1+x2, s3=s2+x3
+//           I = shuffle scan of s3 over lanes; E = I(l-1); tile total = I(31)
+//   warp  = 4 tiles in sequence: c(k+1) = c(k) + total(k)
+//   CTA   = 8 warps: Y = shuffle scan of c(4); X(w) = Y(w-1)
+//   value = ((X + c(k)) + E) + s_j, then a running maximum over the partition
+//           (max is exact, so its order is free) to make the table monotone.
+// Level 1 (l1): float64 exclusive offsets of the partitions, defined as the
+// in-order sum of the partitions' last cdf entries.  They come out of a
+// decoupled look-back over published aggregates.  The look-back adds in a
+// timing-dependent grouping, so every float64 addition is checked with TwoSum;
+// while all of them are exact the result equals the in-order sum bit for bit.
+// If one is inexact (or a bounded wait gives up) the last CTA to finish
+// recomputes l1 strictly in order from the per-partition aggregates.
+//
+// Execution: a persistent, warp-specialised CTA of 10 warps.
+//   warp 8 (loader)    takes tickets (a group of up to 4 consecutive partitions
+//                      each), and stages one partition (16 KiB) per ring slot in
+//                      shared memory with a bulk asynchronous copy that signals
+//                      an mbarrier;
+//   warps 0-7 (compute) wait for a slot, pull it into registers, free the slot,
+//                      scan, and store the cdf with 16-byte streaming stores;
+//   warp 9 (look-back) receives each partition's aggregate through a small ring
+//                      in shared memory, chains the aggregates of a group in
+//                      order, publishes one descriptor per group and looks back
+//                      over earlier groups while the other warps keep streaming.
+// Descriptors carry their own validity: each 64-bit word is (tag << 32 | half of
+// a float64), so a reader needs no fence and one 32-byte read per predecessor.
+// Every wait is bounded; a wait that runs out raises a flag instead of hanging.
+//
+// HBM traffic: 4 B read + 4 B written per priority, plus ~16 B per partition.
+#include "common.h"
+
+namespace gearb {
+namespace {
+
+constexpr int kComputeWarps = 8;
+constexpr int kComputeThreads = kComputeWarps * 32;
+constexpr int kThreads = kComputeThreads + 64;  // + loader warp + look-back warp
+constexpr int kTilesPerWarp = 4;
+constexpr int kPart = kComputeWarps * kTilesPerWarp * 128;
+static_assert(kPart == GEARB_PART, "partition size is part of the ABI");
+constexpr int kStages = 4;   // ring slots of one partition each
+constexpr int kGroupMax = 4; // partitions per ticket
+constexpr int kRing = 16;    // aggregate ring entries (compute -> look-back)
+
+constexpr unsigned kSpinLimit = 1u << 20;  // polls of a shared-memory word / mbarrier before giving up
+constexpr unsigned kLookLimit = 1u << 17;  // polls (x ~100 ns) of a predecessor descriptor
+
+constexpr unsigned kHdrRebuild = 1u;  // header flag: level 1 must be re-summed in order
+constexpr unsigned kFull = 0xffffffffu;
+
+// ---- small PTX wrappers -------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// 1-D bulk asynchronous copy global -> this CTA's shared memory; completes on `bar`.
+__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, unsigned bytes, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_addr(dst_smem)),
+      "l"(src), "r"(bytes), "r"(smem_addr(bar))
+      : "memory");
+}
+__device__ __forceinline__ void named_barrier_compute() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kComputeThreads) : "memory");
+}
+// Same barrier, but every thread also learns whether any of them raised `flag`.
+__device__ __forceinline__ bool named_barrier_compute_or(bool flag) {
+  unsigned r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<unsigned>(flag)), "n"(kComputeThreads)
+      : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void st_u64(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void ld_desc(const unsigned long long *p, unsigned long long w[4]) {
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[0]), "=l"(w[1]) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[2]), "=l"(w[3]) : "l"(p + 2) : "memory");
+}
+__device__ __forceinline__ unsigned ld_u32_relaxed(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ float hs_sum(float v, int lane) {
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float t = __shfl_up_sync(kFull, v, d);
+    if (lane >= d) v = __fadd_rn(t, v);
+  }
+  return v;
+}
+__device__ __forceinline__ float hs_max(float v, int lane) {
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float t = __shfl_up_sync(kFull, v, d);
+    if (lane >= d) v = fmaxf(t, v);
+  }
+  return v;
+}
+
+// s = a + b in float64; raises `inexact` when the addition rounded.
+__device__ __forceinline__ double checked_add(double a, double b, bool &inexact) {
+  const double s = __dadd_rn(a, b);
+  const double bb = __dsub_rn(s, a);
+  const double err = __dadd_rn(__dsub_rn(a, __dsub_rn(s, bb)), __dsub_rn(b, bb));
+  inexact |= (err != 0.0);
+  return s;
+}
+
+// A float64 split over two self-validating 64-bit words.
+__device__ __forceinline__ void publish(unsigned long long *two_words, double v, unsigned tag) {
+  const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(v));
+  const unsigned long long t = static_cast<unsigned long long>(tag) << 32;
+  st_u64(two_words, t | (bits >> 32));
+  st_u64(two_words + 1, t | (bits & 0xffffffffull));
+}
+__device__ __forceinline__ bool decode(unsigned long long hi, unsigned long long lo, unsigned tag, double &v) {
+  if (static_cast<unsigned>(hi >> 32) != tag || static_cast<unsigned>(lo >> 32) != tag) return false;
+  v = __longlong_as_double(static_cast<long long>(((hi & 0xffffffffull) << 32) | (lo & 0xffffffffull)));
+  return true;
+}
+
+struct ScanArgs {
+  const float *prio;
+  float *cdf;
+  double *l1;
+  ScanHeader *hdr;
+  unsigned long long *desc;  // per group: {agg hi, agg lo, prefix hi, prefix lo}
+  double *agg;               // per partition, for the in-order rebuild
+  int32_t *status;
+  int64_t n;
+  unsigned nparts;
+  unsigned group;   // partitions per ticket
+  unsigned ngroups;
+};
+
+struct __align__(128) Smem {
+  float4 stage[kStages][kPart / 4];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  int stage_part[kStages];         // partition staged in the slot, -1 = no more work
+  float wt[2][kComputeWarps];      // warp totals, double-buffered by iteration parity
+  float wm[2][kComputeWarps];      // warp maxima
+  volatile int ring_part[kRing];   // aggregate ring: partition id (-1 = end)
+  volatile float ring_agg[kRing];
+  volatile unsigned ring_head;     // entries produced
+  volatile unsigned ring_tail;     // entries consumed
+  volatile unsigned abort;         // a bounded wait ran out somewhere in this CTA
+};
+
+__device__ __forceinline__ void raise_abort(Smem &sm, const ScanArgs &a) {
+  sm.abort = 1u;
+  atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_SCAN_ABORTED);
+}
+
+// ------------------------------------------------------------------ loader warp
+__device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
+  unsigned it = 0;
+  bool stop = false;
+  while (!stop) {
+    unsigned t = 0;
+    if (lane == 0) t = atomicAdd(&a.hdr->ticket, 1u);
+    t = __shfl_sync(kFull, t, 0);
+    const bool last = t >= a.ngroups;
+    const unsigned count = last ? 1u : min(a.group, a.nparts - t * a.group);
+    for (unsigned k = 0; k < count && !stop; ++k, ++it) {
+      const unsigned s = it % kStages;
+      const unsigned parity = ((it / kStages) & 1u) ^ 1u;
+      unsigned spins = 0;
+      bool ok = false;
+      while (!(ok = mbar_try_wait(&sm.empty[s], parity))) {
+        if (++spins > kSpinLimit || sm.abort) break;
+      }
+      if (!__all_sync(kFull, ok)) {
+        if (lane == 0 && !sm.abort) raise_abort(sm, a);
+        stop = true;
+        break;
+      }
+      if (last) {
+        if (lane == 0) {
+          sm.stage_part[s] = -1;
+          mbar_arrive(&sm.full[s]);
+        }
+        stop = true;
+        break;
+      }
+      const unsigned p = t * a.group + k;
+      const int64_t base = static_cast<int64_t>(p) * kPart;
+      const int64_t valid = (a.n - base < kPart) ? (a.n - base) : kPart;
+      const unsigned bulk_bytes = static_cast<unsigned>((valid * 4) & ~int64_t(15));
+      if (valid < kPart) {
+        // Ragged last partition: the part a bulk copy cannot express is filled by hand.
+        float *st = reinterpret_cast<float *>(sm.stage[s]);
+        for (int e = static_cast<int>(bulk_bytes / 4) + lane; e < kPart; e += 32)
+          st[e] = (e < valid) ? a.prio[base + e] : 0.f;
+        __syncwarp();
+      }
+      if (lane == 0) {
+        sm.stage_part[s] = static_cast<int>(p);
+        if (bulk_bytes) {
+          mbar_arrive_expect_tx(&sm.full[s], bulk_bytes);
+          bulk_load(sm.stage[s], a.prio + base, bulk_bytes, &sm.full[s]);
+        } else {
+          mbar_arrive(&sm.full[s]);
+        }
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------- compute warps
+__device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
+  bool bad = false;
+  for (unsigned it = 0;; ++it) {
+    const unsigned s = it % kStages;
+    const unsigned parity = (it / kStages) & 1u;
+    unsigned spins = 0;
+    bool ok = false;
+    while (!(ok = mbar_try_wait(&sm.full[s], parity))) {
+      if (++spins > kSpinLimit || sm.abort) break;
+    }
+    // A warp that has to leave (its wait ran out, or the loader posted the end marker) still
+    // walks, on zeros, to the first barrier below, which doubles as a vote: either every
+    // compute warp goes on or every one leaves, so no warp is ever left alone in a barrier.
+    const bool lost = !__all_sync(kFull, ok);
+    if (lost && lane == 0 && !sm.abort) raise_abort(sm, a);
+    const int part_raw = lost ? -1 : sm.stage_part[s];  // -1: the loader has no more work
+    const bool leave = part_raw < 0;
+    const int part = leave ? 0 : part_raw;
+    float4 x[kTilesPerWarp];
+#pragma unroll
+    for (int k = 0; k < kTilesPerWarp; ++k)
+      x[k] = leave ? make_float4(0.f, 0.f, 0.f, 0.f) : sm.stage[s][(warp * kTilesPerWarp + k) * 32 + lane];
+    __syncwarp();
+    if (lane == 0 && !leave) mbar_arrive(&sm.empty[s]);
+
+    const int64_t base = static_cast<int64_t>(part) * kPart;
+    const bool full = base + kPart <= a.n;
+    const int buf = it & 1;
+    float sv[kTilesPerWarp][4], E[kTilesPerWarp], c[kTilesPerWarp + 1];
+
+    // ---- lane sums, tile scans, warp carry
+    c[0] = 0.f;
+#pragma unroll
+    for (int k = 0; k < kTilesPerWarp; ++k) {
+      bad |= !(x[k].x >= 0.f) | !(x[k].y >= 0.f) | !(x[k].z >= 0.f) | !(x[k].w >= 0.f);
+      sv[k][0] = x[k].x;
+      sv[k][1] = __fadd_rn(sv[k][0], x[k].y);
+      sv[k][2] = __fadd_rn(sv[k][1], x[k].z);
+      sv[k][3] = __fadd_rn(sv[k][2], x[k].w);
+      const float I = hs_sum(sv[k][3], lane);
+      const float up = __shfl_up_sync(kFull, I, 1);
+      E[k] = lane == 0 ? 0.f : up;
+      c[k + 1] = __fadd_rn(c[k], __shfl_sync(kFull, I, 31));
+    }
+    if (lane == 0) sm.wt[buf][warp] = c[kTilesPerWarp];
+    if (named_barrier_compute_or(leave)) break;
+
+    // ---- scan of the warp totals (every warp repeats it; lanes >= 8 hold zeros)
+    float y = lane < kComputeWarps ? sm.wt[buf][lane] : 0.f;
+    y = hs_sum(y, lane);
+    const float xs = __shfl_sync(kFull, y, warp == 0 ? 0 : warp - 1);
+    const float X = warp == 0 ? 0.f : xs;
+
+    // ---- values, then the running maximum inside the warp
+    float run = 0.f, pre[kTilesPerWarp];
+#pragma unroll
+    for (int k = 0; k < kTilesPerWarp; ++k) {
+      const float b1 = __fadd_rn(X, c[k]);
+      const float b2 = __fadd_rn(b1, E[k]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sv[k][j] = __fadd_rn(b2, sv[k][j]);
+      float lane_top = sv[k][3];
+      if (!full) {
+        // Entries past n take no part in the maximum (their value is never stored).
+        const int64_t e = base + ((warp * kTilesPerWarp + k) * 32 + lane) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (e + j >= a.n) sv[k][j] = 0.f;
+        lane_top = fmaxf(fmaxf(sv[k][0], sv[k][1]), fmaxf(sv[k][2], sv[k][3]));
+      }
+      const float M = hs_max(lane_top, lane);
+      const float up = __shfl_up_sync(kFull, M, 1);
+      pre[k] = fmaxf(run, lane == 0 ? 0.f : up);
+      run = fmaxf(run, __shfl_sync(kFull, M, 31));
+    }
+    if (lane == 0) sm.wm[buf][warp] = run;
+    named_barrier_compute();
+
+    float G = 0.f;
+    for (int w = 0; w < warp; ++w) G = fmaxf(G, sm.wm[buf][w]);
+
+    // ---- the last warp knows the partition's last (= largest) entry: hand it over
+    if (warp == kComputeWarps - 1 && lane == 0) {
+      const unsigned h = sm.ring_head;
+      unsigned sp = 0;
+      while (h - sm.ring_tail >= kRing) {
+        if (++sp > kSpinLimit || sm.abort) break;
+      }
+      sm.ring_part[h % kRing] = part;
+      sm.ring_agg[h % kRing] = fmaxf(G, run);
+      __threadfence_block();
+      sm.ring_head = h + 1;
+    }
+
+    // ---- store
+    if (full) {
+      float4 *dst = reinterpret_cast<float4 *>(a.cdf + base);
+#pragma unroll
+      for (int k = 0; k < kTilesPerWarp; ++k) {
+        const float m = fmaxf(pre[k], G);
+        float4 o;
+        o.x = fmaxf(sv[k][0], m);
+        o.y = fmaxf(sv[k][1], m);
+        o.z = fmaxf(sv[k][2], m);
+        o.w = fmaxf(sv[k][3], m);
+        __stcs(dst + (warp * kTilesPerWarp + k) * 32 + lane, o);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < kTilesPerWarp; ++k) {
+        const float m = fmaxf(pre[k], G);
+        const int64_t e = base + ((warp * kTilesPerWarp + k) * 32 + lane) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (e + j < a.n) a.cdf[e + j] = fmaxf(sv[k][j], m);
+      }
+    }
+  }
+  if (warp == kComputeWarps - 1 && lane == 0) {  // tell the look-back warp there is no more
+    const unsigned h = sm.ring_head;
+    unsigned sp = 0;
+    while (h - sm.ring_tail >= kRing && ++sp < kSpinLimit && !sm.abort) {}
+    sm.ring_part[h % kRing] = -1;
+    __threadfence_block();
+    sm.ring_head = h + 1;
+  }
+  if (__any_sync(kFull, bad) && lane == 0)
+    atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_BAD_PRIORITY);
+}
+
+// --------------------------------------------------------------- look-back warp
+__device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int lane) {
+  const unsigned tagA = (epoch << 2) | 1u, tagP = (epoch << 2) | 2u;
+  bool inexact = false;
+  double run = 0.0;   // in-order sum of the current group's aggregates so far
+  double lane_incl = 0.0;  // lane k keeps the inclusive sum after the group's k-th partition
+  unsigned have = 0;
+  for (;;) {
+    // ---- pop one aggregate
+    const unsigned tl = sm.ring_tail;
+    unsigned spins = 0;
+    bool ok = true;
+    while (sm.ring_head == tl) {
+      if (++spins > kSpinLimit || sm.abort) {
+        ok = false;
+        break;
+      }
+      __nanosleep(32);
+    }
+    if (!__all_sync(kFull, ok)) {
+      if (lane == 0 && !sm.abort) raise_abort(sm, a);
+      break;
+    }
+    const int part = sm.ring_part[tl % kRing];
+    const float aggf = sm.ring_agg[tl % kRing];
+    __syncwarp();
+    if (lane == 0) sm.ring_tail = tl + 1;
+    if (part < 0) break;
+
+    const double ad = static_cast<double>(aggf);
+    if (lane == 0) __stcg(&a.agg[part], ad);
+    const unsigned g = static_cast<unsigned>(part) / a.group;
+    const unsigned k = static_cast<unsigned>(part) - g * a.group;
+    if (k != have) {  // aggregates of a group arrive in order; anything else is a logic error
+      if (lane == 0) raise_abort(sm, a);
+      break;
+    }
+    run = (k == 0) ? ad : checked_add(run, ad, inexact);
+    if (lane == static_cast<int>(k)) lane_incl = run;
+    have = k + 1;
+    const unsigned in_group = min(a.group, a.nparts - g * a.group);
+    if (have < in_group) continue;
+    have = 0;
+
+    // ---- the group is complete: publish its aggregate, look back, publish its prefix
+    const double gsum = run;
+    unsigned long long *mine = a.desc + static_cast<size_t>(g) * 4;
+    double excl = 0.0;
+    bool gave_up = false;
+    if (g > 0) {
+      if (lane == 0) publish(mine, gsum, tagA);
+      long long j = static_cast<long long>(g) - 1;
+      for (;;) {
+        const long long q = j - lane;
+        double val = 0.0;
+        int kind = 2;  // 2 = prefix known, 1 = aggregate known, 0 = nothing yet; "group -1" has prefix 0
+        unsigned polls = 0;
+        for (;;) {
+          if (q >= 0) {
+            unsigned long long w[4];
+            ld_desc(a.desc + static_cast<size_t>(q) * 4, w);
+            kind = decode(w[2], w[3], tagP, val) ? 2 : (decode(w[0], w[1], tagA, val) ? 1 : 0);
+          }
+          if (__all_sync(kFull, kind != 0)) break;
+          ++polls;
+          const bool quit = polls > kLookLimit || sm.abort ||
+                            ((polls & 31u) == 0 && (ld_u32_relaxed(&a.hdr->pad[0]) & kHdrRebuild));
+          if (__any_sync(kFull, quit)) {
+            gave_up = true;
+            break;
+          }
+          __nanosleep(64);
+        }
+        if (gave_up) break;
+        const unsigned pmask = __ballot_sync(kFull, kind == 2);
+        const int fp = pmask ? (__ffs(pmask) - 1) : 32;
+        if (lane > fp) val = 0.0;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+          const double o = __shfl_down_sync(kFull, val, d);
+          val = checked_add(val, o, inexact);
+        }
+        const double wsum = __shfl_sync(kFull, val, 0);
+        excl = checked_add(excl, wsum, inexact);
+        if (pmask) break;
+        j -= 32;
+      }
+    }
+    inexact = __any_sync(kFull, inexact);
+    if (gave_up) {
+      // Nothing to publish; successors find the rebuild flag and stop waiting too.
+      if (lane == 0) {
+        const unsigned old = atomicOr(&a.hdr->pad[0], kHdrRebuild);
+        if (!(old & kHdrRebuild)) atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_LOOKBACK_TIMEOUT);
+      }
+    } else {
+      if (lane == 0) publish(mine + 2, checked_add(excl, gsum, inexact), tagP);
+      if (lane < static_cast<int>(in_group))
+        __stcg(&a.l1[static_cast<size_t>(g) * a.group + lane + 1], checked_add(excl, lane_incl, inexact));
+      if (g == 0 && lane == 0) __stcg(&a.l1[0], 0.0);
+      if (__any_sync(kFull, inexact) && lane == 0) atomicOr(&a.hdr->pad[0], kHdrRebuild);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned epoch = ld_u32_relaxed(&a.hdr->epoch);
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], kComputeWarps);
+    }
+    sm.ring_head = 0;
+    sm.ring_tail = 0;
+    sm.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp < kComputeWarps) compute_warps(sm, a, warp, lane);
+  else if (warp == kComputeWarps) loader_warp(sm, a, lane);
+  else lookback_warp(sm, a, epoch, lane);
+
+  __syncthreads();
+  // Bulk copies still in flight into this CTA's shared memory (only after an abort) must land
+  // before the CTA retires.
+  if (sm.abort && tid == 0) {
+    for (int s = 0; s < kStages; ++s)
+      for (unsigned par = 0; par < 2; ++par) {
+        unsigned spins = 0;
+        while (!mbar_try_wait(&sm.full[s], par) && ++spins < 4096u) {}
+      }
+  }
+
+  // ---- last CTA out: rebuild level 1 in order if asked, then re-arm the header
+  if (tid == 0) {
+    __threadfence();
+    const unsigned d = atomicAdd(&a.hdr->done, 1u);
+    if (d == gridDim.x - 1) {
+      __threadfence();
+      const unsigned flags = atomicOr(&a.hdr->pad[0], 0u);
+      if (flags & kHdrRebuild) {
+        double acc = 0.0;
+        __stcg(&a.l1[0], 0.0);
+        for (unsigned q = 0; q < a.nparts; ++q) {
+          acc = __dadd_rn(acc, __ldcg(&a.agg[q]));
+          __stcg(&a.l1[q + 1], acc);
+        }
+        atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_L1_RESUMMED);
+      }
+      a.hdr->pad[0] = 0u;
+      a.hdr->ticket = 0u;
+      a.hdr->done = 0u;
+      a.hdr->epoch = epoch + 1u;
+      __threadfence();
+    }
+  }
+}
+
+inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
+
+}  // namespace
+
+// Scratch layout: header | descriptors (32 B per partition, enough for any grouping) |
+// per-partition aggregates (8 B).
+int64_t scan_scratch_bytes(int64_t n) {
+  const int64_t nparts = (n + kPart - 1) / kPart;
+  return static_cast<int64_t>(sizeof(ScanHeader)) + align256(nparts * 32) + align256(nparts * 8);
+}
+
+int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
+                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream) {
+  GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
+  GEARB_REQUIRE(prio && cdf && l1 && scratch && status, "scan: null pointer argument");
+  GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(cdf) & 15) == 0,
+                "scan: priorities and cdf must be 16-byte aligned");
+  GEARB_REQUIRE((reinterpret_cast<uintptr_t>(l1) & 7) == 0 &&
+                    (reinterpret_cast<uintptr_t>(scratch) & 255) == 0,
+                "scan: l1 must be 8-byte and scratch 256-byte aligned");
+  const int64_t nparts = (n + kPart - 1) / kPart;
+  GEARB_REQUIRE(nparts < (int64_t(1) << 30), "scan: too many partitions");
+  GEARB_REQUIRE(scratch_bytes >= scan_scratch_bytes(n), "scan: scratch too small (%lld < %lld)",
+                (long long)scratch_bytes, (long long)scan_scratch_bytes(n));
+  char *sc = static_cast<char *>(scratch);
+  if (fresh) {
+    // Only the header and the descriptors must start at zero.
+    GEARB_CUDA(cudaMemsetAsync(sc, 0, sizeof(ScanHeader) + align256(nparts * 32), stream));
+  }
+
+  const size_t smem_bytes = sizeof(Smem) + 128;
+  static int ctas_per_sm = 0;
+  if (ctas_per_sm == 0) {
+    GEARB_CUDA(cudaFuncSetAttribute(scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(smem_bytes)));
+    int v = 0;
+    GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, scan_kernel, kThreads, smem_bytes));
+    ctas_per_sm = v > 0 ? v : 1;
+  }
+  const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
+
+  ScanArgs a;
+  a.prio = prio;
+  a.cdf = cdf;
+  a.l1 = l1;
+  a.hdr = reinterpret_cast<ScanHeader *>(sc);
+  a.desc = reinterpret_cast<unsigned long long *>(sc + sizeof(ScanHeader));
+  a.agg = reinterpret_cast<double *>(sc + sizeof(ScanHeader) + align256(nparts * 32));
+  a.status = status;
+  a.n = n;
+  a.nparts = static_cast<unsigned>(nparts);
+  // Group partitions per ticket only when there is enough work to keep every CTA busy.
+  a.group = nparts >= resident * kGroupMax * 2 ? kGroupMax : (nparts >= resident * 4 ? 2 : 1);
+  a.ngroups = static_cast<unsigned>((nparts + a.group - 1) / a.group);
+
+  int64_t grid = resident;
+  if (grid > a.ngroups) grid = a.ngroups;
+  scan_kernel<<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
+  GEARB_CUDA(cudaGetLastError());
+  return GEARB_OK;
+}
+
+}  // namespace gearb

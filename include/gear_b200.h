@@ -1,0 +1,216 @@
+/*
+ * gear_b200.h -- C ABI of the B200-native replay sample + gather engine.
+ *
+ * Every entry point returns a status code (GEARB_OK == 0), never throws and
+ * never aborts; gearb_last_error() gives the text for the calling thread's last
+ * failure.  Device work is enqueued on the caller's stream and returns
+ * asynchronously, like the reference launchers (which use the c10 current
+ * stream, src/cuda/copy.cu:169,202,236).  `stream` is a cudaStream_t passed as
+ * void*; NULL is the legacy default stream.
+ *
+ * Each declaration cites the interface of bigrl-team/gear it stands in for
+ * (paths relative to that tree).
+ */
+#ifndef GEAR_B200_H_
+#define GEAR_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define GEARB_OK 0
+#define GEARB_ERR_INVALID 1     /* bad argument (reference: std::runtime_error)  */
+#define GEARB_ERR_CUDA 2        /* CUDA runtime failure (reference: assert(0))   */
+#define GEARB_ERR_NOMEM 3
+#define GEARB_ERR_STATE 4       /* object not connected / pattern not set        */
+#define GEARB_ERR_TIMEOUT 5     /* a bounded device-side wait ran out            */
+#define GEARB_ERR_NCCL 6        /* NCCL failure (reference: exit())              */
+#define GEARB_ERR_UNSUPPORTED 7
+
+/* Bits of the device status word written by the kernels (status[0]).        */
+#define GEARB_ST_LOOKBACK_TIMEOUT 0x1 /* scan: a look-back wait gave up; level-1 was rebuilt in order */
+#define GEARB_ST_L1_RESUMMED 0x2      /* scan: a float64 partial sum was inexact; level-1 was rebuilt in order */
+#define GEARB_ST_BAD_PRIORITY 0x4     /* scan: a priority was negative or NaN   */
+#define GEARB_ST_BAD_REQUEST 0x8      /* gather: trajectory index outside the table, request skipped */
+#define GEARB_ST_LEN_CLAMPED 0x10     /* gather: a length beyond trajectory_length was clamped */
+#define GEARB_ST_SCAN_ABORTED 0x20    /* scan: a bounded wait inside a CTA ran out; cdf and l1 are NOT valid */
+/* status[1] = number of variates that landed within one float32 ulp of a
+ * cumulative-priority boundary (search), accumulated until cleared.          */
+#define GEARB_STATUS_WORDS 4
+
+/* ---- constants of the cumulative-priority table ------------------------- */
+#define GEARB_PART 4096 /* priorities per level-2 partition */
+
+/* ---- residency of a trajectory table ------------------------------------ */
+#define GEARB_RES_HOST 1 /* pinned, device-mapped host memory (zero-copy reads) */
+#define GEARB_RES_HBM 2  /* device memory                                       */
+
+/* ---- pad options, same numbering as SubscribePattern::PadOption
+ *      (include/storage/handler.h:21) ------------------------------------- */
+#define GEARB_PAD_INACTIVE 0
+#define GEARB_PAD_HEAD 1
+#define GEARB_PAD_TAIL 2
+
+#define GEARB_MAX_COLUMNS 16
+
+typedef struct gearb_table gearb_table;
+typedef struct gearb_handler gearb_handler;
+typedef struct gearb_indexset gearb_indexset;
+typedef struct gearb_sampler gearb_sampler;
+typedef struct gearb_comm gearb_comm;
+
+const char *gearb_last_error(void);
+int gearb_version(void);
+
+/* gear::cuda::init, src/cuda/init.cu:6-13 (bound as libgear.core.init). */
+int gearb_init(int device);
+/* Device count as print_environ reports it, src/env.cc:55-58. */
+int gearb_device_count(int *count);
+
+/* ======================= trajectory table =============================== */
+/* TrajectoryTable::TrajectoryTable, src/storage/table.cc:8-25, with
+ * ColumnSpec::size (src/storage/specs.cc:10-14) already applied by the caller:
+ * row_bytes[c] is the byte size of one timestep of column c.  Layout is
+ * [trajectory][column][timestep][element].  shm_key != 0 places the host copy
+ * in a System-V segment like SharedMemory (src/memory/shared_memory.cc:35-63);
+ * shm_key == 0 uses cudaHostAlloc(Mapped|Portable) like CudaUVMemory
+ * (src/memory/cuda_uvm.cc:29-32).  Nothing is allocated until connect.      */
+int gearb_table_create(const int64_t *row_bytes, int ncols, int64_t trajectory_length,
+                       int64_t capacity, int residency, int shm_key, int create,
+                       gearb_table **out);
+/* TrajectoryTable::connect, src/storage/table.cc:27: returns the table size in
+ * *nbytes, or fails with GEARB_ERR_STATE when the segment is not there yet
+ * (the Python layer maps that to the reference's -1 and retries).            */
+int gearb_table_connect(gearb_table *t, int64_t *nbytes);
+int gearb_table_destroy(gearb_table *t);
+/* Strides the constructor derives (table.cc:10-24): accu has ncols+1 entries. */
+int gearb_table_layout(const gearb_table *t, int64_t *trajectory_stride, int64_t *nbytes,
+                       int64_t *accu);
+/* TrajectoryTable::get_address, src/storage/table.cc:37 (host pointer, NULL
+ * for an HBM-only table) and its device-visible counterpart.                 */
+void *gearb_table_host_ptr(const gearb_table *t);
+void *gearb_table_device_ptr(const gearb_table *t);
+/* Copy the host image to the HBM copy (allocating it on first use): the
+ * HBM-resident table the reference only declares
+ * (CudaTrajectoryStorageHandler, include/storage/handler.h:89-102).          */
+int gearb_table_upload(gearb_table *t, void *stream);
+/* Byte-range write/read against every resident copy (Uint8Span::copy on a
+ * handler view, include/common/span.h:73-79).                                */
+int gearb_table_write(gearb_table *t, int64_t offset, const void *src, int64_t bytes,
+                      void *stream);
+int gearb_table_read(const gearb_table *t, int64_t offset, void *dst, int64_t bytes);
+
+/* ======================= storage handler ================================ */
+/* get_cpu_handler, src/storage/pybind.cc:157-164 /
+ * CpuTrajectoryStorageHandler ctor, src/storage/handler.cc:42-49.  The handler
+ * borrows the table (non-owning), as in the reference.                       */
+int gearb_handler_create(gearb_table *t, int64_t global_capacity, int64_t w_lb, int64_t w_hb,
+                         int64_t r_lb, int64_t r_hb, gearb_handler **out);
+int gearb_handler_destroy(gearb_handler *h);
+/* CpuTrajectoryStorageHandler::set, src/storage/handler.cc:51-60. */
+int gearb_handler_set(gearb_handler *h, const int64_t *cids, int n, const int32_t *offsets,
+                      const int64_t *lengths, const int32_t *pads);
+/* CpuTrajectoryStorageHandler::sub, src/storage/handler.cc:78-131: host-side
+ * offset arithmetic into three caller arrays; *slot_bytes = length*row.      */
+int gearb_handler_sub(const gearb_handler *h, const int64_t *idx, const int64_t *ts,
+                      const int64_t *len, int64_t n, int column, int64_t *src_off,
+                      int64_t *dst_off, int64_t *copy_len, int64_t *slot_bytes);
+/* CpuTrajectoryStorageHandler::fused_subcopy, src/storage/handler.cc:133-154 +
+ * launch_fused_subcopy_collect, include/kernel_launchers.h:30-41: idx/ts/len
+ * are int64 device arrays, dst is the caller's [n, length, *shape] device
+ * buffer.  Bytes outside the clipped segment are left untouched (the
+ * reference's loader pre-zeroes dst).                                        */
+int gearb_handler_subcopy(gearb_handler *h, const int64_t *idx, const int64_t *ts,
+                          const int64_t *len, int64_t n, int column, void *dst,
+                          int32_t *status, void *stream);
+/* All subscribed columns of a batch in ONE launch (replaces the loader's
+ * per-column Python loop, gear/loader/offline_loader.py:178-203).
+ * zero_fill != 0 also writes the padding of every slot, so dst may be
+ * uninitialised memory.                                                      */
+int gearb_handler_gather(gearb_handler *h, const int32_t *columns, int ncols,
+                         const int64_t *idx, const int64_t *ts, const int64_t *len, int64_t n,
+                         void *const *dst, int zero_fill, int32_t *status, void *stream);
+/* CpuTrajectoryStorageHandler::view / raw, src/storage/handler.cc:223-241. */
+int gearb_handler_view(const gearb_handler *h, int64_t index, int column, void **host_ptr,
+                       int64_t *bytes);
+
+/* launch_vary_stride_copy_collect / launch_fix_stride_copy_collect,
+ * include/kernel_launchers.h:17-28 (libgear.core.vcopy / copy): generic
+ * offset-list gathers with arbitrary byte alignment.                         */
+int gearb_vcopy(const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off,
+                const int64_t *lengths, int64_t n, int64_t max_length, void *stream);
+int gearb_copy(const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off,
+               int64_t n, int64_t length, void *stream);
+
+/* ======================= index set ====================================== */
+/* Indexset / StatusTableShard, include/index/set.h:35-69,191-251: one block
+ * holding int64 timesteps then float32 weights at a 128-byte aligned offset. */
+int gearb_indexset_create(int64_t global_capacity, int64_t local_capacity, int64_t index_offset,
+                          int shared, int shm_key, int create, gearb_indexset **out);
+int gearb_indexset_destroy(gearb_indexset *s);
+int64_t *gearb_indexset_timesteps(const gearb_indexset *s);
+float *gearb_indexset_weights(const gearb_indexset *s);
+
+/* ======================= priority sampling ============================== */
+/* Two-level cumulative table over n float32 priorities: cdf[n] (partition-
+ * local inclusive float32 sums in a fixed order) and l1[nparts+1] (float64
+ * exclusive partition offsets; l1[nparts] is the total).  Replaces
+ * launch_prefix_sum and launch_sum, include/kernel_launchers.h:13-15
+ * (src/cuda/one_dim_prefix_sum.cu, src/cuda/one_dim_sum.cu).                 */
+int64_t gearb_scan_scratch_bytes(int64_t n);
+int gearb_scan(const float *priorities, int64_t n, float *cdf, double *l1, void *scratch,
+               int64_t scratch_bytes, int32_t *status, void *stream);
+/* Batched search on caller-supplied float64 variates (stands where
+ * torch.multinomial is called, gear/sampler/global_sampler.py:170).
+ * flags: GEARB_SEARCH_SCALE -> variates are U[0,1) and are multiplied by the
+ * total on the device; otherwise they are U[0,total).                        */
+#define GEARB_SEARCH_SCALE 1
+int gearb_search(const float *cdf, const double *l1, int64_t n, const double *variates,
+                 int64_t b, int flags, int64_t *out_index, int32_t *status, void *stream);
+/* Uniform draw floor(u*n) on U[0,1) variates (stands where torch.randint is
+ * called, gear/sampler/global_sampler.py:121-129).                           */
+int gearb_sample_uniform(int64_t n, const double *u01, int64_t b, int64_t *out_index,
+                         void *stream);
+/* Flat step index -> (trajectory, timestep, length) request triple;
+ * lengths == NULL means every trajectory has trajectory_length steps.        */
+int gearb_decode(const int64_t *flat, int64_t b, int64_t trajectory_length,
+                 const int64_t *lengths, int64_t index_offset, int64_t *idx, int64_t *ts,
+                 int64_t *len, void *stream);
+
+/* Sampler object: owns cdf, l1, scratch and a status word on the current
+ * device, so that repeated scans need no allocation and no clearing.         */
+int gearb_sampler_create(int64_t n, gearb_sampler **out);
+int gearb_sampler_destroy(gearb_sampler *s);
+int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
+int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, int flags,
+                         int64_t *out_index, void *stream);
+int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status);
+/* Synchronises `stream`, then returns total and the status words. */
+int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t *status);
+
+/* ======================= synthetic data ================================= */
+/* Device-side Philox4x32-10 fills for benchmark tables that are too large to
+ * stage through the host.  kind selects the distribution.                   */
+#define GEARB_FILL_U32 0         /* raw 32-bit words                          */
+#define GEARB_FILL_F32_NORMAL 1  /* N(0,1) float32 (Box-Muller)               */
+#define GEARB_FILL_F32_UNIFORM 2 /* U(a,b) float32                            */
+#define GEARB_FILL_F32_LOGNORMAL 3
+#define GEARB_FILL_I32_RANGE 4   /* int32 uniform in [a,b)                    */
+#define GEARB_FILL_U8 5          /* uniform bytes                             */
+#define GEARB_FILL_U01_F64 6     /* U[0,1) float64 from 53 bits               */
+int gearb_fill(void *dst, int64_t count, int kind, uint64_t seed, uint64_t stream_id,
+               double a, double b, void *stream);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* GEAR_B200_H_ */

@@ -1,0 +1,162 @@
+"""Scan / search / draw parity on the GPU: cumulative table, level-1 offsets and
+sampled indices must equal the oracle's bit for bit on the same priorities and
+the same variates."""
+import numpy as np
+import pytest
+import torch
+
+from gear_b200 import _native as N
+from gear_b200 import core
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+@pytest.mark.parametrize("n", [1, 2, 127, 128, 4095, 4096, 4097, 5 * 4096 + 123, 1 << 20])
+def test_scan_bit_exact(O, n):
+    p = O.synth_lognormal(21, n, n)
+    cdf, l1, status = core.scan(dev(p))
+    torch.cuda.synchronize()
+    ocdf, ol1, total, bad = O.scan(p)
+    assert np.array_equal(cdf.cpu().numpy(), ocdf)
+    assert np.array_equal(l1.cpu().numpy(), ol1)
+    assert status.cpu().tolist()[0] == 0
+
+
+def test_scan_config2_and_search_bit_exact(O):
+    # BASELINE config 2: 1,048,576 LogNormal(0,1) priorities, 4096 variates U[0,total).
+    n, b = 1 << 20, 4096
+    p = O.synth_lognormal(0x6EA20102, 0, n)
+    ocdf, ol1, total, _ = O.scan(p)
+    u = O.synth_u01(0x6EA20202, 0, b) * total
+    cdf, l1, status = core.scan(dev(p))
+    got = core.search(cdf, l1, dev(u), status=status)
+    torch.cuda.synchronize()
+    want, near = O.search(ocdf, ol1, u, want_near=True)
+    assert np.array_equal(got.cpu().numpy(), want)
+    st = status.cpu().tolist()
+    assert st[0] == 0 and st[1] == int(near.sum())
+    # flips against an independent float64 running sum are neighbours and few
+    ref = O.search_f64(p, u)
+    flips = want != ref
+    assert flips.sum() <= 16 and np.all(np.abs(want[flips] - ref[flips]) <= 1)
+
+
+def test_search_edges_zero_priorities_and_scaling(O):
+    n = 3 * 4096 + 77
+    p = O.synth_lognormal(5, 1, n)
+    p[::3] = 0.0
+    p[4096:8192] = 0.0
+    ocdf, ol1, total, _ = O.scan(p)
+    cdf, l1, status = core.scan(dev(p))
+    u = O.synth_u01(6, 1, 3000) * total
+    u[:5] = [0.0, total, np.nextafter(total, 0), -1.0, np.nan]
+    got = core.search(cdf, l1, dev(u)).cpu().numpy()
+    assert np.array_equal(got, O.search(ocdf, ol1, u))
+    assert np.all(p[got] > 0)
+    u01 = O.synth_u01(6, 2, 777)
+    got = core.search(cdf, l1, dev(u01), scale=True).cpu().numpy()
+    assert np.array_equal(got, O.search(ocdf, ol1, u01, scale=True))
+
+
+def test_all_zero_and_bad_priorities(O):
+    p = np.zeros(5000, np.float32)
+    cdf, l1, status = core.scan(dev(p))
+    got = core.search(cdf, l1, dev(np.array([0.0, 0.7]))).cpu().numpy()
+    assert list(got) == [4999, 4999]
+    p = np.ones(9000, np.float32); p[8000] = -2.0
+    _, _, status = core.scan(dev(p))
+    assert status.cpu().tolist()[0] & N.ST_BAD_PRIORITY
+    p[8000] = np.nan
+    _, _, status = core.scan(dev(p))
+    assert status.cpu().tolist()[0] & N.ST_BAD_PRIORITY
+
+
+def test_inexact_level1_is_rebuilt_in_order(O):
+    # Aggregates that differ by ~2^60 make float64 partial sums round; the kernel must
+    # then fall back to the in-order sum, which is what the oracle computes.
+    n = 64 * 4096
+    p = np.full(n, 1.234e-3, np.float32)
+    p[::8192] = 3e18            # every other partition sums to ~3e18, the rest to ~5
+    p[4096 * 33 + 9] = 7.7e5
+    ocdf, ol1, total, _ = O.scan(p)
+    assert len(np.unique(np.diff(ol1))) > 2
+    for _ in range(3):
+        cdf, l1, status = core.scan(dev(p))
+        assert np.array_equal(l1.cpu().numpy(), ol1)
+        assert np.array_equal(cdf.cpu().numpy(), ocdf)
+        assert status.cpu().tolist()[0] & N.ST_L1_RESUMMED
+
+
+def test_sampler_object_repeated_scans(O):
+    n = 37 * 4096 + 11
+    s = core.PrioritySampler(n)
+    for rep in range(4):
+        p = O.synth_lognormal(100 + rep, 0, n)
+        ocdf, ol1, total, _ = O.scan(p)
+        s.scan(dev(p))
+        u = O.synth_u01(200 + rep, 0, 1000)
+        got = s.search(dev(u), scale=True)
+        tot, st = s.result()
+        assert tot == total and st[0] == 0
+        assert np.array_equal(s.cdf.cpu().numpy(), ocdf)
+        assert np.array_equal(s.l1.cpu().numpy(), ol1)
+        assert np.array_equal(got.cpu().numpy(), O.search(ocdf, ol1, u, scale=True))
+
+
+def test_uniform_draw_and_decode(O):
+    u = O.synth_u01(1, 1, 5000)
+    u[:3] = [0.0, 0.9999999999999999, 1.0]
+    n = 4096 * 1000
+    got = core.sample_uniform(n, dev(u))
+    assert np.array_equal(got.cpu().numpy(), O.uniform(u, n))
+    lengths = np.random.default_rng(0).integers(1, 1001, 4096).astype(np.int64)
+    idx, ts, ln = core.decode(got, 1000, lengths=dev(lengths), index_offset=4096)
+    oi, ot, ol = O.decode(got.cpu().numpy(), 1000, lengths=lengths, index_offset=4096)
+    assert np.array_equal(idx.cpu().numpy(), oi) and np.array_equal(ts.cpu().numpy(), ot)
+    assert np.array_equal(ln.cpu().numpy(), ol)
+    idx, ts, ln = core.decode(got, 1000)
+    assert torch.all(ln == 1000) and torch.all(idx * 1000 + ts == got)
+
+
+def test_large_scan_properties_and_oracle(O):
+    # 16M priorities (64 MB, beyond what fits a single wave): bit-exact against the
+    # C oracle, which finishes this size in well under a second.
+    n = 1 << 24
+    p = torch.empty(n, dtype=torch.float32, device=DEV)
+    core.fill(p, N.FILL_F32_LOGNORMAL, seed=31)
+    cdf, l1, status = core.scan(p)
+    hp = p.cpu().numpy()
+    ocdf, ol1, total, _ = O.scan(hp)
+    assert np.array_equal(l1.cpu().numpy(), ol1)
+    assert np.array_equal(cdf.cpu().numpy(), ocdf)
+    assert status.cpu().tolist()[0] == 0
+    u = torch.empty(8192, dtype=torch.float64, device=DEV)
+    core.fill(u, N.FILL_U01_F64, seed=32)
+    got = core.search(cdf, l1, u, scale=True).cpu().numpy()
+    assert np.array_equal(got, O.search(ocdf, ol1, u.cpu().numpy(), scale=True))
+
+
+def test_fill_integer_kinds_match_oracle_philox(O):
+    w = torch.empty(1001, dtype=torch.int32, device=DEV)
+    core.fill(w, N.FILL_U32, seed=0xABCDEF0123, stream_id=5)
+    assert np.array_equal(w.cpu().numpy().view(np.uint32), O.philox_u32(0xABCDEF0123, 5, 0, 1001))
+    core.fill(w, N.FILL_I32_RANGE, seed=9, stream_id=1, a=0, b=50257)
+    assert np.array_equal(w.cpu().numpy(), O.synth_randint(9, 1, 1001, 0, 50257))
+    b = torch.empty(1003, dtype=torch.uint8, device=DEV)
+    core.fill(b[1:], N.FILL_U8, seed=4, count=1002)       # unaligned start
+    assert np.array_equal(b[1:].cpu().numpy(), O.philox_u32(4, 0, 0, 251).view(np.uint8)[:1002])
+    d = torch.empty(500, dtype=torch.float64, device=DEV)
+    core.fill(d, N.FILL_U01_F64, seed=12, stream_id=3)
+    assert np.array_equal(d.cpu().numpy(), O.philox_u01(12, 3, 0, 500))
+    f = torch.empty(4000, dtype=torch.float32, device=DEV)
+    core.fill(f, N.FILL_F32_UNIFORM, seed=13, a=-1.0, b=1.0)
+    assert np.array_equal(f.cpu().numpy(), O.synth_uniform_pm1(13, 0, 4000))
+    core.fill(f, N.FILL_F32_NORMAL, seed=14)
+    np.testing.assert_allclose(f.cpu().numpy(), O.synth_normal(14, 0, 4000), rtol=1e-5, atol=1e-6)
+    core.fill(f, N.FILL_F32_LOGNORMAL, seed=15)
+    np.testing.assert_allclose(f.cpu().numpy(), O.synth_lognormal(15, 0, 4000), rtol=1e-5)
