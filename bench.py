@@ -1,0 +1,406 @@
+#!/usr/bin/env python
+"""Benchmark of the replay sample + gather hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one prioritized sample + gather of a batch: rebuild the cumulative
+priority table (scan), draw B segment starts on supplied variates, gather B x L
+timesteps of every column.
+
+N = 1 runs the HBM-resident decision-transformer table of BASELINE.json
+(100,000 trajectories x 1000 steps, rows 156/24/4/4/1 B, B=1024, L=64).
+N > 1 runs the trajectory-id sharded token table (per GPU 32,000 x 1000 steps of
+4104 B, 1024 requests per rank, L=16) with the cross-shard exchange.
+
+The line printed by rank 0 carries, beside the base keys:
+  roofline      the dominant kernel (scan) against the measured HBM copy peak
+  cpu_baseline  the CPU path timed on this box's host cores (bounded sample)
+  e2e           the same metric through the C ABI with host buffers
+  parity        indices/bytes of one batch checked against the CPU oracle
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "sampled timesteps/sec (prioritized sample + gather)"
+UNIT = "timesteps/s"
+
+C3 = dict(name="hbm_decision_transformer_100Mstep", rows=[156, 24, 4, 4, 1], T=1000, capacity=100_000,
+          B=1024, L=64)
+C5 = dict(name="sharded_token_table_32Mstep_per_gpu", rows=[4096, 4, 4], T=1000, capacity=32_000,
+          B_per_rank=1024, L=16)
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one scan_kernel launch at n = 100,000,000,
+# from the ncu capture summarised in profiles/ (None until a capture exists).
+SCAN_TRAFFIC_BYTES_C3 = None
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi samples of the SM clock and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.rows, self.proc, self.gpu = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        inside = [r for (t, r) in self.rows if t0 <= t <= t1 + 0.05] or [r for (_, r) in self.rows]
+        sm, mx, reasons = [], [], set()
+        for r in inside:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- #
+# our arm
+# --------------------------------------------------------------------------- #
+def fill_table(core, N, table, seed):
+    """Seeded synthetic bytes for the whole table, written in HBM."""
+    core.fill_ptr(table.device_ptr, table.nbytes // 4, N.FILL_U32, seed=seed)
+    if table.nbytes % 4:
+        core.fill_ptr(table.device_ptr + (table.nbytes // 4) * 4, table.nbytes % 4, N.FILL_U8, seed=seed + 1)
+
+
+def run_ours_single(args):
+    import numpy as np
+    import torch
+    from gear_b200 import _native as N
+    from gear_b200 import core
+
+    cfg = C3
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    core.init(0)
+    rows, T, cap, B, L = cfg["rows"], cfg["T"], cfg["capacity"], cfg["B"], cfg["L"]
+    n = cap * T
+    cols = list(range(len(rows)))
+
+    table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
+    table.connect()
+    fill_table(core, N, table, seed=0x6EA20003)
+    handler = core.StorageHandler(table)
+    handler.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * len(rows))
+
+    prio = torch.empty(n, dtype=torch.float32, device=dev)
+    core.fill(prio, N.FILL_F32_LOGNORMAL, seed=0x6EA20103)
+    sampler = core.PrioritySampler(n)
+
+    # variates: a fresh batch per step, all resident before the clock starts
+    nbatches = 16
+    u_dev = torch.empty(nbatches * B, dtype=torch.float64, device=dev)
+    core.fill(u_dev, N.FILL_U01_F64, seed=0x6EA20203)
+    dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=dev) for r in rows]
+    flat = torch.empty(B, dtype=torch.int64, device=dev)
+
+    def step(i):
+        sampler.scan(prio)
+        sampler.sample_gather(handler, u_dev[(i % nbatches) * B:(i % nbatches + 1) * B], cols, dsts,
+                              scale=True, zero_fill=True, out_flat=flat)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+
+    # ---- timed region: K steps, device events; every scan also gets its own event pair
+    K = args.steps
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    scan_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    clocks = ClockSampler(0)
+    clocks.start()
+    time.sleep(0.12)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    ev[0].record()
+    for i in range(K):
+        scan_ev[i][0].record()
+        sampler.scan(prio)
+        scan_ev[i][1].record()
+        sampler.sample_gather(handler, u_dev[(i % nbatches) * B:(i % nbatches + 1) * B], cols, dsts,
+                              scale=True, zero_fill=True, out_flat=flat)
+    ev[1].record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    clk = clocks.stop(t0, t1)
+    ms_total = ev[0].elapsed_time(ev[1])
+    ms_step = ms_total / K
+    scan_ms = sum(a.elapsed_time(b) for a, b in scan_ev) / K
+    total_prio, status = sampler.result()
+
+    gathered = B * L * sum(rows)
+    value = B * L / (ms_step * 1e-3)
+    peak, peak_src = peaks()
+    scan_bytes = 8 * n + 8 * ((n + 4095) // 4096)
+    achieved = scan_bytes / (scan_ms * 1e-3) / 1e9
+
+    # ---- search + gather only ("priorities unchanged" mode), reported beside the headline
+    e2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    e2[0].record()
+    for i in range(K):
+        sampler.sample_gather(handler, u_dev[(i % nbatches) * B:(i % nbatches + 1) * B], cols, dsts,
+                              scale=True, zero_fill=True, out_flat=flat)
+    e2[1].record()
+    torch.cuda.synchronize()
+    sg_ms = e2[0].elapsed_time(e2[1]) / K
+
+    # ---- end to end through the C ABI with host buffers (pinned): variates in, batch out
+    u_host = torch.empty(nbatches * B, dtype=torch.float64).pin_memory()
+    u_host.copy_(u_dev.cpu())
+    u_stage = torch.empty(B, dtype=torch.float64, device=dev)
+    out_host = [torch.empty(B * L * r, dtype=torch.uint8).pin_memory() for r in rows]
+    flat_host = torch.empty(B, dtype=torch.int64).pin_memory()
+
+    def e2e_step(i):
+        u_stage.copy_(u_host[(i % nbatches) * B:(i % nbatches + 1) * B], non_blocking=True)
+        sampler.scan(prio)
+        sampler.sample_gather(handler, u_stage, cols, dsts, scale=True, zero_fill=True, out_flat=flat)
+        for h, d in zip(out_host, dsts):
+            h.copy_(d, non_blocking=True)
+        flat_host.copy_(flat, non_blocking=True)
+        torch.cuda.current_stream().synchronize()   # the caller owns the batch when the call returns
+
+    Ke = max(10, min(K, 400))
+    for i in range(3):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    w0 = time.perf_counter()
+    for i in range(Ke):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - w0) / Ke
+    e2e = {"value": B * L / e2e_s, "unit": UNIT, "h2d_bytes_per_step": B * 8,
+           "d2h_bytes_per_step": gathered + B * 8, "ms_per_step": e2e_s * 1e3, "steps": Ke}
+
+    # ---- parity of one batch against the CPU oracle + CPU baseline (bounded sample)
+    parity, cpu = cpu_check_and_baseline(cfg, table, prio, u_dev[:B], sampler, handler, dsts, flat, args)
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 scan / f64 level-1 / u8 gather", "data": "synthetic (seeded Philox4x32-10, generated in HBM)",
+        "config": {"workload": cfg["name"], "trajectories": cap, "trajectory_length": T, "row_bytes": rows,
+                   "batch": B, "segment_length": L, "priorities": n, "table_bytes": table.nbytes,
+                   "l2": "inputs larger than L2 (400 MB of priorities re-read every step)",
+                   "step": "scan + search + decode + gather"},
+        "gathered_gb_s": 2 * gathered / (ms_step * 1e-3) / 1e9,
+        "step_algorithmic_gb_s": (scan_bytes + 2 * gathered) / (ms_step * 1e-3) / 1e9,
+        "step_frac_of_measured_peak": (scan_bytes + 2 * gathered) / (ms_step * 1e-3) / 1e9 / peak,
+        "step_frac_of_8tbs": (scan_bytes + 2 * gathered) / (ms_step * 1e-3) / 1e9 / 8000.0,
+        "search_gather_only": {"ms_per_step": sg_ms, "timesteps_per_s": B * L / (sg_ms * 1e-3),
+                               "gathered_gb_s": 2 * gathered / (sg_ms * 1e-3) / 1e9},
+        "roofline": {"kernel": "scan_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": SCAN_TRAFFIC_BYTES_C3, "peak_source": peak_src,
+                     "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms},
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 2 * K, "clocks": clk, "parity": parity,
+        "scan_status": status, "total_priority": total_prio,
+    }
+    print(json.dumps(line))
+
+
+def cpu_check_and_baseline(cfg, table, prio, u_first, sampler, handler, dsts, flat, args):
+    """One batch checked against the oracle, then the CPU path timed on a bounded sample."""
+    import numpy as np
+    import torch
+    from oracle import oracle as O
+
+    rows, T, cap, B, L = cfg["rows"], cfg["T"], cfg["capacity"], cfg["B"], cfg["L"]
+    cols = list(range(len(rows)))
+    cores = os.cpu_count() or 1
+    hp = prio.cpu().numpy()
+    u = u_first.cpu().numpy()
+
+    # GPU result of exactly this batch
+    sampler.scan(prio)
+    sampler.sample_gather(handler, u_first.contiguous(), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
+    torch.cuda.synchronize()
+    gflat = flat.cpu().numpy()
+
+    t0 = time.perf_counter()
+    ocdf, ol1, ototal, _ = O.scan_mt(hp, cores)
+    scan_s = time.perf_counter() - t0
+    oflat, near = O.search(ocdf, ol1, u, scale=True, want_near=True)
+    oi, ot, ol = O.decode(oflat, T)
+    index_mismatch = int((gflat != oflat).sum())
+    f64 = O.search_f64(hp, u * ototal)
+    flips = oflat != f64
+    byte_mismatch = 0
+    for c, r in enumerate(rows):
+        s, d, b, slot = handler.sub(oi, ot, ol, c)
+        got = dsts[c].cpu().numpy()
+        for i in range(0, B, 8):      # every 8th request read back from the device table
+            want = table.read(int(s[i]), int(b[i]))
+            byte_mismatch += int((got[d[i]:d[i] + b[i]] != want).sum()) + int(got[i * slot + b[i]:(i + 1) * slot].any())
+    parity = {"index_mismatches_vs_oracle": index_mismatch, "gathered_byte_mismatches": byte_mismatch,
+              "variates_within_1ulp_of_boundary": int(near.sum()),
+              "flips_vs_float64_running_sum": int(flips.sum()),
+              "max_flip_distance": int(np.abs(oflat[flips] - f64[flips]).max()) if flips.any() else 0}
+
+    # ---- CPU baseline: full 100M-priority scan + search + gather from a host slice of the table
+    sub_cap = min(cap, 4000)                      # 756 MB host slice: requests folded into it
+    host_tab = table.read(0, sub_cap * table.trajectory_stride)
+    fi = oi % sub_cap
+    out = [np.empty(B * L * r, np.uint8) for r in rows]
+    accu = np.asarray(table.accu[:len(rows)], np.int64)
+    reps = 3
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        c2, l2, tot2, _ = O.scan_mt(hp, cores, cdf=ocdf)
+        f2 = O.search(c2, l2, u, scale=True)
+        i2, t2, n2 = O.decode(f2, T)
+        O.gather_mt(host_tab, out, i2 % sub_cap, t2, n2, table.trajectory_stride, T, accu, rows,
+                    [0] * len(rows), [L] * len(rows), [0] * len(rows), cores)
+    cpu_s = (time.perf_counter() - t0) / reps
+    kind = "port"
+    ref_note = ""
+    if O.Reference.available():
+        try:
+            ref = O.Reference(rows, T, sub_cap)
+            for c in cols:
+                ref.set(c, 0, L, 2)
+            g_s = ref.time_gather(host_tab, fi, ot, ol, cols, out, cores, 20) / 20
+            ref.close()
+            ref_note = f"; reference sub()+memcpy alone: {g_s * 1e3:.3f} ms/batch"
+            kind = "reference"
+        except Exception as e:  # the compiled reference is optional
+            ref_note = f"; oracle/_ref not usable here ({type(e).__name__})"
+    cpu = {"value": B * L / cpu_s, "unit": UNIT, "cores": cores, "kind": kind, "ms_per_step": cpu_s * 1e3,
+           "sample": f"{reps} full steps: {len(hp)} priorities scanned on {cores} threads + {B} draws + gather from a "
+                     f"{sub_cap}-trajectory host slice of the table (requests folded into it){ref_note}"}
+    return parity, cpu
+
+
+# --------------------------------------------------------------------------- #
+# reference arm: the reference's CPU path on the host cores
+# --------------------------------------------------------------------------- #
+def run_reference(args):
+    import numpy as np
+    from oracle import oracle as O
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = C3 if args.gpus == 1 else None
+    cores = os.cpu_count() or 1
+    if cfg is None:
+        rows, T, L, B = C5["rows"], C5["T"], C5["L"], C5["B_per_rank"] * args.gpus
+        n = 32_000_000 * args.gpus  # every shard's priorities, scanned by the host threads
+        name = C5["name"]
+    else:
+        rows, T, L, B, name = cfg["rows"], cfg["T"], cfg["L"], cfg["B"], cfg["name"]
+        n = 100_000_000            # the full priority vector every step
+    sub_cap = 2000
+    cols = list(range(len(rows)))
+    accu, stride = O.table_layout(rows, T)
+    table = O.philox_u32(1, 0, 0, 1 << 20).view(np.uint8)
+    table = np.resize(table, sub_cap * stride)
+    prio = np.resize(O.synth_lognormal(2, 0, 1 << 20), n)
+    u = O.synth_u01(3, 0, B)
+    out = [np.empty(B * L * r, np.uint8) for r in rows]
+    ref = None
+    kind = "port"
+    if O.Reference.available():
+        try:
+            ref = O.Reference(rows, T, sub_cap)
+            for c in cols:
+                ref.set(c, 0, L, 2)
+            kind = "reference"
+        except Exception:
+            ref = None
+    cdf = np.empty(n, np.float32)
+
+    def step():
+        c2, l2, tot, _ = O.scan_mt(prio, cores, cdf=cdf)
+        f = O.search(c2, l2, u, scale=True)
+        i2, t2, n2 = O.decode(f % (sub_cap * T), T)
+        if ref is not None:
+            ref.time_gather(table, i2, t2, n2, cols, out, cores, 1)
+        else:
+            O.gather_mt(table, out, i2, t2, n2, stride, T, accu[:len(rows)], rows, [0] * len(rows),
+                        [L] * len(rows), [0] * len(rows), cores)
+
+    K, W = min(args.steps, 10), min(max(args.warmup, 1), 2)   # bounded: about 10 CPU steps
+    for _ in range(W):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        step()
+    dt = (time.perf_counter() - t0) / K
+    full_dt = dt
+    value = B * L / full_dt
+    sample = (f"{K} full-size steps on {cores} host threads; each step scans all {n} priorities, draws {B} and "
+              f"gathers from a {sub_cap}-trajectory host table (requests folded into it); "
+              f"addressing by {'the reference sub() compiled from its sources' if kind == 'reference' else 'the oracle port'}")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": K, "warmup": W, "ms_per_step": full_dt * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 scan / f64 level-1 / u8 gather", "data": "synthetic",
+            "config": {"workload": name, "batch": B, "segment_length": L, "row_bytes": rows},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        return run_ours_single(args)
+    from gear_b200 import bench_sharded
+    return bench_sharded.run(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -95,6 +95,8 @@ _SIGS = {
     "gearb_sampler_destroy": (C.c_int, [vp]),
     "gearb_sampler_scan": (C.c_int, [vp, vp, vp]),
     "gearb_sampler_search": (C.c_int, [vp, vp, i64, C.c_int, vp, vp]),
+    "gearb_sampler_sample_gather": (C.c_int, [vp, vp, vp, i64, C.c_int, vp, i64, pi32, C.c_int, C.POINTER(vp),
+                                              C.c_int, vp, vp, vp, vp, vp]),
     "gearb_sampler_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "gearb_sampler_result": (C.c_int, [vp, vp, C.POINTER(f64), pi32]),
     "gearb_fill": (C.c_int, [vp, i64, C.c_int, u64, u64, f64, f64, vp]),

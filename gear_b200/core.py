@@ -354,6 +354,36 @@ class PrioritySampler:
              N.SEARCH_SCALE if scale else 0, _ptr(out), _stream(stream))
         return out
 
+    def sample_gather(self, handler: "StorageHandler", variates: torch.Tensor, columns: Sequence[int],
+                      dsts: Sequence[torch.Tensor], scale: bool = True,
+                      lengths: Optional[torch.Tensor] = None, index_offset: int = 0,
+                      zero_fill: bool = True, out_flat: Optional[torch.Tensor] = None,
+                      out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None,
+                      out_len: Optional[torch.Tensor] = None, stream=None) -> None:
+        """Search every variate, decode it to (trajectory, timestep, length) and gather the
+        listed columns of the handler's table, all in one launch."""
+        if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
+            raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
+        b = variates.numel()
+        if len(dsts) != len(columns):
+            raise GearError(N.ERR_INVALID, "one destination per column is required")
+        for c, d in zip(columns, dsts):
+            p = handler.patterns.get(int(c))
+            if p is not None:
+                need = b * p.length * handler.table.row_bytes[int(c)]
+                if not d.is_cuda or not d.is_contiguous() or d.numel() * d.element_size() < need:
+                    raise GearError(N.ERR_INVALID,
+                                    f"destination of column {c} must be a contiguous CUDA tensor of >= {need} bytes")
+        for name, t in (("out_flat", out_flat), ("out_idx", out_idx), ("out_ts", out_ts), ("out_len", out_len)):
+            if t is not None and (t.dtype != torch.int64 or not t.is_cuda or t.numel() < b):
+                raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
+        nc = len(columns)
+        call("gearb_sampler_sample_gather", self._h, handler._h, _ptr(variates), b,
+             N.SEARCH_SCALE if scale else 0, _ptr(lengths), int(index_offset),
+             (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
+             (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)),
+             _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _ptr(out_len), _stream(stream))
+
     def result(self, stream=None):
         """(total, status words) after synchronising the stream."""
         total = C.c_double(0.0)

@@ -413,20 +413,18 @@ int gearb_handler_sub(const gearb_handler *h, const int64_t *idx, const int64_t 
   return GEARB_OK;
 }
 
-int gearb_handler_gather(gearb_handler *h, const int32_t *columns, int ncols, const int64_t *idx,
-                         const int64_t *ts, const int64_t *len, int64_t n, void *const *dst,
-                         int zero_fill, int32_t *status, void *stream) {
-  GEARB_REQUIRE(h && h->table, "handler_gather: null handler");
-  GEARB_REQUIRE(ncols >= 0 && ncols <= GEARB_MAX_COLUMNS, "handler_gather: %d columns", ncols);
-  GEARB_REQUIRE(n >= 0, "handler_gather: negative request count");
-  if (n == 0 || ncols == 0) return GEARB_OK;
-  GEARB_REQUIRE(columns && idx && ts && len && dst, "handler_gather: null argument");
+// Fills the launch parameters shared by the gather kernels from the handler's patterns.
+static int build_gather_params(gearb_handler *h, const int32_t *columns, int ncols, int64_t n,
+                               void *const *dst, int zero_fill, int32_t *status, GatherParams &p) {
+  GEARB_REQUIRE(h && h->table, "gather: null handler");
+  GEARB_REQUIRE(ncols >= 0 && ncols <= GEARB_MAX_COLUMNS, "gather: %d columns", ncols);
+  GEARB_REQUIRE(n >= 0, "gather: negative request count");
+  GEARB_REQUIRE(ncols == 0 || (columns && dst), "gather: null argument");
   const gearb_table *t = h->table;
   if (!t->connected || !t->device_base())
-    return fail(GEARB_ERR_STATE, "handler_gather: the table has no device-visible copy (connect it first)");
-  GatherParams p{};
+    return fail(GEARB_ERR_STATE, "gather: the table has no device-visible copy (connect it first)");
+  p = GatherParams{};
   p.table = t->device_base();
-  p.idx = idx; p.ts = ts; p.len = len;
   p.n = n;
   p.traj_stride = t->traj_stride;
   p.capacity = t->capacity;
@@ -440,7 +438,7 @@ int gearb_handler_gather(gearb_handler *h, const int32_t *columns, int ncols, co
     const Pattern *pat = nullptr;
     int rc = pattern_of(h, columns[i], &pat);
     if (rc != GEARB_OK) return rc;
-    GEARB_REQUIRE(dst[i], "handler_gather: null destination for column %d", columns[i]);
+    GEARB_REQUIRE(dst[i], "gather: null destination for column %d", columns[i]);
     const int64_t row = t->row_bytes[columns[i]];
     const int64_t slot = row * pat->length;
     if (slot == 0) continue;
@@ -455,11 +453,22 @@ int gearb_handler_gather(gearb_handler *h, const int32_t *columns, int ncols, co
     const int64_t cc = (slot + p.chunk_bytes - 1) / p.chunk_bytes;
     c.chunk_count = static_cast<int32_t>(cc);
     chunks += cc;
-    GEARB_REQUIRE(chunks < (int64_t(1) << 30), "handler_gather: request too large");
+    GEARB_REQUIRE(chunks < (int64_t(1) << 30), "gather: request too large");
   }
   p.ncols = used;
   p.chunks_per_request = static_cast<int32_t>(chunks);
-  if (used == 0) return GEARB_OK;
+  return GEARB_OK;
+}
+
+int gearb_handler_gather(gearb_handler *h, const int32_t *columns, int ncols, const int64_t *idx,
+                         const int64_t *ts, const int64_t *len, int64_t n, void *const *dst,
+                         int zero_fill, int32_t *status, void *stream) {
+  GatherParams p;
+  int rc = build_gather_params(h, columns, ncols, n, dst, zero_fill, status, p);
+  if (rc != GEARB_OK) return rc;
+  if (n == 0 || p.ncols == 0) return GEARB_OK;
+  GEARB_REQUIRE(idx && ts && len, "gather: null request arrays");
+  p.idx = idx; p.ts = ts; p.len = len;
   return launch_gather(p, as_stream(stream));
 }
 
@@ -594,6 +603,22 @@ int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, in
   GEARB_REQUIRE(s, "sampler_search: null sampler");
   return launch_search(s->cdf, s->l1, s->n, variates, b, flags, out_index, s->status,
                        as_stream(stream));
+}
+
+int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double *variates, int64_t b,
+                                int flags, const int64_t *lengths, int64_t index_offset,
+                                const int32_t *columns, int ncols, void *const *dst, int zero_fill,
+                                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
+                                void *stream) {
+  GEARB_REQUIRE(s, "sample_gather: null sampler");
+  GatherParams p;
+  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p);
+  if (rc != GEARB_OK) return rc;
+  GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
+                "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
+                (long long)(h->table->capacity * h->table->T));
+  return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, flags, lengths, index_offset, out_flat,
+                              out_idx, out_ts, out_len, as_stream(stream));
 }
 
 int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status) {

@@ -190,6 +190,17 @@ int gearb_sampler_destroy(gearb_sampler *s);
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
 int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, int flags,
                          int64_t *out_index, void *stream);
+/* Prioritized sample + gather of a whole batch in ONE launch: search each
+ * variate, decode the flat step index i to (trajectory i / T, timestep i % T,
+ * length lengths[trajectory] or T), and gather every listed column of the
+ * handler's table -- the loader's fused_iterate (gear/loader/offline_loader.py:155-204)
+ * without its host round trips.  out_* may each be NULL; out_idx gets
+ * trajectory + index_offset.                                                 */
+int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double *variates,
+                                int64_t b, int flags, const int64_t *lengths, int64_t index_offset,
+                                const int32_t *columns, int ncols, void *const *dst, int zero_fill,
+                                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts,
+                                int64_t *out_len, void *stream);
 int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status);
 /* Synchronises `stream`, then returns total and the status words. */
 int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t *status);

@@ -360,3 +360,80 @@ def comm_order(rank, world):
     o = np.empty(world, np.int32)
     lib().gearo_comm_order(C.c_int(rank), C.c_int(world), _p(o))
     return o
+
+
+# --------------------------------------------------------------------------- #
+# Threaded drivers (timing of the CPU path) and the reference's compiled code
+# --------------------------------------------------------------------------- #
+def scan_mt(prio: np.ndarray, threads: int, cdf: np.ndarray | None = None):
+    """gearo_scan with partitions striped over host threads; same result."""
+    prio = np.ascontiguousarray(prio, dtype=np.float32)
+    n = len(prio)
+    nparts = (n + PART - 1) // PART
+    if cdf is None:
+        cdf = np.empty(n, np.float32)
+    l1 = np.zeros(nparts + 1, np.float64)
+    total = C.c_double(0.0)
+    f = lib().gearo_scan_mt
+    f.restype = C.c_int
+    bad = f(_p(prio), C.c_int64(n), _p(cdf), _p(l1), C.byref(total), C.c_int(int(threads)))
+    return cdf, l1, total.value, int(bad)
+
+
+def gather_mt(table: np.ndarray, dsts, idx, ts, ln, traj_stride, T, col_accu, rows, offsets, lengths,
+              pad_heads, threads: int):
+    """All columns of a batch with zero-filled padding, requests striped over threads."""
+    idx, ts, ln = _i64(idx), _i64(ts), _i64(ln)
+    nc = len(rows)
+    dptr = (C.c_void_p * nc)(*[d.ctypes.data for d in dsts])
+    ca, rw, pl = _i64(col_accu), _i64(rows), _i64(lengths)
+    po = np.ascontiguousarray(offsets, np.int32); ph = np.ascontiguousarray(pad_heads, np.int32)
+    lib().gearo_gather_mt(_p(table), dptr, _p(idx), _p(ts), _p(ln), C.c_int64(len(idx)),
+                          C.c_int64(traj_stride), C.c_int64(T), C.c_int(nc), _p(ca), _p(rw), _p(po), _p(pl),
+                          _p(ph), C.c_int(int(threads)))
+
+
+REF_LIB_PATH = HERE / "_ref" / "libgear_ref.so"
+
+
+class Reference:
+    """The reference's own TableSpec / TrajectoryTable / CpuTrajectoryStorageHandler, compiled
+    unchanged from the reference tree into oracle/_ref/libgear_ref.so (see oracle/Makefile)."""
+
+    @staticmethod
+    def available() -> bool:
+        return REF_LIB_PATH.exists()
+
+    def __init__(self, row_bytes, T, capacity):
+        import torch  # noqa: F401  the library resolves torch / pybind11 symbols from the process
+        self._lib = C.CDLL(str(REF_LIB_PATH))
+        self._lib.gearref_create.restype = C.c_void_p
+        self._lib.gearref_sub.restype = C.c_int64
+        self._lib.gearref_time_gather.restype = C.c_double
+        rb = _i64(row_bytes)
+        self._h = C.c_void_p(self._lib.gearref_create(_p(rb), C.c_int(len(rb)), C.c_int64(T), C.c_int64(capacity)))
+
+    def set(self, column, offset, length, pad):
+        self._lib.gearref_set(self._h, C.c_int(column), C.c_int(offset), C.c_int64(length), C.c_int(pad))
+
+    def sub(self, idx, ts, ln, column):
+        idx, ts, ln = _i64(idx).copy(), _i64(ts).copy(), _i64(ln).copy()
+        n = len(idx)
+        s = np.zeros(n, np.int64); d = np.zeros(n, np.int64); b = np.zeros(n, np.int64)
+        slot = self._lib.gearref_sub(self._h, _p(idx), _p(ts), _p(ln), C.c_int64(n), C.c_int(column),
+                                     _p(s), _p(d), _p(b))
+        return s, d, b, int(slot)
+
+    def time_gather(self, table: np.ndarray, idx, ts, ln, columns, dsts, threads: int, iters: int) -> float:
+        """Seconds for `iters` batches of reference sub() + one memcpy per request."""
+        idx, ts, ln = _i64(idx).copy(), _i64(ts).copy(), _i64(ln).copy()
+        cols = np.ascontiguousarray(columns, np.int32)
+        dptr = (C.c_void_p * len(dsts))(*[d.ctypes.data for d in dsts])
+        return float(self._lib.gearref_time_gather(self._h, _p(table), _p(idx), _p(ts), _p(ln),
+                                                   C.c_int64(len(idx)), _p(cols), C.c_int(len(cols)), dptr,
+                                                   C.c_int(int(threads)), C.c_int(int(iters))))
+
+    def close(self):
+        if self._h:
+            self._lib.gearref_destroy(self._h)
+            self._h = None

@@ -144,3 +144,38 @@ def test_uniform_decode_owner_order(O):
     assert list(o) == [0, 0, 1, 2] and list(l) == [0, 31999, 0, 31999]
     assert list(O.comm_order(0, 4)) == [0, 1, 2, 3]
     assert list(O.comm_order(3, 4)) == [1, 2, 3, 0]
+
+
+def test_threaded_drivers_equal_sequential(O):
+    n = 9 * 4096 + 333
+    p = O.synth_lognormal(3, 3, n)
+    a = O.scan(p)
+    for th in (1, 3, 8):
+        b = O.scan_mt(p, th)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1]) and a[2] == b[2]
+    rows = [20, 3]; T = 40; cap = 11
+    accu, stride = O.table_layout(rows, T)
+    rng = np.random.default_rng(1)
+    table = rng.integers(0, 256, stride * cap, dtype=np.uint8)
+    m = 97
+    idx = rng.integers(0, cap, m); ts = rng.integers(0, T, m); ln = rng.integers(0, T + 1, m)
+    want = [O.fused_subcopy(table, idx, ts, ln, stride, int(accu[c]), T, rows[c], -2, 9, c == 1) for c in range(2)]
+    dsts = [np.full(m * 9 * r, 0xEE, np.uint8) for r in rows]
+    O.gather_mt(table, dsts, idx, ts, ln, stride, T, accu[:2], rows, [-2, -2], [9, 9], [0, 1], threads=4)
+    assert all(np.array_equal(w, d) for w, d in zip(want, dsts))
+
+
+def test_reference_library_when_present(O):
+    if not O.Reference.available():
+        pytest.skip("oracle/_ref/libgear_ref.so is not built on this machine")
+    rows = [68, 24, 4, 1]; T = 1000; cap = 4096
+    ref = O.Reference(rows, T, cap)
+    accu, stride = O.table_layout(rows, T)
+    rng = np.random.default_rng(2)
+    idx = rng.integers(0, cap, 500); ts = rng.integers(0, T, 500); ln = rng.integers(0, T + 1, 500)
+    for col, (off, L, pad) in enumerate([(0, 20, 2), (-7, 20, 1), (5, 3, 0), (-999, 1000, 1)]):
+        ref.set(col, off, L, pad)
+        s, d, b, slot = ref.sub(idx, ts, ln, col)
+        s2, d2, b2, slot2 = O.sub(idx, ts, ln, stride, int(accu[col]), T, rows[col], off, L, pad == 1)
+        assert slot == slot2 and np.array_equal(s, s2) and np.array_equal(d, d2) and np.array_equal(b, b2)
+    ref.close()
