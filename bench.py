@@ -387,13 +387,57 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def run_profile_case(args):
+    """Small single-kernel cases for ncu captures (a few hundred MB on the device):
+    `scan`: --profile-n priorities (default 40M: 320 MB of traffic, larger than L2);
+    `sample_gather`: config-3 rows on a 2,000-trajectory table (378 MB), B=1024, L=64."""
+    import torch
+    from gear_b200 import _native as N
+    from gear_b200 import core
+
+    dev = torch.device("cuda:0")
+    core.init(0)
+    if args.profile == "scan":
+        n = args.profile_n
+        prio = torch.empty(n, dtype=torch.float32, device=dev)
+        core.fill(prio, N.FILL_F32_LOGNORMAL, seed=1)
+        s = core.PrioritySampler(n)
+        for _ in range(args.warmup + args.steps):
+            s.scan(prio)
+        print(json.dumps({"profile": "scan", "n": n, "result": s.result()}))
+        return
+    rows, T, cap, B, L = C3["rows"], C3["T"], 2000, C3["B"], C3["L"]
+    table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
+    table.connect()
+    fill_table(core, N, table, seed=2)
+    h = core.StorageHandler(table)
+    cols = list(range(len(rows)))
+    h.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * len(rows))
+    n = cap * T
+    prio = torch.empty(n, dtype=torch.float32, device=dev)
+    core.fill(prio, N.FILL_F32_LOGNORMAL, seed=3)
+    s = core.PrioritySampler(n)
+    s.scan(prio)
+    u = torch.empty(B, dtype=torch.float64, device=dev)
+    core.fill(u, N.FILL_U01_F64, seed=4)
+    dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=dev) for r in rows]
+    for _ in range(args.warmup + args.steps):
+        s.sample_gather(h, u, cols, dsts, scale=True, zero_fill=True)
+    print(json.dumps({"profile": "sample_gather", "result": s.result()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile", default=None, choices=["scan", "sample_gather"],
+                    help="run one small single-kernel case (for ncu) instead of the benchmark")
+    ap.add_argument("--profile-n", type=int, default=40_000_000, help="priorities for --profile scan")
     args = ap.parse_args()
+    if args.profile:
+        return run_profile_case(args)
     if args.impl == "reference":
         return run_reference(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:

@@ -10,7 +10,7 @@ import os
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "lib" / "libgear_b200.so"
+LIB_PATH = Path(os.environ.get("GEAR_B200_LIB", PKG / "lib" / "libgear_b200.so"))
 
 OK = 0
 ERR_INVALID, ERR_CUDA, ERR_NOMEM, ERR_STATE, ERR_TIMEOUT, ERR_NCCL, ERR_UNSUPPORTED = range(1, 8)

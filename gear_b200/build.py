@@ -45,11 +45,24 @@ def needs_build() -> bool:
     return any(d.stat().st_mtime > LIB.stat().st_mtime for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, defines: list[str] | None = None,
+          out: Path | None = None) -> Path:
+    """Build the library; `defines` (-D flags) and `out` make tuning variants beside the default."""
+    global LIB
+    variant = bool(defines or out)
+    lib_path = Path(out) if out else LIB
+    if not force and not variant and not needs_build():
         return LIB
+    LIB_default, LIB = LIB, lib_path
+    try:
+        return _build(verbose, defines or [])
+    finally:
+        LIB = LIB_default
+
+
+def _build(verbose: bool, defines: list[str]) -> Path:
     LIB.parent.mkdir(parents=True, exist_ok=True)
-    objdir = PKG / "lib" / "obj"
+    objdir = LIB.parent / ("obj_" + LIB.stem if defines else "obj")
     objdir.mkdir(exist_ok=True)
     nvcc = _nvcc()
     objs = []
@@ -57,7 +70,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for src in sources():
         obj = objdir / (src.stem + ".o")
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-I", str(ROOT / "include"), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-I", str(ROOT / "include"), "-I", str(CSRC),
+               "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -51,9 +51,16 @@ constexpr int kThreads = kComputeThreads + 64;  // + loader warp + look-back war
 constexpr int kTilesPerWarp = 4;
 constexpr int kPart = kComputeWarps * kTilesPerWarp * 128;
 static_assert(kPart == GEARB_PART, "partition size is part of the ABI");
-constexpr int kStages = 4;   // ring slots of one partition each
-constexpr int kGroupMax = 4; // partitions per ticket
+#ifndef GEARB_SCAN_STAGES
+#define GEARB_SCAN_STAGES 4
+#endif
+#ifndef GEARB_SCAN_GROUP
+#define GEARB_SCAN_GROUP 4
+#endif
+constexpr int kStages = GEARB_SCAN_STAGES;   // ring slots of one partition each
+constexpr int kGroupMax = GEARB_SCAN_GROUP;  // partitions per ticket
 constexpr int kRing = 16;    // aggregate ring entries (compute -> look-back)
+constexpr int kSuper = 16;   // partitions per look-back descriptor
 
 constexpr unsigned kSpinLimit = 1u << 20;  // polls of a shared-memory word / mbarrier before giving up
 constexpr unsigned kLookLimit = 1u << 17;  // polls (x ~100 ns) of a predecessor descriptor
@@ -117,6 +124,11 @@ __device__ __forceinline__ void ld_desc(const unsigned long long *p, unsigned lo
   asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[0]), "=l"(w[1]) : "l"(p) : "memory");
   asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[2]), "=l"(w[3]) : "l"(p + 2) : "memory");
 }
+__device__ __forceinline__ unsigned long long ld_u64_relaxed(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ unsigned ld_u32_relaxed(const unsigned *p) {
   unsigned v;
   asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -167,13 +179,15 @@ struct ScanArgs {
   float *cdf;
   double *l1;
   ScanHeader *hdr;
-  unsigned long long *desc;  // per group: {agg hi, agg lo, prefix hi, prefix lo}
-  double *agg;               // per partition, for the in-order rebuild
+  unsigned *gcount;          // per super-group: partitions finished (returns to 0 by itself)
+  unsigned long long *desc;  // per super-group: {agg hi, agg lo, prefix hi, prefix lo}
+  unsigned long long *aggw;  // per partition: (tag << 32) | bits of the float32 aggregate
   int32_t *status;
   int64_t n;
   unsigned nparts;
-  unsigned group;   // partitions per ticket
-  unsigned ngroups;
+  unsigned group;    // partitions per ticket (1, 2 or 4: divides kSuper)
+  unsigned ngroups;  // tickets
+  unsigned nsuper;   // super-groups of kSuper partitions
 };
 
 struct __align__(128) Smem {
@@ -300,7 +314,11 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
 
     // ---- scan of the warp totals (every warp repeats it; lanes >= 8 hold zeros)
     float y = lane < kComputeWarps ? sm.wt[buf][lane] : 0.f;
-    y = hs_sum(y, lane);
+#pragma unroll
+    for (int d = 1; d < kComputeWarps; d <<= 1) {  // Hillis-Steele over the 8 warp totals
+      const float t = __shfl_up_sync(kFull, y, d);
+      if (lane >= d) y = __fadd_rn(t, y);
+    }
     const float xs = __shfl_sync(kFull, y, warp == 0 ? 0 : warp - 1);
     const float X = warp == 0 ? 0.f : xs;
 
@@ -382,12 +400,111 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
 }
 
 // --------------------------------------------------------------- look-back warp
-__device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int lane) {
+// Two levels keep the look-back cheap.  A ticket (up to 4 partitions) only publishes its
+// partitions' aggregates and bumps the counter of its super-group (16 partitions); the warp
+// whose bump completes the super-group chains the 16 aggregates in order, publishes ONE
+// descriptor and looks back over earlier super-groups.  The number of look-back
+// participants, and with it the time the prefix needs to travel down the table, drops 4x
+// against one look-back per ticket.
+// The warp that completed group g: chain its aggregates, publish, look back, write l1.
+__device__ void finish_group(const ScanArgs &a, unsigned g, unsigned epoch, int lane) {
   const unsigned tagA = (epoch << 2) | 1u, tagP = (epoch << 2) | 2u;
+  const unsigned first = g * kSuper;
+  const unsigned in_group = min(static_cast<unsigned>(kSuper), a.nparts - first);
   bool inexact = false;
-  double run = 0.0;   // in-order sum of the current group's aggregates so far
-  double lane_incl = 0.0;  // lane k keeps the inclusive sum after the group's k-th partition
-  unsigned have = 0;
+  // The counter says every partition of the group has issued its aggregate; the words carry
+  // their own tag, so poll (normally zero times) until each one is visible.
+  double incl = 0.0;
+  bool late = false;
+  if (lane < static_cast<int>(in_group)) {
+    unsigned polls = 0;
+    for (;;) {
+      const unsigned long long w = ld_u64_relaxed(&a.aggw[first + lane]);
+      if (static_cast<unsigned>(w >> 32) == tagA) {
+        incl = static_cast<double>(__uint_as_float(static_cast<unsigned>(w)));
+        break;
+      }
+      if (++polls > kLookLimit) {
+        late = true;
+        break;
+      }
+      __nanosleep(32);
+    }
+  }
+  if (__any_sync(kFull, late)) {
+    if (lane == 0) {
+      atomicOr(&a.hdr->pad[0], kHdrRebuild);
+      atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_SCAN_ABORTED);
+    }
+    return;
+  }
+  // inclusive in-order sums of the group's aggregates (shuffle scan; exact => order-free)
+#pragma unroll
+  for (int d = 1; d < kSuper; d <<= 1) {
+    const double t = __shfl_up_sync(kFull, incl, d);
+    if (lane >= d) incl = checked_add(t, incl, inexact);
+  }
+  const double gsum = __shfl_sync(kFull, incl, in_group - 1);
+  unsigned long long *mine = a.desc + static_cast<size_t>(g) * 4;
+  double excl = 0.0;
+  bool gave_up = false;
+  if (g > 0) {
+    if (lane == 0) publish(mine, gsum, tagA);
+    long long j = static_cast<long long>(g) - 1;
+    for (;;) {
+      const long long q = j - lane;
+      double val = 0.0;
+      int kind = 2;  // 2 = prefix known, 1 = aggregate known, 0 = nothing yet; "group -1" has prefix 0
+      unsigned polls = 0;
+      for (;;) {
+        if (q >= 0) {
+          unsigned long long w[4];
+          ld_desc(a.desc + static_cast<size_t>(q) * 4, w);
+          kind = decode(w[2], w[3], tagP, val) ? 2 : (decode(w[0], w[1], tagA, val) ? 1 : 0);
+        }
+        if (__all_sync(kFull, kind != 0)) break;
+        ++polls;
+        const bool quit =
+            polls > kLookLimit || ((polls & 31u) == 0 && (ld_u32_relaxed(&a.hdr->pad[0]) & kHdrRebuild));
+        if (__any_sync(kFull, quit)) {
+          gave_up = true;
+          break;
+        }
+        __nanosleep(64);
+      }
+      if (gave_up) break;
+      const unsigned pmask = __ballot_sync(kFull, kind == 2);
+      const int fp = pmask ? (__ffs(pmask) - 1) : 32;
+      if (lane > fp) val = 0.0;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        const double o = __shfl_down_sync(kFull, val, d);
+        val = checked_add(val, o, inexact);
+      }
+      const double wsum = __shfl_sync(kFull, val, 0);
+      excl = checked_add(excl, wsum, inexact);
+      if (pmask) break;
+      j -= 32;
+    }
+  }
+  if (gave_up) {
+    // Nothing to publish; later groups find the rebuild flag and stop waiting too.
+    if (lane == 0) {
+      const unsigned old = atomicOr(&a.hdr->pad[0], kHdrRebuild);
+      if (!(old & kHdrRebuild)) atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_LOOKBACK_TIMEOUT);
+    }
+    return;
+  }
+  if (lane == 0) publish(mine + 2, checked_add(excl, gsum, inexact), tagP);
+  if (lane < static_cast<int>(in_group)) __stcg(&a.l1[first + lane + 1], checked_add(excl, incl, inexact));
+  if (g == 0 && lane == 0) __stcg(&a.l1[0], 0.0);
+  if (__any_sync(kFull, inexact) && lane == 0) atomicOr(&a.hdr->pad[0], kHdrRebuild);
+}
+
+
+__device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int lane) {
+  const unsigned tagA = (epoch << 2) | 1u;
+  unsigned have = 0;  // partitions of the current ticket seen so far
   for (;;) {
     // ---- pop one aggregate
     const unsigned tl = sm.ring_tail;
@@ -398,7 +515,7 @@ __device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int l
         ok = false;
         break;
       }
-      __nanosleep(32);
+      __nanosleep(20);
     }
     if (!__all_sync(kFull, ok)) {
       if (lane == 0 && !sm.abort) raise_abort(sm, a);
@@ -410,78 +527,30 @@ __device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int l
     if (lane == 0) sm.ring_tail = tl + 1;
     if (part < 0) break;
 
-    const double ad = static_cast<double>(aggf);
-    if (lane == 0) __stcg(&a.agg[part], ad);
-    const unsigned g = static_cast<unsigned>(part) / a.group;
-    const unsigned k = static_cast<unsigned>(part) - g * a.group;
-    if (k != have) {  // aggregates of a group arrive in order; anything else is a logic error
+    // The aggregate word validates itself (tag + float bits in one 64-bit store): no fence.
+    if (lane == 0)
+      st_u64(&a.aggw[part], (static_cast<unsigned long long>(tagA) << 32) | __float_as_uint(aggf));
+    const unsigned t = static_cast<unsigned>(part) / a.group;
+    const unsigned k = static_cast<unsigned>(part) - t * a.group;
+    if (k != have) {  // aggregates of a ticket arrive in order; anything else is a logic error
       if (lane == 0) raise_abort(sm, a);
       break;
     }
-    run = (k == 0) ? ad : checked_add(run, ad, inexact);
-    if (lane == static_cast<int>(k)) lane_incl = run;
     have = k + 1;
-    const unsigned in_group = min(a.group, a.nparts - g * a.group);
-    if (have < in_group) continue;
+    const unsigned in_ticket = min(a.group, a.nparts - t * a.group);
+    if (have < in_ticket) continue;
     have = 0;
-
-    // ---- the group is complete: publish its aggregate, look back, publish its prefix
-    const double gsum = run;
-    unsigned long long *mine = a.desc + static_cast<size_t>(g) * 4;
-    double excl = 0.0;
-    bool gave_up = false;
-    if (g > 0) {
-      if (lane == 0) publish(mine, gsum, tagA);
-      long long j = static_cast<long long>(g) - 1;
-      for (;;) {
-        const long long q = j - lane;
-        double val = 0.0;
-        int kind = 2;  // 2 = prefix known, 1 = aggregate known, 0 = nothing yet; "group -1" has prefix 0
-        unsigned polls = 0;
-        for (;;) {
-          if (q >= 0) {
-            unsigned long long w[4];
-            ld_desc(a.desc + static_cast<size_t>(q) * 4, w);
-            kind = decode(w[2], w[3], tagP, val) ? 2 : (decode(w[0], w[1], tagA, val) ? 1 : 0);
-          }
-          if (__all_sync(kFull, kind != 0)) break;
-          ++polls;
-          const bool quit = polls > kLookLimit || sm.abort ||
-                            ((polls & 31u) == 0 && (ld_u32_relaxed(&a.hdr->pad[0]) & kHdrRebuild));
-          if (__any_sync(kFull, quit)) {
-            gave_up = true;
-            break;
-          }
-          __nanosleep(64);
-        }
-        if (gave_up) break;
-        const unsigned pmask = __ballot_sync(kFull, kind == 2);
-        const int fp = pmask ? (__ffs(pmask) - 1) : 32;
-        if (lane > fp) val = 0.0;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-          const double o = __shfl_down_sync(kFull, val, d);
-          val = checked_add(val, o, inexact);
-        }
-        const double wsum = __shfl_sync(kFull, val, 0);
-        excl = checked_add(excl, wsum, inexact);
-        if (pmask) break;
-        j -= 32;
-      }
-    }
-    inexact = __any_sync(kFull, inexact);
-    if (gave_up) {
-      // Nothing to publish; successors find the rebuild flag and stop waiting too.
-      if (lane == 0) {
-        const unsigned old = atomicOr(&a.hdr->pad[0], kHdrRebuild);
-        if (!(old & kHdrRebuild)) atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_LOOKBACK_TIMEOUT);
-      }
-    } else {
-      if (lane == 0) publish(mine + 2, checked_add(excl, gsum, inexact), tagP);
-      if (lane < static_cast<int>(in_group))
-        __stcg(&a.l1[static_cast<size_t>(g) * a.group + lane + 1], checked_add(excl, lane_incl, inexact));
-      if (g == 0 && lane == 0) __stcg(&a.l1[0], 0.0);
-      if (__any_sync(kFull, inexact) && lane == 0) atomicOr(&a.hdr->pad[0], kHdrRebuild);
+#ifdef GEARB_SCAN_NO_LOOKBACK  // timing experiment only: level 1 is left unwritten
+    continue;
+#endif
+    const unsigned sg = static_cast<unsigned>(part) / kSuper;
+    const unsigned in_super = min(static_cast<unsigned>(kSuper), a.nparts - sg * kSuper);
+    unsigned arrived = 0;
+    if (lane == 0) arrived = atomicAdd(&a.gcount[sg], in_ticket) + in_ticket;
+    arrived = __shfl_sync(kFull, arrived, 0);
+    if (arrived == in_super) {
+      if (lane == 0) a.gcount[sg] = 0u;  // last one to touch it: ready for the next launch
+      finish_group(a, sg, epoch, lane);
     }
   }
 }
@@ -531,11 +600,13 @@ __global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
         double acc = 0.0;
         __stcg(&a.l1[0], 0.0);
         for (unsigned q = 0; q < a.nparts; ++q) {
-          acc = __dadd_rn(acc, __ldcg(&a.agg[q]));
+          acc = __dadd_rn(acc, static_cast<double>(__uint_as_float(static_cast<unsigned>(__ldcg(&a.aggw[q])))));
           __stcg(&a.l1[q + 1], acc);
         }
         atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_L1_RESUMMED);
       }
+      if (atomicOr(reinterpret_cast<unsigned *>(a.status), 0u) & GEARB_ST_SCAN_ABORTED)
+        for (unsigned g = 0; g < a.nsuper; ++g) a.gcount[g] = 0u;  // counters may be left half-way
       a.hdr->pad[0] = 0u;
       a.hdr->ticket = 0u;
       a.hdr->done = 0u;
@@ -549,11 +620,13 @@ inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 
 }  // namespace
 
-// Scratch layout: header | descriptors (32 B per partition, enough for any grouping) |
-// per-partition aggregates (8 B).
+// Scratch layout: header | super-group counters (4 B) | super-group descriptors (32 B) |
+// partition aggregate words (8 B).
 int64_t scan_scratch_bytes(int64_t n) {
   const int64_t nparts = (n + kPart - 1) / kPart;
-  return static_cast<int64_t>(sizeof(ScanHeader)) + align256(nparts * 32) + align256(nparts * 8);
+  const int64_t nsuper = (nparts + kSuper - 1) / kSuper;
+  return static_cast<int64_t>(sizeof(ScanHeader)) + align256(nsuper * 4) + align256(nsuper * 32) +
+         align256(nparts * 8);
 }
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
@@ -571,9 +644,13 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   GEARB_REQUIRE(scratch_bytes >= scan_scratch_bytes(n), "scan: scratch too small (%lld < %lld)",
                 (long long)scratch_bytes, (long long)scan_scratch_bytes(n));
   char *sc = static_cast<char *>(scratch);
+  const int64_t nsuper = (nparts + kSuper - 1) / kSuper;
+  const int64_t off_desc = sizeof(ScanHeader) + align256(nsuper * 4);
+  const int64_t off_agg = off_desc + align256(nsuper * 32);
   if (fresh) {
-    // Only the header and the descriptors must start at zero.
-    GEARB_CUDA(cudaMemsetAsync(sc, 0, sizeof(ScanHeader) + align256(nparts * 32), stream));
+    // Everything must start at zero: the epoch restarts at 0, so a stale tagged word could
+    // otherwise pass for a fresh one.
+    GEARB_CUDA(cudaMemsetAsync(sc, 0, static_cast<size_t>(scan_scratch_bytes(n)), stream));
   }
 
   const size_t smem_bytes = sizeof(Smem) + 128;
@@ -592,8 +669,10 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.cdf = cdf;
   a.l1 = l1;
   a.hdr = reinterpret_cast<ScanHeader *>(sc);
-  a.desc = reinterpret_cast<unsigned long long *>(sc + sizeof(ScanHeader));
-  a.agg = reinterpret_cast<double *>(sc + sizeof(ScanHeader) + align256(nparts * 32));
+  a.gcount = reinterpret_cast<unsigned *>(sc + sizeof(ScanHeader));
+  a.desc = reinterpret_cast<unsigned long long *>(sc + off_desc);
+  a.aggw = reinterpret_cast<unsigned long long *>(sc + off_agg);
+  a.nsuper = static_cast<unsigned>(nsuper);
   a.status = status;
   a.n = n;
   a.nparts = static_cast<unsigned>(nparts);
