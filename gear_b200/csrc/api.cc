@@ -415,7 +415,8 @@ int gearb_handler_sub(const gearb_handler *h, const int64_t *idx, const int64_t 
 
 // Fills the launch parameters shared by the gather kernels from the handler's patterns.
 static int build_gather_params(gearb_handler *h, const int32_t *columns, int ncols, int64_t n,
-                               void *const *dst, int zero_fill, int32_t *status, GatherParams &p) {
+                               void *const *dst, int zero_fill, int32_t *status, GatherParams &p,
+                               int piece_bytes = 2048) {
   GEARB_REQUIRE(h && h->table, "gather: null handler");
   GEARB_REQUIRE(ncols >= 0 && ncols <= GEARB_MAX_COLUMNS, "gather: %d columns", ncols);
   GEARB_REQUIRE(n >= 0, "gather: negative request count");
@@ -431,8 +432,8 @@ static int build_gather_params(gearb_handler *h, const int32_t *columns, int nco
   p.T = t->T;
   p.status = status;
   p.zero_fill = zero_fill ? 1 : 0;
-  p.chunk_bytes = 2048;
-  int64_t chunks = 0;
+  p.chunk_bytes = piece_bytes;
+  int64_t chunks = 0, stage = 0;
   int used = 0;
   for (int i = 0; i < ncols; ++i) {
     const Pattern *pat = nullptr;
@@ -450,6 +451,8 @@ static int build_gather_params(gearb_handler *h, const int32_t *columns, int nco
     c.pat_length = static_cast<int32_t>(pat->length);
     c.pad_head = pat->pad == GEARB_PAD_HEAD;
     c.chunk_first = static_cast<int32_t>(chunks);
+    c.stage_off = static_cast<int32_t>(stage < (int64_t(1) << 30) ? stage : 0);
+    stage += round_up(slot + 32, 128);  // covering 16-byte blocks of a misaligned segment fit
     const int64_t cc = (slot + p.chunk_bytes - 1) / p.chunk_bytes;
     c.chunk_count = static_cast<int32_t>(cc);
     chunks += cc;
@@ -457,6 +460,8 @@ static int build_gather_params(gearb_handler *h, const int32_t *columns, int nco
   }
   p.ncols = used;
   p.chunks_per_request = static_cast<int32_t>(chunks);
+  // Small requests from an HBM table are staged through shared memory by the fused kernel.
+  p.stage_bytes = (t->hbm && stage > 0 && stage <= 24 * 1024) ? static_cast<int32_t>(stage) : 0;
   return GEARB_OK;
 }
 
@@ -612,7 +617,7 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
                                 void *stream) {
   GEARB_REQUIRE(s, "sample_gather: null sampler");
   GatherParams p;
-  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p);
+  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
   if (rc != GEARB_OK) return rc;
   GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,

@@ -69,6 +69,8 @@ struct GatherColumn {
   int32_t pad_head;    // 1 when PadOption::kHead
   int32_t chunk_first; // first chunk id of this column inside a request
   int32_t chunk_count; // chunks this column's slot is cut into
+  int32_t stage_off;   // byte offset of this column's staging area in shared memory
+  int32_t reserved;
 };
 
 struct GatherParams {
@@ -83,6 +85,8 @@ struct GatherParams {
   int32_t chunks_per_request;
   int32_t chunk_bytes;
   int32_t zero_fill;
+  int32_t stage_bytes;  // > 0: a request's columns fit this much shared memory and the table is in HBM
+  int32_t reserved;
   GatherColumn cols[GEARB_MAX_COLUMNS];
 };
 

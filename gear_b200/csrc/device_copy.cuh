@@ -9,8 +9,6 @@
 namespace gearb {
 namespace dev {
 
-constexpr int kUnroll = 4;
-
 __device__ __forceinline__ uint4 ld_nc(const uint4 *p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -44,9 +42,19 @@ __device__ __forceinline__ uint4 shift_pair(const uint4 &a, const uint4 &b, unsi
   return o;
 }
 
+template <bool kSmemSrc>
+__device__ __forceinline__ uint4 load16(const uint4 *p) {
+  if constexpr (kSmemSrc) return *p;  // staged in shared memory: an ordinary load
+  else return ld_nc(p);
+}
+
 // One warp copies nbytes from s to d; any alignment on either side.
 // Reads touch only 16-byte aligned blocks that contain at least one source byte.
-__device__ __forceinline__ void warp_copy(uint8_t *d, const uint8_t *s, int nbytes, int lane) {
+// kSmemSrc: the source was staged in shared memory.
+template <bool kSmemSrc>
+__device__ __forceinline__ void warp_copy_t(uint8_t *d, const uint8_t *s, int nbytes, int lane) {
+  // Loads in flight per lane: global sources need several to cover the latency, shared ones do not.
+  constexpr int kUnroll = kSmemSrc ? 1 : 4;
   int head = static_cast<int>((16u - (reinterpret_cast<uintptr_t>(d) & 15u)) & 15u);
   if (head > nbytes) head = nbytes;
   if (lane < head) d[lane] = s[lane];
@@ -62,7 +70,7 @@ __device__ __forceinline__ void warp_copy(uint8_t *d, const uint8_t *s, int nbyt
       uint4 r[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
-        if (v0 + 32 * u < nvec) r[u] = ld_nc(sv + v0 + 32 * u);
+        if (v0 + 32 * u < nvec) r[u] = load16<kSmemSrc>(sv + v0 + 32 * u);
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
         if (v0 + 32 * u < nvec) dv[v0 + 32 * u] = r[u];
@@ -75,8 +83,8 @@ __device__ __forceinline__ void warp_copy(uint8_t *d, const uint8_t *s, int nbyt
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
         if (v0 + 32 * u < nvec) {
-          a[u] = ld_nc(sv + v0 + 32 * u);
-          b[u] = ld_nc(sv + v0 + 32 * u + 1);
+          a[u] = load16<kSmemSrc>(sv + v0 + 32 * u);
+          b[u] = load16<kSmemSrc>(sv + v0 + 32 * u + 1);
         }
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u)
@@ -86,6 +94,10 @@ __device__ __forceinline__ void warp_copy(uint8_t *d, const uint8_t *s, int nbyt
   const int done = nvec << 4;
   const int tail = nbytes - done;
   if (lane < tail) d[done + lane] = s[done + lane];
+}
+
+__device__ __forceinline__ void warp_copy(uint8_t *d, const uint8_t *s, int nbytes, int lane) {
+  warp_copy_t<false>(d, s, nbytes, lane);
 }
 
 __device__ __forceinline__ void warp_zero(uint8_t *d, int nbytes, int lane) {
@@ -103,41 +115,44 @@ __device__ __forceinline__ void warp_zero(uint8_t *d, int nbytes, int lane) {
 }
 
 
-// One warp handles piece `cq` of column `col` for request g = (idx, ts, len):
-// copies the part of the clipped segment that falls into the piece and, when
-// asked, zero-fills the padding that falls into it.
-__device__ __forceinline__ void gather_piece(const GatherParams &P, const GatherColumn &col, int cq,
-                                             int64_t g, int64_t idx, int64_t ts, int64_t len, int lane,
+// The clipped segment of column `col` for request (idx, ts, len): first timestep and byte
+// count, the addressing of CpuTrajectoryStorageHandler::sub (handler.cc:104-115).
+__device__ __forceinline__ void clip_segment(const GatherParams &P, const GatherColumn &col, int64_t idx,
+                                             int64_t ts, int64_t len, int64_t &start, int64_t &bytes,
                                              unsigned &flags) {
-  const int64_t row = col.row;
-  const int64_t slot = row * col.pat_length;
-  int64_t bytes = 0, start = 0;
+  bytes = 0;
+  start = 0;
   if (idx < 0 || idx >= P.capacity) {
     flags |= GEARB_ST_BAD_REQUEST;
-  } else {
-    if (len > P.T) {
-      len = P.T;
-      flags |= GEARB_ST_LEN_CLAMPED;
-    }
-    start = ts + col.pat_offset;
-    if (start < 0) start = 0;
-    int64_t end = start + col.pat_length;
-    if (end > len) end = len;
-    const int64_t steps = end - start;
-    bytes = steps > 0 ? steps * row : 0;
+    return;
   }
+  if (len > P.T) {
+    len = P.T;
+    flags |= GEARB_ST_LEN_CLAMPED;
+  }
+  start = ts + col.pat_offset;
+  if (start < 0) start = 0;
+  int64_t end = start + col.pat_length;
+  if (end > len) end = len;
+  const int64_t steps = end - start;
+  bytes = steps > 0 ? steps * static_cast<int64_t>(col.row) : 0;
+}
+
+// One warp handles piece `cq` of request g's slot of column `col`: copies the part of the
+// segment (`bytes` bytes starting at `data`) that falls into the piece and, when asked,
+// zero-fills the padding that falls into it.
+template <bool kSmemSrc>
+__device__ __forceinline__ void copy_piece(const GatherParams &P, const GatherColumn &col, int cq, int64_t g,
+                                           const uint8_t *data, int64_t bytes, int lane) {
+  const int64_t slot = static_cast<int64_t>(col.row) * col.pat_length;
   const int64_t data_off = col.pad_head ? slot - bytes : 0;
   const int64_t c0 = static_cast<int64_t>(cq) * P.chunk_bytes;
   int64_t c1 = c0 + P.chunk_bytes;
   if (c1 > slot) c1 = slot;
   uint8_t *dslot = col.dst + g * slot;
-
   const int64_t lo = c0 > data_off ? c0 : data_off;
   const int64_t hi = c1 < data_off + bytes ? c1 : data_off + bytes;
-  if (hi > lo) {
-    const uint8_t *src = P.table + idx * P.traj_stride + col.col_offset + start * row;
-    warp_copy(dslot + lo, src + (lo - data_off), static_cast<int>(hi - lo), lane);
-  }
+  if (hi > lo) warp_copy_t<kSmemSrc>(dslot + lo, data + (lo - data_off), static_cast<int>(hi - lo), lane);
   if (P.zero_fill) {
     // padding before the data (head padding) and after it (tail padding)
     const int64_t z1 = c1 < data_off ? c1 : data_off;
@@ -145,6 +160,21 @@ __device__ __forceinline__ void gather_piece(const GatherParams &P, const Gather
     const int64_t z0 = c0 > data_off + bytes ? c0 : data_off + bytes;
     if (c1 > z0) warp_zero(dslot + z0, static_cast<int>(c1 - z0), lane);
   }
+}
+
+// Address of the segment's first byte in the table.
+__device__ __forceinline__ const uint8_t *segment_src(const GatherParams &P, const GatherColumn &col, int64_t idx,
+                                                      int64_t start) {
+  return P.table + idx * P.traj_stride + col.col_offset + start * static_cast<int64_t>(col.row);
+}
+
+// Straight from the table (HBM or mapped host memory) to the destination.
+__device__ __forceinline__ void gather_piece(const GatherParams &P, const GatherColumn &col, int cq,
+                                             int64_t g, int64_t idx, int64_t ts, int64_t len, int lane,
+                                             unsigned &flags) {
+  int64_t start, bytes;
+  clip_segment(P, col, idx, ts, len, start, bytes, flags);
+  copy_piece<false>(P, col, cq, g, bytes > 0 ? segment_src(P, col, idx, start) : P.table, bytes, lane);
 }
 
 // Column that owns piece q of a request (pieces are numbered column by column).

@@ -3,13 +3,21 @@
 // The reference does this in four steps with the host in between: sample
 // (gear/sampler/global_sampler.py:93-152), partition (offline_loader.py:123-140),
 // read the timesteps on the host (:168-177) and one fused_subcopy launch per
-// column (:178-203).  Here one CTA serves one request end to end:
-//   1. the whole CTA searches the two-level cumulative table for the request's
-//      variate, 128 probes per round (two or three rounds per level);
+// column (:178-203).  Here one CTA of four warps serves one request end to end:
+//   1. the CTA searches the two-level cumulative table for the request's variate,
+//      256 probes per round (two per thread), two rounds per level; the probe
+//      loads of a level's first round do not depend on the value they are compared
+//      with, so they are issued together with the load of that value;
 //   2. the flat step index is decoded to GEAR's (trajectory, timestep, length);
-//   3. the CTA's four warps copy the request's slots of every subscribed column.
+//   3. the request's columns are staged in shared memory by bulk asynchronous copies that
+//      are all in flight at once (when they fit and the table is in HBM), and the four warps
+//      realign them into the destination slots; larger requests are copied directly.
 // Results are identical to search_kernel + decode_kernel + gather_kernel run one
 // after the other; only the launches and the index round trip through HBM go.
+//
+// The kernel is launched with programmatic stream serialisation: its CTAs may be
+// scheduled while the kernel before it in the stream (normally the scan) drains,
+// and wait in griddepcontrol.wait until that kernel's results are visible.
 #include "common.h"
 #include "device_copy.cuh"
 
@@ -18,35 +26,82 @@ namespace {
 
 constexpr int kThreads = 128;
 constexpr int kWarps = kThreads / 32;
+constexpr int kSlots = 2 * kThreads;  // probes per round
 constexpr unsigned kFull = 0xffffffffu;
+constexpr unsigned kWaitLimit = 1u << 20;  // mbarrier polls before a staged copy is declared lost
 
-// First q in [lo, hi] with a[q] > v, given a[hi] > v; all kThreads threads take part.
-template <typename T>
-__device__ __forceinline__ int64_t block_upper_bound(const T *a, int64_t lo, int64_t hi, T v,
-                                                     unsigned (*masks)[kWarps], int &round) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  for (;;) {
-    const int64_t width = hi - lo + 1;
-    const int64_t step = (width + kThreads - 1) / kThreads;
-    int64_t q = lo + (tid + 1) * step - 1;
-    if (q > hi) q = hi;
-    const unsigned m = __ballot_sync(kFull, __ldg(a + q) > v);
-    unsigned(&slot)[kWarps] = masks[round & 1];
-    ++round;
-    if (lane == 0) slot[warp] = m;
-    __syncthreads();
-    int first = kThreads - 1;  // the last thread probes hi, which is known to be greater
-#pragma unroll
-    for (int w = kWarps - 1; w >= 0; --w) {
-      const unsigned mw = slot[w];
-      if (mw) first = w * 32 + __ffs(mw) - 1;
-    }
-    int64_t qf = lo + (first + 1) * step - 1;
-    if (qf > hi) qf = hi;
-    if (first > 0) lo = lo + first * step;
-    hi = qf;
-    if (step == 1 || lo >= hi) return hi;
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// 1-D bulk asynchronous copy global -> this CTA's shared memory; completes on `bar`.
+__device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, unsigned bytes, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_addr(dst_smem)),
+      "l"(src), "r"(bytes), "r"(smem_addr(bar))
+      : "memory");
+}
+
+struct Range {
+  int64_t lo, hi;  // the answer (first index whose entry is greater) lies in [lo, hi]
+  int64_t step;
+};
+
+__device__ __forceinline__ void probe_positions(const Range &r, int64_t &q0, int64_t &q1, int64_t &step) {
+  const int64_t width = r.hi - r.lo + 1;
+  step = (width + kSlots - 1) / kSlots;
+  q0 = r.lo + (static_cast<int64_t>(threadIdx.x) + 1) * step - 1;
+  q1 = r.lo + (static_cast<int64_t>(threadIdx.x) + kThreads + 1) * step - 1;
+  if (q0 > r.hi) q0 = r.hi;
+  if (q1 > r.hi) q1 = r.hi;
+}
+
+// Narrow [lo, hi] to the slot of the first probe that compared greater.  Returns that slot.
+// Slot s probes lo + (s+1)*step - 1 (clamped); slot kSlots-1 always probes hi, whose entry is
+// known to be greater.
+__device__ __forceinline__ int resolve(Range &r, int64_t step, bool gt0, bool gt1, unsigned (*masks)[2 * kWarps],
+                                       int &round) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned m0 = __ballot_sync(kFull, gt0), m1 = __ballot_sync(kFull, gt1);
+  unsigned *slot = masks[round & 1];
+  ++round;
+  if (lane == 0) {
+    slot[warp] = m0;
+    slot[kWarps + warp] = m1;
   }
+  __syncthreads();
+  int first = kSlots - 1;
+#pragma unroll
+  for (int w = 2 * kWarps - 1; w >= 0; --w) {
+    const unsigned mw = slot[w];
+    if (mw) first = w * 32 + __ffs(mw) - 1;
+  }
+  int64_t qf = r.lo + (static_cast<int64_t>(first) + 1) * step - 1;
+  if (qf > r.hi) qf = r.hi;
+  if (first > 0) r.lo = r.lo + static_cast<int64_t>(first) * step;
+  r.hi = qf;
+  return first;
 }
 
 struct SampleArgs {
@@ -59,40 +114,103 @@ struct SampleArgs {
   int flags;
 };
 
-__global__ void __launch_bounds__(kThreads, 8)
+__global__ void __launch_bounds__(kThreads, 7)
 sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a) {
-  __shared__ unsigned masks[2][kWarps];
+  extern __shared__ __align__(128) uint8_t stage[];  // P.stage_bytes of staging area
+  __shared__ unsigned masks[2][2 * kWarps];
+  __shared__ float vals[kSlots];
+  __shared__ uint64_t stage_bar;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  unsigned flags = 0;
-  int near_count = 0;
+  unsigned flags = 0, stage_parity = 0;
   int round = 0;
-  const double total = __ldg(a.l1 + a.nparts);
+  if (threadIdx.x == 0) {
+    mbar_init(&stage_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  // Everything this kernel reads may have been written by the kernel before it in the stream.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   for (int64_t g = blockIdx.x; g < P.n; g += gridDim.x) {
+    // ---- level 1, first round: the probes and the variate travel together
+    Range r1{0, a.nparts - 1, 0};
+    int64_t q0, q1, step;
+    probe_positions(r1, q0, q1, step);
+    double p0 = __ldg(a.l1 + 1 + q0), p1 = __ldg(a.l1 + 1 + q1);
+    const double total = __ldg(a.l1 + a.nparts);
+    double v = __ldg(a.u + g);
     int64_t flat;
     if (!(total > 0.0)) {
       flat = a.n - 1;  // nothing selectable: defined as the last index
     } else {
-      double v = __ldg(a.u + g);
       if (a.flags & GEARB_SEARCH_SCALE) v = __dmul_rn(v, total);
       if (!(v >= 0.0)) v = 0.0;
       if (!(v < total)) v = __longlong_as_double(__double_as_longlong(total) - 1);
-      const int64_t p = block_upper_bound<double>(a.l1 + 1, 0, a.nparts - 1, v, masks, round);
+      for (;;) {
+        resolve(r1, step, p0 > v, p1 > v, masks, round);
+        if (step == 1 || r1.lo >= r1.hi) break;
+        probe_positions(r1, q0, q1, step);
+        p0 = __ldg(a.l1 + 1 + q0);
+        p1 = __ldg(a.l1 + 1 + q1);
+      }
+      const int64_t p = r1.hi;
+
+      // ---- level 2, first round: probes, the partition's offset and its last entry together
       const int64_t base = p * GEARB_PART;
       const int64_t valid = (a.n - base < GEARB_PART) ? (a.n - base) : GEARB_PART;
-      float r = __double2float_rn(__dsub_rn(v, __ldg(a.l1 + p)));
-      const float last = __ldg(a.cdf + base + valid - 1);
+      const float *cp = a.cdf + base;
+      Range r2{0, valid - 1, 0};
+      probe_positions(r2, q0, q1, step);
+      float c0 = __ldg(cp + q0), c1 = __ldg(cp + q1);
+      const double off = __ldg(a.l1 + p);
+      const float last = __ldg(cp + valid - 1);
+      float r = __double2float_rn(__dsub_rn(v, off));
       if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
-      const int64_t j = block_upper_bound<float>(a.cdf + base, 0, valid - 1, r, masks, round);
+      int first;
+      for (;;) {
+        if (step == 1) {  // keep the last round's entries: the boundary check below reads two of them
+          vals[threadIdx.x] = c0;
+          vals[threadIdx.x + kThreads] = c1;
+        }
+        first = resolve(r2, step, c0 > r, c1 > r, masks, round);
+        if (step == 1 || r2.lo >= r2.hi) break;
+        probe_positions(r2, q0, q1, step);
+        c0 = __ldg(cp + q0);
+        c1 = __ldg(cp + q1);
+      }
+      const int64_t j = r2.hi;
       flat = base + j;
-      if (threadIdx.x == 0 && P.status) {
-        bool near = __uint_as_float(__float_as_uint(r) + 1u) >= __ldg(a.cdf + flat);
-        if (j > 0 && r == __ldg(a.cdf + flat - 1)) near = true;
-        near_count += near;
+
+      // ---- variates within one ulp of a boundary of the chosen entry
+      if (P.status && threadIdx.x == 0) {
+        // After a round with step 1, slot `first` held cdf[j] and slot `first-1` held cdf[j-1].
+        float hi_v, lo_v = 0.f;
+        if (step == 1) {
+          hi_v = vals[first];
+          if (first > 0) lo_v = vals[first - 1];
+          else if (j > 0) lo_v = __ldg(cp + j - 1);
+        } else {
+          hi_v = __ldg(cp + j);
+          if (j > 0) lo_v = __ldg(cp + j - 1);
+        }
+        const bool near = (__uint_as_float(__float_as_uint(r) + 1u) >= hi_v) || (j > 0 && r == lo_v);
+        if (near) atomicAdd(P.status + 1, 1);
       }
     }
-    const int64_t t = flat / P.T;
-    const int64_t ts = flat - t * P.T;
+
+    // ---- decode
+    int64_t t, ts;
+    if (((static_cast<uint64_t>(flat) | static_cast<uint64_t>(P.T)) >> 32) == 0) {
+      const unsigned f32 = static_cast<unsigned>(flat), T32 = static_cast<unsigned>(P.T);
+      const unsigned tq = f32 / T32;
+      t = tq;
+      ts = f32 - tq * T32;
+    } else {
+      t = flat / P.T;
+      ts = flat - t * P.T;
+    }
     const int64_t len = a.lengths ? __ldg(a.lengths + t) : P.T;
     if (threadIdx.x == 0) {
       if (a.out_flat) a.out_flat[g] = flat;
@@ -100,15 +218,64 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
       if (a.out_ts) a.out_ts[g] = ts;
       if (a.out_len) a.out_len[g] = len;
     }
-    for (int q = warp; q < P.chunks_per_request; q += kWarps) {
-      const int c = dev::column_of_piece(P, q);
-      dev::gather_piece(P, P.cols[c], q - P.cols[c].chunk_first, g, t, ts, len, lane, flags);
+
+    // ---- gather
+    if (P.stage_bytes > 0) {
+      // Staged: thread 0 starts one bulk asynchronous copy per column (the 16-byte blocks that
+      // cover the clipped segment) into shared memory, so every column of the request is in
+      // flight at once; then the warps realign from shared memory to the destination.
+      if (threadIdx.x == 0) {
+        unsigned total_tx = 0;
+        for (int c = 0; c < P.ncols; ++c) {
+          int64_t start, bytes;
+          dev::clip_segment(P, P.cols[c], t, ts, len, start, bytes, flags);
+          if (bytes > 0) {
+            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start));
+            total_tx += static_cast<unsigned>(((src & 15u) + bytes + 15) & ~int64_t(15));
+          }
+        }
+        if (total_tx) mbar_arrive_expect_tx(&stage_bar, total_tx);
+        else mbar_arrive(&stage_bar);
+        for (int c = 0; c < P.ncols; ++c) {
+          int64_t start, bytes;
+          unsigned ignore = 0;
+          dev::clip_segment(P, P.cols[c], t, ts, len, start, bytes, ignore);
+          if (bytes > 0) {
+            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start));
+            const unsigned cover = static_cast<unsigned>(((src & 15u) + bytes + 15) & ~int64_t(15));
+            bulk_load(stage + P.cols[c].stage_off, reinterpret_cast<const void *>(src & ~uintptr_t(15)), cover,
+                      &stage_bar);
+          }
+        }
+      }
+      unsigned polls = 0;
+      bool ok;
+      while (!(ok = mbar_try_wait(&stage_bar, stage_parity)))
+        if (++polls > kWaitLimit) break;
+      stage_parity ^= 1u;
+      if (__syncthreads_or(!ok)) {  // a copy never landed: report, do not touch the staging area
+        if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
+        break;
+      }
+      for (int q = warp; q < P.chunks_per_request; q += kWarps) {
+        const int c = dev::column_of_piece(P, q);
+        const GatherColumn &col = P.cols[c];
+        int64_t start, bytes;
+        unsigned ignore = 0;
+        dev::clip_segment(P, col, t, ts, len, start, bytes, ignore);
+        const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start));
+        dev::copy_piece<true>(P, col, q - col.chunk_first, g, stage + col.stage_off + (src & 15u), bytes, lane);
+      }
+      __syncthreads();  // the staging area is free for the next request
+    } else {
+      // Direct: the request's pieces, column by column, dealt to the four warps.
+      for (int q = warp; q < P.chunks_per_request; q += kWarps) {
+        const int c = dev::column_of_piece(P, q);
+        dev::gather_piece(P, P.cols[c], q - P.cols[c].chunk_first, g, t, ts, len, lane, flags);
+      }
     }
   }
-  if (P.status) {
-    if (flags && lane == 0) atomicOr(reinterpret_cast<unsigned *>(P.status), flags);
-    if (near_count) atomicAdd(P.status + 1, near_count);
-  }
+  if (P.status && flags && lane == 0) atomicOr(reinterpret_cast<unsigned *>(P.status), flags);
 }
 
 }  // namespace
@@ -129,8 +296,18 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
   int64_t grid = p.n;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
   if (grid > cap) grid = cap;
-  sample_gather_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(p, a);
-  GEARB_CUDA(cudaGetLastError());
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = p.stage_bytes > 0 ? static_cast<size_t>(p.stage_bytes) : 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, sample_gather_kernel, p, a));
   return GEARB_OK;
 }
 

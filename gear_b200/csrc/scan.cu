@@ -560,6 +560,9 @@ __global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
   Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned epoch = ld_u32_relaxed(&a.hdr->epoch);
+  // A kernel launched behind this one with programmatic stream serialisation may be scheduled
+  // as this grid drains; it still waits (griddepcontrol.wait) for this grid to complete.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
