@@ -88,6 +88,8 @@ _SIGS = {
     "gearb_indexset_weights": (vp, [vp]),
     "gearb_scan_scratch_bytes": (i64, [i64]),
     "gearb_scan": (C.c_int, [vp, i64, vp, vp, vp, i64, vp, vp]),
+    "gearb_scan_static": (C.c_int, [vp, i64, vp, vp, vp, vp]),
+    "gearb_scan_static_max_n": (i64, []),
     "gearb_search": (C.c_int, [vp, vp, i64, vp, i64, C.c_int, vp, vp, vp]),
     "gearb_sample_uniform": (C.c_int, [i64, vp, i64, vp, vp]),
     "gearb_decode": (C.c_int, [vp, i64, i64, vp, i64, vp, vp, vp, vp]),

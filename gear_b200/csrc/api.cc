@@ -39,16 +39,14 @@ int fail(int code, const char *fmt, ...) {
 }
 
 int sm_count() {
-  static std::mutex mu;
-  static std::map<int, int> cache;
+  constexpr int kMaxDevices = 64;
+  static int cache[kMaxDevices] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 1;
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = cache.find(dev);
-  if (it != cache.end()) return it->second;
+  if (dev >= 0 && dev < kMaxDevices && cache[dev] > 0) return cache[dev];
   int n = 0;
   if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
-  cache[dev] = n;
+  if (dev >= 0 && dev < kMaxDevices) cache[dev] = n;
   return n;
 }
 
@@ -549,6 +547,13 @@ int gearb_scan(const float *priorities, int64_t n, float *cdf, double *l1, void 
                int64_t scratch_bytes, int32_t *status, void *stream) {
   return launch_scan(priorities, n, cdf, l1, scratch, scratch_bytes, status, 1, as_stream(stream));
 }
+
+int gearb_scan_static(const float *priorities, int64_t n, float *cdf, double *l1, int32_t *status,
+                      void *stream) {
+  return launch_scan_static(priorities, n, cdf, l1, status, as_stream(stream));
+}
+
+int64_t gearb_scan_static_max_n(void) { return static_scan_max_n(); }
 
 int gearb_search(const float *cdf, const double *l1, int64_t n, const double *variates, int64_t b,
                  int flags, int64_t *out_index, int32_t *status, void *stream) {

@@ -36,22 +36,23 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 int sm_count();
 
 // ---- scan ------------------------------------------------------------------
-// Layout of the scan scratch block (all offsets 256-byte aligned):
-//   header   : ScanHeader
-//   state[P] : uint32  (epoch << 2) | {0 none, 1 aggregate published, 2 prefix published}
-//   agg[P]   : float64 partition aggregates
+// First block of the scan scratch (the rest is laid out in scan.cu).
 struct ScanHeader {
-  unsigned int ticket;  // next partition to hand out
+  unsigned int ticket;  // next ticket (group of partitions) to hand out
   unsigned int done;    // CTAs that have finished
   unsigned int epoch;   // launch counter; state words of other epochs read as "none"
-  unsigned int pad[61];
+  unsigned int pad[61];  // pad[0]: flags of the running launch
 };
 static_assert(sizeof(ScanHeader) == 256, "header is one 256-byte block");
 
 int64_t scan_scratch_bytes(int64_t n);
 // fresh != 0: scratch contents are unknown, clear them first (one memset).
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
-                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream);
+                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream,
+                int64_t layout_n = 0);
+int64_t static_scan_max_n();
+int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
+                       cudaStream_t stream);
 int launch_search(const float *cdf, const double *l1, int64_t n, const double *u, int64_t b,
                   int flags, int64_t *out, int32_t *status, cudaStream_t stream);
 int launch_uniform(int64_t n, const double *u01, int64_t b, int64_t *out, cudaStream_t stream);

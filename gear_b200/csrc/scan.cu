@@ -40,6 +40,8 @@
 // Every wait is bounded; a wait that runs out raises a flag instead of hanging.
 //
 // HBM traffic: 4 B read + 4 B written per priority, plus ~16 B per partition.
+#include <mutex>
+
 #include "common.h"
 
 namespace gearb {
@@ -633,7 +635,7 @@ int64_t scan_scratch_bytes(int64_t n) {
 }
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
-                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream) {
+                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, int64_t layout_n) {
   GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
   GEARB_REQUIRE(prio && cdf && l1 && scratch && status, "scan: null pointer argument");
   GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
@@ -648,12 +650,18 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
                 (long long)scratch_bytes, (long long)scan_scratch_bytes(n));
   char *sc = static_cast<char *>(scratch);
   const int64_t nsuper = (nparts + kSuper - 1) / kSuper;
-  const int64_t off_desc = sizeof(ScanHeader) + align256(nsuper * 4);
-  const int64_t off_agg = off_desc + align256(nsuper * 32);
+  // A scratch block that serves calls of different sizes keeps ONE layout (that of layout_n):
+  // the counters of a larger call must never land on words a smaller call used for something else.
+  if (layout_n < n) layout_n = n;
+  const int64_t lay_parts = (layout_n + kPart - 1) / kPart;
+  const int64_t lay_super = (lay_parts + kSuper - 1) / kSuper;
+  GEARB_REQUIRE(scratch_bytes >= scan_scratch_bytes(layout_n), "scan: scratch too small for its layout");
+  const int64_t off_desc = sizeof(ScanHeader) + align256(lay_super * 4);
+  const int64_t off_agg = off_desc + align256(lay_super * 32);
   if (fresh) {
     // Everything must start at zero: the epoch restarts at 0, so a stale tagged word could
     // otherwise pass for a fresh one.
-    GEARB_CUDA(cudaMemsetAsync(sc, 0, static_cast<size_t>(scan_scratch_bytes(n)), stream));
+    GEARB_CUDA(cudaMemsetAsync(sc, 0, static_cast<size_t>(scan_scratch_bytes(layout_n)), stream));
   }
 
   const size_t smem_bytes = sizeof(Smem) + 128;
@@ -688,6 +696,57 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   scan_kernel<<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
   GEARB_CUDA(cudaGetLastError());
   return GEARB_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Scratch that lives in the library image, for gearb_scan_static.
+//
+// kStaticMaxN priorities need kStaticScratchBytes of scratch; every device that loads this
+// library reserves that much global memory until the process exits.
+constexpr int64_t kStaticMaxN = int64_t(1) << 28;  // 268,435,456 priorities = 65,536 partitions
+constexpr int64_t kStaticParts = kStaticMaxN / kPart;
+constexpr int64_t kStaticSuper = kStaticParts / kSuper;
+constexpr int64_t kStaticScratchBytes =
+    sizeof(ScanHeader) + kStaticSuper * 4 + kStaticSuper * 32 + kStaticParts * 8;  // 672,000 B
+static_assert(kStaticSuper * 4 % 256 == 0 && kStaticSuper * 32 % 256 == 0 && kStaticParts * 8 % 256 == 0,
+              "the static scratch uses the same 256-byte aligned layout as scan_scratch_bytes()");
+
+// In host code this name is only a handle for the symbol, not a device address: the address
+// each device gave the array is asked for with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScratchBytes];
+
+int64_t static_scan_max_n() { return kStaticMaxN; }
+
+int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
+                       cudaStream_t stream) {
+  GEARB_REQUIRE(n > 0, "scan_static: n must be positive (got %lld)", (long long)n);
+  if (n > kStaticMaxN)
+    return fail(GEARB_ERR_UNSUPPORTED,
+                "scan_static: %lld priorities exceed the built-in scratch (at most %lld); use gearb_scan "
+                "with caller-provided scratch",
+                (long long)n, (long long)kStaticMaxN);
+  // One-time set-up per device, with that device current: ask the runtime where this device
+  // keeps the array.  No allocation happens here or anywhere else on this path.
+  constexpr int kMaxDevices = 64;
+  static void *scratch_of_device[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  GEARB_CUDA(cudaGetDevice(&dev));
+  GEARB_REQUIRE(dev >= 0 && dev < kMaxDevices, "scan_static: device ordinal %d not supported", dev);
+  void *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!scratch_of_device[dev]) {
+      void *ptr = nullptr;
+      GEARB_CUDA(cudaGetSymbolAddress(&ptr, g_static_scan_scratch));
+      scratch_of_device[dev] = ptr;
+    }
+    scratch = scratch_of_device[dev];
+  }
+  // The array starts zeroed when the module is loaded and every launch leaves it re-armed
+  // (ticket and counters back at zero, epoch advanced, older words invalid by their tag), so
+  // nothing has to be cleared between calls.
+  return launch_scan(prio, n, cdf, l1, scratch, kStaticScratchBytes, status, /*fresh=*/0, stream, kStaticMaxN);
 }
 
 }  // namespace gearb

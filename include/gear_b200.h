@@ -166,6 +166,24 @@ float *gearb_indexset_weights(const gearb_indexset *s);
 int64_t gearb_scan_scratch_bytes(int64_t n);
 int gearb_scan(const float *priorities, int64_t n, float *cdf, double *l1, void *scratch,
                int64_t scratch_bytes, int32_t *status, void *stream);
+/* gearb_scan without any allocation by anyone: the scratch is an array inside the
+ * library image (672,000 bytes of device memory on every GPU that loads the library,
+ * held until the process exits), enough for n <= gearb_scan_static_max_n() =
+ * 268,435,456 priorities; a larger n is refused with GEARB_ERR_UNSUPPORTED.
+ * No counterpart in the reference -- it is for callers that must not, or cannot,
+ * allocate device memory when they need a scan: code on a latency-critical path, where
+ * cudaMalloc would stall every stream of the device; a process whose device memory has
+ * all been handed to another allocator (a framework's caching pool), where a late
+ * cudaMalloc can simply fail; a plain C caller that does not want to own and size a
+ * scratch buffer.  Inputs and outputs are still the caller's.  Results are identical to
+ * gearb_scan's.  The first call on a device looks up the array's address on that
+ * device (a host-side query, with that device current); make that first call before
+ * starting any stream capture.  All calls on a device share the one array: calls whose
+ * kernels overlap on the GPU (two streams, two threads) race and give wrong tables --
+ * serialise them, or use gearb_scan with separate scratch.                          */
+int gearb_scan_static(const float *priorities, int64_t n, float *cdf, double *l1, int32_t *status,
+                      void *stream);
+int64_t gearb_scan_static_max_n(void);
 /* Batched search on caller-supplied float64 variates (stands where
  * torch.multinomial is called, gear/sampler/global_sampler.py:170).
  * flags: GEARB_SEARCH_SCALE -> variates are U[0,1) and are multiplied by the
