@@ -29,6 +29,7 @@ PAD_INACTIVE, PAD_HEAD, PAD_TAIL = 0, 1, 2
 MAX_COLUMNS = 16
 SEARCH_SCALE = 1
 
+DT_F32, DT_F64, DT_I64, DT_F16 = range(4)
 FILL_U32, FILL_F32_NORMAL, FILL_F32_UNIFORM, FILL_F32_LOGNORMAL, FILL_I32_RANGE, FILL_U8, FILL_U01_F64 = range(7)
 
 
@@ -101,6 +102,15 @@ _SIGS = {
                                               C.c_int, vp, vp, vp, vp, vp]),
     "gearb_sampler_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "gearb_sampler_result": (C.c_int, [vp, vp, C.POINTER(f64), pi32]),
+    "gearb_comm_unique_id": (C.c_int, [C.c_char_p]),
+    "gearb_comm_create": (C.c_int, [C.c_int, C.c_int, C.c_char_p, C.POINTER(vp)]),
+    "gearb_comm_destroy": (C.c_int, [vp]),
+    "gearb_comm_info": (C.c_int, [vp, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int)]),
+    "gearb_comm_send": (C.c_int, [vp, vp, i64, C.c_int, vp]),
+    "gearb_comm_recv": (C.c_int, [vp, vp, i64, C.c_int, vp]),
+    "gearb_comm_allreduce_sum": (C.c_int, [vp, vp, i64, C.c_int, vp]),
+    "gearb_comm_allgather": (C.c_int, [vp, vp, vp, i64, vp]),
+    "gearb_comm_alltoallv": (C.c_int, [vp, C.c_int, C.POINTER(vp), pi64, pi64, C.POINTER(vp), pi64, pi64, vp]),
     "gearb_fill": (C.c_int, [vp, i64, C.c_int, u64, u64, f64, f64, vp]),
 }
 

@@ -38,6 +38,22 @@ def _nvcc() -> str:
     return exe
 
 
+def nccl_include() -> list[str]:
+    """Directory of nccl.h (types only; the functions are looked up at run time)."""
+    cands = [Path("/usr/include/nccl.h")]
+    try:
+        import importlib.util
+        spec = importlib.util.find_spec("nvidia.nccl")
+        if spec and spec.submodule_search_locations:
+            cands.append(Path(list(spec.submodule_search_locations)[0]) / "include" / "nccl.h")
+    except Exception:
+        pass
+    for c in cands:
+        if c.exists():
+            return ["-I", str(c.parent)]
+    raise RuntimeError("nccl.h not found (needed for its type definitions)")
+
+
 def needs_build() -> bool:
     if not LIB.exists():
         return True
@@ -71,6 +87,7 @@ def _build(verbose: bool, defines: list[str]) -> Path:
         obj = objdir / (src.stem + ".o")
         objs.append(obj)
         cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-I", str(ROOT / "include"), "-I", str(CSRC),
+               *nccl_include(),
                "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")

@@ -1,0 +1,179 @@
+"""Trajectory-id sharded replay table: global prioritized sampling with one payload exchange.
+
+Sharding follows the reference's loader: the table is cut into blocks of
+`capacity_per_rank` trajectories, `owner(g) = g // capacity_per_rank`
+(gear/loader/offline_loader.py:131-137), and rank i consumes slice i of the globally
+sorted batch (`torch.sort` in gear/sampler/global_sampler.py:131, slices in
+offline_loader.py:127-131).  What changes is the traffic:
+
+* the reference gathers candidate indices on dp-rank 0 and broadcasts the sampled ones
+  with three point-to-point messages per peer and direction (global_sampler.py:22-56,
+  105-152); here every rank already holds the whole batch of variates (they come from a
+  counter-based generator or from the caller), the shard totals are all-gathered (8 bytes
+  per rank), and every rank derives the complete routing on its own -- no request exchange;
+* the reference moves segments with one ncclSend / ncclRecv per segment
+  (src/storage/handler.cc:178-191,208-220); here an owner searches and gathers all segments
+  asked of it in ONE launch, straight into per-requester regions of a send buffer, and one
+  grouped all-to-all per step (`gearb_comm_alltoallv`) lands them in the requester's final
+  tensors, which are ordered by owner because the batch is sorted.
+
+`route` and `exchange_plan` are pure host functions (numpy); they are what the CPU-rank
+tests exercise.  `ShardedReplay` wires them to the kernels and to NCCL.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+__all__ = ["route", "exchange_plan", "Plan", "ShardedReplay"]
+
+
+def route(totals: np.ndarray, u01_sorted: np.ndarray, world: int):
+    """Owner and owner-local variate of every request of the global batch.
+
+    totals       float64[world]  total priority of each shard (its l1[-1])
+    u01_sorted   float64[B]      the global batch's U[0,1) variates, ascending
+    Returns (owner int32[B], residual float64[B], requester int32[B]).
+    A request with variate u goes to the shard j with prefix[j] <= u*total < prefix[j+1];
+    its residual u*total - prefix[j] is a variate in [0, totals[j]) for the owner's table.
+    """
+    totals = np.asarray(totals, np.float64)
+    u = np.asarray(u01_sorted, np.float64)
+    B = len(u)
+    if B % world:
+        raise ValueError(f"global batch {B} is not a multiple of the world size {world}")
+    prefix = np.zeros(world + 1, np.float64)
+    acc = 0.0
+    for j in range(world):           # in-order float64 sum, like level 1 of the cumulative table
+        acc = acc + float(totals[j])
+        prefix[j + 1] = acc
+    total = prefix[world]
+    v = u * total
+    v = np.where(v >= 0.0, v, 0.0)
+    v = np.where(v < total, v, np.nextafter(total, 0.0))
+    owner = np.searchsorted(prefix[1:], v, side="right").astype(np.int32)
+    owner = np.minimum(owner, world - 1)
+    residual = v - prefix[owner]
+    top = np.nextafter(totals[owner], 0.0)
+    residual = np.where(residual < totals[owner], residual, top)
+    requester = (np.arange(B) // (B // world)).astype(np.int32)
+    return owner, residual, requester
+
+
+@dataclass
+class Plan:
+    """Counts and displacements of one rank, in requests (multiply by a column's slot bytes)."""
+    mine: np.ndarray         # positions in the global batch that this rank owns, in batch order
+    send_count: np.ndarray   # int64[W]: requests this rank serves for each requester
+    send_first: np.ndarray   # int64[W]: first of them inside `mine`
+    recv_count: np.ndarray   # int64[W]: requests of this rank's slice served by each owner
+    recv_first: np.ndarray   # int64[W]: first slot of them inside the slice (sorted batch => contiguous)
+    slice_owner: np.ndarray  # int32[b]: owner of every slot of this rank's slice
+
+
+def exchange_plan(owner: np.ndarray, requester: np.ndarray, rank: int, world: int) -> Plan:
+    """Who sends how much to whom, derived locally from the routing of the whole batch."""
+    owner = np.asarray(owner); requester = np.asarray(requester)
+    mine = np.nonzero(owner == rank)[0]                      # ascending => grouped by requester
+    send_count = np.bincount(requester[mine], minlength=world).astype(np.int64)
+    send_first = np.concatenate([[0], np.cumsum(send_count)[:-1]]).astype(np.int64)
+    sl = np.nonzero(requester == rank)[0]
+    slice_owner = owner[sl].astype(np.int32)
+    if len(slice_owner) > 1 and np.any(np.diff(slice_owner) < 0):
+        raise ValueError("the batch is not sorted: a rank's slice must be contiguous by owner")
+    recv_count = np.bincount(slice_owner, minlength=world).astype(np.int64)
+    recv_first = np.concatenate([[0], np.cumsum(recv_count)[:-1]]).astype(np.int64)
+    return Plan(mine, send_count, send_first, recv_count, recv_first, slice_owner)
+
+
+class ShardedReplay:
+    """One rank's shard (table + priorities) plus the exchange.
+
+    table/handler/sampler are gear_b200.core objects of the local shard; `comm` is a
+    gear_b200.comm.Communicator (or None when world == 1).
+    """
+
+    def __init__(self, handler, sampler, columns: Sequence[int], rank: int, world: int, comm=None,
+                 max_global_batch: int = 8192):
+        import torch
+        from . import _native as N
+        self.torch, self.N = torch, N
+        self.handler, self.sampler, self.columns = handler, sampler, [int(c) for c in columns]
+        self.rank, self.world, self.comm = int(rank), int(world), comm
+        if world > 1 and comm is None:
+            raise ValueError("a communicator is required when world > 1")
+        t = handler.table
+        self.slots = [handler.patterns[c].length * t.row_bytes[c] for c in self.columns]
+        self.n_local = sampler.n
+        self.maxB = int(max_global_batch)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.dev = dev
+        b = self.maxB // world
+        # worst case: every request of the batch is served by this rank
+        self.send = [torch.empty(self.maxB * s, dtype=torch.uint8, device=dev) for s in self.slots]
+        self.send_flat = torch.empty(self.maxB, dtype=torch.int64, device=dev)
+        self.recv = [torch.empty(b * s, dtype=torch.uint8, device=dev) for s in self.slots]
+        self.recv_flat = torch.empty(b, dtype=torch.int64, device=dev)
+        self.totals_dev = torch.empty(world, dtype=torch.float64, device=dev)
+        self.totals_host = torch.empty(world, dtype=torch.float64).pin_memory()
+        self.res_host = torch.empty(self.maxB, dtype=torch.float64).pin_memory()
+        self.res_dev = torch.empty(self.maxB, dtype=torch.float64, device=dev)
+        self.owner_base = torch.empty(b, dtype=torch.int64, device=dev)
+        self.owner_base_host = torch.empty(b, dtype=torch.int64).pin_memory()
+        self.last_plan: Optional[Plan] = None
+
+    # -- step pieces (separate so that a benchmark can time them) ---------------------------
+    def scan(self, priorities):
+        self.sampler.scan(priorities)
+
+    def gather_totals(self) -> np.ndarray:
+        """Shard totals of every rank on the host (one 8-byte-per-rank collective + one sync)."""
+        torch = self.torch
+        nparts = (self.n_local + self.N.PART - 1) // self.N.PART
+        mine = self.sampler.l1[nparts:nparts + 1]
+        if self.world == 1:
+            self.totals_dev.copy_(mine)
+        else:
+            self.comm.allgather(mine, self.totals_dev)
+        self.totals_host.copy_(self.totals_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.totals_host.numpy().copy()
+
+    def step(self, priorities, u01_sorted: np.ndarray, rescan: bool = True):
+        """One global batch.  Returns (column byte tensors of this rank's slice, global step ids)."""
+        torch = self.torch
+        B = len(u01_sorted)
+        if B > self.maxB or B % self.world:
+            raise ValueError(f"global batch {B}: at most {self.maxB} and a multiple of {self.world}")
+        b = B // self.world
+        if rescan:
+            self.scan(priorities)
+        totals = self.gather_totals()
+        owner, residual, requester = route(totals, u01_sorted, self.world)
+        plan = exchange_plan(owner, requester, self.rank, self.world)
+        self.last_plan = plan
+        m = len(plan.mine)
+
+        # owner role: search + gather everything asked of this shard, grouped by requester
+        direct = self.world == 1
+        dsts = self.recv if direct else self.send
+        flat = self.recv_flat if direct else self.send_flat
+        if m:
+            self.res_host[:m].copy_(torch.from_numpy(residual[plan.mine]))
+            self.res_dev[:m].copy_(self.res_host[:m], non_blocking=True)
+            self.sampler.sample_gather(self.handler, self.res_dev[:m], self.columns, dsts, scale=False,
+                                       zero_fill=True, out_flat=flat)
+        if not direct:
+            bufs_s = self.send + [self.send_flat]
+            bufs_r = self.recv + [self.recv_flat]
+            sizes = self.slots + [8]
+            self.comm.alltoallv(bufs_s, bufs_r, sizes, plan.send_first, plan.send_count, plan.recv_first,
+                                plan.recv_count)
+        # global step id = owner * steps_per_shard + owner-local index
+        self.owner_base_host[:b].copy_(torch.from_numpy(plan.slice_owner.astype(np.int64) * self.n_local))
+        self.owner_base[:b].copy_(self.owner_base_host[:b], non_blocking=True)
+        gflat = self.recv_flat[:b] + self.owner_base[:b]
+        return [r[: b * s] for r, s in zip(self.recv, self.slots)], gflat

@@ -223,6 +223,37 @@ int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int3
 /* Synchronises `stream`, then returns total and the status words. */
 int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t *status);
 
+/* ======================= communication ================================== */
+/* create_nccl_id, src/nccl_comm.cc:4-10: 128 bytes to hand to every rank.       */
+int gearb_comm_unique_id(char *id128);
+/* NcclCommunicator::NcclCommunicator, src/nccl_comm.cc:12-17 (ncclCommInitRank on
+ * the current device); CpuTrajectoryStorageHandler::connect, handler.cc:156-158. */
+int gearb_comm_create(int rank, int world, const char *id128, gearb_comm **out);
+int gearb_comm_destroy(gearb_comm *c);
+/* get_rank / get_size / get_device, src/nccl_comm.cc:23-31. */
+int gearb_comm_info(const gearb_comm *c, int *rank, int *world, int *device);
+/* NcclCommunicator::send / recv, src/nccl_comm.cc:33-47, counted in bytes. */
+int gearb_comm_send(gearb_comm *c, const void *buf, int64_t bytes, int peer, void *stream);
+int gearb_comm_recv(gearb_comm *c, void *buf, int64_t bytes, int peer, void *stream);
+/* NcclCommunicator::allreduce (ncclSum, in place), src/nccl_comm.cc:49-55. */
+#define GEARB_DT_F32 0
+#define GEARB_DT_F64 1
+#define GEARB_DT_I64 2
+#define GEARB_DT_F16 3
+int gearb_comm_allreduce_sum(gearb_comm *c, void *buf, int64_t count, int dtype, void *stream);
+int gearb_comm_allgather(gearb_comm *c, const void *send, void *recv, int64_t bytes_per_rank,
+                         void *stream);
+/* The exchange the reference declares and leaves empty (group_exchange,
+ * src/nccl_comm.cc:83-86), standing in for the per-segment ncclSend / ncclRecv
+ * loops of subsend / subrecv (src/storage/handler.cc:178-191,208-220): for each of
+ * nbuf buffer pairs b and each peer p, send_bytes[b*W+p] bytes at send[b] +
+ * send_off[b*W+p] go to p and recv_bytes[b*W+p] bytes from p land at recv[b] +
+ * recv_off[b*W+p], all in one NCCL group.  The block a rank addresses to itself is a
+ * device copy.                                                                  */
+int gearb_comm_alltoallv(gearb_comm *c, int nbuf, const void *const *send, const int64_t *send_off,
+                         const int64_t *send_bytes, void *const *recv, const int64_t *recv_off,
+                         const int64_t *recv_bytes, void *stream);
+
 /* ======================= synthetic data ================================= */
 /* Device-side Philox4x32-10 fills for benchmark tables that are too large to
  * stage through the host.  kind selects the distribution.                   */
