@@ -184,10 +184,18 @@ def sharded_parity(replay, table, handler, prio, u_sorted, rank, world, dev, T, 
         dist.all_reduce(mism)
     out = None
     if rank == 0:
+        # The sharded draw is defined shard by shard: each shard's own cumulative table, shard
+        # totals summed in rank order, then the owner-local search.  (It coincides with one table
+        # over the concatenated priorities only when a shard holds a whole number of partitions.)
         from oracle import oracle as O
-        gp = torch.cat(allp).cpu().numpy()
-        cdf, l1, total, _ = O.scan_mt(gp, os.cpu_count() or 1)
-        want = O.search(cdf, l1, u_sorted, scale=True)
+        from .sharded import route
+        scans = [O.scan_mt(p.cpu().numpy(), os.cpu_count() or 1) for p in allp]
+        totals = np.array([sc[2] for sc in scans])
+        owner, residual, _ = route(totals, u_sorted, world)
+        want = np.empty(len(u_sorted), np.int64)
+        for j in range(world):
+            m = owner == j
+            want[m] = O.search(scans[j][0], scans[j][1], residual[m]) + j * n_local
         got = torch.cat(allf).cpu().numpy()
         out = {"index_mismatches_vs_oracle": int((got != want).sum()), "gathered_byte_mismatches": int(mism[0]),
                "requests_byte_checked": int(mism[1])}

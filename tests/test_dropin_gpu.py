@@ -1,0 +1,90 @@
+"""GEAR's loader / sampler / copy API on the GPU through the mirrors, checked against the
+oracle: next(loader) must return the bytes the oracle gathers for the indices the sampler
+reports, for uniform and weighted sampling, host-mapped and HBM-resident tables."""
+import numpy as np
+import pytest
+import torch
+
+import gear_b200.dropin
+
+gear_b200.dropin.install()
+
+import gear  # noqa: E402
+import libgear.core as glibc  # noqa: E402
+from gear.dataset import SharedDataset  # noqa: E402
+from gear.loader import OfflineLoader  # noqa: E402
+from gear.mpu import ModelParallelismUnit  # noqa: E402
+from gear.specs import TableSpec  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def test_reference_test_copy():
+    # tests/test_copy.py of the reference, verbatim in meaning
+    device = torch.device("cuda:0")
+    column_shapes = (4, 3, 2)
+    data = torch.ones((32, 100) + column_shapes, dtype=torch.float32, device="cpu", pin_memory=True)
+    copied = torch.zeros((10,) + column_shapes, dtype=torch.float32, device=device)
+    src_offset = torch.zeros(1, dtype=torch.long, device=device)
+    dst_offset = torch.zeros(1, dtype=torch.long, device=device)
+    stride = copied.numel() * copied.element_size() * torch.ones(1, dtype=torch.long, device=device)
+    glibc.copy_debug(data, copied, src_offset, dst_offset, stride, stride[0])
+    torch.cuda.synchronize()
+    assert torch.all(copied)
+
+
+def _dataset(O, cap, T, key, residency):
+    spec = TableSpec.create(0, 1, T, cap, [dict(shape=[17], dtype=torch.float32, name="obs"),
+                                           dict(shape=[6], dtype=torch.float32, name="act"),
+                                           dict(shape=[], dtype=torch.float32, name="rew"),
+                                           dict(shape=[], dtype=torch.uint8, name="done")])
+    ds = SharedDataset.create(spec, create=True, key=key, residency="host")
+    rng = np.random.default_rng(key)
+    for i in range(cap):
+        cols = [torch.from_numpy(rng.standard_normal((T, 17)).astype(np.float32)),
+                torch.from_numpy(rng.uniform(-1, 1, (T, 6)).astype(np.float32)),
+                torch.from_numpy(rng.standard_normal(T).astype(np.float32)),
+                torch.from_numpy((np.arange(T) == T - 1).astype(np.uint8))]
+        ds[i] = (float(rng.lognormal()), int(rng.integers(1, T + 1)), cols)
+    if residency == "hbm":
+        ds.to_hbm()
+    return ds
+
+
+@pytest.mark.parametrize("residency", ["host", "hbm"])
+@pytest.mark.parametrize("method", ["Uniform", "Weighted"])
+def test_offline_loader_matches_oracle(O, residency, method):
+    gear.init(0)
+    cap, T, B, L = 64, 50, 32, 20
+    ds = _dataset(O, cap, T, key=7000 + len(residency) + len(method), residency=residency)
+    mpu = ModelParallelismUnit(device=torch.device("cuda:0"), dp_rank=0, dp_world_size=1)
+    pats = [dict(name="obs", offset=-L, length=L, pad="head"), dict(name="act", offset=-L, length=L, pad="head"),
+            dict(name="done", offset=-3, length=5, pad="tail")]
+    loader = OfflineLoader(ds, B, mpu, method, pats)
+    img = np.array(ds._table._t.host_view(), copy=True)
+    rows = [68, 24, 4, 1]
+    accu, stride = O.table_layout(rows, T)
+    for _ in range(3):
+        tss, data = next(loader)
+        torch.cuda.synchronize()
+        # the sampler's last draw, sorted, is what the loader gathered
+        idx = torch.sort(loader._indices[loader._sampler._cache]).values.cpu().numpy()
+        lens = ds.timesteps.numpy()[idx]
+        assert np.array_equal(tss.cpu().numpy(), lens)
+        assert list(data[0].shape) == [B, L, 17] and data[0].dtype == torch.float32 and data[2].dtype == torch.uint8
+        for out, (col, off, ln, head) in zip(data, [(0, -L, L, True), (1, -L, L, True), (3, -3, 5, False)]):
+            want = O.fused_subcopy(img, idx, lens, lens, stride, int(accu[col]), T, rows[col], off, ln, head)
+            assert np.array_equal(out.cpu().numpy().view(np.uint8).reshape(-1), want)
+    if method == "Weighted":
+        # same variates => same indices as the oracle's search on the same weights
+        w = ds.weights.numpy().astype(np.float32)
+        ocdf, ol1, _, _ = O.scan(w)
+        u = O.philox_u01(42, loader._sampler._calls - 1, 0, B)
+        assert np.array_equal(np.sort(O.search(ocdf, ol1, u, scale=True)), idx)
+    # the two-step route (host sub + vcopy) gives the same tensors as the fused one
+    sel = torch.arange(0, cap, 3)
+    fused = loader.exposed_fused_iterate(sel)
+    _, two_step = loader.exposed_low_level_controlled_iterate(sel)
+    torch.cuda.synchronize()
+    for a, b in zip(fused, two_step):
+        assert torch.equal(a, b)
