@@ -42,8 +42,9 @@ C5 = dict(name="sharded_token_table_32Mstep_per_gpu", rows=[4096, 4, 4], T=1000,
           B_per_rank=1024, L=16)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one scan_kernel launch at n = 100,000,000,
-# from the ncu capture summarised in profiles/ (None until a capture exists).
-SCAN_TRAFFIC_BYTES_C3 = None
+# from the one-pass ncu capture summarised in profiles/scan_kernel_100M_priorities.md (the part of the
+# 400 MB of output that is still dirty in L2 at kernel end is not in it).
+SCAN_TRAFFIC_BYTES_C3 = 741_204_736
 
 
 def peaks():
