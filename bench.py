@@ -192,6 +192,21 @@ def run_ours_single(args):
     torch.cuda.synchronize()
     sg_ms = e2[0].elapsed_time(e2[1]) / K
 
+    # ---- incremental mode: the B priorities of the previous batch change, only their partitions
+    #      are rescanned (reported beside the headline; the headline rescans everything)
+    new_val = torch.empty(nbatches * B, dtype=torch.float32, device=dev)
+    core.fill(new_val, N.FILL_F32_LOGNORMAL, seed=0x6EA20303)
+    e3 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    sampler.scan(prio)
+    e3[0].record()
+    for i in range(K):
+        j = i % nbatches
+        sampler.update(prio, flat, new_val[j * B:(j + 1) * B])     # the indices drawn by the previous step
+        sampler.sample_gather(handler, u_dev[j * B:(j + 1) * B], cols, dsts, scale=True, zero_fill=True, out_flat=flat)
+    e3[1].record()
+    torch.cuda.synchronize()
+    upd_ms = e3[0].elapsed_time(e3[1]) / K
+
     # ---- end to end through the C ABI with host buffers (pinned): variates in, batch out
     u_host = torch.empty(nbatches * B, dtype=torch.float64).pin_memory()
     u_host.copy_(u_dev.cpu())
@@ -237,6 +252,9 @@ def run_ours_single(args):
         "step_frac_of_8tbs": (scan_bytes + 2 * gathered) / (ms_step * 1e-3) / 1e9 / 8000.0,
         "search_gather_only": {"ms_per_step": sg_ms, "timesteps_per_s": B * L / (sg_ms * 1e-3),
                                "gathered_gb_s": 2 * gathered / (sg_ms * 1e-3) / 1e9},
+        "incremental_update": {"ms_per_step": upd_ms, "timesteps_per_s": B * L / (upd_ms * 1e-3),
+                               "step": f"update {B} priorities (rescan of the touched partitions + level 1) + "
+                                       "search + decode + gather"},
         "roofline": {"kernel": "scan_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                      "frac": achieved / peak, "traffic": SCAN_TRAFFIC_BYTES_C3, "peak_source": peak_src,
                      "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms},

@@ -344,6 +344,15 @@ class PrioritySampler:
             raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
         call("gearb_sampler_scan", self._h, _ptr(priorities), _stream(stream))
 
+    def update(self, priorities: torch.Tensor, idx: torch.Tensor, values: torch.Tensor, stream=None) -> None:
+        """priorities[idx] = values, then rescan only the touched partitions (after a scan())."""
+        if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
+            raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
+        if values.dtype != torch.float32 or not values.is_cuda or values.numel() != idx.numel():
+            raise GearError(N.ERR_INVALID, "values must be a float32 CUDA tensor, one per index")
+        call("gearb_sampler_update", self._h, _ptr(priorities), _dev_i64(idx, "idx"), _ptr(values.contiguous()),
+             idx.numel(), _stream(stream))
+
     def search(self, variates: torch.Tensor, scale: bool = False, out: Optional[torch.Tensor] = None,
                stream=None) -> torch.Tensor:
         if variates.dtype != torch.float64 or not variates.is_cuda:

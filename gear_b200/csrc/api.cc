@@ -186,6 +186,7 @@ struct gearb_sampler {
   float *cdf = nullptr;
   double *l1 = nullptr;
   void *scratch = nullptr;
+  void *upd = nullptr;  // dirty flags + list of touched partitions for incremental updates
   int32_t *status = nullptr;
 };
 
@@ -580,6 +581,8 @@ int gearb_sampler_create(int64_t n, gearb_sampler **out) {
   if (e == cudaSuccess) e = cudaMalloc(&s->cdf, static_cast<size_t>(round_up(n * 4, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->l1, static_cast<size_t>(round_up((s->nparts + 1) * 8, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->scratch, static_cast<size_t>(s->scratch_bytes));
+  if (e == cudaSuccess) e = cudaMalloc(&s->upd, static_cast<size_t>(update_scratch_bytes(n)));
+  if (e == cudaSuccess) e = cudaMemset(s->upd, 0, static_cast<size_t>(update_scratch_bytes(n)));
   if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
   if (e == cudaSuccess) e = cudaMemset(s->scratch, 0, static_cast<size_t>(s->scratch_bytes));
   if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
@@ -597,6 +600,7 @@ int gearb_sampler_destroy(gearb_sampler *s) {
   if (s->cdf) (void)cudaFree(s->cdf);
   if (s->l1) (void)cudaFree(s->l1);
   if (s->scratch) (void)cudaFree(s->scratch);
+  if (s->upd) (void)cudaFree(s->upd);
   if (s->status) (void)cudaFree(s->status);
   delete s;
   return GEARB_OK;
@@ -606,6 +610,13 @@ int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) 
   GEARB_REQUIRE(s, "sampler_scan: null sampler");
   return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
                      as_stream(stream));
+}
+
+int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx, const float *values, int64_t m,
+                         void *stream) {
+  GEARB_REQUIRE(s, "sampler_update: null sampler");
+  return launch_update(priorities, s->n, s->cdf, s->l1, scan_aggregate_words(s->scratch, s->n), s->upd, idx,
+                       values, m, s->status, as_stream(stream));
 }
 
 int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, int flags,

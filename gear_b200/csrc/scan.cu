@@ -717,6 +717,14 @@ static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScra
 
 int64_t static_scan_max_n() { return kStaticMaxN; }
 
+// Where a scratch block laid out for layout_n priorities keeps its per-partition aggregate words.
+unsigned long long *scan_aggregate_words(void *scratch, int64_t layout_n) {
+  const int64_t lay_parts = (layout_n + kPart - 1) / kPart;
+  const int64_t lay_super = (lay_parts + kSuper - 1) / kSuper;
+  return reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + sizeof(ScanHeader) +
+                                                align256(lay_super * 4) + align256(lay_super * 32));
+}
+
 int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
                        cudaStream_t stream) {
   GEARB_REQUIRE(n > 0, "scan_static: n must be positive (got %lld)", (long long)n);

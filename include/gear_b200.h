@@ -206,6 +206,13 @@ int gearb_decode(const int64_t *flat, int64_t b, int64_t trajectory_length,
 int gearb_sampler_create(int64_t n, gearb_sampler **out);
 int gearb_sampler_destroy(gearb_sampler *s);
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
+/* Incremental update after a gearb_sampler_scan of the same array: priorities[idx[i]] =
+ * values[i] for i < m (idx, values: device arrays), then only the partitions that were touched
+ * are rescanned and the partition offsets rebuilt.  The table afterwards is bit-identical to a
+ * full scan of the updated priorities.  Host counterparts in the reference: Indexset::set_weight,
+ * include/index/set.h:245-247; WeightUpdateRequestArray, src/index/request.cc:41-75.         */
+int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx, const float *values,
+                         int64_t m, void *stream);
 int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, int flags,
                          int64_t *out_index, void *stream);
 /* Prioritized sample + gather of a whole batch in ONE launch: search each

@@ -160,3 +160,49 @@ def test_fill_integer_kinds_match_oracle_philox(O):
     np.testing.assert_allclose(f.cpu().numpy(), O.synth_normal(14, 0, 4000), rtol=1e-5, atol=1e-6)
     core.fill(f, N.FILL_F32_LOGNORMAL, seed=15)
     np.testing.assert_allclose(f.cpu().numpy(), O.synth_lognormal(15, 0, 4000), rtol=1e-5)
+
+
+@pytest.mark.parametrize("n", [4096 * 3 + 17, 1 << 20])
+def test_incremental_update_equals_full_scan(O, n):
+    rng = np.random.default_rng(n)
+    p = O.synth_lognormal(55, n, n)
+    s = core.PrioritySampler(n)
+    dp = dev(p)
+    s.scan(dp)
+    for rep in range(3):
+        m = [1, 100, 3000][rep]
+        idx = rng.integers(0, n, m).astype(np.int64)
+        idx = np.unique(idx)                        # one writer per entry keeps the host copy well defined
+        if rep == 1:
+            idx[-1] = n - 1                         # the ragged last partition
+        val = rng.lognormal(0, 1, len(idx)).astype(np.float32)
+        val[::7] = 0.0
+        p[idx] = val
+        s.update(dp, dev(idx), dev(val))
+        tot, st = s.result()
+        ocdf, ol1, ototal, _ = O.scan(p)
+        assert np.array_equal(dp.cpu().numpy(), p)
+        assert np.array_equal(s.cdf.cpu().numpy(), ocdf)
+        assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal and st[0] == 0
+    # a full scan afterwards still works (scratch left consistent)
+    s.scan(dp)
+    assert np.array_equal(s.l1.cpu().numpy(), O.scan(p)[1])
+
+
+def test_incremental_update_inexact_level1_and_bad_index(O):
+    n = 32 * 4096
+    p = np.full(n, 1.234e-3, np.float32)
+    s = core.PrioritySampler(n)
+    dp = dev(p)
+    s.scan(dp)
+    idx = np.array([0, 8192, 5 * 4096 + 3], np.int64); val = np.array([3e18, 3e18, 7.7e5], np.float32)
+    p[idx] = val
+    s.update(dp, dev(idx), dev(val))
+    tot, st = s.result()
+    ocdf, ol1, _, _ = O.scan(p)
+    assert np.array_equal(s.l1.cpu().numpy(), ol1) and np.array_equal(s.cdf.cpu().numpy(), ocdf)
+    assert st[0] & N.ST_L1_RESUMMED
+    s.update(dp, dev(np.array([n, -1], np.int64)), dev(np.array([1.0, 1.0], np.float32)))
+    _, st = s.result()
+    assert st[0] & N.ST_BAD_REQUEST
+    assert np.array_equal(dp.cpu().numpy(), p)
