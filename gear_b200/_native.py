@@ -101,6 +101,8 @@ _SIGS = {
     "gearb_sampler_search": (C.c_int, [vp, vp, i64, C.c_int, vp, vp]),
     "gearb_sampler_sample_gather": (C.c_int, [vp, vp, vp, i64, C.c_int, vp, i64, pi32, C.c_int, C.POINTER(vp),
                                               C.c_int, vp, vp, vp, vp, vp]),
+    "gearb_sampler_sample_gather_affine": (C.c_int, [vp, vp, vp, i64, f64, f64, vp, i64, pi32, C.c_int,
+                                                     C.POINTER(vp), C.c_int, vp, vp, vp, vp, vp]),
     "gearb_sampler_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "gearb_sampler_result": (C.c_int, [vp, vp, C.POINTER(f64), pi32]),
     "gearb_comm_unique_id": (C.c_int, [C.c_char_p]),

@@ -368,9 +368,11 @@ class PrioritySampler:
                       lengths: Optional[torch.Tensor] = None, index_offset: int = 0,
                       zero_fill: bool = True, out_flat: Optional[torch.Tensor] = None,
                       out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None,
-                      out_len: Optional[torch.Tensor] = None, stream=None) -> None:
+                      out_len: Optional[torch.Tensor] = None, stream=None,
+                      affine: Optional[tuple] = None) -> None:
         """Search every variate, decode it to (trajectory, timestep, length) and gather the
-        listed columns of the handler's table, all in one launch."""
+        listed columns of the handler's table, all in one launch.  affine=(mul, sub): the
+        variates belong to a global draw over several shards and become u*mul - sub first."""
         if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
             raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
         b = variates.numel()
@@ -387,6 +389,12 @@ class PrioritySampler:
             if t is not None and (t.dtype != torch.int64 or not t.is_cuda or t.numel() < b):
                 raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
         nc = len(columns)
+        if affine is not None:
+            call("gearb_sampler_sample_gather_affine", self._h, handler._h, _ptr(variates), b, float(affine[0]),
+                 float(affine[1]), _ptr(lengths), int(index_offset), (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
+                 (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)),
+                 _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _ptr(out_len), _stream(stream))
+            return
         call("gearb_sampler_sample_gather", self._h, handler._h, _ptr(variates), b,
              N.SEARCH_SCALE if scale else 0, _ptr(lengths), int(index_offset),
              (C.c_int32 * nc)(*[int(c) for c in columns]), nc,

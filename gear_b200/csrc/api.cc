@@ -626,12 +626,29 @@ int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, in
                        as_stream(stream));
 }
 
+int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const double *variates, int64_t b,
+                                       double mul, double sub, const int64_t *lengths, int64_t index_offset,
+                                       const int32_t *columns, int ncols, void *const *dst, int zero_fill,
+                                       int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
+                                       void *stream) {
+  GEARB_REQUIRE(s, "sample_gather: null sampler");
+  GatherParams p;
+  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
+  if (rc != GEARB_OK) return rc;
+  GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
+                "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
+                (long long)(h->table->capacity * h->table->T));
+  return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, GEARB_SEARCH_AFFINE, lengths, index_offset,
+                              out_flat, out_idx, out_ts, out_len, as_stream(stream), mul, sub);
+}
+
 int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double *variates, int64_t b,
                                 int flags, const int64_t *lengths, int64_t index_offset,
                                 const int32_t *columns, int ncols, void *const *dst, int zero_fill,
                                 int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
                                 void *stream) {
   GEARB_REQUIRE(s, "sample_gather: null sampler");
+  GEARB_REQUIRE((flags & ~GEARB_SEARCH_SCALE) == 0, "sample_gather: unknown flag");
   GatherParams p;
   int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
   if (rc != GEARB_OK) return rc;

@@ -99,7 +99,7 @@ int launch_gather(const GatherParams &p, cudaStream_t stream);
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
-                         cudaStream_t stream);
+                         cudaStream_t stream, double mul = 1.0, double sub = 0.0);
 int launch_vcopy(const uint8_t *src, uint8_t *dst, const int64_t *src_off,
                  const int64_t *dst_off, const int64_t *lengths, int64_t fixed_length,
                  int64_t n, int64_t max_length, cudaStream_t stream);

@@ -112,6 +112,7 @@ struct SampleArgs {
   int64_t *out_flat, *out_idx, *out_ts, *out_len;  // each may be null
   int64_t n, nparts, index_offset;
   int flags;
+  double mul, sub;  // GEARB_SEARCH_AFFINE: variate -> variate * mul - sub (global draw -> this shard)
 };
 
 __global__ void __launch_bounds__(kThreads, 7)
@@ -146,6 +147,13 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
       flat = a.n - 1;  // nothing selectable: defined as the last index
     } else {
       if (a.flags & GEARB_SEARCH_SCALE) v = __dmul_rn(v, total);
+      if (a.flags & GEARB_SEARCH_AFFINE) {
+        // global draw -> this shard: clamp into [0, mul) as the router does, then shift
+        v = __dmul_rn(v, a.mul);
+        if (!(v >= 0.0)) v = 0.0;
+        if (!(v < a.mul)) v = __longlong_as_double(__double_as_longlong(a.mul) - 1);
+        v = __dsub_rn(v, a.sub);
+      }
       if (!(v >= 0.0)) v = 0.0;
       if (!(v < total)) v = __longlong_as_double(__double_as_longlong(total) - 1);
       for (;;) {
@@ -283,7 +291,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, double mul, double sub) {
   GEARB_REQUIRE(n > 0, "sample_gather: the priority table is empty");
   if (p.n == 0) return GEARB_OK;
   GEARB_REQUIRE(cdf && l1 && u, "sample_gather: null pointer argument");
@@ -293,6 +301,8 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
   a.n = n; a.nparts = (n + GEARB_PART - 1) / GEARB_PART;
   a.index_offset = index_offset;
   a.flags = flags;
+  a.mul = mul;
+  a.sub = sub;
   int64_t grid = p.n;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
   if (grid > cap) grid = cap;

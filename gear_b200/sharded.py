@@ -28,7 +28,7 @@ from typing import Optional, Sequence
 
 import numpy as np
 
-__all__ = ["route", "exchange_plan", "Plan", "ShardedReplay"]
+__all__ = ["route", "exchange_plan", "plan_sorted", "Plan", "ShardedReplay"]
 
 
 def route(totals: np.ndarray, u01_sorted: np.ndarray, world: int):
@@ -89,6 +89,46 @@ def exchange_plan(owner: np.ndarray, requester: np.ndarray, rank: int, world: in
     return Plan(mine, send_count, send_first, recv_count, recv_first, slice_owner)
 
 
+def plan_sorted(totals: np.ndarray, u01_sorted: np.ndarray, rank: int, world: int):
+    """The same routing as route() + exchange_plan() for an ASCENDING batch, in O(world log B):
+    owners rise with the variate, so the requests a shard owns are one contiguous run of the
+    batch.  Returns (plan, total, prefix) where plan.mine is that run as a range."""
+    totals = np.asarray(totals, np.float64)
+    u = np.asarray(u01_sorted, np.float64)
+    B = len(u)
+    if B % world:
+        raise ValueError(f"global batch {B} is not a multiple of the world size {world}")
+    b = B // world
+    prefix = np.zeros(world + 1, np.float64)
+    acc = 0.0
+    for j in range(world):
+        acc = acc + float(totals[j])
+        prefix[j + 1] = acc
+    total = prefix[world]
+    v = u * total
+    v = np.where(v >= 0.0, v, 0.0)
+    v = np.where(v < total, v, np.nextafter(total, 0.0))
+    # shard j owns the requests with prefix[j] <= v < prefix[j+1]; the last shard with mass takes the rest
+    cut = np.searchsorted(v, prefix[1:world], side="left")
+    bounds = np.concatenate([[0], cut, [B]]).astype(np.int64)
+    for j in range(world - 1, 0, -1):            # a trailing shard without mass owns nothing
+        if totals[j] > 0.0:
+            break
+        bounds[j] = B
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    slices = np.arange(world + 1, dtype=np.int64) * b
+
+    def overlap(a0, a1, b0, b1):
+        return np.maximum(np.minimum(a1, b1) - np.maximum(a0, b0), 0)
+
+    send_count = overlap(lo, hi, slices[:-1], slices[1:]).astype(np.int64)
+    send_first = np.concatenate([[0], np.cumsum(send_count)[:-1]]).astype(np.int64)
+    recv_count = overlap(bounds[:-1], bounds[1:], slices[rank], slices[rank + 1]).astype(np.int64)
+    recv_first = np.concatenate([[0], np.cumsum(recv_count)[:-1]]).astype(np.int64)
+    slice_owner = np.repeat(np.arange(world, dtype=np.int32), recv_count)
+    return Plan(np.arange(lo, hi), send_count, send_first, recv_count, recv_first, slice_owner), total, prefix
+
+
 class ShardedReplay:
     """One rank's shard (table + priorities) plus the exchange.
 
@@ -141,6 +181,37 @@ class ShardedReplay:
         self.totals_host.copy_(self.totals_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self.totals_host.numpy().copy()
+
+    def step_sorted(self, priorities, u01_sorted: np.ndarray, u01_sorted_dev, rescan: bool = True):
+        """One global batch whose ascending variates are already on the device as well
+        (u01_sorted_dev: float64 CUDA tensor with the same values).  The owner reads its run of
+        the batch in place and maps it into its own table inside the kernel, so the host only
+        does O(world) work per step."""
+        torch = self.torch
+        B = len(u01_sorted)
+        if B > self.maxB or B % self.world:
+            raise ValueError(f"global batch {B}: at most {self.maxB} and a multiple of {self.world}")
+        b = B // self.world
+        if rescan:
+            self.scan(priorities)
+        totals = self.gather_totals()
+        plan, total, prefix = plan_sorted(totals, u01_sorted, self.rank, self.world)
+        self.last_plan = plan
+        m = len(plan.mine)
+        direct = self.world == 1
+        dsts = self.recv if direct else self.send
+        flat = self.recv_flat if direct else self.send_flat
+        if m:
+            lo = int(plan.mine[0])
+            self.sampler.sample_gather(self.handler, u01_sorted_dev[lo:lo + m], self.columns, dsts, zero_fill=True,
+                                       out_flat=flat, affine=(total, prefix[self.rank]))
+        if not direct:
+            self.comm.alltoallv(self.send + [self.send_flat], self.recv + [self.recv_flat], self.slots + [8],
+                                plan.send_first, plan.send_count, plan.recv_first, plan.recv_count)
+        self.owner_base_host[:b].copy_(torch.from_numpy(plan.slice_owner.astype(np.int64) * self.n_local))
+        self.owner_base[:b].copy_(self.owner_base_host[:b], non_blocking=True)
+        gflat = self.recv_flat[:b] + self.owner_base[:b]
+        return [r[: b * s] for r, s in zip(self.recv, self.slots)], gflat
 
     def step(self, priorities, u01_sorted: np.ndarray, rescan: bool = True):
         """One global batch.  Returns (column byte tensors of this rank's slice, global step ids)."""

@@ -189,6 +189,7 @@ int64_t gearb_scan_static_max_n(void);
  * flags: GEARB_SEARCH_SCALE -> variates are U[0,1) and are multiplied by the
  * total on the device; otherwise they are U[0,total).                        */
 #define GEARB_SEARCH_SCALE 1
+#define GEARB_SEARCH_AFFINE 2 /* internal to gearb_sampler_sample_gather_affine */
 int gearb_search(const float *cdf, const double *l1, int64_t n, const double *variates,
                  int64_t b, int flags, int64_t *out_index, int32_t *status, void *stream);
 /* Uniform draw floor(u*n) on U[0,1) variates (stands where torch.randint is
@@ -226,6 +227,15 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
                                 const int32_t *columns, int ncols, void *const *dst, int zero_fill,
                                 int64_t *out_flat, int64_t *out_idx, int64_t *out_ts,
                                 int64_t *out_len, void *stream);
+/* The same for one shard of a sharded table: a variate u of the GLOBAL draw becomes
+ * u * mul - sub before the search (mul = total priority of all shards, sub = total of the
+ * shards before this one), clamped into this shard's range.  Stands where an owner answers
+ * the requests of its peers, CpuTrajectoryStorageHandler::subsend, src/storage/handler.cc:160-193. */
+int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const double *variates,
+                                       int64_t b, double mul, double sub, const int64_t *lengths,
+                                       int64_t index_offset, const int32_t *columns, int ncols,
+                                       void *const *dst, int zero_fill, int64_t *out_flat,
+                                       int64_t *out_idx, int64_t *out_ts, int64_t *out_len, void *stream);
 int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status);
 /* Synchronises `stream`, then returns total and the status words. */
 int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t *status);

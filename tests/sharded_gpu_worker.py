@@ -59,7 +59,10 @@ def main():
         u01 = np.sort(O.synth_u01(300 + trial, 0, B))
         if trial == 2:
             u01[:] = np.sort(O.synth_u01(400, 0, B) * 0.01)     # every request lands on shard 0
-        outs, gflat = replay.step(dprio, u01)
+        if trial == 1:      # the device-resident route: same result by construction
+            outs, gflat = replay.step_sorted(dprio, u01, torch.from_numpy(u01).to(dev))
+        else:
+            outs, gflat = replay.step(dprio, u01)
         torch.cuda.synchronize()
         want_flat = O.search(gcdf, gl1, u01, scale=True)[rank * b:(rank + 1) * b]
         assert np.array_equal(gflat.cpu().numpy(), want_flat), (rank, trial)

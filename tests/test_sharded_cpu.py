@@ -43,3 +43,30 @@ def test_exchange_plan_counts_and_order():
     assert list(p2.slice_owner) == [1, 2] and list(p2.recv_count) == [0, 1, 1, 0] and list(p2.recv_first) == [0, 0, 1, 2]
     with pytest.raises(ValueError):
         exchange_plan(owner[::-1].copy(), req, 1, 4)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_plan_sorted_equals_route_plus_exchange_plan(world):
+    from gear_b200.sharded import plan_sorted
+    rng = np.random.default_rng(world)
+    for trial in range(20):
+        totals = rng.lognormal(3, 1, world)
+        if trial % 3 == 0 and world > 1:
+            totals[rng.integers(0, world)] = 0.0          # a shard without mass
+        if trial % 5 == 0 and world > 2:
+            totals[-1] = 0.0
+        B = 16 * world
+        u = np.sort(rng.random(B))
+        if trial == 7:
+            u[:] = np.sort(rng.random(B) * 1e-3)          # everything on the first shard
+        owner, residual, requester = route(totals, u, world)
+        for rank in range(world):
+            a = exchange_plan(owner, requester, rank, world)
+            b, total, prefix = plan_sorted(totals, u, rank, world)
+            assert np.array_equal(a.mine, b.mine), (trial, rank)
+            assert np.array_equal(a.send_count, b.send_count) and np.array_equal(a.send_first, b.send_first)
+            assert np.array_equal(a.recv_count, b.recv_count) and np.array_equal(a.recv_first, b.recv_first)
+            assert np.array_equal(a.slice_owner, b.slice_owner)
+            # what the kernel computes from (u, mul=total, sub=prefix[rank]) is route()'s residual
+            v = np.minimum(u[b.mine] * total, np.nextafter(total, 0.0)) - prefix[rank]
+            assert np.array_equal(np.where(v < totals[rank], v, np.nextafter(totals[rank], 0.0)), residual[b.mine])
