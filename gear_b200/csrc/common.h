@@ -91,7 +91,7 @@ struct GatherParams {
   int32_t chunk_bytes;
   int32_t zero_fill;
   int32_t stage_bytes;  // > 0: a request's columns fit this much shared memory and the table is in HBM
-  int32_t reserved;
+  int32_t ring;         // 1: larger requests stream through per-warp rings of bulk copies
   GatherColumn cols[GEARB_MAX_COLUMNS];
 };
 

@@ -162,6 +162,39 @@ __device__ __forceinline__ void copy_piece(const GatherParams &P, const GatherCo
   }
 }
 
+// What piece `cq` of request g's slot of column `col` consists of: `len` data bytes going to
+// `dst` (their offset inside the clipped segment is `seg_off`), and up to two runs of padding.
+struct PieceInfo {
+  uint8_t *dst;
+  int64_t seg_off;
+  int len;
+  uint8_t *zero_a, *zero_b;
+  int zero_a_len, zero_b_len;
+};
+
+__device__ __forceinline__ PieceInfo piece_info(const GatherParams &P, const GatherColumn &col, int cq, int64_t g,
+                                                int64_t bytes) {
+  const int64_t slot = static_cast<int64_t>(col.row) * col.pat_length;
+  const int64_t data_off = col.pad_head ? slot - bytes : 0;
+  const int64_t c0 = static_cast<int64_t>(cq) * P.chunk_bytes;
+  int64_t c1 = c0 + P.chunk_bytes;
+  if (c1 > slot) c1 = slot;
+  uint8_t *dslot = col.dst + g * slot;
+  const int64_t lo = c0 > data_off ? c0 : data_off;
+  const int64_t hi = c1 < data_off + bytes ? c1 : data_off + bytes;
+  PieceInfo pi;
+  pi.dst = dslot + lo;
+  pi.seg_off = lo - data_off;
+  pi.len = hi > lo ? static_cast<int>(hi - lo) : 0;
+  const int64_t z1 = c1 < data_off ? c1 : data_off;
+  pi.zero_a = dslot + c0;
+  pi.zero_a_len = (P.zero_fill && z1 > c0) ? static_cast<int>(z1 - c0) : 0;
+  const int64_t z0 = c0 > data_off + bytes ? c0 : data_off + bytes;
+  pi.zero_b = dslot + z0;
+  pi.zero_b_len = (P.zero_fill && c1 > z0) ? static_cast<int>(c1 - z0) : 0;
+  return pi;
+}
+
 // Address of the segment's first byte in the table.
 __device__ __forceinline__ const uint8_t *segment_src(const GatherParams &P, const GatherColumn &col, int64_t idx,
                                                       int64_t start) {

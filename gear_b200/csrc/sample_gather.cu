@@ -28,6 +28,8 @@ constexpr int kThreads = 128;
 constexpr int kWarps = kThreads / 32;
 constexpr int kSlots = 2 * kThreads;  // probes per round
 constexpr unsigned kFull = 0xffffffffu;
+constexpr int kRingSlots = 3;            // per-warp ring of bulk copies for large requests
+constexpr int kRingSlotBytes = 4096 + 128;  // one 4 KiB piece plus the 16-byte blocks around a misaligned one
 constexpr unsigned kWaitLimit = 1u << 20;  // mbarrier polls before a staged copy is declared lost
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) {
@@ -121,11 +123,16 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
   __shared__ unsigned masks[2][2 * kWarps];
   __shared__ float vals[kSlots];
   __shared__ uint64_t stage_bar;
+  __shared__ uint64_t ring_bar[kWarps][kRingSlots];
+  unsigned ring_it = 0;  // pieces this warp has pushed through its ring so far
+  bool ring_dead = false;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned flags = 0, stage_parity = 0;
   int round = 0;
   if (threadIdx.x == 0) {
     mbar_init(&stage_bar, 1);
+    for (int w = 0; w < kWarps; ++w)
+      for (int r = 0; r < kRingSlots; ++r) mbar_init(&ring_bar[w][r], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -275,6 +282,66 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
         dev::copy_piece<true>(P, col, q - col.chunk_first, g, stage + col.stage_off + (src & 15u), bytes, lane);
       }
       __syncthreads();  // the staging area is free for the next request
+    } else if (P.ring) {
+      // Ring: a request too large to stage whole.  Each warp streams its pieces (4 KiB of a
+      // slot each) through a private ring of bulk asynchronous copies that runs kRingSlots - 1
+      // pieces ahead of the copy-out, so the loads in flight do not depend on registers.  Works
+      // the same from HBM, from a peer's memory and from mapped host memory.
+      uint8_t *ring = stage + static_cast<size_t>(warp) * kRingSlots * kRingSlotBytes;
+      const int npieces =
+          (!ring_dead && warp < P.chunks_per_request) ? (P.chunks_per_request - warp + kWarps - 1) / kWarps : 0;
+      auto describe = [&](int k, dev::PieceInfo &pi, uintptr_t &src) {
+        const int q = warp + k * kWarps;
+        const int c = dev::column_of_piece(P, q);
+        const GatherColumn &col = P.cols[c];
+        int64_t start, bytes;
+        dev::clip_segment(P, col, t, ts, len, start, bytes, flags);
+        pi = dev::piece_info(P, col, q - col.chunk_first, g, bytes);
+        src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start)) + static_cast<uintptr_t>(pi.seg_off);
+      };
+      auto issue = [&](int k) {  // lane 0
+        dev::PieceInfo pi;
+        uintptr_t src;
+        describe(k, pi, src);
+        const unsigned s_ = (ring_it + k) % kRingSlots;
+        if (pi.len > 0) {
+          const unsigned cover = static_cast<unsigned>(((src & 15u) + pi.len + 15) & ~15u);
+          mbar_arrive_expect_tx(&ring_bar[warp][s_], cover);
+          bulk_load(ring + s_ * kRingSlotBytes, reinterpret_cast<const void *>(src & ~uintptr_t(15)), cover,
+                    &ring_bar[warp][s_]);
+        } else {
+          mbar_arrive(&ring_bar[warp][s_]);
+        }
+      };
+      if (lane == 0)
+        for (int k = 0; k < kRingSlots && k < npieces; ++k) issue(k);
+      bool lost = false;
+      for (int k = 0; k < npieces; ++k) {
+        const unsigned it = ring_it + k, s_ = it % kRingSlots, parity = (it / kRingSlots) & 1u;
+        unsigned polls = 0;
+        bool ok;
+        while (!(ok = mbar_try_wait(&ring_bar[warp][s_], parity)))
+          if (++polls > kWaitLimit) break;
+        if (!__all_sync(kFull, ok)) {
+          lost = true;
+          break;
+        }
+        dev::PieceInfo pi;
+        uintptr_t src;
+        describe(k, pi, src);
+        if (pi.len > 0) dev::warp_copy_t<true>(pi.dst, ring + s_ * kRingSlotBytes + (src & 15u), pi.len, lane);
+        if (pi.zero_a_len) dev::warp_zero(pi.zero_a, pi.zero_a_len, lane);
+        if (pi.zero_b_len) dev::warp_zero(pi.zero_b, pi.zero_b_len, lane);
+        __syncwarp();
+        if (lane == 0 && k + kRingSlots < npieces) issue(k + kRingSlots);
+      }
+      ring_it += npieces;
+      if (lost) {
+        // Copies may still be in flight into this warp's ring: it copies nothing from now on,
+        // but keeps walking the loop, whose search rounds contain CTA-wide barriers.
+        if (lane == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
+        ring_dead = true;
+      }
     } else {
       // Direct: the request's pieces, column by column, dealt to the four warps.
       for (int q = warp; q < P.chunks_per_request; q += kWarps) {
@@ -310,7 +377,14 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = p.stage_bytes > 0 ? static_cast<size_t>(p.stage_bytes) : 0;
+  constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kRingSlots * kRingSlotBytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    GEARB_CUDA(cudaFuncSetAttribute(sample_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(kRingBytes)));
+    attr_set = true;
+  }
+  cfg.dynamicSmemBytes = p.stage_bytes > 0 ? static_cast<size_t>(p.stage_bytes) : (p.ring ? kRingBytes : 0);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
