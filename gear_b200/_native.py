@@ -27,6 +27,8 @@ PART = 4096
 RES_HOST, RES_HBM = 1, 2
 PAD_INACTIVE, PAD_HEAD, PAD_TAIL = 0, 1, 2
 MAX_COLUMNS = 16
+MAX_SHARDS = 16
+IPC_HANDLE_BYTES = 64
 SEARCH_SCALE = 1
 
 DT_F32, DT_F64, DT_I64, DT_F16 = range(4)
@@ -103,6 +105,11 @@ _SIGS = {
                                               C.c_int, vp, vp, vp, vp, vp]),
     "gearb_sampler_sample_gather_affine": (C.c_int, [vp, vp, vp, i64, f64, f64, vp, i64, pi32, C.c_int,
                                                      C.POINTER(vp), C.c_int, vp, vp, vp, vp, vp]),
+    "gearb_ipc_export": (C.c_int, [vp, vp]),
+    "gearb_ipc_open": (C.c_int, [vp, C.POINTER(vp)]),
+    "gearb_ipc_close": (C.c_int, [vp]),
+    "gearb_sampler_pull": (C.c_int, [vp, vp, C.c_int, vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), vp, i64,
+                                     pi32, C.c_int, C.POINTER(vp), C.c_int, C.c_int, vp, vp, vp, vp]),
     "gearb_sampler_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "gearb_sampler_result": (C.c_int, [vp, vp, C.POINTER(f64), pi32]),
     "gearb_comm_unique_id": (C.c_int, [C.c_char_p]),

@@ -1,11 +1,15 @@
 """Multi-GPU leg of bench.py: the trajectory-id sharded token table of BASELINE.json.
 
 Per GPU: 32,000 trajectories x 1000 steps, rows 4096/4/4 bytes (131.3 GB in HBM), one float32
-priority per step.  Per step every rank rescans its priorities, the shard totals are
-all-gathered, the global sorted batch of 1024 x world variates is routed, owners search +
-gather in one launch into per-requester send regions, and one grouped NCCL all-to-all lands
-each rank's 1024 segments of L=16 in its output tensors.  Weak scaling: per-GPU table and
-per-GPU batch are fixed.
+priority per step.  Two ways of moving the segments are timed on the same table and batches:
+* all-to-all: every rank rescans its priorities, the shard totals are all-gathered, the global
+  sorted batch of 1024 x world variates is routed on the host, owners search + gather in one
+  launch into per-requester send regions, and one grouped NCCL all-to-all lands each rank's 1024
+  segments of L=16 in its output tensors;
+* pull (the headline): after the scan and the all-gather of the totals, each rank's single launch
+  routes its 1024 requests, searches the owners' cumulative tables and copies the segments out of
+  the owners' HBM over NVLink.
+Weak scaling: per-GPU table and per-GPU batch are fixed.
 """
 from __future__ import annotations
 
@@ -70,45 +74,64 @@ def run(args):
         torch.cuda.synchronize()
 
     W_ = max(args.warmup, 3)
-    for i in range(W_):
-        replay.step_sorted(prio, batches[i % nb], batches_dev[i % nb])
-    barrier()
-
     K = args.steps
     clocks = B.ClockSampler(local)
-    if rank == 0:
-        clocks.start()
-        time.sleep(0.12)
-    scan_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    t0 = time.time()
-    e0.record()
-    for i in range(K):
-        scan_ev[i][0].record()
-        replay.scan(prio)
-        scan_ev[i][1].record()
-        replay.step_sorted(prio, batches[i % nb], batches_dev[i % nb], rescan=False)
-    e1.record()
-    barrier()
-    t1 = time.time()
-    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    scan_ms = torch.tensor([sum(a.elapsed_time(c) for a, c in scan_ev) / K], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        dist.all_reduce(scan_ms, op=dist.ReduceOp.MAX)
-    ms_step = float(ms[0]) / K
-    clk = clocks.stop(t0, t1) if rank == 0 else None
+
+    def timed(step, sample_clocks):
+        """W_ warm-up steps, then K timed ones: (ms per step, ms per scan, clock record), max over ranks."""
+        for i in range(W_):
+            step(i, True)
+        barrier()
+        if sample_clocks and rank == 0:
+            clocks.start()
+            time.sleep(0.12)
+        scan_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        t0 = time.time()
+        e0.record()
+        for i in range(K):
+            scan_ev[i][0].record()
+            replay.scan_for_step()
+            scan_ev[i][1].record()
+            step(i, False)
+        e1.record()
+        barrier()
+        t1 = time.time()
+        ms = torch.tensor([e0.elapsed_time(e1) / K, sum(a.elapsed_time(c) for a, c in scan_ev) / K],
+                          dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        clk = clocks.stop(t0, t1) if (sample_clocks and rank == 0) else None
+        return float(ms[0]), float(ms[1]), clk
+
+    # mode 1: owners search + gather into send regions, one grouped NCCL all-to-all per step
+    replay.scan_for_step = lambda: replay.scan(prio)
+    a2a_ms, a2a_scan_ms, clk_a2a = timed(
+        lambda i, rescan: replay.step_sorted(prio, batches[i % nb], batches_dev[i % nb], rescan=rescan),
+        sample_clocks=False)
+    parity_a2a = sharded_parity(replay, table, handler, prio, batches[0], rank, world, dev, T, rows, L, b, "alltoall")
+
+    # mode 2: no exchange step -- requesters read the owners' HBM in place over NVLink
+    replay.enable_pull(double_buffer=True, ring=bool(os.environ.get("GEAR_BENCH_PULL_RING")))
+    replay.scan_for_step = lambda: replay.pull_scan(prio)
+    pull_ms, pull_scan_ms, clk = timed(
+        lambda i, rescan: replay.step_pull(prio, batches_dev[i % nb], rescan=rescan), sample_clocks=True)
+    parity = sharded_parity(replay, table, handler, prio, batches[0], rank, world, dev, T, rows, L, b, "pull")
+    ms_step, scan_ms = pull_ms, pull_scan_ms
 
     # ---- end to end: the rank's slice goes back to pinned host memory every step
     slots = [L * r for r in rows]
     out_host = [torch.empty(b * s, dtype=torch.uint8).pin_memory() for s in slots]
     idx_host = torch.empty(b, dtype=torch.int64).pin_memory()
+    u_host = [torch.from_numpy(x).pin_memory() for x in batches]
+    u_dev = torch.empty(Bg, dtype=torch.float64, device=dev)
     Ke = max(5, min(K, 100))
     barrier()
     w0 = time.perf_counter()
     for i in range(Ke):
-        colsout, gflat = replay.step(prio, batches[i % nb])       # variates start on the host here
+        u_dev.copy_(u_host[i % nb], non_blocking=True)            # variates start on the host here
+        colsout, gflat = replay.step_pull(prio, u_dev)
         for h, d in zip(out_host, colsout):
             h.copy_(d, non_blocking=True)
         idx_host.copy_(gflat, non_blocking=True)
@@ -118,15 +141,12 @@ def run(args):
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
 
-    # ---- parity of one batch: indices against the oracle on all shards' priorities, bytes of
-    #      locally owned requests against read-backs of the table
-    parity = sharded_parity(replay, table, handler, prio, batches[0], rank, world, dev, T, rows, L, b)
-
+    replay.disable_pull()
     if rank == 0:
         gathered = b * sum(slots)                      # per rank
         peak, peak_src = B.peaks()
         scan_bytes = 8 * n_local + 8 * ((n_local + 4095) // 4096)
-        achieved = scan_bytes / (float(scan_ms[0]) * 1e-3) / 1e9
+        achieved = scan_bytes / (scan_ms * 1e-3) / 1e9
         line = {
             "metric": B.METRIC, "value": Bg * L / (ms_step * 1e-3), "unit": B.UNIT, "n_gpus": world, "steps": K,
             "warmup": W_, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -135,12 +155,18 @@ def run(args):
                        "batch_per_gpu": b, "global_batch": Bg, "segment_length": L, "priorities_per_gpu": n_local,
                        "table_bytes_per_gpu": table.nbytes, "parallelism": f"trajectory-id shards x{world}",
                        "l2": "inputs larger than L2 (128 MB of priorities re-read every step per GPU)",
-                       "step": "scan + all-gather totals + route + search/gather + all-to-all"},
+                       "step": "scan + all-gather of shard totals + one launch that routes, searches and gathers "
+                               "from the owners' HBM over NVLink (no exchange step)"},
+            "exchange_modes": {
+                "pull_over_nvlink": {"ms_per_step": pull_ms, "value": Bg * L / (pull_ms * 1e-3), "parity": parity},
+                "nccl_alltoall": {"ms_per_step": a2a_ms, "value": Bg * L / (a2a_ms * 1e-3), "parity": parity_a2a,
+                                  "step": "scan + all-gather totals + host routing + owner search/gather + "
+                                          "grouped ncclSend/ncclRecv all-to-all"}},
             "gathered_gb_s": 2 * gathered * world / (ms_step * 1e-3) / 1e9,
             "exchanged_bytes_per_step_per_gpu": int(gathered * (world - 1) / world),
             "roofline": {"kernel": "scan_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                         "algorithmic_bytes": scan_bytes, "avg_launch_ms": float(scan_ms[0])},
+                         "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms},
             "cpu_baseline": None,
             "e2e": {"value": Bg * L / float(e2e_s[0]), "unit": B.UNIT, "h2d_bytes_per_step": 8 * Bg * world,
                     "d2h_bytes_per_step": (gathered + 8 * b) * world, "ms_per_step": float(e2e_s[0]) * 1e3, "steps": Ke},
@@ -152,14 +178,28 @@ def run(args):
         dist.destroy_process_group()
 
 
-def sharded_parity(replay, table, handler, prio, u_sorted, rank, world, dev, T, rows, L, b):
+def sharded_parity(replay, table, handler, prio, u_sorted, rank, world, dev, T, rows, L, b, mode):
+    """Parity of one batch: indices of every rank's slice against the oracle on all shards'
+    priorities; bytes of the requests this rank owns itself against read-backs of its table; in
+    pull mode additionally every byte of the slice against the all-to-all mode's result."""
     import torch
     import torch.distributed as dist
+    from .sharded import plan_sorted
     n_local = prio.numel()
-    colsout, gflat = replay.step_sorted(prio, u_sorted, torch.from_numpy(u_sorted).to(dev))
-    torch.cuda.synchronize()
+    cross = None
+    if mode == "pull":
+        ref_cols, ref_flat = replay.step_sorted(prio, u_sorted, torch.from_numpy(u_sorted).to(dev))
+        ref_cols, ref_flat = [c.clone() for c in ref_cols], ref_flat.clone()
+        colsout, gflat = replay.step_pull(prio, torch.from_numpy(u_sorted).to(dev))
+        torch.cuda.synchronize()
+        cross = sum(int((a != c).sum()) for a, c in zip(ref_cols, colsout)) + int((ref_flat != gflat).sum())
+        del ref_cols
+        plan, _, _ = plan_sorted(replay.gather_totals(), u_sorted, rank, world)
+    else:
+        colsout, gflat = replay.step_sorted(prio, u_sorted, torch.from_numpy(u_sorted).to(dev))
+        torch.cuda.synchronize()
+        plan = replay.last_plan
     gflat_h = gflat.cpu().numpy()
-    plan = replay.last_plan
     # bytes: requests of my slice that I own myself, against table read-backs
     byte_mismatch = checked = 0
     own = np.nonzero(plan.slice_owner == rank)[0][::8]
@@ -180,7 +220,7 @@ def sharded_parity(replay, table, handler, prio, u_sorted, rank, world, dev, T, 
     if world > 1:
         dist.all_gather(allp, prio)
         dist.all_gather(allf, gflat.contiguous())
-    mism = torch.tensor([byte_mismatch, checked], dtype=torch.int64, device=dev)
+    mism = torch.tensor([byte_mismatch, checked, cross or 0], dtype=torch.int64, device=dev)
     if world > 1:
         dist.all_reduce(mism)
     out = None
@@ -200,4 +240,6 @@ def sharded_parity(replay, table, handler, prio, u_sorted, rank, world, dev, T, 
         got = torch.cat(allf).cpu().numpy()
         out = {"index_mismatches_vs_oracle": int((got != want).sum()), "gathered_byte_mismatches": int(mism[0]),
                "requests_byte_checked": int(mism[1])}
+        if mode == "pull":
+            out["mismatches_vs_alltoall_mode_all_bytes"] = int(mism[2])
     return out

@@ -20,7 +20,7 @@ from ._native import GearError, call, lib
 __all__ = [
     "GearError", "SubscribePattern", "TrajectoryTable", "StorageHandler", "Indexset",
     "PrioritySampler", "scan", "search", "sample_uniform", "decode", "fill", "vcopy", "copy",
-    "init", "device_count",
+    "init", "device_count", "ipc_export", "ipc_open", "ipc_close",
 ]
 
 
@@ -401,6 +401,41 @@ class PrioritySampler:
              (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)),
              _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _ptr(out_len), _stream(stream))
 
+    def pull(self, handler: "StorageHandler", totals: torch.Tensor, cdfs: Sequence[int], l1s: Sequence[int],
+             tables: Sequence[int], variates: torch.Tensor, columns: Sequence[int], dsts: Sequence[torch.Tensor],
+             zero_fill: bool = True, ring: bool = False, out_flat: Optional[torch.Tensor] = None,
+             out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None, stream=None) -> None:
+        """This rank's slice of a global batch, read in place from `len(tables)` equal shards.
+
+        totals: float64 CUDA tensor, one total priority per shard.  cdfs / l1s / tables: device
+        addresses (ints) of every shard's tables, valid on the current device -- this process's
+        own allocations or mappings from ipc_open().  variates are U[0,1) of the global draw."""
+        w = len(tables)
+        if not (len(cdfs) == len(l1s) == w) or totals.dtype != torch.float64 or not totals.is_cuda \
+                or totals.numel() < w:
+            raise GearError(N.ERR_INVALID, "pull: one cdf, l1, table and float64 CUDA total per shard")
+        if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
+            raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
+        b = variates.numel()
+        if len(dsts) != len(columns):
+            raise GearError(N.ERR_INVALID, "one destination per column is required")
+        for c, d in zip(columns, dsts):
+            p = handler.patterns.get(int(c))
+            if p is not None:
+                need = b * p.length * handler.table.row_bytes[int(c)]
+                if not d.is_cuda or not d.is_contiguous() or d.numel() * d.element_size() < need:
+                    raise GearError(N.ERR_INVALID,
+                                    f"destination of column {c} must be a contiguous CUDA tensor of >= {need} bytes")
+        for name, t in (("out_flat", out_flat), ("out_idx", out_idx), ("out_ts", out_ts)):
+            if t is not None and (t.dtype != torch.int64 or not t.is_cuda or t.numel() < b):
+                raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
+        nc = len(columns)
+        arr = lambda v: (C.c_void_p * w)(*[int(x) for x in v])
+        call("gearb_sampler_pull", self._h, handler._h, w, _ptr(totals), arr(cdfs), arr(l1s), arr(tables),
+             _ptr(variates), b, (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
+             (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)), int(bool(ring)),
+             _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _stream(stream))
+
     def result(self, stream=None):
         """(total, status words) after synchronising the stream."""
         total = C.c_double(0.0)
@@ -462,3 +497,23 @@ def copy(src_ptr: int, dst: torch.Tensor, src_off: torch.Tensor, dst_off: torch.
     n = min(src_off.numel(), dst_off.numel())
     call("gearb_copy", C.c_void_p(src_ptr), _ptr(dst), _dev_i64(src_off, "src_offsets"),
          _dev_i64(dst_off, "dst_offsets"), n, int(length), _stream(stream))
+
+
+def ipc_export(device_ptr: int) -> bytes:
+    """64-byte handle of a device allocation of this process, for the other ranks of the box."""
+    buf = C.create_string_buffer(N.IPC_HANDLE_BYTES)
+    call("gearb_ipc_export", C.c_void_p(int(device_ptr)), buf)
+    return buf.raw
+
+
+def ipc_open(handle: bytes) -> int:
+    """Map another rank's allocation into this process; returns its address on the current device."""
+    if len(handle) != N.IPC_HANDLE_BYTES:
+        raise GearError(N.ERR_INVALID, f"an ipc handle has {N.IPC_HANDLE_BYTES} bytes")
+    out = C.c_void_p(0)
+    call("gearb_ipc_open", C.create_string_buffer(bytes(handle), N.IPC_HANDLE_BYTES), C.byref(out))
+    return out.value
+
+
+def ipc_close(device_ptr: int) -> None:
+    call("gearb_ipc_close", C.c_void_p(int(device_ptr)))

@@ -665,6 +665,47 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
                               out_idx, out_ts, out_len, as_stream(stream));
 }
 
+int gearb_ipc_export(const void *device_ptr, void *handle64) {
+  GEARB_REQUIRE(device_ptr && handle64, "ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == GEARB_IPC_HANDLE_BYTES, "handle size");
+  cudaIpcMemHandle_t hd;
+  GEARB_CUDA(cudaIpcGetMemHandle(&hd, const_cast<void *>(device_ptr)));
+  memcpy(handle64, &hd, sizeof(hd));
+  return GEARB_OK;
+}
+
+int gearb_ipc_open(const void *handle64, void **device_ptr) {
+  GEARB_REQUIRE(device_ptr && handle64, "ipc_open: null argument");
+  cudaIpcMemHandle_t hd;
+  memcpy(&hd, handle64, sizeof(hd));
+  GEARB_CUDA(cudaIpcOpenMemHandle(device_ptr, hd, cudaIpcMemLazyEnablePeerAccess));
+  return GEARB_OK;
+}
+
+int gearb_ipc_close(void *device_ptr) {
+  GEARB_REQUIRE(device_ptr, "ipc_close: null argument");
+  GEARB_CUDA(cudaIpcCloseMemHandle(device_ptr));
+  return GEARB_OK;
+}
+
+int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, const double *totals,
+                       const void *const *cdf, const void *const *l1, const void *const *table,
+                       const double *variates, int64_t b, const int32_t *columns, int ncols,
+                       void *const *dst, int zero_fill, int ring, int64_t *out_flat, int64_t *out_idx,
+                       int64_t *out_ts, void *stream) {
+  GEARB_REQUIRE(s, "pull: null sampler");
+  GatherParams p;
+  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
+  if (rc != GEARB_OK) return rc;
+  GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
+                "pull: %lld priorities but a shard holds only %lld steps", (long long)s->n,
+                (long long)(h->table->capacity * h->table->T));
+  GEARB_REQUIRE(h->table->hbm, "pull: the shards must be in device memory");
+  if (p.stage_bytes == 0) p.ring = ring ? 1 : 0;
+  return launch_pull(p, world, totals, cdf, l1, table, s->n, variates, out_flat, out_idx, out_ts,
+                     as_stream(stream));
+}
+
 int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status) {
   GEARB_REQUIRE(s, "sampler_buffers: null sampler");
   if (cdf) *cdf = s->cdf;

@@ -196,18 +196,19 @@ __device__ __forceinline__ PieceInfo piece_info(const GatherParams &P, const Gat
 }
 
 // Address of the segment's first byte in the table.
+// `table` is the base of the table that holds trajectory idx: P.table, or a peer shard's.
 __device__ __forceinline__ const uint8_t *segment_src(const GatherParams &P, const GatherColumn &col, int64_t idx,
-                                                      int64_t start) {
-  return P.table + idx * P.traj_stride + col.col_offset + start * static_cast<int64_t>(col.row);
+                                                      int64_t start, const uint8_t *table) {
+  return table + idx * P.traj_stride + col.col_offset + start * static_cast<int64_t>(col.row);
 }
 
 // Straight from the table (HBM or mapped host memory) to the destination.
 __device__ __forceinline__ void gather_piece(const GatherParams &P, const GatherColumn &col, int cq,
                                              int64_t g, int64_t idx, int64_t ts, int64_t len, int lane,
-                                             unsigned &flags) {
+                                             unsigned &flags, const uint8_t *table) {
   int64_t start, bytes;
   clip_segment(P, col, idx, ts, len, start, bytes, flags);
-  copy_piece<false>(P, col, cq, g, bytes > 0 ? segment_src(P, col, idx, start) : P.table, bytes, lane);
+  copy_piece<false>(P, col, cq, g, bytes > 0 ? segment_src(P, col, idx, start, table) : table, bytes, lane);
 }
 
 // Column that owns piece q of a request (pieces are numbered column by column).

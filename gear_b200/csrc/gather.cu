@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(kThreads) gather_kernel(const __grid_constant_
     const int q = static_cast<int>(item - g * P.chunks_per_request);
     const int c = dev::column_of_piece(P, q);
     dev::gather_piece(P, P.cols[c], q - P.cols[c].chunk_first, g, __ldg(P.idx + g), __ldg(P.ts + g),
-                      __ldg(P.len + g), lane, flags);
+                      __ldg(P.len + g), lane, flags, P.table);
   }
   if (flags && P.status && lane == 0) atomicOr(reinterpret_cast<unsigned *>(P.status), flags);
 }

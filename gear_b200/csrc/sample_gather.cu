@@ -117,8 +117,23 @@ struct SampleArgs {
   double mul, sub;  // GEARB_SEARCH_AFFINE: variate -> variate * mul - sub (global draw -> this shard)
 };
 
-__global__ void __launch_bounds__(kThreads, 7)
-sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a) {
+// Sharded table read in place: every request is routed to the shard that owns its variate, and
+// that shard's cumulative table and trajectory table are read through peer pointers (another
+// GPU's memory mapped into this process, or other allocations of this GPU).
+struct PeerArgs {
+  int world;             // 0: not sharded
+  const double *totals;  // float64[world], total priority of every shard (device memory)
+  const float *cdf[GEARB_MAX_SHARDS];
+  const double *l1[GEARB_MAX_SHARDS];
+  const uint8_t *table[GEARB_MAX_SHARDS];
+};
+
+enum { kStaged = 0, kRing = 1, kDirect = 2 };  // how a request's bytes travel, one instance each
+
+template <bool kPeers, int kPath>
+__global__ void __launch_bounds__(kThreads, kPath == kDirect ? 5 : 7)
+sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
+                     const __grid_constant__ PeerArgs peers) {
   extern __shared__ __align__(128) uint8_t stage[];  // P.stage_bytes of staging area
   __shared__ unsigned masks[2][2 * kWarps];
   __shared__ float vals[kSlots];
@@ -142,13 +157,42 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   for (int64_t g = blockIdx.x; g < P.n; g += gridDim.x) {
+    // ---- which shard: sharded tables route the request by the shard totals first
+    const float *cdf = a.cdf;
+    const double *l1 = a.l1;
+    const uint8_t *table = P.table;
+    double v = __ldg(a.u + g);
+    int owner = 0;
+    if (kPeers) {
+      // In-order float64 prefix of the shard totals, as the host router computes it
+      // (route() in gear_b200/sharded.py): shard j owns prefix[j] <= v < prefix[j+1].
+      double gtotal = 0.0;
+      for (int j = 0; j < peers.world; ++j) gtotal = __dadd_rn(gtotal, __ldg(peers.totals + j));
+      v = __dmul_rn(v, gtotal);
+      if (!(v >= 0.0)) v = 0.0;
+      if (!(v < gtotal)) v = __longlong_as_double(__double_as_longlong(gtotal) - 1);
+      double acc = 0.0, before = 0.0;
+      owner = peers.world - 1;
+      for (int j = 0; j < peers.world; ++j) {
+        before = acc;
+        acc = __dadd_rn(before, __ldg(peers.totals + j));
+        if (acc > v) {
+          owner = j;
+          break;
+        }
+      }
+      v = __dsub_rn(v, before);
+      cdf = peers.cdf[owner];
+      l1 = peers.l1[owner];
+      table = peers.table[owner];
+    }
+
     // ---- level 1, first round: the probes and the variate travel together
     Range r1{0, a.nparts - 1, 0};
     int64_t q0, q1, step;
     probe_positions(r1, q0, q1, step);
-    double p0 = __ldg(a.l1 + 1 + q0), p1 = __ldg(a.l1 + 1 + q1);
-    const double total = __ldg(a.l1 + a.nparts);
-    double v = __ldg(a.u + g);
+    double p0 = __ldg(l1 + 1 + q0), p1 = __ldg(l1 + 1 + q1);
+    const double total = __ldg(l1 + a.nparts);
     int64_t flat;
     if (!(total > 0.0)) {
       flat = a.n - 1;  // nothing selectable: defined as the last index
@@ -167,19 +211,19 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
         resolve(r1, step, p0 > v, p1 > v, masks, round);
         if (step == 1 || r1.lo >= r1.hi) break;
         probe_positions(r1, q0, q1, step);
-        p0 = __ldg(a.l1 + 1 + q0);
-        p1 = __ldg(a.l1 + 1 + q1);
+        p0 = __ldg(l1 + 1 + q0);
+        p1 = __ldg(l1 + 1 + q1);
       }
       const int64_t p = r1.hi;
 
       // ---- level 2, first round: probes, the partition's offset and its last entry together
       const int64_t base = p * GEARB_PART;
       const int64_t valid = (a.n - base < GEARB_PART) ? (a.n - base) : GEARB_PART;
-      const float *cp = a.cdf + base;
+      const float *cp = cdf + base;
       Range r2{0, valid - 1, 0};
       probe_positions(r2, q0, q1, step);
       float c0 = __ldg(cp + q0), c1 = __ldg(cp + q1);
-      const double off = __ldg(a.l1 + p);
+      const double off = __ldg(l1 + p);
       const float last = __ldg(cp + valid - 1);
       float r = __double2float_rn(__dsub_rn(v, off));
       if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
@@ -228,14 +272,15 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
     }
     const int64_t len = a.lengths ? __ldg(a.lengths + t) : P.T;
     if (threadIdx.x == 0) {
-      if (a.out_flat) a.out_flat[g] = flat;
-      if (a.out_idx) a.out_idx[g] = t + a.index_offset;
+      // sharded: global ids, shard `owner` holds steps [owner*n, (owner+1)*n)
+      if (a.out_flat) a.out_flat[g] = flat + (kPeers ? owner * a.n : 0);
+      if (a.out_idx) a.out_idx[g] = t + a.index_offset + (kPeers ? owner * P.capacity : 0);
       if (a.out_ts) a.out_ts[g] = ts;
       if (a.out_len) a.out_len[g] = len;
     }
 
     // ---- gather
-    if (P.stage_bytes > 0) {
+    if (kPath == kStaged) {
       // Staged: thread 0 starts one bulk asynchronous copy per column (the 16-byte blocks that
       // cover the clipped segment) into shared memory, so every column of the request is in
       // flight at once; then the warps realign from shared memory to the destination.
@@ -245,7 +290,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
           int64_t start, bytes;
           dev::clip_segment(P, P.cols[c], t, ts, len, start, bytes, flags);
           if (bytes > 0) {
-            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start));
+            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start, table));
             total_tx += static_cast<unsigned>(((src & 15u) + bytes + 15) & ~int64_t(15));
           }
         }
@@ -256,7 +301,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
           unsigned ignore = 0;
           dev::clip_segment(P, P.cols[c], t, ts, len, start, bytes, ignore);
           if (bytes > 0) {
-            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start));
+            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start, table));
             const unsigned cover = static_cast<unsigned>(((src & 15u) + bytes + 15) & ~int64_t(15));
             bulk_load(stage + P.cols[c].stage_off, reinterpret_cast<const void *>(src & ~uintptr_t(15)), cover,
                       &stage_bar);
@@ -278,11 +323,11 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
         int64_t start, bytes;
         unsigned ignore = 0;
         dev::clip_segment(P, col, t, ts, len, start, bytes, ignore);
-        const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start));
+        const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start, table));
         dev::copy_piece<true>(P, col, q - col.chunk_first, g, stage + col.stage_off + (src & 15u), bytes, lane);
       }
       __syncthreads();  // the staging area is free for the next request
-    } else if (P.ring) {
+    } else if (kPath == kRing) {
       // Ring: a request too large to stage whole.  Each warp streams its pieces (4 KiB of a
       // slot each) through a private ring of bulk asynchronous copies that runs kRingSlots - 1
       // pieces ahead of the copy-out, so the loads in flight do not depend on registers.  Works
@@ -297,7 +342,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
         int64_t start, bytes;
         dev::clip_segment(P, col, t, ts, len, start, bytes, flags);
         pi = dev::piece_info(P, col, q - col.chunk_first, g, bytes);
-        src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start)) + static_cast<uintptr_t>(pi.seg_off);
+        src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start, table)) + static_cast<uintptr_t>(pi.seg_off);
       };
       auto issue = [&](int k) {  // lane 0
         dev::PieceInfo pi;
@@ -346,13 +391,48 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a)
       // Direct: the request's pieces, column by column, dealt to the four warps.
       for (int q = warp; q < P.chunks_per_request; q += kWarps) {
         const int c = dev::column_of_piece(P, q);
-        dev::gather_piece(P, P.cols[c], q - P.cols[c].chunk_first, g, t, ts, len, lane, flags);
+        dev::gather_piece(P, P.cols[c], q - P.cols[c].chunk_first, g, t, ts, len, lane, flags, table);
       }
     }
   }
   if (P.status && flags && lane == 0) atomicOr(reinterpret_cast<unsigned *>(P.status), flags);
 }
 
+}  // namespace
+
+namespace {
+int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers, cudaStream_t stream) {
+  int64_t grid = p.n;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
+  if (grid > cap) grid = cap;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kRingSlots * kRingSlotBytes;
+  static bool attr_set = false;
+  if (!attr_set) {
+    GEARB_CUDA(cudaFuncSetAttribute(sample_gather_kernel<false, kRing>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRingBytes)));
+    GEARB_CUDA(cudaFuncSetAttribute(sample_gather_kernel<true, kRing>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRingBytes)));
+    attr_set = true;
+  }
+  const int path = p.stage_bytes > 0 ? kStaged : (p.ring ? kRing : kDirect);
+  cfg.dynamicSmemBytes = path == kStaged ? static_cast<size_t>(p.stage_bytes) : (path == kRing ? kRingBytes : 0);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  using Kernel = void (*)(const GatherParams, const SampleArgs, const PeerArgs);
+  static const Kernel table[2][3] = {
+      {sample_gather_kernel<false, kStaged>, sample_gather_kernel<false, kRing>, sample_gather_kernel<false, kDirect>},
+      {sample_gather_kernel<true, kStaged>, sample_gather_kernel<true, kRing>, sample_gather_kernel<true, kDirect>}};
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, table[peers.world > 0][path], p, a, peers));
+  return GEARB_OK;
+}
 }  // namespace
 
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
@@ -370,29 +450,32 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
   a.flags = flags;
   a.mul = mul;
   a.sub = sub;
-  int64_t grid = p.n;
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
-  if (grid > cap) grid = cap;
+  PeerArgs peers = {};
+  return launch_any(p, a, peers, stream);
+}
 
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(grid));
-  cfg.blockDim = dim3(kThreads);
-  constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kRingSlots * kRingSlotBytes;
-  static bool attr_set = false;
-  if (!attr_set) {
-    GEARB_CUDA(cudaFuncSetAttribute(sample_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(kRingBytes)));
-    attr_set = true;
+int launch_pull(const GatherParams &p, int world, const double *totals, const void *const *peer_cdf,
+                const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
+                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream) {
+  GEARB_REQUIRE(n > 0, "pull: the priority table is empty");
+  GEARB_REQUIRE(world >= 1 && world <= GEARB_MAX_SHARDS, "pull: %d shards, at most %d", world, GEARB_MAX_SHARDS);
+  if (p.n == 0) return GEARB_OK;
+  GEARB_REQUIRE(totals && peer_cdf && peer_l1 && peer_table && u, "pull: null pointer argument");
+  PeerArgs peers = {};
+  peers.world = world;
+  peers.totals = totals;
+  for (int j = 0; j < world; ++j) {
+    GEARB_REQUIRE(peer_cdf[j] && peer_l1[j] && peer_table[j], "pull: null pointer for shard %d", j);
+    peers.cdf[j] = static_cast<const float *>(peer_cdf[j]);
+    peers.l1[j] = static_cast<const double *>(peer_l1[j]);
+    peers.table[j] = static_cast<const uint8_t *>(peer_table[j]);
   }
-  cfg.dynamicSmemBytes = p.stage_bytes > 0 ? static_cast<size_t>(p.stage_bytes) : (p.ring ? kRingBytes : 0);
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  GEARB_CUDA(cudaLaunchKernelEx(&cfg, sample_gather_kernel, p, a));
-  return GEARB_OK;
+  SampleArgs a = {};
+  a.cdf = peers.cdf[0]; a.l1 = peers.l1[0]; a.u = u;
+  a.out_flat = out_flat; a.out_idx = out_idx; a.out_ts = out_ts;
+  a.n = n; a.nparts = (n + GEARB_PART - 1) / GEARB_PART;
+  a.mul = 1.0;
+  return launch_any(p, a, peers, stream);
 }
 
 }  // namespace gearb

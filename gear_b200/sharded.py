@@ -19,6 +19,15 @@ offline_loader.py:127-131).  What changes is the traffic:
 
 `route` and `exchange_plan` are pure host functions (numpy); they are what the CPU-rank
 tests exercise.  `ShardedReplay` wires them to the kernels and to NCCL.
+
+A third mode leaves the exchange out altogether (`enable_pull` + `step_pull`): every rank maps
+its peers' tables and cumulative-priority tables into its own address space, and the REQUESTER's
+kernel routes each request by the all-gathered shard totals (the same arithmetic as `route`),
+searches the owner's tables and copies the segment out of the owner's HBM over NVLink, straight
+into its final tensors.  The all-gather of the totals is the step's only collective and also its
+only synchronisation: with two alternating cumulative tables per rank, a rank cannot start
+overwriting a table that a peer may still be reading (the peer's next all-gather contribution
+comes after its reads in stream order, and this rank's overwrite comes after that all-gather).
 """
 from __future__ import annotations
 
@@ -248,3 +257,89 @@ class ShardedReplay:
         self.owner_base[:b].copy_(self.owner_base_host[:b], non_blocking=True)
         gflat = self.recv_flat[:b] + self.owner_base[:b]
         return [r[: b * s] for r, s in zip(self.recv, self.slots)], gflat
+
+    # -- exchange-free mode: requesters read the owners' memory in place ---------------------
+    def enable_pull(self, double_buffer: bool = True, ring: bool = False) -> None:
+        """Map every peer's shard into this process (collective: every rank calls it once).
+
+        double_buffer: alternate between two cumulative tables so that the totals' all-gather is
+        the only synchronisation of a step; otherwise one table and a second (8-byte) collective
+        closes every step.  ring: stream large requests through bulk-copy rings instead of plain
+        16-byte loads."""
+        torch = self.torch
+        from . import core
+        if self.handler.table.device_ptr == 0:
+            raise ValueError("pull mode needs the shards in device memory")
+        self._pull_ring = bool(ring)
+        self._pull_samplers = [self.sampler] + ([core.PrioritySampler(self.n_local)] if double_buffer else [])
+        self._pull_k = -1
+        own = [self.handler.table.device_ptr]
+        for sm in self._pull_samplers:
+            own += [sm.cdf_ptr, sm.l1_ptr]
+        nh = len(own)
+        self._pull_mapped = []
+        if self.world == 1:
+            ptrs = [own]
+        else:
+            H = self.N.IPC_HANDLE_BYTES
+            mine = b"".join(core.ipc_export(p) for p in own)
+            send = torch.frombuffer(bytearray(mine), dtype=torch.uint8).to(self.dev)
+            recv = torch.empty(self.world * nh * H, dtype=torch.uint8, device=self.dev)
+            self.comm.allgather(send, recv)
+            torch.cuda.current_stream().synchronize()
+            blob = recv.cpu().numpy().tobytes()
+            ptrs = []
+            for j in range(self.world):
+                if j == self.rank:
+                    ptrs.append(own)
+                    continue
+                row = [core.ipc_open(blob[(j * nh + i) * H:(j * nh + i + 1) * H]) for i in range(nh)]
+                self._pull_mapped += row
+                ptrs.append(row)
+        self._pull_tables = [row[0] for row in ptrs]
+        self._pull_cdfs = [[row[1 + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
+        self._pull_l1s = [[row[2 + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
+        self._pull_fence = torch.zeros(1, dtype=torch.float32, device=self.dev)
+
+    def disable_pull(self) -> None:
+        """Unmap the peers' memory (collective; call before any rank frees its shard)."""
+        from . import core
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.comm.allreduce(self._pull_fence)          # nobody is still reading
+            self.torch.cuda.synchronize()
+        for p in self._pull_mapped:
+            core.ipc_close(p)
+        self._pull_mapped = []
+
+    def pull_scan(self, priorities) -> None:
+        """Rebuild this shard's cumulative table into the buffer the next step_pull(rescan=False) reads."""
+        self._pull_k += 1
+        self._pull_samplers[self._pull_k % len(self._pull_samplers)].scan(priorities)
+
+    def step_pull(self, priorities, u01_sorted_dev, rescan: bool = True):
+        """One global batch without an exchange step: nothing on the host depends on device
+        results, so consecutive steps queue back to back on the stream.  u01_sorted_dev: the
+        batch's ascending U[0,1) variates as a float64 CUDA tensor (the same on every rank).
+        Returns (column byte tensors of this rank's slice, global step ids)."""
+        B = u01_sorted_dev.numel()
+        if B > self.maxB or B % self.world:
+            raise ValueError(f"global batch {B}: at most {self.maxB} and a multiple of {self.world}")
+        b = B // self.world
+        nbuf = len(self._pull_samplers)
+        if rescan or self._pull_k < 0:
+            self.pull_scan(priorities)
+        k = self._pull_k % nbuf
+        sm = self._pull_samplers[k]
+        nparts = (self.n_local + self.N.PART - 1) // self.N.PART
+        mine = sm.l1[nparts:nparts + 1]
+        if self.world == 1:
+            self.totals_dev.copy_(mine)
+        else:
+            self.comm.allgather(mine, self.totals_dev)   # every shard's scan is complete once this lands
+        sm.pull(self.handler, self.totals_dev, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables,
+                u01_sorted_dev[self.rank * b:(self.rank + 1) * b], self.columns, self.recv, zero_fill=True,
+                ring=self._pull_ring, out_flat=self.recv_flat)
+        if nbuf == 1 and self.world > 1:
+            self.comm.allreduce(self._pull_fence)        # the next scan must not overtake the peers' reads
+        return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]

@@ -58,6 +58,7 @@ extern "C" {
 #define GEARB_PAD_TAIL 2
 
 #define GEARB_MAX_COLUMNS 16
+#define GEARB_MAX_SHARDS 16 /* shards one pull launch can address */
 
 typedef struct gearb_table gearb_table;
 typedef struct gearb_handler gearb_handler;
@@ -270,6 +271,35 @@ int gearb_comm_allgather(gearb_comm *c, const void *send, void *recv, int64_t by
 int gearb_comm_alltoallv(gearb_comm *c, int nbuf, const void *const *send, const int64_t *send_off,
                          const int64_t *send_bytes, void *const *recv, const int64_t *recv_off,
                          const int64_t *recv_bytes, void *stream);
+
+/* ---- sharded table read in place over NVLink ------------------------------
+ * Between GPUs of one box the reference moves every segment with its own ncclSend /
+ * ncclRecv pair (subsend / subrecv, src/storage/handler.cc:160-222).  Here a shard's
+ * table and cumulative-priority tables can instead be mapped into the peers' address
+ * space, and the REQUESTER searches and gathers from the owner's memory with ordinary
+ * and bulk loads: no send buffer, no exchange step.                           */
+#define GEARB_IPC_HANDLE_BYTES 64
+/* Handle of a device allocation of this process (table, cdf, l1 as returned by
+ * gearb_table_device_ptr / gearb_sampler_buffers) to pass to the other ranks.   */
+int gearb_ipc_export(const void *device_ptr, void *handle64);
+/* Map another rank's allocation; the pointer is valid on the current device.    */
+int gearb_ipc_open(const void *handle64, void **device_ptr);
+int gearb_ipc_close(void *device_ptr);
+/* One rank's slice of a global batch, pulled from `world` equal shards: request g
+ * scales its variate in [0,1) by the sum of totals[] (float64[world] in device memory,
+ * each shard's total priority, e.g. from gearb_comm_allgather), finds the owning
+ * shard j by the in-order prefix of totals[], searches cdf[j] / l1[j] with the
+ * remainder and gathers the listed columns from table[j] into dst.  Every shard has
+ * the layout of `h`'s table and `s`'s number of priorities; entry `rank` of the
+ * pointer arrays is this rank's own memory.  out_flat gets the global step id
+ * j * n + i, out_idx the global trajectory j * capacity + i / T.  The caller orders
+ * this launch after all shards' scans and the next scan after all peers' pulls
+ * (a collective on the same stream does both).                                  */
+int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, const double *totals,
+                       const void *const *cdf, const void *const *l1, const void *const *table,
+                       const double *variates, int64_t b, const int32_t *columns, int ncols,
+                       void *const *dst, int zero_fill, int ring, int64_t *out_flat, int64_t *out_idx,
+                       int64_t *out_ts, void *stream);
 
 /* ======================= synthetic data ================================= */
 /* Device-side Philox4x32-10 fills for benchmark tables that are too large to

@@ -70,6 +70,28 @@ def main():
         for c in cols:
             want = O.fused_subcopy(gimg, gi, gt, gl, stride, int(accu[c]), T, rows[c], 0, L, False)
             assert np.array_equal(outs[c].cpu().numpy(), want), (rank, trial, c)
+
+    # exchange-free mode: the requester reads the owners' memory in place
+    small = core.StorageHandler(table)                       # short segments: the staged copy path
+    small.set(cols, [core.SubscribePattern(-1, 3, N.PAD_HEAD)] * len(rows))
+    for mode, (double_buffer, ring, hd, off, Lm, head) in enumerate(
+            [(True, False, handler, 0, L, False), (False, True, handler, 0, L, False), (True, False, small, -1, 3, True)]):
+        rp = ShardedReplay(hd, sampler, cols, rank, W, comm, max_global_batch=B)
+        rp.enable_pull(double_buffer=double_buffer, ring=ring)
+        for trial in range(4):
+            u01 = np.sort(O.synth_u01(500 + trial, mode, B))
+            if trial == 2:
+                u01[:] = np.sort(O.synth_u01(600, mode, B) * 0.01)
+            outs, gflat = rp.step_pull(dprio, torch.from_numpy(u01).to(dev), rescan=(trial != 3))
+            torch.cuda.synchronize()
+            want_flat = O.search(gcdf, gl1, u01, scale=True)[rank * b:(rank + 1) * b]
+            assert np.array_equal(gflat.cpu().numpy(), want_flat), ("pull", mode, rank, trial)
+            gi, gt, gl = O.decode(want_flat, T)
+            for c in cols:
+                want = O.fused_subcopy(gimg, gi, gt, gl, stride, int(accu[c]), T, rows[c], off, Lm, head)
+                assert np.array_equal(outs[c].cpu().numpy(), want), ("pull", mode, rank, trial, c)
+        assert sampler.result()[1][0] == 0
+        rp.disable_pull()
     if W > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -93,3 +93,68 @@ def test_fused_subset_of_columns_and_offset(O):
     assert np.array_equal(d2.cpu().numpy(), O.fused_subcopy(img, oi, ot, ol, t.trajectory_stride, t.accu[2], T, 2, 1, 3, True))
     with pytest.raises(core.GearError):      # more priorities than the table has steps
         core.PrioritySampler(n + 1).sample_gather(h, dev(u), [0], [d0])
+
+
+@pytest.mark.parametrize("rows,T,cap,L,pad,off,ring", [
+    ([4096, 4, 4], 100, 50, 16, N.PAD_TAIL, 0, False),       # config 5 rows: plain 16-byte loads
+    ([4096, 4, 4], 100, 50, 16, N.PAD_HEAD, -15, True),      # the same through bulk-copy rings
+    ([156, 24, 4, 4, 1], 200, 40, 64, N.PAD_TAIL, 0, False), # short requests: staged in shared memory
+    ([3, 7, 13], 37, 300, 9, N.PAD_HEAD, -4, False),
+])
+def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ring):
+    # Three equal shards held by one process stand for three ranks: the kernel routes every
+    # request by the shard totals and reads the owner's tables through the pointer arrays.  The
+    # expected result is defined shard by shard: route() on the host, then the owner's search.
+    from gear_b200.sharded import route
+    W, B = 3, 255
+    n = cap * T - 5                     # not a whole number of partitions, and fewer steps than the table
+    shards = []
+    for j in range(W):
+        t, img = build(O, rows, T, cap, seed=40 + j)
+        prio = O.synth_lognormal(50 + j, 0, n)
+        prio[j::4] = 0.0
+        if j == 1:
+            prio *= 3.0
+        s = core.PrioritySampler(n)
+        s.scan(dev(prio))
+        shards.append((t, img, prio, s, O.scan(prio)))
+    h = core.StorageHandler(shards[0][0])
+    cols = list(range(len(rows)))
+    h.set(cols, [core.SubscribePattern(off, L, pad)] * len(rows))
+    totals = np.array([sh[4][2] for sh in shards])
+    for trial in range(3):
+        u = np.sort(O.synth_u01(60 + trial, 0, B))
+        if trial == 1:
+            u[:4] = [0.0, 1e-300, 0.5, np.nextafter(1.0, 0.0)]
+            u = np.sort(u)
+        if trial == 2:
+            totals_used = totals.copy(); totals_used[2] = 0.0   # a shard without mass owns nothing
+        else:
+            totals_used = totals
+        dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=DEV) for r in rows]
+        oflat = torch.empty(B, dtype=torch.int64, device=DEV); oidx = torch.empty_like(oflat); ots = torch.empty_like(oflat)
+        shards[0][3].pull(h, dev(totals_used), [sh[3].cdf_ptr for sh in shards], [sh[3].l1_ptr for sh in shards],
+                          [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
+                          out_flat=oflat, out_idx=oidx, out_ts=ots)
+        torch.cuda.synchronize()
+        owner, residual, _ = route(totals_used, np.resize(u, B + (-B) % W), W)   # padded to a multiple of W
+        owner, residual = owner[:B], residual[:B]
+        want_flat = np.empty(B, np.int64)
+        for j in range(W):
+            m = owner == j
+            want_flat[m] = O.search(shards[j][4][0], shards[j][4][1], residual[m]) + j * n
+        assert np.array_equal(oflat.cpu().numpy(), want_flat)
+        loc = want_flat - owner * n
+        assert np.array_equal(oidx.cpu().numpy(), loc // T + owner * cap)
+        assert np.array_equal(ots.cpu().numpy(), loc % T)
+        oi, ot, ol = O.decode(loc, T)
+        for c, r in enumerate(rows):
+            want = np.empty(B * L * r, np.uint8)
+            for j in range(W):
+                m = np.nonzero(owner == j)[0]
+                t, img = shards[j][0], shards[j][1]
+                part = O.fused_subcopy(img, oi[m], ot[m], ol[m], t.trajectory_stride, t.accu[c], T, r, off, L,
+                                       pad == N.PAD_HEAD)
+                want.reshape(B, L * r)[m] = part.reshape(len(m), L * r)
+            assert np.array_equal(dsts[c].cpu().numpy(), want), (trial, c)
+    assert shards[0][3].result()[1][0] == 0
