@@ -593,9 +593,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile", default=None, choices=["scan", "sample_gather"],
                     help="run one small single-kernel case (for ncu) instead of the benchmark")
-    ap.add_argument("--workload", default="default", choices=["default", "c2", "c4"],
+    ap.add_argument("--workload", default="default", choices=["default", "c2", "c4", "c5"],
                     help="default: config 3 at one GPU, the sharded config 5 at several; c2 / c4: BASELINE.json's "
-                         "index-only and zero-copy configurations")
+                         "index-only and zero-copy configurations; c5: one shard of config 5 on one GPU")
     ap.add_argument("--profile-n", type=int, default=40_000_000, help="priorities for --profile scan")
     args = ap.parse_args()
     if args.profile:
@@ -606,7 +606,7 @@ def main():
         return run_index_only(args)
     if args.workload == "c4":
         return run_zero_copy(args)
-    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1 and args.workload != "c5":
         return run_ours_single(args)
     from gear_b200 import bench_sharded
     return bench_sharded.run(args)

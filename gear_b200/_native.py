@@ -108,7 +108,7 @@ _SIGS = {
     "gearb_ipc_export": (C.c_int, [vp, vp]),
     "gearb_ipc_open": (C.c_int, [vp, C.POINTER(vp)]),
     "gearb_ipc_close": (C.c_int, [vp]),
-    "gearb_sampler_pull": (C.c_int, [vp, vp, C.c_int, vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), vp, i64,
+    "gearb_sampler_pull": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), vp, i64,
                                      pi32, C.c_int, C.POINTER(vp), C.c_int, C.c_int, vp, vp, vp, vp]),
     "gearb_sampler_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "gearb_sampler_result": (C.c_int, [vp, vp, C.POINTER(f64), pi32]),

@@ -105,6 +105,19 @@ def run(args):
         clk = clocks.stop(t0, t1) if (sample_clocks and rank == 0) else None
         return float(ms[0]), float(ms[1]), clk
 
+    # One GPU alone on the same shard and per-GPU batch (no peers, no collective): the number the
+    # multi-GPU values are to be compared with for weak scaling.
+    solo_ms = None
+    if world > 1:
+        full = replay
+        solo_u = [x[rank::world].contiguous() for x in batches_dev]
+        replay = ShardedReplay(handler, sampler, cols, 0, 1, None, max_global_batch=b)
+        replay.enable_pull(double_buffer=True, ring=False)
+        replay.scan_for_step = lambda: replay.pull_scan(prio)
+        solo_ms, _, _ = timed(lambda i, rescan: replay.step_pull(prio, solo_u[i % nb], rescan=rescan), False)
+        replay.disable_pull()
+        replay = full
+
     # mode 1: owners search + gather into send regions, one grouped NCCL all-to-all per step
     replay.scan_for_step = lambda: replay.scan(prio)
     a2a_ms, a2a_scan_ms, clk_a2a = timed(
@@ -113,7 +126,8 @@ def run(args):
     parity_a2a = sharded_parity(replay, table, handler, prio, batches[0], rank, world, dev, T, rows, L, b, "alltoall")
 
     # mode 2: no exchange step -- requesters read the owners' HBM in place over NVLink
-    replay.enable_pull(double_buffer=True, ring=bool(os.environ.get("GEAR_BENCH_PULL_RING")))
+    ring = os.environ.get("GEAR_BENCH_PULL_RING", "1") != "0"      # tuning knob; rings are the default
+    replay.enable_pull(double_buffer=True, ring=ring)
     replay.scan_for_step = lambda: replay.pull_scan(prio)
     pull_ms, pull_scan_ms, clk = timed(
         lambda i, rescan: replay.step_pull(prio, batches_dev[i % nb], rescan=rescan), sample_clocks=True)
@@ -162,6 +176,9 @@ def run(args):
                 "nccl_alltoall": {"ms_per_step": a2a_ms, "value": Bg * L / (a2a_ms * 1e-3), "parity": parity_a2a,
                                   "step": "scan + all-gather totals + host routing + owner search/gather + "
                                           "grouped ncclSend/ncclRecv all-to-all"}},
+            "one_gpu_same_workload": None if solo_ms is None else {
+                "ms_per_step": solo_ms, "value": b * L / (solo_ms * 1e-3), "unit": B.UNIT,
+                "note": "each GPU alone on its own shard with the same per-GPU batch, max over ranks"},
             "gathered_gb_s": 2 * gathered * world / (ms_step * 1e-3) / 1e9,
             "exchanged_bytes_per_step_per_gpu": int(gathered * (world - 1) / world),
             "roofline": {"kernel": "scan_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

@@ -404,12 +404,14 @@ class PrioritySampler:
     def pull(self, handler: "StorageHandler", totals: torch.Tensor, cdfs: Sequence[int], l1s: Sequence[int],
              tables: Sequence[int], variates: torch.Tensor, columns: Sequence[int], dsts: Sequence[torch.Tensor],
              zero_fill: bool = True, ring: bool = False, out_flat: Optional[torch.Tensor] = None,
-             out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None, stream=None) -> None:
+             out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None, stream=None,
+             self_shard: int = -1) -> None:
         """This rank's slice of a global batch, read in place from `len(tables)` equal shards.
 
         totals: float64 CUDA tensor, one total priority per shard.  cdfs / l1s / tables: device
         addresses (ints) of every shard's tables, valid on the current device -- this process's
-        own allocations or mappings from ipc_open().  variates are U[0,1) of the global draw."""
+        own allocations or mappings from ipc_open().  variates are U[0,1) of the global draw.
+        self_shard: the shard in this GPU's own memory (its large requests skip the ring)."""
         w = len(tables)
         if not (len(cdfs) == len(l1s) == w) or totals.dtype != torch.float64 or not totals.is_cuda \
                 or totals.numel() < w:
@@ -431,7 +433,7 @@ class PrioritySampler:
                 raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
         nc = len(columns)
         arr = lambda v: (C.c_void_p * w)(*[int(x) for x in v])
-        call("gearb_sampler_pull", self._h, handler._h, w, _ptr(totals), arr(cdfs), arr(l1s), arr(tables),
+        call("gearb_sampler_pull", self._h, handler._h, w, int(self_shard), _ptr(totals), arr(cdfs), arr(l1s), arr(tables),
              _ptr(variates), b, (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
              (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)), int(bool(ring)),
              _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _stream(stream))

@@ -688,7 +688,7 @@ int gearb_ipc_close(void *device_ptr) {
   return GEARB_OK;
 }
 
-int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, const double *totals,
+int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, int self, const double *totals,
                        const void *const *cdf, const void *const *l1, const void *const *table,
                        const double *variates, int64_t b, const int32_t *columns, int ncols,
                        void *const *dst, int zero_fill, int ring, int64_t *out_flat, int64_t *out_idx,
@@ -702,7 +702,7 @@ int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, const doub
                 (long long)(h->table->capacity * h->table->T));
   GEARB_REQUIRE(h->table->hbm, "pull: the shards must be in device memory");
   if (p.stage_bytes == 0) p.ring = ring ? 1 : 0;
-  return launch_pull(p, world, totals, cdf, l1, table, s->n, variates, out_flat, out_idx, out_ts,
+  return launch_pull(p, world, self, totals, cdf, l1, table, s->n, variates, out_flat, out_idx, out_ts,
                      as_stream(stream));
 }
 

@@ -100,7 +100,7 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
                          cudaStream_t stream, double mul = 1.0, double sub = 0.0);
-int launch_pull(const GatherParams &p, int world, const double *totals, const void *const *peer_cdf,
+int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,
                 const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
                 int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream);
 int launch_vcopy(const uint8_t *src, uint8_t *dst, const int64_t *src_off,

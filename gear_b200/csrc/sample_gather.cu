@@ -122,16 +122,19 @@ struct SampleArgs {
 // GPU's memory mapped into this process, or other allocations of this GPU).
 struct PeerArgs {
   int world;             // 0: not sharded
+  int self;              // the shard that lives in this GPU's own memory, or -1
   const double *totals;  // float64[world], total priority of every shard (device memory)
   const float *cdf[GEARB_MAX_SHARDS];
   const double *l1[GEARB_MAX_SHARDS];
   const uint8_t *table[GEARB_MAX_SHARDS];
 };
 
-enum { kStaged = 0, kRing = 1, kDirect = 2 };  // how a request's bytes travel, one instance each
+// How a request's bytes travel, one kernel instance each.  Resident CTAs per SM: the ring's
+// shared memory (50.7 KB per CTA) allows four anyway, so that instance may use more registers.
+enum { kStaged = 0, kRing = 1, kDirect = 2 };
 
 template <bool kPeers, int kPath>
-__global__ void __launch_bounds__(kThreads, kPath == kDirect ? 5 : 7)
+__global__ void __launch_bounds__(kThreads, kPath == kStaged ? 7 : (kPath == kRing ? 4 : 5))
 sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
                      const __grid_constant__ PeerArgs peers) {
   extern __shared__ __align__(128) uint8_t stage[];  // P.stage_bytes of staging area
@@ -327,11 +330,13 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
         dev::copy_piece<true>(P, col, q - col.chunk_first, g, stage + col.stage_off + (src & 15u), bytes, lane);
       }
       __syncthreads();  // the staging area is free for the next request
-    } else if (kPath == kRing) {
+    } else if (kPath == kRing && !(kPeers && owner == peers.self)) {
       // Ring: a request too large to stage whole.  Each warp streams its pieces (4 KiB of a
       // slot each) through a private ring of bulk asynchronous copies that runs kRingSlots - 1
       // pieces ahead of the copy-out, so the loads in flight do not depend on registers.  Works
-      // the same from HBM, from a peer's memory and from mapped host memory.
+      // the same from HBM, from a peer's memory and from mapped host memory.  (Requests that a
+      // sharded table routes to this GPU's own shard take the direct path below: from local HBM
+      // plain loads are faster.)
       uint8_t *ring = stage + static_cast<size_t>(warp) * kRingSlots * kRingSlotBytes;
       const int npieces =
           (!ring_dead && warp < P.chunks_per_request) ? (P.chunks_per_request - warp + kWarps - 1) / kWarps : 0;
@@ -454,7 +459,7 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
   return launch_any(p, a, peers, stream);
 }
 
-int launch_pull(const GatherParams &p, int world, const double *totals, const void *const *peer_cdf,
+int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,
                 const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
                 int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream) {
   GEARB_REQUIRE(n > 0, "pull: the priority table is empty");
@@ -463,6 +468,7 @@ int launch_pull(const GatherParams &p, int world, const double *totals, const vo
   GEARB_REQUIRE(totals && peer_cdf && peer_l1 && peer_table && u, "pull: null pointer argument");
   PeerArgs peers = {};
   peers.world = world;
+  peers.self = self;
   peers.totals = totals;
   for (int j = 0; j < world; ++j) {
     GEARB_REQUIRE(peer_cdf[j] && peer_l1[j] && peer_table[j], "pull: null pointer for shard %d", j);

@@ -339,7 +339,7 @@ class ShardedReplay:
             self.comm.allgather(mine, self.totals_dev)   # every shard's scan is complete once this lands
         sm.pull(self.handler, self.totals_dev, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables,
                 u01_sorted_dev[self.rank * b:(self.rank + 1) * b], self.columns, self.recv, zero_fill=True,
-                ring=self._pull_ring, out_flat=self.recv_flat)
+                ring=self._pull_ring, out_flat=self.recv_flat, self_shard=self.rank)
         if nbuf == 1 and self.world > 1:
             self.comm.allreduce(self._pull_fence)        # the next scan must not overtake the peers' reads
         return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]

@@ -290,12 +290,14 @@ int gearb_ipc_close(void *device_ptr);
  * each shard's total priority, e.g. from gearb_comm_allgather), finds the owning
  * shard j by the in-order prefix of totals[], searches cdf[j] / l1[j] with the
  * remainder and gathers the listed columns from table[j] into dst.  Every shard has
- * the layout of `h`'s table and `s`'s number of priorities; entry `rank` of the
- * pointer arrays is this rank's own memory.  out_flat gets the global step id
+ * the layout of `h`'s table and `s`'s number of priorities; entry `self` of the
+ * pointer arrays is memory of this GPU (-1: none is).  ring != 0 streams large requests
+ * from other GPUs through rings of bulk copies in shared memory (faster over NVLink);
+ * requests of shard `self` and ring == 0 use plain 16-byte loads.  out_flat gets the global step id
  * j * n + i, out_idx the global trajectory j * capacity + i / T.  The caller orders
  * this launch after all shards' scans and the next scan after all peers' pulls
  * (a collective on the same stream does both).                                  */
-int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, const double *totals,
+int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, int self, const double *totals,
                        const void *const *cdf, const void *const *l1, const void *const *table,
                        const double *variates, int64_t b, const int32_t *columns, int ncols,
                        void *const *dst, int zero_fill, int ring, int64_t *out_flat, int64_t *out_idx,

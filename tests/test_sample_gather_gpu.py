@@ -135,7 +135,7 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
         oflat = torch.empty(B, dtype=torch.int64, device=DEV); oidx = torch.empty_like(oflat); ots = torch.empty_like(oflat)
         shards[0][3].pull(h, dev(totals_used), [sh[3].cdf_ptr for sh in shards], [sh[3].l1_ptr for sh in shards],
                           [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
-                          out_flat=oflat, out_idx=oidx, out_ts=ots)
+                          out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1))
         torch.cuda.synchronize()
         owner, residual, _ = route(totals_used, np.resize(u, B + (-B) % W), W)   # padded to a multiple of W
         owner, residual = owner[:B], residual[:B]
