@@ -339,10 +339,16 @@ class PrioritySampler:
         call("gearb_sampler_buffers", self._h, C.byref(c), C.byref(l), C.byref(s))
         self.cdf_ptr, self.l1_ptr, self.status_ptr = c.value, l.value, s.value
 
-    def scan(self, priorities: torch.Tensor, stream=None) -> None:
+    def scan(self, priorities: torch.Tensor, stream=None, store: bool = True) -> None:
+        """Build the two-level table.  store=False keeps only the partition offsets and the total
+        (half the memory traffic); sample_gather then rebuilds the partition each request falls
+        into from `priorities`, which must stay unchanged (and alive) until then.  search() and
+        pull() need store=True."""
         if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
             raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
-        call("gearb_sampler_scan", self._h, _ptr(priorities), _stream(stream))
+        call("gearb_sampler_scan" if store else "gearb_sampler_scan_totals", self._h, _ptr(priorities),
+             _stream(stream))
+        self._lazy_source = None if store else priorities      # keeps the array alive
 
     def update(self, priorities: torch.Tensor, idx: torch.Tensor, values: torch.Tensor, stream=None) -> None:
         """priorities[idx] = values, then rescan only the touched partitions (after a scan())."""

@@ -188,6 +188,7 @@ struct gearb_sampler {
   void *scratch = nullptr;
   void *upd = nullptr;  // dirty flags + list of touched partitions for incremental updates
   int32_t *status = nullptr;
+  const float *lazy_prio = nullptr;  // set by scan_totals: level 2 is rebuilt from these on demand
 };
 
 extern "C" {
@@ -612,8 +613,17 @@ int gearb_sampler_destroy(gearb_sampler *s) {
   return GEARB_OK;
 }
 
+int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream) {
+  GEARB_REQUIRE(s, "sampler_scan_totals: null sampler");
+  int rc = launch_scan(priorities, s->n, nullptr, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
+                       as_stream(stream));
+  if (rc == GEARB_OK) s->lazy_prio = priorities;
+  return rc;
+}
+
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan: null sampler");
+  s->lazy_prio = nullptr;
   return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
                      as_stream(stream));
 }
@@ -621,13 +631,16 @@ int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) 
 int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx, const float *values, int64_t m,
                          void *stream) {
   GEARB_REQUIRE(s, "sampler_update: null sampler");
-  return launch_update(priorities, s->n, s->cdf, s->l1, scan_aggregate_words(s->scratch, s->n), s->upd, idx,
+  GEARB_REQUIRE(!s->lazy_prio || s->lazy_prio == priorities,
+                "sampler_update: not the array the table was built from");
+  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1, scan_aggregate_words(s->scratch, s->n), s->upd, idx,
                        values, m, s->status, as_stream(stream));
 }
 
 int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, int flags,
                          int64_t *out_index, void *stream) {
   GEARB_REQUIRE(s, "sampler_search: null sampler");
+  if (s->lazy_prio) return fail(GEARB_ERR_STATE, "sampler_search: the table was built without its level-2 entries");
   return launch_search(s->cdf, s->l1, s->n, variates, b, flags, out_index, s->status,
                        as_stream(stream));
 }
@@ -645,7 +658,7 @@ int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
                 (long long)(h->table->capacity * h->table->T));
   return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, GEARB_SEARCH_AFFINE, lengths, index_offset,
-                              out_flat, out_idx, out_ts, out_len, as_stream(stream), mul, sub);
+                              out_flat, out_idx, out_ts, out_len, as_stream(stream), mul, sub, s->lazy_prio);
 }
 
 int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double *variates, int64_t b,
@@ -662,7 +675,7 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
                 (long long)(h->table->capacity * h->table->T));
   return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, flags, lengths, index_offset, out_flat,
-                              out_idx, out_ts, out_len, as_stream(stream));
+                              out_idx, out_ts, out_len, as_stream(stream), 1.0, 0.0, s->lazy_prio);
 }
 
 int gearb_ipc_export(const void *device_ptr, void *handle64) {
@@ -694,6 +707,7 @@ int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, int self, 
                        void *const *dst, int zero_fill, int ring, int64_t *out_flat, int64_t *out_idx,
                        int64_t *out_ts, void *stream) {
   GEARB_REQUIRE(s, "pull: null sampler");
+  if (s->lazy_prio) return fail(GEARB_ERR_STATE, "pull: the table was built without its level-2 entries");
   GatherParams p;
   int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
   if (rc != GEARB_OK) return rc;

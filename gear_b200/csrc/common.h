@@ -99,7 +99,8 @@ int launch_gather(const GatherParams &p, cudaStream_t stream);
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
-                         cudaStream_t stream, double mul = 1.0, double sub = 0.0);
+                         cudaStream_t stream, double mul = 1.0, double sub = 0.0,
+                         const float *lazy_prio = nullptr);
 int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,
                 const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
                 int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream);

@@ -20,6 +20,7 @@
 // and wait in griddepcontrol.wait until that kernel's results are visible.
 #include "common.h"
 #include "device_copy.cuh"
+#include "scan_tree.cuh"
 
 namespace gearb {
 namespace {
@@ -107,7 +108,8 @@ __device__ __forceinline__ int resolve(Range &r, int64_t step, bool gt0, bool gt
 }
 
 struct SampleArgs {
-  const float *cdf;
+  const float *cdf;   // level-2 table, or null when it is rebuilt from `prio` on the fly
+  const float *prio;  // the priorities the level-1 table was built from (only when cdf is null)
   const double *l1;
   const double *u;
   const int64_t *lengths;  // per-trajectory lengths or null
@@ -133,8 +135,14 @@ struct PeerArgs {
 // shared memory (50.7 KB per CTA) allows four anyway, so that instance may use more registers.
 enum { kStaged = 0, kRing = 1, kDirect = 2 };
 
-template <bool kPeers, int kPath>
-__global__ void __launch_bounds__(kThreads, kPath == kStaged ? 7 : (kPath == kRing ? 4 : 5))
+constexpr int kLazyBytes = GEARB_PART * 4 + kWarps * 512;  // a partition of priorities + exchange areas
+
+// kLazy: there is no stored level-2 table.  The CTA fetches the chosen partition's 4096
+// priorities (one 16 KiB bulk copy), rebuilds the partition's entries with the scan's own
+// addition tree, and searches them in shared memory.  The scan then only has to read the
+// priorities (4 bytes each) instead of reading them and writing a table (8 bytes each).
+template <bool kPeers, int kPath, bool kLazy>
+__global__ void __launch_bounds__(kThreads, kPath == kStaged ? (kLazy ? 6 : 7) : (kPath == kRing ? 4 : 5))
 sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
                      const __grid_constant__ PeerArgs peers) {
   extern __shared__ __align__(128) uint8_t stage[];  // P.stage_bytes of staging area
@@ -142,6 +150,9 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
   __shared__ float vals[kSlots];
   __shared__ uint64_t stage_bar;
   __shared__ uint64_t ring_bar[kWarps][kRingSlots];
+  __shared__ float blk_total[8], blk_max[8];
+  __shared__ int warp_best[kWarps];
+  __shared__ float warp_lo[kWarps];
   unsigned ring_it = 0;  // pieces this warp has pushed through its ring so far
   bool ring_dead = false;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -219,46 +230,147 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
       }
       const int64_t p = r1.hi;
 
-      // ---- level 2, first round: probes, the partition's offset and its last entry together
       const int64_t base = p * GEARB_PART;
       const int64_t valid = (a.n - base < GEARB_PART) ? (a.n - base) : GEARB_PART;
-      const float *cp = cdf + base;
-      Range r2{0, valid - 1, 0};
-      probe_positions(r2, q0, q1, step);
-      float c0 = __ldg(cp + q0), c1 = __ldg(cp + q1);
-      const double off = __ldg(l1 + p);
-      const float last = __ldg(cp + valid - 1);
-      float r = __double2float_rn(__dsub_rn(v, off));
-      if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
-      int first;
-      for (;;) {
-        if (step == 1) {  // keep the last round's entries: the boundary check below reads two of them
-          vals[threadIdx.x] = c0;
-          vals[threadIdx.x + kThreads] = c1;
-        }
-        first = resolve(r2, step, c0 > r, c1 > r, masks, round);
-        if (step == 1 || r2.lo >= r2.hi) break;
+      if (!kLazy) {
+        // ---- level 2, first round: probes, the partition's offset and its last entry together
+        const float *cp = cdf + base;
+        Range r2{0, valid - 1, 0};
         probe_positions(r2, q0, q1, step);
-        c0 = __ldg(cp + q0);
-        c1 = __ldg(cp + q1);
-      }
-      const int64_t j = r2.hi;
-      flat = base + j;
-
-      // ---- variates within one ulp of a boundary of the chosen entry
-      if (P.status && threadIdx.x == 0) {
-        // After a round with step 1, slot `first` held cdf[j] and slot `first-1` held cdf[j-1].
-        float hi_v, lo_v = 0.f;
-        if (step == 1) {
-          hi_v = vals[first];
-          if (first > 0) lo_v = vals[first - 1];
-          else if (j > 0) lo_v = __ldg(cp + j - 1);
-        } else {
-          hi_v = __ldg(cp + j);
-          if (j > 0) lo_v = __ldg(cp + j - 1);
+        float c0 = __ldg(cp + q0), c1 = __ldg(cp + q1);
+        const double off = __ldg(l1 + p);
+        const float last = __ldg(cp + valid - 1);
+        float r = __double2float_rn(__dsub_rn(v, off));
+        if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
+        int first;
+        for (;;) {
+          if (step == 1) {  // keep the last round's entries: the boundary check below reads two of them
+            vals[threadIdx.x] = c0;
+            vals[threadIdx.x + kThreads] = c1;
+          }
+          first = resolve(r2, step, c0 > r, c1 > r, masks, round);
+          if (step == 1 || r2.lo >= r2.hi) break;
+          probe_positions(r2, q0, q1, step);
+          c0 = __ldg(cp + q0);
+          c1 = __ldg(cp + q1);
         }
-        const bool near = (__uint_as_float(__float_as_uint(r) + 1u) >= hi_v) || (j > 0 && r == lo_v);
-        if (near) atomicAdd(P.status + 1, 1);
+        const int64_t j = r2.hi;
+        flat = base + j;
+
+        // ---- variates within one ulp of a boundary of the chosen entry
+        if (P.status && threadIdx.x == 0) {
+          // After a round with step 1, slot `first` held cdf[j] and slot `first-1` held cdf[j-1].
+          float hi_v, lo_v = 0.f;
+          if (step == 1) {
+            hi_v = vals[first];
+            if (first > 0) lo_v = vals[first - 1];
+            else if (j > 0) lo_v = __ldg(cp + j - 1);
+          } else {
+            hi_v = __ldg(cp + j);
+            if (j > 0) lo_v = __ldg(cp + j - 1);
+          }
+          const bool near = (__uint_as_float(__float_as_uint(r) + 1u) >= hi_v) || (j > 0 && r == lo_v);
+          if (near) atomicAdd(P.status + 1, 1);
+        }
+      } else {
+        // ---- level 2 rebuilt from the priorities
+        float *pv = reinterpret_cast<float *>(stage);
+        float4 *pv4 = reinterpret_cast<float4 *>(stage);
+        float *xs = pv + GEARB_PART + warp * 128;
+        const float *src = a.prio + base;
+        if (valid == GEARB_PART) {
+          if (threadIdx.x == 0) {
+            mbar_arrive_expect_tx(&stage_bar, GEARB_PART * 4);
+            bulk_load(pv, src, GEARB_PART * 4, &stage_bar);
+          }
+        } else {  // the ragged last partition: by hand, zeros past the end
+          for (int e = threadIdx.x; e < GEARB_PART; e += kThreads) pv[e] = e < valid ? __ldg(src + e) : 0.f;
+          __syncthreads();
+          if (threadIdx.x == 0) mbar_arrive(&stage_bar);
+        }
+        const double off = __ldg(l1 + p);
+        unsigned polls = 0;
+        bool ok;
+        while (!(ok = mbar_try_wait(&stage_bar, stage_parity)))
+          if (++polls > kWaitLimit) break;
+        stage_parity ^= 1u;
+        if (__syncthreads_or(!ok)) {
+          if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
+          break;
+        }
+        bool bad = false;  // the scan has already reported negative or NaN priorities
+        float sv[4][4], top[4];
+        float4 x[4];
+        // first pass: block totals (warp w: blocks w and w + 4)
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          const int blk = warp + h * kWarps;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) x[k] = pv4[(blk * 4 + k) * 32 + lane];
+          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bad);
+          if (lane == 0) blk_total[blk] = gq.total;
+        }
+        __syncthreads();
+        // second pass: values, written back over the priorities; block maxima
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          const int blk = warp + h * kWarps;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) x[k] = pv4[(blk * 4 + k) * 32 + lane];
+          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bad);
+          float X = 0.f;
+          for (int w = 0; w < blk; ++w) X = __fadd_rn(X, blk_total[w]);
+          tree::block_values(X, gq, xs, lane, sv, top, false, base + blk * tree::kBlockValues, a.n);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            pv4[(blk * 4 + k) * 32 + lane] = make_float4(sv[k][0], sv[k][1], sv[k][2], sv[k][3]);
+          const float m = tree::block_max(top);
+          if (lane == 0) blk_max[blk] = m;
+        }
+        __syncthreads();
+        float last = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) last = fmaxf(last, blk_max[w]);
+        float r = __double2float_rn(__dsub_rn(v, off));
+        if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
+        // The stored table would be the running maximum of these values; its first entry above r
+        // is the first VALUE above r, because the maximum passes r exactly where a value does.
+        int best = GEARB_PART;
+#pragma unroll 8
+        for (int i = GEARB_PART / kThreads - 1; i >= 0; --i) {
+          const int e = i * kThreads + threadIdx.x;
+          if (pv[e] > r) best = e;
+        }
+        best = __reduce_min_sync(kFull, best);
+        if (lane == 0) warp_best[warp] = best;
+        __syncthreads();
+        int j = warp_best[0];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) j = min(j, warp_best[w]);
+        if (j >= valid) j = static_cast<int>(valid) - 1;  // cannot happen while r < last; keeps the index in range
+        flat = base + j;
+        if (P.status) {
+          // ---- variates within one ulp of a boundary of the chosen entry: the entry itself is
+          // value j (it exceeds everything before it); its predecessor is the largest value before j
+          float lo = 0.f;
+#pragma unroll 8
+          for (int i = 0; i < GEARB_PART / kThreads; ++i) {
+            const int e = i * kThreads + threadIdx.x;
+            if (e < j) lo = fmaxf(lo, pv[e]);
+          }
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) lo = fmaxf(lo, __shfl_xor_sync(kFull, lo, d));
+          if (lane == 0) warp_lo[warp] = lo;
+          __syncthreads();
+          if (threadIdx.x == 0) {
+            float lo_v = 0.f;
+            for (int w = 0; w < kWarps; ++w) lo_v = fmaxf(lo_v, warp_lo[w]);
+            const float hi_v = pv[j];
+            const bool near = (__uint_as_float(__float_as_uint(r) + 1u) >= hi_v) || (j > 0 && r == lo_v);
+            if (near) atomicAdd(P.status + 1, 1);
+          }
+        }
+        __syncthreads();  // the partition's values are dead: the gather may reuse the area
       }
     }
 
@@ -415,27 +527,38 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(kThreads);
   constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kRingSlots * kRingSlotBytes;
+  using Kernel = void (*)(const GatherParams, const SampleArgs, const PeerArgs);
+  // [peers][lazy][path]; a sharded table read in place always has its stored level-2 tables
+  static const Kernel table[2][2][3] = {
+      {{sample_gather_kernel<false, kStaged, false>, sample_gather_kernel<false, kRing, false>,
+        sample_gather_kernel<false, kDirect, false>},
+       {sample_gather_kernel<false, kStaged, true>, sample_gather_kernel<false, kRing, true>,
+        sample_gather_kernel<false, kDirect, true>}},
+      {{sample_gather_kernel<true, kStaged, false>, sample_gather_kernel<true, kRing, false>,
+        sample_gather_kernel<true, kDirect, false>},
+       {nullptr, nullptr, nullptr}}};
   static bool attr_set = false;
   if (!attr_set) {
-    GEARB_CUDA(cudaFuncSetAttribute(sample_gather_kernel<false, kRing>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRingBytes)));
-    GEARB_CUDA(cudaFuncSetAttribute(sample_gather_kernel<true, kRing>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRingBytes)));
+    for (int pe = 0; pe < 2; ++pe)
+      for (int lz = 0; lz < 2; ++lz)
+        if (table[pe][lz][kRing])
+          GEARB_CUDA(cudaFuncSetAttribute(table[pe][lz][kRing], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(kRingBytes)));
     attr_set = true;
   }
   const int path = p.stage_bytes > 0 ? kStaged : (p.ring ? kRing : kDirect);
-  cfg.dynamicSmemBytes = path == kStaged ? static_cast<size_t>(p.stage_bytes) : (path == kRing ? kRingBytes : 0);
+  const bool lazy = a.cdf == nullptr;
+  GEARB_REQUIRE(!(lazy && peers.world > 0), "pull: the shards need their stored level-2 tables");
+  size_t smem = path == kStaged ? static_cast<size_t>(p.stage_bytes) : (path == kRing ? kRingBytes : 0);
+  if (lazy && smem < static_cast<size_t>(kLazyBytes)) smem = kLazyBytes;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  using Kernel = void (*)(const GatherParams, const SampleArgs, const PeerArgs);
-  static const Kernel table[2][3] = {
-      {sample_gather_kernel<false, kStaged>, sample_gather_kernel<false, kRing>, sample_gather_kernel<false, kDirect>},
-      {sample_gather_kernel<true, kStaged>, sample_gather_kernel<true, kRing>, sample_gather_kernel<true, kDirect>}};
-  GEARB_CUDA(cudaLaunchKernelEx(&cfg, table[peers.world > 0][path], p, a, peers));
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, table[peers.world > 0][lazy][path], p, a, peers));
   return GEARB_OK;
 }
 }  // namespace
@@ -443,12 +566,14 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
-                         cudaStream_t stream, double mul, double sub) {
+                         cudaStream_t stream, double mul, double sub, const float *lazy_prio) {
   GEARB_REQUIRE(n > 0, "sample_gather: the priority table is empty");
   if (p.n == 0) return GEARB_OK;
-  GEARB_REQUIRE(cdf && l1 && u, "sample_gather: null pointer argument");
+  GEARB_REQUIRE((cdf || lazy_prio) && l1 && u, "sample_gather: null pointer argument");
+  GEARB_REQUIRE(!lazy_prio || (reinterpret_cast<uintptr_t>(lazy_prio) & 15) == 0,
+                "sample_gather: the priorities must be 16-byte aligned");
   SampleArgs a;
-  a.cdf = cdf; a.l1 = l1; a.u = u; a.lengths = lengths;
+  a.cdf = lazy_prio ? nullptr : cdf; a.prio = lazy_prio; a.l1 = l1; a.u = u; a.lengths = lengths;
   a.out_flat = out_flat; a.out_idx = out_idx; a.out_ts = out_ts; a.out_len = out_len;
   a.n = n; a.nparts = (n + GEARB_PART - 1) / GEARB_PART;
   a.index_offset = index_offset;
@@ -477,7 +602,7 @@ int launch_pull(const GatherParams &p, int world, int self, const double *totals
     peers.table[j] = static_cast<const uint8_t *>(peer_table[j]);
   }
   SampleArgs a = {};
-  a.cdf = peers.cdf[0]; a.l1 = peers.l1[0]; a.u = u;
+  a.cdf = peers.cdf[0]; a.prio = nullptr; a.l1 = peers.l1[0]; a.u = u;
   a.out_flat = out_flat; a.out_idx = out_idx; a.out_ts = out_ts;
   a.n = n; a.nparts = (n + GEARB_PART - 1) / GEARB_PART;
   a.mul = 1.0;

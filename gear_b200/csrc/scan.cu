@@ -43,6 +43,7 @@
 #include <mutex>
 
 #include "common.h"
+#include "scan_tree.cuh"
 
 namespace gearb {
 namespace {
@@ -137,23 +138,6 @@ __device__ __forceinline__ unsigned ld_u32_relaxed(const unsigned *p) {
   return v;
 }
 
-__device__ __forceinline__ float hs_sum(float v, int lane) {
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const float t = __shfl_up_sync(kFull, v, d);
-    if (lane >= d) v = __fadd_rn(t, v);
-  }
-  return v;
-}
-__device__ __forceinline__ float hs_max(float v, int lane) {
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const float t = __shfl_up_sync(kFull, v, d);
-    if (lane >= d) v = fmaxf(t, v);
-  }
-  return v;
-}
-
 // s = a + b in float64; raises `inexact` when the addition rounded.
 __device__ __forceinline__ double checked_add(double a, double b, bool &inexact) {
   const double s = __dadd_rn(a, b);
@@ -199,6 +183,7 @@ struct __align__(128) Smem {
   int stage_part[kStages];         // partition staged in the slot, -1 = no more work
   float wt[2][kComputeWarps];      // warp totals, double-buffered by iteration parity
   float wm[2][kComputeWarps];      // warp maxima
+  alignas(16) float xs[kComputeWarps][128];    // per-warp exchange area: one float per chunk of the warp's block
   volatile int ring_part[kRing];   // aggregate ring: partition id (-1 = end)
   volatile float ring_agg[kRing];
   volatile unsigned ring_head;     // entries produced
@@ -266,9 +251,29 @@ __device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
   }
 }
 
+// One partition's aggregate from the compute warps to the look-back warp.
+__device__ __forceinline__ void hand_over(Smem &sm, int part, float agg) {
+  const unsigned h = sm.ring_head;
+  unsigned sp = 0;
+  while (h - sm.ring_tail >= kRing) {
+    if (++sp > kSpinLimit || sm.abort) break;
+  }
+  sm.ring_part[h % kRing] = part;
+  sm.ring_agg[h % kRing] = agg;
+  __threadfence_block();
+  sm.ring_head = h + 1;
+}
+
 // ----------------------------------------------------------------- compute warps
+// Warp w scans block w (512 values) of the staged partition.  Lane l holds chunk 32k + l of
+// the block for k = 0..3 (the float4 it can fetch without a bank conflict); the step from
+// "one chunk per lane and tile" to "four consecutive chunks per lane" -- which makes one
+// shuffle scan per block enough -- goes through a 512-byte exchange area in shared memory.
+// kStore = false: only the partition's last (largest) entry is produced, nothing is stored.
+template <bool kStore>
 __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
   bool bad = false;
+  float *xs = sm.xs[warp];
   for (unsigned it = 0;; ++it) {
     const unsigned s = it % kStages;
     const unsigned parity = (it / kStages) & 1u;
@@ -293,96 +298,58 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
     if (lane == 0 && !leave) mbar_arrive(&sm.empty[s]);
 
     const int64_t base = static_cast<int64_t>(part) * kPart;
-    const bool full = base + kPart <= a.n;
+    const int64_t e0 = base + warp * tree::kBlockValues;  // this warp's block
     const int buf = it & 1;
-    float sv[kTilesPerWarp][4], E[kTilesPerWarp], c[kTilesPerWarp + 1];
+    float sv[kTilesPerWarp][4], top[kTilesPerWarp];
 
-    // ---- lane sums, tile scans, warp carry
-    c[0] = 0.f;
-#pragma unroll
-    for (int k = 0; k < kTilesPerWarp; ++k) {
-      bad |= !(x[k].x >= 0.f) | !(x[k].y >= 0.f) | !(x[k].z >= 0.f) | !(x[k].w >= 0.f);
-      sv[k][0] = x[k].x;
-      sv[k][1] = __fadd_rn(sv[k][0], x[k].y);
-      sv[k][2] = __fadd_rn(sv[k][1], x[k].z);
-      sv[k][3] = __fadd_rn(sv[k][2], x[k].w);
-      const float I = hs_sum(sv[k][3], lane);
-      const float up = __shfl_up_sync(kFull, I, 1);
-      E[k] = lane == 0 ? 0.f : up;
-      c[k + 1] = __fadd_rn(c[k], __shfl_sync(kFull, I, 31));
-    }
-    if (lane == 0) sm.wt[buf][warp] = c[kTilesPerWarp];
+    // ---- first pass: sums inside the block; block totals meet in shared memory
+    const tree::Group g = tree::block_sums(x, xs, lane, sv, bad);
+    if (lane == 0) sm.wt[buf][warp] = g.total;
     if (named_barrier_compute_or(leave)) break;
 
-    // ---- scan of the warp totals (every warp repeats it; lanes >= 8 hold zeros)
-    float y = lane < kComputeWarps ? sm.wt[buf][lane] : 0.f;
-#pragma unroll
-    for (int d = 1; d < kComputeWarps; d <<= 1) {  // Hillis-Steele over the 8 warp totals
-      const float t = __shfl_up_sync(kFull, y, d);
-      if (lane >= d) y = __fadd_rn(t, y);
-    }
-    const float xs = __shfl_sync(kFull, y, warp == 0 ? 0 : warp - 1);
-    const float X = warp == 0 ? 0.f : xs;
+    // ---- offset of this warp's block: the totals of the blocks before it, in sequence
+    float X = 0.f;
+    for (int w = 0; w < warp; ++w) X = __fadd_rn(X, sm.wt[buf][w]);
 
-    // ---- values, then the running maximum inside the warp
-    float run = 0.f, pre[kTilesPerWarp];
-#pragma unroll
-    for (int k = 0; k < kTilesPerWarp; ++k) {
-      const float b1 = __fadd_rn(X, c[k]);
-      const float b2 = __fadd_rn(b1, E[k]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) sv[k][j] = __fadd_rn(b2, sv[k][j]);
-      float lane_top = sv[k][3];
-      if (!full) {
-        // Entries past n take no part in the maximum (their value is never stored).
-        const int64_t e = base + ((warp * kTilesPerWarp + k) * 32 + lane) * 4;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (e + j >= a.n) sv[k][j] = 0.f;
-        lane_top = fmaxf(fmaxf(sv[k][0], sv[k][1]), fmaxf(sv[k][2], sv[k][3]));
+    // ---- second pass: values (kStore) or only each chunk's largest one
+    tree::block_values(X, g, xs, lane, sv, top, !kStore, e0, a.n);
+
+    if (!kStore) {
+      // ---- the partition's largest entry is all that is needed
+      const float m = tree::block_max(top);
+      if (lane == 0) sm.wm[buf][warp] = m;
+      named_barrier_compute();
+      if (warp == kComputeWarps - 1 && lane == 0) {
+        float G = 0.f;
+        for (int w = 0; w < kComputeWarps; ++w) G = fmaxf(G, sm.wm[buf][w]);
+        hand_over(sm, part, G);
       }
-      const float M = hs_max(lane_top, lane);
-      const float up = __shfl_up_sync(kFull, M, 1);
-      pre[k] = fmaxf(run, lane == 0 ? 0.f : up);
-      run = fmaxf(run, __shfl_sync(kFull, M, 31));
+      continue;
     }
+
+    // ---- running maximum, block by block
+    const float run = tree::block_prefix_max(top, xs, lane);
     if (lane == 0) sm.wm[buf][warp] = run;
     named_barrier_compute();
-
     float G = 0.f;
     for (int w = 0; w < warp; ++w) G = fmaxf(G, sm.wm[buf][w]);
-
-    // ---- the last warp knows the partition's last (= largest) entry: hand it over
-    if (warp == kComputeWarps - 1 && lane == 0) {
-      const unsigned h = sm.ring_head;
-      unsigned sp = 0;
-      while (h - sm.ring_tail >= kRing) {
-        if (++sp > kSpinLimit || sm.abort) break;
-      }
-      sm.ring_part[h % kRing] = part;
-      sm.ring_agg[h % kRing] = fmaxf(G, run);
-      __threadfence_block();
-      sm.ring_head = h + 1;
-    }
+    // the last warp knows the partition's last (= largest) entry
+    if (warp == kComputeWarps - 1 && lane == 0) hand_over(sm, part, fmaxf(G, run));
 
     // ---- store
-    if (full) {
-      float4 *dst = reinterpret_cast<float4 *>(a.cdf + base);
+    if (e0 + tree::kBlockValues <= a.n) {
+      float4 *dst = reinterpret_cast<float4 *>(a.cdf + e0);
 #pragma unroll
       for (int k = 0; k < kTilesPerWarp; ++k) {
-        const float m = fmaxf(pre[k], G);
-        float4 o;
-        o.x = fmaxf(sv[k][0], m);
-        o.y = fmaxf(sv[k][1], m);
-        o.z = fmaxf(sv[k][2], m);
-        o.w = fmaxf(sv[k][3], m);
-        __stcs(dst + (warp * kTilesPerWarp + k) * 32 + lane, o);
+        const float m = fmaxf(G, xs[k * 32 + lane]);
+        __stcs(dst + k * 32 + lane,
+               make_float4(fmaxf(sv[k][0], m), fmaxf(sv[k][1], m), fmaxf(sv[k][2], m), fmaxf(sv[k][3], m)));
       }
     } else {
 #pragma unroll
       for (int k = 0; k < kTilesPerWarp; ++k) {
-        const float m = fmaxf(pre[k], G);
-        const int64_t e = base + ((warp * kTilesPerWarp + k) * 32 + lane) * 4;
+        const float m = fmaxf(G, xs[k * 32 + lane]);
+        const int64_t e = e0 + (k * 32 + lane) * 4;
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           if (e + j < a.n) a.cdf[e + j] = fmaxf(sv[k][j], m);
@@ -557,44 +524,8 @@ __device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int l
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
-  extern __shared__ unsigned char smem_raw[];
-  Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const unsigned epoch = ld_u32_relaxed(&a.hdr->epoch);
-  // A kernel launched behind this one with programmatic stream serialisation may be scheduled
-  // as this grid drains; it still waits (griddepcontrol.wait) for this grid to complete.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-
-  if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&sm.full[s], 1);
-      mbar_init(&sm.empty[s], kComputeWarps);
-    }
-    sm.ring_head = 0;
-    sm.ring_tail = 0;
-    sm.abort = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  __syncthreads();
-
-  if (warp < kComputeWarps) compute_warps(sm, a, warp, lane);
-  else if (warp == kComputeWarps) loader_warp(sm, a, lane);
-  else lookback_warp(sm, a, epoch, lane);
-
-  __syncthreads();
-  // Bulk copies still in flight into this CTA's shared memory (only after an abort) must land
-  // before the CTA retires.
-  if (sm.abort && tid == 0) {
-    for (int s = 0; s < kStages; ++s)
-      for (unsigned par = 0; par < 2; ++par) {
-        unsigned spins = 0;
-        while (!mbar_try_wait(&sm.full[s], par) && ++spins < 4096u) {}
-      }
-  }
-
-  // ---- last CTA out: rebuild level 1 in order if asked, then re-arm the header
+// Last CTA out: rebuild level 1 in order if asked, then re-arm the header for the next launch.
+__device__ void finish_launch(const ScanArgs &a, unsigned epoch, int tid) {
   if (tid == 0) {
     __threadfence();
     const unsigned d = atomicAdd(&a.hdr->done, 1u);
@@ -621,6 +552,47 @@ __global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
   }
 }
 
+template <bool kStore>
+__global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned epoch = ld_u32_relaxed(&a.hdr->epoch);
+  // A kernel launched behind this one with programmatic stream serialisation may be scheduled
+  // as this grid drains; it still waits (griddepcontrol.wait) for this grid to complete.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], kComputeWarps);
+    }
+    sm.ring_head = 0;
+    sm.ring_tail = 0;
+    sm.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp < kComputeWarps) compute_warps<kStore>(sm, a, warp, lane);
+  else if (warp == kComputeWarps) loader_warp(sm, a, lane);
+  else lookback_warp(sm, a, epoch, lane);
+
+  __syncthreads();
+  // Bulk copies still in flight into this CTA's shared memory (only after an abort) must land
+  // before the CTA retires.
+  if (sm.abort && tid == 0) {
+    for (int s = 0; s < kStages; ++s)
+      for (unsigned par = 0; par < 2; ++par) {
+        unsigned spins = 0;
+        while (!mbar_try_wait(&sm.full[s], par) && ++spins < 4096u) {}
+      }
+  }
+
+  finish_launch(a, epoch, tid);
+}
+
 inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 
 }  // namespace
@@ -637,7 +609,7 @@ int64_t scan_scratch_bytes(int64_t n) {
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, int64_t layout_n) {
   GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
-  GEARB_REQUIRE(prio && cdf && l1 && scratch && status, "scan: null pointer argument");
+  GEARB_REQUIRE(prio && l1 && scratch && status, "scan: null pointer argument");  // cdf may be null
   GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
                     (reinterpret_cast<uintptr_t>(cdf) & 15) == 0,
                 "scan: priorities and cdf must be 16-byte aligned");
@@ -664,20 +636,9 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
     GEARB_CUDA(cudaMemsetAsync(sc, 0, static_cast<size_t>(scan_scratch_bytes(layout_n)), stream));
   }
 
-  const size_t smem_bytes = sizeof(Smem) + 128;
-  static int ctas_per_sm = 0;
-  if (ctas_per_sm == 0) {
-    GEARB_CUDA(cudaFuncSetAttribute(scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem_bytes)));
-    int v = 0;
-    GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, scan_kernel, kThreads, smem_bytes));
-    ctas_per_sm = v > 0 ? v : 1;
-  }
-  const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
-
   ScanArgs a;
   a.prio = prio;
-  a.cdf = cdf;
+  a.cdf = cdf;  // null: only level 1 and the aggregates are produced
   a.l1 = l1;
   a.hdr = reinterpret_cast<ScanHeader *>(sc);
   a.gcount = reinterpret_cast<unsigned *>(sc + sizeof(ScanHeader));
@@ -687,13 +648,27 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.status = status;
   a.n = n;
   a.nparts = static_cast<unsigned>(nparts);
+
+  const size_t smem_bytes = sizeof(Smem) + 128;
+  static int ctas_per_sm = 0;
+  if (ctas_per_sm == 0) {
+    GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(smem_bytes)));
+    GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(smem_bytes)));
+    int v = 0;
+    GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, scan_kernel<true>, kThreads, smem_bytes));
+    ctas_per_sm = v > 0 ? v : 1;
+  }
+  const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
   // Group partitions per ticket only when there is enough work to keep every CTA busy.
   a.group = nparts >= resident * kGroupMax * 2 ? kGroupMax : (nparts >= resident * 4 ? 2 : 1);
   a.ngroups = static_cast<unsigned>((nparts + a.group - 1) / a.group);
 
   int64_t grid = resident;
   if (grid > a.ngroups) grid = a.ngroups;
-  scan_kernel<<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
+  if (a.cdf) scan_kernel<true><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
+  else scan_kernel<false><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
   GEARB_CUDA(cudaGetLastError());
   return GEARB_OK;
 }

@@ -17,33 +17,17 @@
 //   rescan_kernel   one CTA per listed partition: load, scan, store cdf and the aggregate word
 //   level1_kernel   one CTA: offsets from all aggregate words; clears the list for the next call
 #include "common.h"
+#include "scan_tree.cuh"
 
 namespace gearb {
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
-constexpr int kTilesPerWarp = 4;
 constexpr int kPart = GEARB_PART;
 constexpr unsigned kFull = 0xffffffffu;
-static_assert(kWarps * kTilesPerWarp * 128 == kPart, "same partition shape as scan_kernel");
+static_assert(kWarps * tree::kBlockValues == kPart, "one warp per block of the partition");
 
-__device__ __forceinline__ float hs_sum(float v, int lane) {
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const float t = __shfl_up_sync(kFull, v, d);
-    if (lane >= d) v = __fadd_rn(t, v);
-  }
-  return v;
-}
-__device__ __forceinline__ float hs_max(float v, int lane) {
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const float t = __shfl_up_sync(kFull, v, d);
-    if (lane >= d) v = fmaxf(t, v);
-  }
-  return v;
-}
 __device__ __forceinline__ double checked_add(double a, double b, bool &inexact) {
   const double s = __dadd_rn(a, b);
   const double bb = __dsub_rn(s, a);
@@ -68,90 +52,64 @@ __global__ void mark_kernel(float *prio, int64_t n, const int64_t *idx, const fl
   if (atomicExch(&dirty[p], 1u) == 0u) list[atomicAdd(count, 1u)] = p;
 }
 
-// Same tree as the compute warps of scan_kernel: 8 warps x 4 tiles of 128, Hillis-Steele per
-// tile, carry inside the warp, Hillis-Steele over the warp totals, running maximum.
+// Same tree as the compute warps of scan_kernel (scan_tree.cuh): warp w scans block w.
+// cdf == nullptr: the table is kept without its level-2 entries, only the aggregate is redone.
 __global__ void __launch_bounds__(kThreads) rescan_kernel(const float *prio, int64_t n, float *cdf,
                                                           unsigned long long *aggw, const unsigned *list,
                                                           const unsigned *count, unsigned *dirty) {
   __shared__ float wt[kWarps], wm[kWarps];
+  __shared__ __align__(16) float xs_all[kWarps][128];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  float *xs = xs_all[warp];
   const unsigned total = *count;
+  bool bad = false;  // priorities were checked when they were written (mark_kernel)
   for (unsigned li = blockIdx.x; li < total; li += gridDim.x) {
     const unsigned p = list[li];
     const int64_t base = static_cast<int64_t>(p) * kPart;
-    const bool full = base + kPart <= n;
-    float sv[kTilesPerWarp][4], E[kTilesPerWarp], c[kTilesPerWarp + 1];
-    c[0] = 0.f;
+    const int64_t e0 = base + warp * tree::kBlockValues;
+    float4 x[4];
+    float sv[4][4], top[4];
 #pragma unroll
-    for (int k = 0; k < kTilesPerWarp; ++k) {
-      const int64_t e = base + ((warp * kTilesPerWarp + k) * 32 + lane) * 4;
-      float4 x;
-      if (full) {
-        x = *reinterpret_cast<const float4 *>(prio + e);
+    for (int k = 0; k < 4; ++k) {
+      const int64_t e = e0 + (k * 32 + lane) * 4;
+      if (e + 4 <= n) {
+        x[k] = *reinterpret_cast<const float4 *>(prio + e);
       } else {
-        x.x = (e + 0 < n) ? prio[e + 0] : 0.f;
-        x.y = (e + 1 < n) ? prio[e + 1] : 0.f;
-        x.z = (e + 2 < n) ? prio[e + 2] : 0.f;
-        x.w = (e + 3 < n) ? prio[e + 3] : 0.f;
+        x[k].x = (e + 0 < n) ? prio[e + 0] : 0.f;
+        x[k].y = (e + 1 < n) ? prio[e + 1] : 0.f;
+        x[k].z = (e + 2 < n) ? prio[e + 2] : 0.f;
+        x[k].w = (e + 3 < n) ? prio[e + 3] : 0.f;
       }
-      sv[k][0] = x.x;
-      sv[k][1] = __fadd_rn(sv[k][0], x.y);
-      sv[k][2] = __fadd_rn(sv[k][1], x.z);
-      sv[k][3] = __fadd_rn(sv[k][2], x.w);
-      const float I = hs_sum(sv[k][3], lane);
-      const float up = __shfl_up_sync(kFull, I, 1);
-      E[k] = lane == 0 ? 0.f : up;
-      c[k + 1] = __fadd_rn(c[k], __shfl_sync(kFull, I, 31));
     }
-    if (lane == 0) wt[warp] = c[kTilesPerWarp];
+    const tree::Group g = tree::block_sums(x, xs, lane, sv, bad);
+    if (lane == 0) wt[warp] = g.total;
     __syncthreads();
-    float y = lane < kWarps ? wt[lane] : 0.f;
+    float X = 0.f;
+    for (int w = 0; w < warp; ++w) X = __fadd_rn(X, wt[w]);
+    tree::block_values(X, g, xs, lane, sv, top, cdf == nullptr, e0, n);
+    float G = 0.f, run;
+    if (cdf == nullptr) {
+      run = tree::block_max(top);
+      if (lane == 0) wm[warp] = run;
+      __syncthreads();
+      for (int w = 0; w < warp; ++w) G = fmaxf(G, wm[w]);
+    } else {
+      run = tree::block_prefix_max(top, xs, lane);
+      if (lane == 0) wm[warp] = run;
+      __syncthreads();
+      for (int w = 0; w < warp; ++w) G = fmaxf(G, wm[w]);
 #pragma unroll
-    for (int d = 1; d < kWarps; d <<= 1) {
-      const float t = __shfl_up_sync(kFull, y, d);
-      if (lane >= d) y = __fadd_rn(t, y);
-    }
-    const float xs = __shfl_sync(kFull, y, warp == 0 ? 0 : warp - 1);
-    const float X = warp == 0 ? 0.f : xs;
-    float run = 0.f, pre[kTilesPerWarp];
+      for (int k = 0; k < 4; ++k) {
+        const float m = fmaxf(G, xs[k * 32 + lane]);
+        const int64_t e = e0 + (k * 32 + lane) * 4;
+        if (e + 4 <= n) {
+          *reinterpret_cast<float4 *>(cdf + e) =
+              make_float4(fmaxf(sv[k][0], m), fmaxf(sv[k][1], m), fmaxf(sv[k][2], m), fmaxf(sv[k][3], m));
+        } else {
 #pragma unroll
-    for (int k = 0; k < kTilesPerWarp; ++k) {
-      const float b1 = __fadd_rn(X, c[k]);
-      const float b2 = __fadd_rn(b1, E[k]);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) sv[k][j] = __fadd_rn(b2, sv[k][j]);
-      float lane_top = sv[k][3];
-      if (!full) {
-        const int64_t e = base + ((warp * kTilesPerWarp + k) * 32 + lane) * 4;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (e + j >= n) sv[k][j] = 0.f;
-        lane_top = fmaxf(fmaxf(sv[k][0], sv[k][1]), fmaxf(sv[k][2], sv[k][3]));
-      }
-      const float M = hs_max(lane_top, lane);
-      const float up = __shfl_up_sync(kFull, M, 1);
-      pre[k] = fmaxf(run, lane == 0 ? 0.f : up);
-      run = fmaxf(run, __shfl_sync(kFull, M, 31));
-    }
-    if (lane == 0) wm[warp] = run;
-    __syncthreads();
-    float G = 0.f;
-    for (int w = 0; w < warp; ++w) G = fmaxf(G, wm[w]);
-#pragma unroll
-    for (int k = 0; k < kTilesPerWarp; ++k) {
-      const float m = fmaxf(pre[k], G);
-      const int64_t e = base + ((warp * kTilesPerWarp + k) * 32 + lane) * 4;
-      if (full) {
-        float4 o;
-        o.x = fmaxf(sv[k][0], m);
-        o.y = fmaxf(sv[k][1], m);
-        o.z = fmaxf(sv[k][2], m);
-        o.w = fmaxf(sv[k][3], m);
-        *reinterpret_cast<float4 *>(cdf + e) = o;
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (e + j < n) cdf[e + j] = fmaxf(sv[k][j], m);
+          for (int j = 0; j < 4; ++j)
+            if (e + j < n) cdf[e + j] = fmaxf(sv[k][j], m);
+        }
       }
     }
     if (tid == kThreads - 1) {
@@ -232,7 +190,7 @@ int launch_update(float *prio, int64_t n, float *cdf, double *l1, unsigned long 
                   const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream) {
   GEARB_REQUIRE(n > 0 && m >= 0, "update: bad sizes");
   if (m == 0) return GEARB_OK;
-  GEARB_REQUIRE(prio && cdf && l1 && aggw && upd && idx && val && status, "update: null pointer argument");
+  GEARB_REQUIRE(prio && l1 && aggw && upd && idx && val && status, "update: null pointer argument");  // cdf may be null
   const int64_t nparts = (n + kPart - 1) / kPart;
   const int64_t seg = (nparts * 4 + 255) & ~int64_t(255);
   unsigned *dirty = reinterpret_cast<unsigned *>(upd);

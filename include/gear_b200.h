@@ -208,6 +208,14 @@ int gearb_decode(const int64_t *flat, int64_t b, int64_t trajectory_length,
 int gearb_sampler_create(int64_t n, gearb_sampler **out);
 int gearb_sampler_destroy(gearb_sampler *s);
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
+/* The same scan without storing the level-2 table: only the partition offsets (l1) and the
+ * total are produced, so the scan reads 4 bytes per priority and writes next to nothing.
+ * gearb_sampler_sample_gather then rebuilds the one partition each request falls into from
+ * `priorities` (16 KiB per request, the scan's own addition tree), with the same result bit
+ * for bit.  `priorities` must stay unchanged (except through gearb_sampler_update) until the
+ * last such call.  gearb_sampler_search and gearb_sampler_pull need the stored table and
+ * return GEARB_ERR_STATE until the next gearb_sampler_scan.                                */
+int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream);
 /* Incremental update after a gearb_sampler_scan of the same array: priorities[idx[i]] =
  * values[i] for i < m (idx, values: device arrays), then only the partitions that were touched
  * are rescanned and the partition offsets rebuilt.  The table afterwards is bit-identical to a

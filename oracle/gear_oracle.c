@@ -27,9 +27,8 @@
 #include <string.h>
 
 #define GEARO_PART 4096  /* priorities per partition (level-2 scan unit)   */
-#define GEARO_TILE 128   /* elements one warp covers with one float4 load */
-#define GEARO_WARPS 8    /* warps per partition                            */
-#define GEARO_TILES_PER_WARP 4
+#define GEARO_BLOCK 512  /* values per block of 32 groups of 16             */
+#define GEARO_BLOCKS 8   /* blocks per partition                            */
 
 /* ------------------------------------------------------------------------- */
 /* Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1,2,3",
@@ -172,19 +171,20 @@ void gearo_fused_subcopy(const uint8_t *table, uint8_t *dst, const int64_t *idx,
  * inclusive float32 scan with this fixed addition tree (the shape sketched by
  * the reference's unfinished kernel: four values per thread added in sequence,
  * src/cuda/one_dim_prefix_sum.cu:40-49; Hillis-Steele shuffle scan over the 32
- * lanes of a warp, :23-28; a second scan over the warp totals, :192-201):
+ * lanes of a warp, :23-28; a second pass over the warp totals, :192-201):
  *
- *   tile  = 128 consecutive values; lane l owns 4l..4l+3:
- *           s0=x0, s1=s0+x1, s2=s1+x2, s3=s2+x3
- *           I  = Hillis-Steele inclusive scan of s3 over lanes (d=1,2,4,8,16)
- *           E  = I of lane l-1 (0 for lane 0); tile total = I of lane 31
- *   warp  = 4 consecutive tiles; carry c0=0, c(k+1)=c(k)+tile_total(k)
- *   block = 8 warps; Y = Hillis-Steele inclusive scan of the warp totals c4
- *           (d=1,2,4); X(w) = Y(w-1), X(0)=0
- *   value = ((X(w) + c(k)) + E) + s_j
+ *   chunk = 4 consecutive values: s0=x0, s1=s0+x1, s2=s1+x2, s3=s2+x3; T=s3
+ *   group = 4 consecutive chunks: g0=T0, g1=g0+T1, g2=g1+T2, g3=g2+T3
+ *   block = 32 consecutive groups (512 values):
+ *           I = Hillis-Steele inclusive scan of g3 over the groups (d=1,2,4,8,16)
+ *           E = I of group q-1 (0 for q=0); block total = I of group 31
+ *   part  = 8 consecutive blocks: X(0)=0, X(w+1) = X(w) + total(w)
+ *   chunk offset O = X(w) + E(q) for the group's first chunk, (X(w) + E(q)) + g(i-1)
+ *           for its chunk i = 1..3
+ *   value = O + s_j
  *
  * followed by a running maximum over the partition, which removes the one-ulp
- * inversions a tree-shaped float scan can leave between lanes, so that the
+ * inversions a tree-shaped float scan can leave between chunks, so that the
  * stored table is non-decreasing and "first entry greater than r" is well
  * defined for any search order.  Entries past n count as zero.
  *
@@ -204,52 +204,43 @@ static void hs_scan32(float v[32]) {
 
 static void scan_partition(const float *x, int64_t valid, float *out) {
   /* x: up to GEARO_PART inputs (valid of them real), out: GEARO_PART values */
-  float s[GEARO_PART];           /* per-lane running sums s0..s3             */
-  float E[GEARO_PART / 4];       /* lane exclusive offset within its tile    */
-  float c[GEARO_WARPS][GEARO_TILES_PER_WARP + 1];
-  for (int w = 0; w < GEARO_WARPS; ++w) {
-    c[w][0] = 0.0f;
-    for (int k = 0; k < GEARO_TILES_PER_WARP; ++k) {
-      const int t = w * GEARO_TILES_PER_WARP + k;
-      float I[32];
-      for (int l = 0; l < 32; ++l) {
-        const int e = t * GEARO_TILE + 4 * l;
-        float a0 = (e + 0 < valid) ? x[e + 0] : 0.0f;
-        float a1 = (e + 1 < valid) ? x[e + 1] : 0.0f;
-        float a2 = (e + 2 < valid) ? x[e + 2] : 0.0f;
-        float a3 = (e + 3 < valid) ? x[e + 3] : 0.0f;
-        float s0 = a0;
-        float s1 = s0 + a1;
-        float s2 = s1 + a2;
-        float s3 = s2 + a3;
-        s[e + 0] = s0; s[e + 1] = s1; s[e + 2] = s2; s[e + 3] = s3;
-        I[l] = s3;
-      }
-      hs_scan32(I);
-      for (int l = 0; l < 32; ++l) E[t * 32 + l] = (l == 0) ? 0.0f : I[l - 1];
-      c[w][k + 1] = c[w][k] + I[31];
-    }
-  }
-  float Y[GEARO_WARPS];
-  for (int w = 0; w < GEARO_WARPS; ++w) Y[w] = c[w][GEARO_TILES_PER_WARP];
-  for (int d = 1; d < GEARO_WARPS; d <<= 1) {
-    float nv[GEARO_WARPS];
-    for (int w = 0; w < GEARO_WARPS; ++w) nv[w] = (w >= d) ? (Y[w - d] + Y[w]) : Y[w];
-    memcpy(Y, nv, sizeof(nv));
-  }
-  float run = 0.0f;
-  for (int w = 0; w < GEARO_WARPS; ++w) {
-    const float X = (w == 0) ? 0.0f : Y[w - 1];
-    for (int k = 0; k < GEARO_TILES_PER_WARP; ++k) {
-      const int t = w * GEARO_TILES_PER_WARP + k;
-      const float b1 = X + c[w][k];
-      for (int l = 0; l < 32; ++l) {
-        const float b2 = b1 + E[t * 32 + l];
+  float s[GEARO_PART];               /* running sums inside each chunk           */
+  float gprev[GEARO_PART / 4];       /* g(i-1) of every chunk (unused for i = 0) */
+  float E[GEARO_PART / 16];          /* exclusive offset of every group          */
+  float Y[GEARO_BLOCKS];
+  for (int w = 0; w < GEARO_BLOCKS; ++w) {
+    float I[32];
+    for (int q = 0; q < 32; ++q) {
+      float g = 0.0f;
+      for (int i = 0; i < 4; ++i) {
+        const int e = w * GEARO_BLOCK + 16 * q + 4 * i;
+        float acc = 0.0f;
         for (int j = 0; j < 4; ++j) {
-          const int e = t * GEARO_TILE + 4 * l + j;
-          float v = b2 + s[e];
+          const float a = (e + j < valid) ? x[e + j] : 0.0f;
+          acc = (j == 0) ? a : acc + a;
+          s[e + j] = acc;
+        }
+        gprev[e / 4] = g;
+        g = (i == 0) ? acc : g + acc;
+      }
+      I[q] = g;
+    }
+    hs_scan32(I);
+    Y[w] = I[31];
+    for (int q = 0; q < 32; ++q) E[w * 32 + q] = (q == 0) ? 0.0f : I[q - 1];
+  }
+  float run = 0.0f, X = 0.0f;
+  for (int w = 0; w < GEARO_BLOCKS; ++w) {
+    if (w > 0) X = X + Y[w - 1];
+    for (int q = 0; q < 32; ++q) {
+      const float b = X + E[w * 32 + q];
+      for (int i = 0; i < 4; ++i) {
+        const int e0 = w * GEARO_BLOCK + 16 * q + 4 * i;
+        const float off = (i == 0) ? b : b + gprev[e0 / 4];
+        for (int j = 0; j < 4; ++j) {
+          const float v = off + s[e0 + j];
           if (v > run) run = v;
-          out[e] = run;
+          out[e0 + j] = run;
         }
       }
     }

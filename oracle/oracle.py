@@ -27,8 +27,7 @@ LIB_PATH = HERE / "_build" / "libgear_oracle.so"
 
 PART = 4096
 TILE = 128
-WARPS = 8
-TILES_PER_WARP = 4
+BLOCKS = 8
 
 
 def build(force: bool = False) -> Path:
@@ -248,30 +247,36 @@ def _hs(v: np.ndarray, axis_len: int) -> np.ndarray:
 
 
 def np_scan(prio: np.ndarray):
-    """numpy restatement of the scan tree (one_dim_prefix_sum.cu:40-49,23-28,192-201)."""
+    """numpy restatement of the scan tree (one_dim_prefix_sum.cu:40-49,23-28,192-201):
+    chunks of 4 in sequence, groups of 4 chunk totals in sequence, Hillis-Steele over the 32
+    groups of a block, the 8 blocks of a partition in sequence, then a running maximum."""
     prio = np.asarray(prio, dtype=np.float32)
     n = len(prio)
     nparts = (n + PART - 1) // PART
     x = np.zeros(nparts * PART, np.float32)
     x[:n] = prio
-    x = x.reshape(nparts, WARPS, TILES_PER_WARP, 32, 4)
+    x = x.reshape(nparts, BLOCKS, 32, 4, 4)               # [P, block, group, chunk, value]
     s = np.empty_like(x)
     s[..., 0] = x[..., 0]
     for j in range(1, 4):
         s[..., j] = s[..., j - 1] + x[..., j]
-    I = _hs(s[..., 3].copy(), 32)                       # [P,W,K,32]
+    T = s[..., 3]                                          # [P,W,32,4] chunk totals
+    g = np.empty_like(T)
+    g[..., 0] = T[..., 0]
+    for i in range(1, 4):
+        g[..., i] = g[..., i - 1] + T[..., i]
+    I = _hs(g[..., 3].copy(), 32)                          # [P,W,32]
     E = np.zeros_like(I)
     E[..., 1:] = I[..., :-1]
-    tt = I[..., 31]                                      # [P,W,K]
-    c = np.zeros((nparts, WARPS, TILES_PER_WARP + 1), np.float32)
-    for k in range(TILES_PER_WARP):
-        c[..., k + 1] = c[..., k] + tt[..., k]
-    Y = _hs(c[..., TILES_PER_WARP].copy(), WARPS)        # [P,W]
-    X = np.zeros_like(Y)
-    X[:, 1:] = Y[:, :-1]
-    b1 = X[:, :, None] + c[..., :TILES_PER_WARP]         # [P,W,K]
-    b2 = b1[..., None] + E                               # [P,W,K,32]
-    o = b2[..., None] + s                                # [P,W,K,32,4]
+    X = np.zeros((nparts, BLOCKS), np.float32)             # block offsets, added in sequence
+    for w in range(1, BLOCKS):
+        X[:, w] = X[:, w - 1] + I[:, w - 1, 31]
+    b = X[:, :, None] + E                                  # [P,W,32]
+    off = np.empty_like(T)
+    off[..., 0] = b
+    for i in range(1, 4):
+        off[..., i] = b + g[..., i - 1]
+    o = off[..., None] + s                                 # [P,W,32,4,4]
     o = o.reshape(nparts, PART).astype(np.float32)
     cdf = np.maximum.accumulate(o, axis=1)
     last_idx = np.minimum(np.arange(1, nparts + 1) * PART, n) - 1

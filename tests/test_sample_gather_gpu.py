@@ -30,7 +30,8 @@ def build(O, rows, T, cap, seed):
     ([4096, 4, 4], 100, 50, 64, 16, N.PAD_HEAD, -15),           # config 5 rows, head padding
     ([3, 7, 13], 37, 300, 333, 9, N.PAD_HEAD, -4),
 ])
-def test_fused_equals_oracle_and_separate_kernels(O, rows, T, cap, B, L, pad, off):
+@pytest.mark.parametrize("store", [True, False])      # False: level 2 rebuilt per request from the priorities
+def test_fused_equals_oracle_and_separate_kernels(O, rows, T, cap, B, L, pad, off, store):
     t, img = build(O, rows, T, cap, seed=len(rows))
     h = core.StorageHandler(t)
     cols = list(range(len(rows)))
@@ -43,8 +44,12 @@ def test_fused_equals_oracle_and_separate_kernels(O, rows, T, cap, B, L, pad, of
     u01 = O.synth_u01(78, n, B)
 
     s = core.PrioritySampler(n)
-    s.scan(dev(prio))
+    dprio = dev(prio)
+    s.scan(dprio, store=store)
     dl = dev(lengths)
+    if not store:
+        with pytest.raises(core.GearError):
+            s.search(dev(u01), scale=True)
     dsts = [torch.full((B * L * r,), 0x5A, dtype=torch.uint8, device=DEV) for r in rows]
     outs = [torch.empty(B, dtype=torch.int64, device=DEV) for _ in range(4)]
     s.sample_gather(h, dev(u01), cols, dsts, scale=True, lengths=dl, index_offset=0,
@@ -64,6 +69,7 @@ def test_fused_equals_oracle_and_separate_kernels(O, rows, T, cap, B, L, pad, of
         assert np.array_equal(dsts[c].cpu().numpy(), want), c
 
     # the three-kernel route gives the same bytes
+    s.scan(dprio)
     flat = s.search(dev(u01), scale=True)
     idx, ts, ln = core.decode(flat, T, lengths=dl)
     dsts2 = [torch.full((B * L * r,), 0xA5, dtype=torch.uint8, device=DEV) for r in rows]

