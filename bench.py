@@ -45,6 +45,8 @@ C5 = dict(name="sharded_token_table_32Mstep_per_gpu", rows=[4096, 4, 4], T=1000,
 # from the one-pass ncu capture summarised in profiles/scan_kernel_100M_priorities.md (the part of the
 # 400 MB of output that is still dirty in L2 at kernel end is not in it).
 SCAN_TRAFFIC_BYTES_C3 = 741_204_736
+# The same for the totals-only instance (no level-2 table written): 400,064,768 B read + 338,688 B written.
+SCAN_TOTALS_TRAFFIC_BYTES_C3 = 400_403_456
 
 
 def peaks():
@@ -142,48 +144,58 @@ def run_ours_single(args):
     dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=dev) for r in rows]
     flat = torch.empty(B, dtype=torch.int64, device=dev)
 
-    def step(i):
-        sampler.scan(prio)
-        sampler.sample_gather(handler, u_dev[(i % nbatches) * B:(i % nbatches + 1) * B], cols, dsts,
-                              scale=True, zero_fill=True, out_flat=flat)
+    def batch(i):
+        return u_dev[(i % nbatches) * B:(i % nbatches + 1) * B]
 
-    for i in range(max(args.warmup, 3)):
-        step(i)
-    torch.cuda.synchronize()
-
-    # ---- timed region: K steps, device events; every scan also gets its own event pair
     K = args.steps
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    scan_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     clocks = ClockSampler(0)
-    clocks.start()
-    time.sleep(0.12)
-    torch.cuda.synchronize()
-    t0 = time.time()
-    ev[0].record()
-    for i in range(K):
-        scan_ev[i][0].record()
-        sampler.scan(prio)
-        scan_ev[i][1].record()
-        sampler.sample_gather(handler, u_dev[(i % nbatches) * B:(i % nbatches + 1) * B], cols, dsts,
-                              scale=True, zero_fill=True, out_flat=flat)
-    ev[1].record()
-    torch.cuda.synchronize()
-    t1 = time.time()
-    clk = clocks.stop(t0, t1)
-    ms_total = ev[0].elapsed_time(ev[1])
-    ms_step = ms_total / K
-    scan_ms = sum(a.elapsed_time(b) for a, b in scan_ev) / K
+
+    def timed_steps(store, sample_clocks):
+        """K full steps (scan + one-launch search/decode/gather); every scan gets its own event pair.
+        store=True: the scan writes the level-2 table and the sampling kernel searches it;
+        store=False: the scan keeps only the partition offsets and the sampling kernel rebuilds
+        the one partition each request falls into from the priorities."""
+        for i in range(max(args.warmup, 3)):
+            sampler.scan(prio, store=store)
+            sampler.sample_gather(handler, batch(i), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        scan_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+        if sample_clocks:
+            clocks.start()
+            time.sleep(0.12)
+        torch.cuda.synchronize()
+        t0 = time.time()
+        ev[0].record()
+        for i in range(K):
+            scan_ev[i][0].record()
+            sampler.scan(prio, store=store)
+            scan_ev[i][1].record()
+            sampler.sample_gather(handler, batch(i), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
+        ev[1].record()
+        torch.cuda.synchronize()
+        t1 = time.time()
+        clk = clocks.stop(t0, t1) if sample_clocks else None
+        return ev[0].elapsed_time(ev[1]) / K, sum(a.elapsed_time(b) for a, b in scan_ev) / K, clk
+
+    stored_ms, stored_scan_ms, _ = timed_steps(True, False)
+    ms_step, scan_ms, clk = timed_steps(False, True)          # the headline
     total_prio, status = sampler.result()
 
     gathered = B * L * sum(rows)
     value = B * L / (ms_step * 1e-3)
     peak, peak_src = peaks()
-    scan_bytes = 8 * n + 8 * ((n + 4095) // 4096)
+    nparts = (n + 4095) // 4096
+    scan_bytes = 4 * n + 8 * nparts                    # totals-only scan: priorities read, offsets written
+    stored_scan_bytes = 8 * n + 8 * nparts             # storing scan: also 4 B written per priority
     achieved = scan_bytes / (scan_ms * 1e-3) / 1e9
+    stored_achieved = stored_scan_bytes / (stored_scan_ms * 1e-3) / 1e9
+    step_bytes = scan_bytes + 2 * gathered + B * 4096 * 4   # + one 16 KiB partition re-read per request
+    stored_step_bytes = stored_scan_bytes + 2 * gathered
 
     # ---- search + gather only ("priorities unchanged" mode), reported beside the headline
     e2 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    sampler.scan(prio, store=False)
     e2[0].record()
     for i in range(K):
         sampler.sample_gather(handler, u_dev[(i % nbatches) * B:(i % nbatches + 1) * B], cols, dsts,
@@ -197,7 +209,7 @@ def run_ours_single(args):
     new_val = torch.empty(nbatches * B, dtype=torch.float32, device=dev)
     core.fill(new_val, N.FILL_F32_LOGNORMAL, seed=0x6EA20303)
     e3 = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    sampler.scan(prio)
+    sampler.scan(prio, store=False)
     e3[0].record()
     for i in range(K):
         j = i % nbatches
@@ -216,7 +228,7 @@ def run_ours_single(args):
 
     def e2e_step(i):
         u_stage.copy_(u_host[(i % nbatches) * B:(i % nbatches + 1) * B], non_blocking=True)
-        sampler.scan(prio)
+        sampler.scan(prio, store=False)
         sampler.sample_gather(handler, u_stage, cols, dsts, scale=True, zero_fill=True, out_flat=flat)
         for h, d in zip(out_host, dsts):
             h.copy_(d, non_blocking=True)
@@ -236,7 +248,10 @@ def run_ours_single(args):
            "d2h_bytes_per_step": gathered + B * 8, "ms_per_step": e2e_s * 1e3, "steps": Ke}
 
     # ---- parity of one batch against the CPU oracle + CPU baseline (bounded sample)
-    parity, cpu = cpu_check_and_baseline(cfg, table, prio, u_dev[:B], sampler, handler, dsts, flat, args)
+    core.fill(prio, N.FILL_F32_LOGNORMAL, seed=0x6EA20103)      # undo the incremental mode's updates
+    parity, cpu = cpu_check_and_baseline(cfg, table, prio, u_dev[:B], sampler, handler, dsts, flat, args, store=False)
+    parity_stored, _ = cpu_check_and_baseline(cfg, table, prio, u_dev[:B], sampler, handler, dsts, flat, args,
+                                              store=True, want_cpu=False)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": max(args.warmup, 3),
@@ -245,26 +260,36 @@ def run_ours_single(args):
         "config": {"workload": cfg["name"], "trajectories": cap, "trajectory_length": T, "row_bytes": rows,
                    "batch": B, "segment_length": L, "priorities": n, "table_bytes": table.nbytes,
                    "l2": "inputs larger than L2 (400 MB of priorities re-read every step)",
-                   "step": "scan + search + decode + gather"},
+                   "step": "totals-only scan (partition offsets, no stored level-2 table) + one launch that "
+                           "searches, rebuilds the chosen partition's entries, decodes and gathers"},
         "gathered_gb_s": 2 * gathered / (ms_step * 1e-3) / 1e9,
-        "step_algorithmic_gb_s": (scan_bytes + 2 * gathered) / (ms_step * 1e-3) / 1e9,
-        "step_frac_of_measured_peak": (scan_bytes + 2 * gathered) / (ms_step * 1e-3) / 1e9 / peak,
-        "step_frac_of_8tbs": (scan_bytes + 2 * gathered) / (ms_step * 1e-3) / 1e9 / 8000.0,
+        "step_algorithmic_gb_s": step_bytes / (ms_step * 1e-3) / 1e9,
+        "step_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+        "step_frac_of_8tbs": step_bytes / (ms_step * 1e-3) / 1e9 / 8000.0,
+        "stored_table_mode": {
+            "step": "scan that stores the level-2 table (8 B per priority) + search + decode + gather",
+            "ms_per_step": stored_ms, "timesteps_per_s": B * L / (stored_ms * 1e-3),
+            "scan_ms": stored_scan_ms, "scan_algorithmic_bytes": stored_scan_bytes,
+            "scan_achieved_gb_s": stored_achieved, "scan_frac_of_measured_peak": stored_achieved / peak,
+            "scan_traffic": SCAN_TRAFFIC_BYTES_C3,
+            "step_algorithmic_gb_s": stored_step_bytes / (stored_ms * 1e-3) / 1e9,
+            "step_frac_of_measured_peak": stored_step_bytes / (stored_ms * 1e-3) / 1e9 / peak,
+            "step_frac_of_8tbs": stored_step_bytes / (stored_ms * 1e-3) / 1e9 / 8000.0, "parity": parity_stored},
         "search_gather_only": {"ms_per_step": sg_ms, "timesteps_per_s": B * L / (sg_ms * 1e-3),
                                "gathered_gb_s": 2 * gathered / (sg_ms * 1e-3) / 1e9},
         "incremental_update": {"ms_per_step": upd_ms, "timesteps_per_s": B * L / (upd_ms * 1e-3),
                                "step": f"update {B} priorities (rescan of the touched partitions + level 1) + "
                                        "search + decode + gather"},
-        "roofline": {"kernel": "scan_kernel", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": SCAN_TRAFFIC_BYTES_C3, "peak_source": peak_src,
-                     "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms},
+        "roofline": {"kernel": "scan_kernel<false> (totals only)", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "unit": "GB/s", "frac": achieved / peak, "traffic": SCAN_TOTALS_TRAFFIC_BYTES_C3,
+                     "peak_source": peak_src, "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 2 * K, "clocks": clk, "parity": parity,
         "scan_status": status, "total_priority": total_prio,
     }
     print(json.dumps(line))
 
 
-def cpu_check_and_baseline(cfg, table, prio, u_first, sampler, handler, dsts, flat, args):
+def cpu_check_and_baseline(cfg, table, prio, u_first, sampler, handler, dsts, flat, args, store=True, want_cpu=True):
     """One batch checked against the oracle, then the CPU path timed on a bounded sample."""
     import numpy as np
     import torch
@@ -277,7 +302,7 @@ def cpu_check_and_baseline(cfg, table, prio, u_first, sampler, handler, dsts, fl
     u = u_first.cpu().numpy()
 
     # GPU result of exactly this batch
-    sampler.scan(prio)
+    sampler.scan(prio, store=store)
     sampler.sample_gather(handler, u_first.contiguous(), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
     torch.cuda.synchronize()
     gflat = flat.cpu().numpy()
@@ -301,6 +326,9 @@ def cpu_check_and_baseline(cfg, table, prio, u_first, sampler, handler, dsts, fl
               "variates_within_1ulp_of_boundary": int(near.sum()),
               "flips_vs_float64_running_sum": int(flips.sum()),
               "max_flip_distance": int(np.abs(oflat[flips] - f64[flips]).max()) if flips.any() else 0}
+
+    if not want_cpu:
+        return parity, None
 
     # ---- CPU baseline: full 100M-priority scan + search + gather from a host slice of the table
     sub_cap = min(cap, 4000)                      # 756 MB host slice: requests folded into it
@@ -556,14 +584,14 @@ def run_profile_case(args):
 
     dev = torch.device("cuda:0")
     core.init(0)
-    if args.profile == "scan":
+    if args.profile in ("scan", "scan_totals"):
         n = args.profile_n
         prio = torch.empty(n, dtype=torch.float32, device=dev)
         core.fill(prio, N.FILL_F32_LOGNORMAL, seed=1)
         s = core.PrioritySampler(n)
         for _ in range(args.warmup + args.steps):
-            s.scan(prio)
-        print(json.dumps({"profile": "scan", "n": n, "result": s.result()}))
+            s.scan(prio, store=args.profile == "scan")
+        print(json.dumps({"profile": args.profile, "n": n, "result": s.result()}))
         return
     rows, T, cap, B, L = C3["rows"], C3["T"], 2000, C3["B"], C3["L"]
     table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
@@ -576,13 +604,13 @@ def run_profile_case(args):
     prio = torch.empty(n, dtype=torch.float32, device=dev)
     core.fill(prio, N.FILL_F32_LOGNORMAL, seed=3)
     s = core.PrioritySampler(n)
-    s.scan(prio)
+    s.scan(prio, store=args.profile == "sample_gather")
     u = torch.empty(B, dtype=torch.float64, device=dev)
     core.fill(u, N.FILL_U01_F64, seed=4)
     dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=dev) for r in rows]
     for _ in range(args.warmup + args.steps):
         s.sample_gather(h, u, cols, dsts, scale=True, zero_fill=True)
-    print(json.dumps({"profile": "sample_gather", "result": s.result()}))
+    print(json.dumps({"profile": args.profile, "result": s.result()}))
 
 
 def main():
@@ -591,7 +619,7 @@ def main():
     ap.add_argument("--steps", type=int, default=3000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default=None, choices=["scan", "sample_gather"],
+    ap.add_argument("--profile", default=None, choices=["scan", "scan_totals", "sample_gather", "sample_gather_lazy"],
                     help="run one small single-kernel case (for ncu) instead of the benchmark")
     ap.add_argument("--workload", default="default", choices=["default", "c2", "c4", "c5"],
                     help="default: config 3 at one GPU, the sharded config 5 at several; c2 / c4: BASELINE.json's "

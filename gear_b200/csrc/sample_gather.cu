@@ -142,7 +142,7 @@ constexpr int kLazyBytes = GEARB_PART * 4 + kWarps * 512;  // a partition of pri
 // addition tree, and searches them in shared memory.  The scan then only has to read the
 // priorities (4 bytes each) instead of reading them and writing a table (8 bytes each).
 template <bool kPeers, int kPath, bool kLazy>
-__global__ void __launch_bounds__(kThreads, kPath == kStaged ? (kLazy ? 6 : 7) : (kPath == kRing ? 4 : 5))
+__global__ void __launch_bounds__(kThreads, kPath == kStaged ? 7 : (kPath == kRing ? 4 : 5))
 sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
                      const __grid_constant__ PeerArgs peers) {
   extern __shared__ __align__(128) uint8_t stage[];  // P.stage_bytes of staging area

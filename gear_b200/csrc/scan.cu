@@ -5,17 +5,14 @@
 // The reference kernel is unfinished and has no caller; what is kept from it is
 // the shape of the addition tree (four values per thread in sequence, :40-49; a
 // Hillis-Steele shuffle scan over the lanes of a warp, :23-28; a second scan
-// over warp totals, :192-201; partition descriptors with a status word for the
+// pass over warp totals, :192-201; partition descriptors with a status word for the
 // look-back, one_dim_prefix_sum.cuh:5-10).
 //
-// Level 2 (cdf): each 4096-entry partition is scanned on its own, in float32,
-// with a fixed tree, so the stored values do not depend on scheduling:
-//   tile  = 128 values, lane l owns 4l..4l+3: s0=x0, s1=s0+x1, s2=s1+x2, s3=s2+x3
-//           I = shuffle scan of s3 over lanes; E = I(l-1); tile total = I(31)
-//   warp  = 4 tiles in sequence: c(k+1) = c(k) + total(k)
-//   CTA   = 8 warps: Y = shuffle scan of c(4); X(w) = Y(w-1)
-//   value = ((X + c(k)) + E) + s_j, then a running maximum over the partition
-//           (max is exact, so its order is free) to make the table monotone.
+// Level 2 (cdf): each 4096-entry partition is scanned on its own, in float32, with the
+// fixed tree written out in scan_tree.cuh (chunks of 4 in sequence, groups of 4 chunk totals
+// in sequence, one Hillis-Steele shuffle scan over the 32 groups of a 512-value block, the
+// 8 blocks of the partition in sequence, then a running maximum), so the values do not
+// depend on scheduling.  Warp w of the CTA scans block w.
 // Level 1 (l1): float64 exclusive offsets of the partitions, defined as the
 // in-order sum of the partitions' last cdf entries.  They come out of a
 // decoupled look-back over published aggregates.  The look-back adds in a
@@ -30,7 +27,8 @@
 //                      shared memory with a bulk asynchronous copy that signals
 //                      an mbarrier;
 //   warps 0-7 (compute) wait for a slot, pull it into registers, free the slot,
-//                      scan, and store the cdf with 16-byte streaming stores;
+//                      scan, and store the cdf with 16-byte streaming stores (or, in
+//                      the totals-only instance, keep just the partition's last entry);
 //   warp 9 (look-back) receives each partition's aggregate through a small ring
 //                      in shared memory, chains the aggregates of a group in
 //                      order, publishes one descriptor per group and looks back
@@ -39,7 +37,8 @@
 // a float64), so a reader needs no fence and one 32-byte read per predecessor.
 // Every wait is bounded; a wait that runs out raises a flag instead of hanging.
 //
-// HBM traffic: 4 B read + 4 B written per priority, plus ~16 B per partition.
+// HBM traffic: 4 B read + 4 B written per priority, plus ~16 B per partition; the
+// totals-only instance (cdf == nullptr) writes nothing per priority.
 #include <mutex>
 
 #include "common.h"
@@ -63,7 +62,10 @@ static_assert(kPart == GEARB_PART, "partition size is part of the ABI");
 constexpr int kStages = GEARB_SCAN_STAGES;   // ring slots of one partition each
 constexpr int kGroupMax = GEARB_SCAN_GROUP;  // partitions per ticket
 constexpr int kRing = 16;    // aggregate ring entries (compute -> look-back)
-constexpr int kSuper = 16;   // partitions per look-back descriptor
+#ifndef GEARB_SCAN_SUPER
+#define GEARB_SCAN_SUPER 32
+#endif
+constexpr int kSuper = GEARB_SCAN_SUPER;  // partitions per look-back descriptor (at most 32: one lane each)
 
 constexpr unsigned kSpinLimit = 1u << 20;  // polls of a shared-memory word / mbarrier before giving up
 constexpr unsigned kLookLimit = 1u << 17;  // polls (x ~100 ns) of a predecessor descriptor
@@ -171,7 +173,8 @@ struct ScanArgs {
   int32_t *status;
   int64_t n;
   unsigned nparts;
-  unsigned group;    // partitions per ticket (1, 2 or 4: divides kSuper)
+  unsigned group;    // partitions per ticket (1, 2 or 4: divides kSuper) for the first `nbig` tickets;
+  unsigned nbig;     // the tickets after them hold one partition each, which evens out the finish
   unsigned ngroups;  // tickets
   unsigned nsuper;   // super-groups of kSuper partitions
 };
@@ -181,8 +184,8 @@ struct __align__(128) Smem {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   int stage_part[kStages];         // partition staged in the slot, -1 = no more work
-  float wt[2][kComputeWarps];      // warp totals, double-buffered by iteration parity
-  float wm[2][kComputeWarps];      // warp maxima
+  float wt[2][kComputeWarps];      // block totals, double-buffered by iteration parity
+  float wm[2][kComputeWarps];      // block maxima
   alignas(16) float xs[kComputeWarps][128];    // per-warp exchange area: one float per chunk of the warp's block
   volatile int ring_part[kRing];   // aggregate ring: partition id (-1 = end)
   volatile float ring_agg[kRing];
@@ -200,12 +203,16 @@ __device__ __forceinline__ void raise_abort(Smem &sm, const ScanArgs &a) {
 __device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
   unsigned it = 0;
   bool stop = false;
+  // The ticket after the current one is requested before the current one is served, so the
+  // round trip of the atomic is hidden behind four partitions' worth of copies.
+  unsigned ahead = 0;
+  if (lane == 0) ahead = atomicAdd(&a.hdr->ticket, 1u);
   while (!stop) {
-    unsigned t = 0;
-    if (lane == 0) t = atomicAdd(&a.hdr->ticket, 1u);
-    t = __shfl_sync(kFull, t, 0);
+    const unsigned t = __shfl_sync(kFull, ahead, 0);
+    if (lane == 0 && t < a.ngroups) ahead = atomicAdd(&a.hdr->ticket, 1u);
     const bool last = t >= a.ngroups;
-    const unsigned count = last ? 1u : min(a.group, a.nparts - t * a.group);
+    const unsigned first = t < a.nbig ? t * a.group : a.nbig * a.group + (t - a.nbig);
+    const unsigned count = (last || t >= a.nbig) ? 1u : a.group;
     for (unsigned k = 0; k < count && !stop; ++k, ++it) {
       const unsigned s = it % kStages;
       const unsigned parity = ((it / kStages) & 1u) ^ 1u;
@@ -227,7 +234,7 @@ __device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
         stop = true;
         break;
       }
-      const unsigned p = t * a.group + k;
+      const unsigned p = first + k;
       const int64_t base = static_cast<int64_t>(p) * kPart;
       const int64_t valid = (a.n - base < kPart) ? (a.n - base) : kPart;
       const unsigned bulk_bytes = static_cast<unsigned>((valid * 4) & ~int64_t(15));
@@ -499,14 +506,14 @@ __device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int l
     // The aggregate word validates itself (tag + float bits in one 64-bit store): no fence.
     if (lane == 0)
       st_u64(&a.aggw[part], (static_cast<unsigned long long>(tagA) << 32) | __float_as_uint(aggf));
-    const unsigned t = static_cast<unsigned>(part) / a.group;
-    const unsigned k = static_cast<unsigned>(part) - t * a.group;
+    const bool big = static_cast<unsigned>(part) < a.nbig * a.group;
+    const unsigned k = big ? static_cast<unsigned>(part) % a.group : 0u;
     if (k != have) {  // aggregates of a ticket arrive in order; anything else is a logic error
       if (lane == 0) raise_abort(sm, a);
       break;
     }
     have = k + 1;
-    const unsigned in_ticket = min(a.group, a.nparts - t * a.group);
+    const unsigned in_ticket = big ? a.group : 1u;
     if (have < in_ticket) continue;
     have = 0;
 #ifdef GEARB_SCAN_NO_LOOKBACK  // timing experiment only: level 1 is left unwritten
@@ -663,7 +670,10 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
   // Group partitions per ticket only when there is enough work to keep every CTA busy.
   a.group = nparts >= resident * kGroupMax * 2 ? kGroupMax : (nparts >= resident * 4 ? 2 : 1);
-  a.ngroups = static_cast<unsigned>((nparts + a.group - 1) / a.group);
+  // The last stretch (about two partitions per resident CTA) goes out one partition per ticket.
+  const int64_t tail = resident * 2 < nparts ? resident * 2 : nparts;
+  a.nbig = static_cast<unsigned>((nparts - tail) / a.group);
+  a.ngroups = static_cast<unsigned>(a.nbig + (nparts - static_cast<int64_t>(a.nbig) * a.group));
 
   int64_t grid = resident;
   if (grid > a.ngroups) grid = a.ngroups;
