@@ -53,9 +53,11 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
 int64_t static_scan_max_n();
 int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
                        cudaStream_t stream);
-unsigned long long *scan_aggregate_words(void *scratch, int64_t layout_n);
+float *scan_aggregate_words(void *scratch, int64_t layout_n);
+int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
+                  cudaStream_t stream);
 int64_t update_scratch_bytes(int64_t n);
-int launch_update(float *prio, int64_t n, float *cdf, double *l1, unsigned long long *aggw, void *upd,
+int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, void *upd,
                   const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream);
 int launch_search(const float *cdf, const double *l1, int64_t n, const double *u, int64_t b,
                   int flags, int64_t *out, int32_t *status, cudaStream_t stream);

@@ -298,7 +298,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
           if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
           break;
         }
-        bool bad = false;  // the scan has already reported negative or NaN priorities
+        unsigned bits = 0;  // ignored: the scan has already reported bad priorities
         float sv[4][4], top[4];
         float4 x[4];
         // first pass: block totals (warp w: blocks w and w + 4)
@@ -307,7 +307,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
           const int blk = warp + h * kWarps;
 #pragma unroll
           for (int k = 0; k < 4; ++k) x[k] = pv4[(blk * 4 + k) * 32 + lane];
-          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bad);
+          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bits);
           if (lane == 0) blk_total[blk] = gq.total;
         }
         __syncthreads();
@@ -317,7 +317,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
           const int blk = warp + h * kWarps;
 #pragma unroll
           for (int k = 0; k < 4; ++k) x[k] = pv4[(blk * 4 + k) * 32 + lane];
-          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bad);
+          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bits);
           float X = 0.f;
           for (int w = 0; w < blk; ++w) X = __fadd_rn(X, blk_total[w]);
           tree::block_values(X, gq, xs, lane, sv, top, false, base + blk * tree::kBlockValues, a.n);

@@ -13,28 +13,21 @@
 // in sequence, one Hillis-Steele shuffle scan over the 32 groups of a 512-value block, the
 // 8 blocks of the partition in sequence, then a running maximum), so the values do not
 // depend on scheduling.  Warp w of the CTA scans block w.
-// Level 1 (l1): float64 exclusive offsets of the partitions, defined as the
-// in-order sum of the partitions' last cdf entries.  They come out of a
-// decoupled look-back over published aggregates.  The look-back adds in a
-// timing-dependent grouping, so every float64 addition is checked with TwoSum;
-// while all of them are exact the result equals the in-order sum bit for bit.
-// If one is inexact (or a bounded wait gives up) the last CTA to finish
-// recomputes l1 strictly in order from the per-partition aggregates.
+// Level 1 (l1): float64 exclusive offsets of the partitions, defined as the in-order sum of
+// the partitions' aggregates (the eight block totals of a partition added in sequence).  This
+// kernel leaves every partition's aggregate in global memory; a second, small launch
+// (level1.cu) turns the aggregates into l1 (for small tables the last CTA does it on the spot).  An earlier version chained the offsets through a
+// decoupled look-back while streaming: at 6 TB/s the look-back could not keep up with the
+// partitions (37 of 105 us at 1e8 priorities), the separate launch costs a few us.
 //
-// Execution: a persistent, warp-specialised CTA of 10 warps.
+// Execution: a persistent, warp-specialised CTA of 9 warps.
 //   warp 8 (loader)    takes tickets (a group of up to 4 consecutive partitions
 //                      each), and stages one partition (16 KiB) per ring slot in
 //                      shared memory with a bulk asynchronous copy that signals
 //                      an mbarrier;
 //   warps 0-7 (compute) wait for a slot, pull it into registers, free the slot,
 //                      scan, and store the cdf with 16-byte streaming stores (or, in
-//                      the totals-only instance, keep just the partition's last entry);
-//   warp 9 (look-back) receives each partition's aggregate through a small ring
-//                      in shared memory, chains the aggregates of a group in
-//                      order, publishes one descriptor per group and looks back
-//                      over earlier groups while the other warps keep streaming.
-// Descriptors carry their own validity: each 64-bit word is (tag << 32 | half of
-// a float64), so a reader needs no fence and one 32-byte read per predecessor.
+//                      the totals-only instance, keep just the block totals).
 // Every wait is bounded; a wait that runs out raises a flag instead of hanging.
 //
 // HBM traffic: 4 B read + 4 B written per priority, plus ~16 B per partition; the
@@ -42,6 +35,7 @@
 #include <mutex>
 
 #include "common.h"
+#include "level1.cuh"
 #include "scan_tree.cuh"
 
 namespace gearb {
@@ -49,7 +43,7 @@ namespace {
 
 constexpr int kComputeWarps = 8;
 constexpr int kComputeThreads = kComputeWarps * 32;
-constexpr int kThreads = kComputeThreads + 64;  // + loader warp + look-back warp
+constexpr int kThreads = kComputeThreads + 32;  // + loader warp
 constexpr int kTilesPerWarp = 4;
 constexpr int kPart = kComputeWarps * kTilesPerWarp * 128;
 static_assert(kPart == GEARB_PART, "partition size is part of the ABI");
@@ -61,16 +55,8 @@ static_assert(kPart == GEARB_PART, "partition size is part of the ABI");
 #endif
 constexpr int kStages = GEARB_SCAN_STAGES;   // ring slots of one partition each
 constexpr int kGroupMax = GEARB_SCAN_GROUP;  // partitions per ticket
-constexpr int kRing = 16;    // aggregate ring entries (compute -> look-back)
-#ifndef GEARB_SCAN_SUPER
-#define GEARB_SCAN_SUPER 32
-#endif
-constexpr int kSuper = GEARB_SCAN_SUPER;  // partitions per look-back descriptor (at most 32: one lane each)
-
 constexpr unsigned kSpinLimit = 1u << 20;  // polls of a shared-memory word / mbarrier before giving up
-constexpr unsigned kLookLimit = 1u << 17;  // polls (x ~100 ns) of a predecessor descriptor
 
-constexpr unsigned kHdrRebuild = 1u;  // header flag: level 1 must be re-summed in order
 constexpr unsigned kFull = 0xffffffffu;
 
 // ---- small PTX wrappers -------------------------------------------------------
@@ -122,61 +108,19 @@ __device__ __forceinline__ bool named_barrier_compute_or(bool flag) {
       : "memory");
   return r != 0;
 }
-__device__ __forceinline__ void st_u64(unsigned long long *p, unsigned long long v) {
-  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
-__device__ __forceinline__ void ld_desc(const unsigned long long *p, unsigned long long w[4]) {
-  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[0]), "=l"(w[1]) : "l"(p) : "memory");
-  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w[2]), "=l"(w[3]) : "l"(p + 2) : "memory");
-}
-__device__ __forceinline__ unsigned long long ld_u64_relaxed(const unsigned long long *p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned ld_u32_relaxed(const unsigned *p) {
-  unsigned v;
-  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// s = a + b in float64; raises `inexact` when the addition rounded.
-__device__ __forceinline__ double checked_add(double a, double b, bool &inexact) {
-  const double s = __dadd_rn(a, b);
-  const double bb = __dsub_rn(s, a);
-  const double err = __dadd_rn(__dsub_rn(a, __dsub_rn(s, bb)), __dsub_rn(b, bb));
-  inexact |= (err != 0.0);
-  return s;
-}
-
-// A float64 split over two self-validating 64-bit words.
-__device__ __forceinline__ void publish(unsigned long long *two_words, double v, unsigned tag) {
-  const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(v));
-  const unsigned long long t = static_cast<unsigned long long>(tag) << 32;
-  st_u64(two_words, t | (bits >> 32));
-  st_u64(two_words + 1, t | (bits & 0xffffffffull));
-}
-__device__ __forceinline__ bool decode(unsigned long long hi, unsigned long long lo, unsigned tag, double &v) {
-  if (static_cast<unsigned>(hi >> 32) != tag || static_cast<unsigned>(lo >> 32) != tag) return false;
-  v = __longlong_as_double(static_cast<long long>(((hi & 0xffffffffull) << 32) | (lo & 0xffffffffull)));
-  return true;
-}
-
 struct ScanArgs {
   const float *prio;
   float *cdf;
   double *l1;
   ScanHeader *hdr;
-  unsigned *gcount;          // per super-group: partitions finished (returns to 0 by itself)
-  unsigned long long *desc;  // per super-group: {agg hi, agg lo, prefix hi, prefix lo}
-  unsigned long long *aggw;  // per partition: (tag << 32) | bits of the float32 aggregate
+  float *aggw;               // per partition: its aggregate
   int32_t *status;
   int64_t n;
   unsigned nparts;
-  unsigned group;    // partitions per ticket (1, 2 or 4: divides kSuper) for the first `nbig` tickets;
+  unsigned group;    // partitions per ticket (1, 2 or 4) for the first `nbig` tickets;
   unsigned nbig;     // the tickets after them hold one partition each, which evens out the finish
   unsigned ngroups;  // tickets
-  unsigned nsuper;   // super-groups of kSuper partitions
+  int inline_level1;  // the last CTA builds l1 itself (small tables)
 };
 
 struct __align__(128) Smem {
@@ -187,10 +131,6 @@ struct __align__(128) Smem {
   float wt[2][kComputeWarps];      // block totals, double-buffered by iteration parity
   float wm[2][kComputeWarps];      // block maxima
   alignas(16) float xs[kComputeWarps][128];    // per-warp exchange area: one float per chunk of the warp's block
-  volatile int ring_part[kRing];   // aggregate ring: partition id (-1 = end)
-  volatile float ring_agg[kRing];
-  volatile unsigned ring_head;     // entries produced
-  volatile unsigned ring_tail;     // entries consumed
   volatile unsigned abort;         // a bounded wait ran out somewhere in this CTA
 };
 
@@ -258,17 +198,9 @@ __device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
   }
 }
 
-// One partition's aggregate from the compute warps to the look-back warp.
-__device__ __forceinline__ void hand_over(Smem &sm, int part, float agg) {
-  const unsigned h = sm.ring_head;
-  unsigned sp = 0;
-  while (h - sm.ring_tail >= kRing) {
-    if (++sp > kSpinLimit || sm.abort) break;
-  }
-  sm.ring_part[h % kRing] = part;
-  sm.ring_agg[h % kRing] = agg;
-  __threadfence_block();
-  sm.ring_head = h + 1;
+// One partition's aggregate to its word in global memory (read back by the last CTA).
+__device__ __forceinline__ void hand_over(const ScanArgs &a, int part, float agg) {
+  a.aggw[part] = agg;
 }
 
 // ----------------------------------------------------------------- compute warps
@@ -279,7 +211,7 @@ __device__ __forceinline__ void hand_over(Smem &sm, int part, float agg) {
 // kStore = false: only the partition's last (largest) entry is produced, nothing is stored.
 template <bool kStore>
 __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
-  bool bad = false;
+  unsigned bits = 0;  // OR of the bit patterns seen: the sign bit ends up set if a priority was bad
   float *xs = sm.xs[warp];
   for (unsigned it = 0;; ++it) {
     const unsigned s = it % kStages;
@@ -303,45 +235,44 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
       x[k] = leave ? make_float4(0.f, 0.f, 0.f, 0.f) : sm.stage[s][(warp * kTilesPerWarp + k) * 32 + lane];
     __syncwarp();
     if (lane == 0 && !leave) mbar_arrive(&sm.empty[s]);
+    const int buf = it & 1;
+
+    if (!kStore) {
+      // ---- totals only: the block totals are all the partition's aggregate needs
+      const float total = tree::block_total(x, xs, lane, bits);
+      if (lane == 0) sm.wt[buf][warp] = total;
+      if (named_barrier_compute_or(leave)) break;
+      if (warp == kComputeWarps - 1 && lane == 0) {
+        float X = 0.f;
+#pragma unroll
+        for (int w = 0; w < kComputeWarps; ++w) X = __fadd_rn(X, sm.wt[buf][w]);
+        hand_over(a, part, X);
+      }
+      continue;  // wt[buf] is next written two rounds on, behind the next round's barrier
+    }
 
     const int64_t base = static_cast<int64_t>(part) * kPart;
     const int64_t e0 = base + warp * tree::kBlockValues;  // this warp's block
-    const int buf = it & 1;
     float sv[kTilesPerWarp][4], top[kTilesPerWarp];
 
     // ---- first pass: sums inside the block; block totals meet in shared memory
-    const tree::Group g = tree::block_sums(x, xs, lane, sv, bad);
+    const tree::Group g = tree::block_sums(x, xs, lane, sv, bits);
     if (lane == 0) sm.wt[buf][warp] = g.total;
     if (named_barrier_compute_or(leave)) break;
 
     // ---- offset of this warp's block: the totals of the blocks before it, in sequence
     float X = 0.f;
     for (int w = 0; w < warp; ++w) X = __fadd_rn(X, sm.wt[buf][w]);
+    // the last warp also knows the partition's aggregate X(8): hand it over
+    if (warp == kComputeWarps - 1 && lane == 0) hand_over(a, part, __fadd_rn(X, g.total));
 
-    // ---- second pass: values (kStore) or only each chunk's largest one
-    tree::block_values(X, g, xs, lane, sv, top, !kStore, e0, a.n);
-
-    if (!kStore) {
-      // ---- the partition's largest entry is all that is needed
-      const float m = tree::block_max(top);
-      if (lane == 0) sm.wm[buf][warp] = m;
-      named_barrier_compute();
-      if (warp == kComputeWarps - 1 && lane == 0) {
-        float G = 0.f;
-        for (int w = 0; w < kComputeWarps; ++w) G = fmaxf(G, sm.wm[buf][w]);
-        hand_over(sm, part, G);
-      }
-      continue;
-    }
-
-    // ---- running maximum, block by block
+    // ---- second pass: values, then the running maximum block by block
+    tree::block_values(X, g, xs, lane, sv, top, false, e0, a.n);
     const float run = tree::block_prefix_max(top, xs, lane);
     if (lane == 0) sm.wm[buf][warp] = run;
     named_barrier_compute();
     float G = 0.f;
     for (int w = 0; w < warp; ++w) G = fmaxf(G, sm.wm[buf][w]);
-    // the last warp knows the partition's last (= largest) entry
-    if (warp == kComputeWarps - 1 && lane == 0) hand_over(sm, part, fmaxf(G, run));
 
     // ---- store
     if (e0 + tree::kBlockValues <= a.n) {
@@ -363,208 +294,41 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
       }
     }
   }
-  if (warp == kComputeWarps - 1 && lane == 0) {  // tell the look-back warp there is no more
-    const unsigned h = sm.ring_head;
-    unsigned sp = 0;
-    while (h - sm.ring_tail >= kRing && ++sp < kSpinLimit && !sm.abort) {}
-    sm.ring_part[h % kRing] = -1;
-    __threadfence_block();
-    sm.ring_head = h + 1;
-  }
-  if (__any_sync(kFull, bad) && lane == 0)
+  if (__any_sync(kFull, (bits >> 31) != 0) && lane == 0)
     atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_BAD_PRIORITY);
 }
 
-// --------------------------------------------------------------- look-back warp
-// Two levels keep the look-back cheap.  A ticket (up to 4 partitions) only publishes its
-// partitions' aggregates and bumps the counter of its super-group (16 partitions); the warp
-// whose bump completes the super-group chains the 16 aggregates in order, publishes ONE
-// descriptor and looks back over earlier super-groups.  The number of look-back
-// participants, and with it the time the prefix needs to travel down the table, drops 4x
-// against one look-back per ticket.
-// The warp that completed group g: chain its aggregates, publish, look back, write l1.
-__device__ void finish_group(const ScanArgs &a, unsigned g, unsigned epoch, int lane) {
-  const unsigned tagA = (epoch << 2) | 1u, tagP = (epoch << 2) | 2u;
-  const unsigned first = g * kSuper;
-  const unsigned in_group = min(static_cast<unsigned>(kSuper), a.nparts - first);
-  bool inexact = false;
-  // The counter says every partition of the group has issued its aggregate; the words carry
-  // their own tag, so poll (normally zero times) until each one is visible.
-  double incl = 0.0;
-  bool late = false;
-  if (lane < static_cast<int>(in_group)) {
-    unsigned polls = 0;
-    for (;;) {
-      const unsigned long long w = ld_u64_relaxed(&a.aggw[first + lane]);
-      if (static_cast<unsigned>(w >> 32) == tagA) {
-        incl = static_cast<double>(__uint_as_float(static_cast<unsigned>(w)));
-        break;
-      }
-      if (++polls > kLookLimit) {
-        late = true;
-        break;
-      }
-      __nanosleep(32);
-    }
-  }
-  if (__any_sync(kFull, late)) {
-    if (lane == 0) {
-      atomicOr(&a.hdr->pad[0], kHdrRebuild);
-      atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_SCAN_ABORTED);
-    }
-    return;
-  }
-  // inclusive in-order sums of the group's aggregates (shuffle scan; exact => order-free)
-#pragma unroll
-  for (int d = 1; d < kSuper; d <<= 1) {
-    const double t = __shfl_up_sync(kFull, incl, d);
-    if (lane >= d) incl = checked_add(t, incl, inexact);
-  }
-  const double gsum = __shfl_sync(kFull, incl, in_group - 1);
-  unsigned long long *mine = a.desc + static_cast<size_t>(g) * 4;
-  double excl = 0.0;
-  bool gave_up = false;
-  if (g > 0) {
-    if (lane == 0) publish(mine, gsum, tagA);
-    long long j = static_cast<long long>(g) - 1;
-    for (;;) {
-      const long long q = j - lane;
-      double val = 0.0;
-      int kind = 2;  // 2 = prefix known, 1 = aggregate known, 0 = nothing yet; "group -1" has prefix 0
-      unsigned polls = 0;
-      for (;;) {
-        if (q >= 0) {
-          unsigned long long w[4];
-          ld_desc(a.desc + static_cast<size_t>(q) * 4, w);
-          kind = decode(w[2], w[3], tagP, val) ? 2 : (decode(w[0], w[1], tagA, val) ? 1 : 0);
-        }
-        if (__all_sync(kFull, kind != 0)) break;
-        ++polls;
-        const bool quit =
-            polls > kLookLimit || ((polls & 31u) == 0 && (ld_u32_relaxed(&a.hdr->pad[0]) & kHdrRebuild));
-        if (__any_sync(kFull, quit)) {
-          gave_up = true;
-          break;
-        }
-        __nanosleep(64);
-      }
-      if (gave_up) break;
-      const unsigned pmask = __ballot_sync(kFull, kind == 2);
-      const int fp = pmask ? (__ffs(pmask) - 1) : 32;
-      if (lane > fp) val = 0.0;
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) {
-        const double o = __shfl_down_sync(kFull, val, d);
-        val = checked_add(val, o, inexact);
-      }
-      const double wsum = __shfl_sync(kFull, val, 0);
-      excl = checked_add(excl, wsum, inexact);
-      if (pmask) break;
-      j -= 32;
-    }
-  }
-  if (gave_up) {
-    // Nothing to publish; later groups find the rebuild flag and stop waiting too.
-    if (lane == 0) {
-      const unsigned old = atomicOr(&a.hdr->pad[0], kHdrRebuild);
-      if (!(old & kHdrRebuild)) atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_LOOKBACK_TIMEOUT);
-    }
-    return;
-  }
-  if (lane == 0) publish(mine + 2, checked_add(excl, gsum, inexact), tagP);
-  if (lane < static_cast<int>(in_group)) __stcg(&a.l1[first + lane + 1], checked_add(excl, incl, inexact));
-  if (g == 0 && lane == 0) __stcg(&a.l1[0], 0.0);
-  if (__any_sync(kFull, inexact) && lane == 0) atomicOr(&a.hdr->pad[0], kHdrRebuild);
-}
-
-
-__device__ void lookback_warp(Smem &sm, const ScanArgs &a, unsigned epoch, int lane) {
-  const unsigned tagA = (epoch << 2) | 1u;
-  unsigned have = 0;  // partitions of the current ticket seen so far
-  for (;;) {
-    // ---- pop one aggregate
-    const unsigned tl = sm.ring_tail;
-    unsigned spins = 0;
-    bool ok = true;
-    while (sm.ring_head == tl) {
-      if (++spins > kSpinLimit || sm.abort) {
-        ok = false;
-        break;
-      }
-      __nanosleep(20);
-    }
-    if (!__all_sync(kFull, ok)) {
-      if (lane == 0 && !sm.abort) raise_abort(sm, a);
-      break;
-    }
-    const int part = sm.ring_part[tl % kRing];
-    const float aggf = sm.ring_agg[tl % kRing];
-    __syncwarp();
-    if (lane == 0) sm.ring_tail = tl + 1;
-    if (part < 0) break;
-
-    // The aggregate word validates itself (tag + float bits in one 64-bit store): no fence.
-    if (lane == 0)
-      st_u64(&a.aggw[part], (static_cast<unsigned long long>(tagA) << 32) | __float_as_uint(aggf));
-    const bool big = static_cast<unsigned>(part) < a.nbig * a.group;
-    const unsigned k = big ? static_cast<unsigned>(part) % a.group : 0u;
-    if (k != have) {  // aggregates of a ticket arrive in order; anything else is a logic error
-      if (lane == 0) raise_abort(sm, a);
-      break;
-    }
-    have = k + 1;
-    const unsigned in_ticket = big ? a.group : 1u;
-    if (have < in_ticket) continue;
-    have = 0;
-#ifdef GEARB_SCAN_NO_LOOKBACK  // timing experiment only: level 1 is left unwritten
-    continue;
-#endif
-    const unsigned sg = static_cast<unsigned>(part) / kSuper;
-    const unsigned in_super = min(static_cast<unsigned>(kSuper), a.nparts - sg * kSuper);
-    unsigned arrived = 0;
-    if (lane == 0) arrived = atomicAdd(&a.gcount[sg], in_ticket) + in_ticket;
-    arrived = __shfl_sync(kFull, arrived, 0);
-    if (arrived == in_super) {
-      if (lane == 0) a.gcount[sg] = 0u;  // last one to touch it: ready for the next launch
-      finish_group(a, sg, epoch, lane);
-    }
-  }
-}
-
-// Last CTA out: rebuild level 1 in order if asked, then re-arm the header for the next launch.
-__device__ void finish_launch(const ScanArgs &a, unsigned epoch, int tid) {
+// Last CTA out: the header is re-armed for the next launch.  For a small table the last CTA
+// also builds level 1 on the spot (a few hundred aggregates cost less than another launch).
+__device__ void finish_launch(Smem &sm, const ScanArgs &a, int tid) {
+  __shared__ int is_last;
   if (tid == 0) {
-    __threadfence();
+    __threadfence();  // this CTA's aggregates before its count
     const unsigned d = atomicAdd(&a.hdr->done, 1u);
-    if (d == gridDim.x - 1) {
-      __threadfence();
-      const unsigned flags = atomicOr(&a.hdr->pad[0], 0u);
-      if (flags & kHdrRebuild) {
-        double acc = 0.0;
-        __stcg(&a.l1[0], 0.0);
-        for (unsigned q = 0; q < a.nparts; ++q) {
-          acc = __dadd_rn(acc, static_cast<double>(__uint_as_float(static_cast<unsigned>(__ldcg(&a.aggw[q])))));
-          __stcg(&a.l1[q + 1], acc);
-        }
-        atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_L1_RESUMMED);
-      }
-      if (atomicOr(reinterpret_cast<unsigned *>(a.status), 0u) & GEARB_ST_SCAN_ABORTED)
-        for (unsigned g = 0; g < a.nsuper; ++g) a.gcount[g] = 0u;  // counters may be left half-way
-      a.hdr->pad[0] = 0u;
-      a.hdr->ticket = 0u;
-      a.hdr->done = 0u;
-      a.hdr->epoch = epoch + 1u;
-      __threadfence();
-    }
+    is_last = d == gridDim.x - 1;
+    __threadfence();
+  }
+  __syncthreads();
+  if (!is_last) return;
+  if (a.inline_level1) {
+    static_assert(sizeof(sm.stage) >= level1::kTile * sizeof(float), "the ring doubles as level 1's tile");
+    // after an abort some aggregates are stale and copies may still land in the ring: leave l1 alone
+    const unsigned aborted = atomicOr(reinterpret_cast<unsigned *>(a.status), 0u) & GEARB_ST_SCAN_ABORTED;
+    if (!aborted) level1::build(a.aggw, a.nparts, a.l1, a.status, reinterpret_cast<float *>(sm.stage));
+    __syncthreads();
+  }
+  if (tid == 0) {
+    a.hdr->ticket = 0u;
+    a.hdr->done = 0u;
+    __threadfence();
   }
 }
 
 template <bool kStore>
-__global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
+__global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const ScanArgs a) {
   extern __shared__ unsigned char smem_raw[];
   Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const unsigned epoch = ld_u32_relaxed(&a.hdr->epoch);
   // A kernel launched behind this one with programmatic stream serialisation may be scheduled
   // as this grid drains; it still waits (griddepcontrol.wait) for this grid to complete.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -574,8 +338,6 @@ __global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], kComputeWarps);
     }
-    sm.ring_head = 0;
-    sm.ring_tail = 0;
     sm.abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -583,8 +345,7 @@ __global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
   __syncthreads();
 
   if (warp < kComputeWarps) compute_warps<kStore>(sm, a, warp, lane);
-  else if (warp == kComputeWarps) loader_warp(sm, a, lane);
-  else lookback_warp(sm, a, epoch, lane);
+  else loader_warp(sm, a, lane);
 
   __syncthreads();
   // Bulk copies still in flight into this CTA's shared memory (only after an abort) must land
@@ -597,20 +358,17 @@ __global__ void __launch_bounds__(kThreads, 3) scan_kernel(const ScanArgs a) {
       }
   }
 
-  finish_launch(a, epoch, tid);
+  finish_launch(sm, a, tid);
 }
 
 inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
 
 }  // namespace
 
-// Scratch layout: header | super-group counters (4 B) | super-group descriptors (32 B) |
-// partition aggregate words (8 B).
+// Scratch layout: header (256 B) | partition aggregates (float32 each).
 int64_t scan_scratch_bytes(int64_t n) {
   const int64_t nparts = (n + kPart - 1) / kPart;
-  const int64_t nsuper = (nparts + kSuper - 1) / kSuper;
-  return static_cast<int64_t>(sizeof(ScanHeader)) + align256(nsuper * 4) + align256(nsuper * 32) +
-         align256(nparts * 8);
+  return static_cast<int64_t>(sizeof(ScanHeader)) + align256(nparts * 4);
 }
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
@@ -628,19 +386,10 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   GEARB_REQUIRE(scratch_bytes >= scan_scratch_bytes(n), "scan: scratch too small (%lld < %lld)",
                 (long long)scratch_bytes, (long long)scan_scratch_bytes(n));
   char *sc = static_cast<char *>(scratch);
-  const int64_t nsuper = (nparts + kSuper - 1) / kSuper;
-  // A scratch block that serves calls of different sizes keeps ONE layout (that of layout_n):
-  // the counters of a larger call must never land on words a smaller call used for something else.
-  if (layout_n < n) layout_n = n;
-  const int64_t lay_parts = (layout_n + kPart - 1) / kPart;
-  const int64_t lay_super = (lay_parts + kSuper - 1) / kSuper;
-  GEARB_REQUIRE(scratch_bytes >= scan_scratch_bytes(layout_n), "scan: scratch too small for its layout");
-  const int64_t off_desc = sizeof(ScanHeader) + align256(lay_super * 4);
-  const int64_t off_agg = off_desc + align256(lay_super * 32);
+  (void)layout_n;  // the aggregate words start right behind the header whatever the size
   if (fresh) {
-    // Everything must start at zero: the epoch restarts at 0, so a stale tagged word could
-    // otherwise pass for a fresh one.
-    GEARB_CUDA(cudaMemsetAsync(sc, 0, static_cast<size_t>(scan_scratch_bytes(layout_n)), stream));
+    // the header's ticket and CTA counters must start at zero
+    GEARB_CUDA(cudaMemsetAsync(sc, 0, sizeof(ScanHeader), stream));
   }
 
   ScanArgs a;
@@ -648,25 +397,25 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.cdf = cdf;  // null: only level 1 and the aggregates are produced
   a.l1 = l1;
   a.hdr = reinterpret_cast<ScanHeader *>(sc);
-  a.gcount = reinterpret_cast<unsigned *>(sc + sizeof(ScanHeader));
-  a.desc = reinterpret_cast<unsigned long long *>(sc + off_desc);
-  a.aggw = reinterpret_cast<unsigned long long *>(sc + off_agg);
-  a.nsuper = static_cast<unsigned>(nsuper);
+  a.aggw = reinterpret_cast<float *>(sc + sizeof(ScanHeader));
   a.status = status;
   a.n = n;
   a.nparts = static_cast<unsigned>(nparts);
 
   const size_t smem_bytes = sizeof(Smem) + 128;
-  static int ctas_per_sm = 0;
-  if (ctas_per_sm == 0) {
+  static int ctas_by_instance[2] = {0, 0};  // [storing?]
+  if (ctas_by_instance[0] == 0) {
     GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(smem_bytes)));
     GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(smem_bytes)));
     int v = 0;
     GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, scan_kernel<true>, kThreads, smem_bytes));
-    ctas_per_sm = v > 0 ? v : 1;
+    ctas_by_instance[1] = v > 0 ? v : 1;
+    GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, scan_kernel<false>, kThreads, smem_bytes));
+    ctas_by_instance[0] = v > 0 ? v : 1;
   }
+  const int ctas_per_sm = ctas_by_instance[cdf != nullptr];
   const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
   // Group partitions per ticket only when there is enough work to keep every CTA busy.
   a.group = nparts >= resident * kGroupMax * 2 ? kGroupMax : (nparts >= resident * 4 ? 2 : 1);
@@ -675,12 +424,14 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.nbig = static_cast<unsigned>((nparts - tail) / a.group);
   a.ngroups = static_cast<unsigned>(a.nbig + (nparts - static_cast<int64_t>(a.nbig) * a.group));
 
+  a.inline_level1 = nparts <= 1024;
   int64_t grid = resident;
   if (grid > a.ngroups) grid = a.ngroups;
   if (a.cdf) scan_kernel<true><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
   else scan_kernel<false><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
   GEARB_CUDA(cudaGetLastError());
-  return GEARB_OK;
+  // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
+  return a.inline_level1 ? GEARB_OK : launch_level1(a.aggw, nparts, l1, nullptr, status, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -690,11 +441,7 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
 // library reserves that much global memory until the process exits.
 constexpr int64_t kStaticMaxN = int64_t(1) << 28;  // 268,435,456 priorities = 65,536 partitions
 constexpr int64_t kStaticParts = kStaticMaxN / kPart;
-constexpr int64_t kStaticSuper = kStaticParts / kSuper;
-constexpr int64_t kStaticScratchBytes =
-    sizeof(ScanHeader) + kStaticSuper * 4 + kStaticSuper * 32 + kStaticParts * 8;  // 672,000 B
-static_assert(kStaticSuper * 4 % 256 == 0 && kStaticSuper * 32 % 256 == 0 && kStaticParts * 8 % 256 == 0,
-              "the static scratch uses the same 256-byte aligned layout as scan_scratch_bytes()");
+constexpr int64_t kStaticScratchBytes = sizeof(ScanHeader) + kStaticParts * 4;  // 262,400 B
 
 // In host code this name is only a handle for the symbol, not a device address: the address
 // each device gave the array is asked for with cudaGetSymbolAddress below.
@@ -702,12 +449,9 @@ static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScra
 
 int64_t static_scan_max_n() { return kStaticMaxN; }
 
-// Where a scratch block laid out for layout_n priorities keeps its per-partition aggregate words.
-unsigned long long *scan_aggregate_words(void *scratch, int64_t layout_n) {
-  const int64_t lay_parts = (layout_n + kPart - 1) / kPart;
-  const int64_t lay_super = (lay_parts + kSuper - 1) / kSuper;
-  return reinterpret_cast<unsigned long long *>(static_cast<char *>(scratch) + sizeof(ScanHeader) +
-                                                align256(lay_super * 4) + align256(lay_super * 32));
+// Where a scratch block keeps its per-partition aggregate words.
+float *scan_aggregate_words(void *scratch, int64_t) {
+  return reinterpret_cast<float *>(static_cast<char *>(scratch) + sizeof(ScanHeader));
 }
 
 int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
@@ -736,9 +480,8 @@ int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int
     }
     scratch = scratch_of_device[dev];
   }
-  // The array starts zeroed when the module is loaded and every launch leaves it re-armed
-  // (ticket and counters back at zero, epoch advanced, older words invalid by their tag), so
-  // nothing has to be cleared between calls.
+  // The array starts zeroed when the module is loaded and every launch leaves its header
+  // re-armed (ticket and CTA counter back at zero), so nothing has to be cleared between calls.
   return launch_scan(prio, n, cdf, l1, scratch, kStaticScratchBytes, status, /*fresh=*/0, stream, kStaticMaxN);
 }
 

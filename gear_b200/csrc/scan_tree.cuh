@@ -8,7 +8,8 @@
 //   group = 4 consecutive chunks: g0=T0, g1=g0+T1, g2=g1+T2, g3=g2+T3
 //   block = 32 consecutive groups (512 values): I = Hillis-Steele inclusive scan of g3 over
 //           the groups; E = I of group q-1 (0 for q=0); block total = I of group 31
-//   part  = 8 consecutive blocks: X(0)=0, X(w+1) = X(w) + total(w)
+//   part  = 8 consecutive blocks: X(0)=0, X(w+1) = X(w) + total(w); X(8) is the partition's
+//           AGGREGATE, the number level 1 is built from
 //   chunk offset O = X + E for a group's first chunk, (X + E) + g(i-1) for its chunk i=1..3
 //   value = O + s_j, then a running maximum over the partition (max is exact, so its order is
 //           free) makes the table monotone.
@@ -52,17 +53,30 @@ struct Group {
   float total;       // block total (the same in every lane)
 };
 
-// First pass: chunk sums sv[k][0..3] of the lane's four chunks, group sums, scan over the block.
-// `bad` is raised by a negative or NaN priority.
-__device__ __forceinline__ Group block_sums(const float4 (&x)[4], float *xs, int lane, float (&sv)[4][4], bool &bad) {
+// A priority is bad when its sign bit is set (negative, or -0.0) or it is NaN.  The check is
+// folded into `bits`: the OR of all bit patterns seen, plus the sign bit when a block total is
+// NaN (a NaN anywhere in a block survives into its total).  Bad <=> bits >> 31.
+__device__ __forceinline__ void note_bits(const float4 (&x)[4], unsigned &bits) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    bad |= !(fminf(fminf(x[k].x, x[k].y), fminf(x[k].z, x[k].w)) >= 0.f);
+    bits |= __float_as_uint(x[k].x) | __float_as_uint(x[k].y);
+    bits |= __float_as_uint(x[k].z) | __float_as_uint(x[k].w);
+  }
+}
+__device__ __forceinline__ void note_total(float total, unsigned &bits) {
+  if (!(total == total)) bits |= 0x80000000u;
+}
+
+// First pass: chunk sums sv[k][0..3] of the lane's four chunks, group sums, scan over the block.
+__device__ __forceinline__ Group block_sums(const float4 (&x)[4], float *xs, int lane, float (&sv)[4][4],
+                                            unsigned &bits) {
+  note_bits(x, bits);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
     sv[k][0] = x[k].x;
     sv[k][1] = __fadd_rn(sv[k][0], x[k].y);
     sv[k][2] = __fadd_rn(sv[k][1], x[k].z);
     sv[k][3] = __fadd_rn(sv[k][2], x[k].w);
-    bad |= !(sv[k][3] >= 0.f);  // a NaN anywhere in the chunk survives into its total
     xs[k * 32 + lane] = sv[k][3];
   }
   __syncwarp();
@@ -76,7 +90,30 @@ __device__ __forceinline__ Group block_sums(const float4 (&x)[4], float *xs, int
   const float up = __shfl_up_sync(kAll, I, 1);
   g.E = lane == 0 ? 0.f : up;
   g.total = __shfl_sync(kAll, I, 31);
+  note_total(g.total, bits);
   return g;
+}
+
+// The block total alone (every lane gets it).  The last element of a Hillis-Steele scan is the
+// balanced tree (lower half + upper half at every level), which a butterfly reduction computes
+// in the lane that is the upper half at every level: lane 31.
+__device__ __forceinline__ float block_total(const float4 (&x)[4], float *xs, int lane, unsigned &bits) {
+  note_bits(x, bits);
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    xs[k * 32 + lane] = __fadd_rn(__fadd_rn(__fadd_rn(x[k].x, x[k].y), x[k].z), x[k].w);
+  __syncwarp();
+  const float4 t4 = reinterpret_cast<const float4 *>(xs)[lane];
+  float v = __fadd_rn(__fadd_rn(__fadd_rn(t4.x, t4.y), t4.z), t4.w);
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const float o = __shfl_xor_sync(kAll, v, d);
+    v = (lane & d) ? __fadd_rn(o, v) : __fadd_rn(v, o);  // lower + upper either way
+  }
+  const float total = __shfl_sync(kAll, v, 31);
+  note_total(total, bits);
+  __syncwarp();  // the exchange area may be rewritten by the caller's next block
+  return total;
 }
 
 // Second pass, given the block's offset X: makes sv the block's values (all of them, or with

@@ -15,7 +15,7 @@
 //
 //   mark_kernel     priorities[idx[i]] = value[i]; each touched partition enters a list once
 //   rescan_kernel   one CTA per listed partition: load, scan, store cdf and the aggregate word
-//   level1_kernel   one CTA: offsets from all aggregate words; clears the list for the next call
+//   launch_level1   (level1.cu) offsets from all aggregates; clears the list for the next call
 #include "common.h"
 #include "scan_tree.cuh"
 
@@ -28,14 +28,6 @@ constexpr int kPart = GEARB_PART;
 constexpr unsigned kFull = 0xffffffffu;
 static_assert(kWarps * tree::kBlockValues == kPart, "one warp per block of the partition");
 
-__device__ __forceinline__ double checked_add(double a, double b, bool &inexact) {
-  const double s = __dadd_rn(a, b);
-  const double bb = __dsub_rn(s, a);
-  const double err = __dadd_rn(__dsub_rn(a, __dsub_rn(s, bb)), __dsub_rn(b, bb));
-  inexact |= (err != 0.0);
-  return s;
-}
-
 __global__ void mark_kernel(float *prio, int64_t n, const int64_t *idx, const float *val, int64_t m,
                             unsigned *dirty, unsigned *list, unsigned *count, int32_t *status) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -46,7 +38,8 @@ __global__ void mark_kernel(float *prio, int64_t n, const int64_t *idx, const fl
     return;
   }
   const float v = val[i];
-  if (!(v >= 0.f)) atomicOr(reinterpret_cast<unsigned *>(status), GEARB_ST_BAD_PRIORITY);
+  if ((__float_as_uint(v) >> 31) || !(v == v))  // sign bit set (negative or -0.0) or NaN
+    atomicOr(reinterpret_cast<unsigned *>(status), GEARB_ST_BAD_PRIORITY);
   prio[k] = v;  // two updates of one index in a batch: one of them wins, as with any scatter
   const unsigned p = static_cast<unsigned>(k / kPart);
   if (atomicExch(&dirty[p], 1u) == 0u) list[atomicAdd(count, 1u)] = p;
@@ -55,14 +48,14 @@ __global__ void mark_kernel(float *prio, int64_t n, const int64_t *idx, const fl
 // Same tree as the compute warps of scan_kernel (scan_tree.cuh): warp w scans block w.
 // cdf == nullptr: the table is kept without its level-2 entries, only the aggregate is redone.
 __global__ void __launch_bounds__(kThreads) rescan_kernel(const float *prio, int64_t n, float *cdf,
-                                                          unsigned long long *aggw, const unsigned *list,
+                                                          float *aggw, const unsigned *list,
                                                           const unsigned *count, unsigned *dirty) {
   __shared__ float wt[kWarps], wm[kWarps];
   __shared__ __align__(16) float xs_all[kWarps][128];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   float *xs = xs_all[warp];
   const unsigned total = *count;
-  bool bad = false;  // priorities were checked when they were written (mark_kernel)
+  unsigned bits = 0;  // priorities were checked when they were written (mark_kernel)
   for (unsigned li = blockIdx.x; li < total; li += gridDim.x) {
     const unsigned p = list[li];
     const int64_t base = static_cast<int64_t>(p) * kPart;
@@ -81,22 +74,17 @@ __global__ void __launch_bounds__(kThreads) rescan_kernel(const float *prio, int
         x[k].w = (e + 3 < n) ? prio[e + 3] : 0.f;
       }
     }
-    const tree::Group g = tree::block_sums(x, xs, lane, sv, bad);
+    const tree::Group g = tree::block_sums(x, xs, lane, sv, bits);
     if (lane == 0) wt[warp] = g.total;
     __syncthreads();
     float X = 0.f;
     for (int w = 0; w < warp; ++w) X = __fadd_rn(X, wt[w]);
-    tree::block_values(X, g, xs, lane, sv, top, cdf == nullptr, e0, n);
-    float G = 0.f, run;
-    if (cdf == nullptr) {
-      run = tree::block_max(top);
+    if (cdf != nullptr) {
+      tree::block_values(X, g, xs, lane, sv, top, false, e0, n);
+      const float run = tree::block_prefix_max(top, xs, lane);
       if (lane == 0) wm[warp] = run;
       __syncthreads();
-      for (int w = 0; w < warp; ++w) G = fmaxf(G, wm[w]);
-    } else {
-      run = tree::block_prefix_max(top, xs, lane);
-      if (lane == 0) wm[warp] = run;
-      __syncthreads();
+      float G = 0.f;
       for (int w = 0; w < warp; ++w) G = fmaxf(G, wm[w]);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -113,68 +101,10 @@ __global__ void __launch_bounds__(kThreads) rescan_kernel(const float *prio, int
       }
     }
     if (tid == kThreads - 1) {
-      // only the float bits are read back (level1_kernel, and scan_kernel's in-order rebuild)
-      aggw[p] = static_cast<unsigned long long>(__float_as_uint(fmaxf(G, run)));
+      aggw[p] = __fadd_rn(X, g.total);  // aggregate X(8)
       dirty[p] = 0u;
     }
     __syncthreads();  // wt / wm are reused by the next listed partition
-  }
-}
-
-// l1[0] = 0, l1[p+1] = l1[p] + aggregate(p), in order.  Computed as: each thread sums a run of
-// consecutive aggregates, a block-wide scan joins the runs; every addition is checked, and if
-// any rounded thread 0 repeats the whole sum strictly in order (then grouping matters).
-__global__ void __launch_bounds__(1024) level1_kernel(const unsigned long long *aggw, unsigned nparts, double *l1,
-                                                      unsigned *count, int32_t *status) {
-  __shared__ double warp_tot[32];
-  __shared__ int any_inexact;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) any_inexact = 0;
-  const unsigned per = (nparts + 1023) / 1024;
-  const unsigned lo = min(nparts, tid * per), hi = min(nparts, lo + per);
-  bool inexact = false;
-  double run = 0.0;
-  for (unsigned q = lo; q < hi; ++q)
-    run = checked_add(run, static_cast<double>(__uint_as_float(static_cast<unsigned>(aggw[q]))), inexact);
-  double incl = run;
-#pragma unroll
-  for (int d = 1; d < 32; d <<= 1) {
-    const double t = __shfl_up_sync(kFull, incl, d);
-    if (lane >= d) incl = checked_add(t, incl, inexact);
-  }
-  if (lane == 31) warp_tot[warp] = incl;
-  __syncthreads();
-  if (warp == 0) {
-    double w = warp_tot[lane];
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const double t = __shfl_up_sync(kFull, w, d);
-      if (lane >= d) w = checked_add(t, w, inexact);
-    }
-    warp_tot[lane] = w;
-  }
-  __syncthreads();
-  // exclusive offset of this thread's run: warps before this one + lanes before this one
-  const double up = __shfl_up_sync(kFull, incl, 1);
-  const double excl = checked_add(warp == 0 ? 0.0 : warp_tot[warp - 1], lane == 0 ? 0.0 : up, inexact);
-  double acc = excl;
-  for (unsigned q = lo; q < hi; ++q) {
-    acc = checked_add(acc, static_cast<double>(__uint_as_float(static_cast<unsigned>(aggw[q]))), inexact);
-    l1[q + 1] = acc;
-  }
-  if (inexact) atomicOr(&any_inexact, 1);
-  __syncthreads();
-  if (tid == 0) {
-    l1[0] = 0.0;
-    if (any_inexact) {
-      double a = 0.0;
-      for (unsigned q = 0; q < nparts; ++q) {
-        a = __dadd_rn(a, static_cast<double>(__uint_as_float(static_cast<unsigned>(aggw[q]))));
-        l1[q + 1] = a;
-      }
-      atomicOr(reinterpret_cast<unsigned *>(status), GEARB_ST_L1_RESUMMED);
-    }
-    *count = 0u;
   }
 }
 
@@ -186,7 +116,7 @@ int64_t update_scratch_bytes(int64_t n) {
   return ((nparts * 4 + 255) & ~int64_t(255)) * 2 + 256;
 }
 
-int launch_update(float *prio, int64_t n, float *cdf, double *l1, unsigned long long *aggw, void *upd,
+int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, void *upd,
                   const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream) {
   GEARB_REQUIRE(n > 0 && m >= 0, "update: bad sizes");
   if (m == 0) return GEARB_OK;
@@ -204,8 +134,11 @@ int launch_update(float *prio, int64_t n, float *cdf, double *l1, unsigned long 
   if (grid > cap) grid = cap;
   rescan_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(prio, n, cdf, aggw, list, count, dirty);
   GEARB_CUDA(cudaGetLastError());
-  level1_kernel<<<1, 1024, 0, stream>>>(aggw, static_cast<unsigned>(nparts), l1, count, status);
-  GEARB_CUDA(cudaGetLastError());
+  // l1 from all aggregates (level1.cu); the list of touched partitions is cleared for the next call
+  {
+    int rc = launch_level1(aggw, nparts, l1, count, status, stream);
+    if (rc != GEARB_OK) return rc;
+  }
   return GEARB_OK;
 }
 

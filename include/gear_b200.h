@@ -34,9 +34,9 @@ extern "C" {
 #define GEARB_ERR_UNSUPPORTED 7
 
 /* Bits of the device status word written by the kernels (status[0]).        */
-#define GEARB_ST_LOOKBACK_TIMEOUT 0x1 /* scan: a look-back wait gave up; level-1 was rebuilt in order */
+#define GEARB_ST_LOOKBACK_TIMEOUT 0x1 /* reserved (raised by an earlier look-back scheme; never set now)  */
 #define GEARB_ST_L1_RESUMMED 0x2      /* scan: a float64 partial sum was inexact; level-1 was rebuilt in order */
-#define GEARB_ST_BAD_PRIORITY 0x4     /* scan: a priority was negative or NaN   */
+#define GEARB_ST_BAD_PRIORITY 0x4     /* scan: a priority had its sign bit set (negative, -0.0) or was NaN */
 #define GEARB_ST_BAD_REQUEST 0x8      /* gather: trajectory index outside the table, request skipped */
 #define GEARB_ST_LEN_CLAMPED 0x10     /* gather: a length beyond trajectory_length was clamped */
 #define GEARB_ST_SCAN_ABORTED 0x20    /* scan: a bounded wait inside a CTA ran out; cdf and l1 are NOT valid */
@@ -168,7 +168,7 @@ int64_t gearb_scan_scratch_bytes(int64_t n);
 int gearb_scan(const float *priorities, int64_t n, float *cdf, double *l1, void *scratch,
                int64_t scratch_bytes, int32_t *status, void *stream);
 /* gearb_scan without any allocation by anyone: the scratch is an array inside the
- * library image (672,000 bytes of device memory on every GPU that loads the library,
+ * library image (262,400 bytes of device memory on every GPU that loads the library,
  * held until the process exits), enough for n <= gearb_scan_static_max_n() =
  * 268,435,456 priorities; a larger n is refused with GEARB_ERR_UNSUPPORTED.
  * No counterpart in the reference -- it is for callers that must not, or cannot,

@@ -24,7 +24,7 @@ void gearo_fused_subcopy(const uint8_t *table, uint8_t *dst, const int64_t *idx,
 typedef struct {
   const float *prio;
   float *cdf;
-  double *agg; /* last cdf entry of every partition */
+  double *agg; /* aggregate of every partition */
   int64_t n, p0, p1;
   int bad;
 } scan_job;
@@ -36,7 +36,7 @@ static void *scan_worker(void *arg) {
     const int64_t lo = p * GEARO_PART;
     const int64_t valid = (j->n - lo < GEARO_PART) ? (j->n - lo) : GEARO_PART;
     j->bad |= gearo_scan(j->prio + lo, valid, j->cdf + lo, l1, &total);
-    j->agg[p] = (double)j->cdf[lo + valid - 1];
+    j->agg[p] = l1[1];
   }
   return NULL;
 }

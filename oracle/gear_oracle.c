@@ -188,8 +188,10 @@ void gearo_fused_subcopy(const uint8_t *table, uint8_t *dst, const int64_t *idx,
  * stored table is non-decreasing and "first entry greater than r" is well
  * defined for any search order.  Entries past n count as zero.
  *
- * Level 1: l1[0]=0, l1[p+1] = l1[p] + (double)cdf[last entry of partition p],
- * added in partition order in float64.  total = l1[nparts].
+ * Level 1: l1[0]=0, l1[p+1] = l1[p] + (double)aggregate(p), added in partition order in
+ * float64, where aggregate(p) = X(8) is the partition's eight block totals added in sequence
+ * (it can differ from the partition's last cdf entry by an ulp; the search pulls a variate
+ * that lands on or above the last entry just below it).  total = l1[nparts].
  *
  * The sum of the reference's one_dimension_sum (src/cuda/one_dim_sum.cu:22-74)
  * is folded into this: `total` replaces it, without the atomicAdd whose order
@@ -202,8 +204,9 @@ static void hs_scan32(float v[32]) {
   }
 }
 
-static void scan_partition(const float *x, int64_t valid, float *out) {
-  /* x: up to GEARO_PART inputs (valid of them real), out: GEARO_PART values */
+static float scan_partition(const float *x, int64_t valid, float *out) {
+  /* x: up to GEARO_PART inputs (valid of them real), out: GEARO_PART values.
+   * Returns the partition's aggregate: its block totals added in sequence.   */
   float s[GEARO_PART];               /* running sums inside each chunk           */
   float gprev[GEARO_PART / 4];       /* g(i-1) of every chunk (unused for i = 0) */
   float E[GEARO_PART / 16];          /* exclusive offset of every group          */
@@ -245,10 +248,11 @@ static void scan_partition(const float *x, int64_t valid, float *out) {
       }
     }
   }
+  return X + Y[GEARO_BLOCKS - 1];
 }
 
-/* Returns 0, or 1 when a priority is negative or NaN (the table is then
- * meaningless; the CUDA path raises the same flag).                          */
+/* Returns 0, or 1 when a priority has its sign bit set (negative, or -0.0) or is NaN (the
+ * table is then meaningless; the CUDA path raises the same flag).            */
 int gearo_scan(const float *prio, int64_t n, float *cdf, double *l1 /* nparts+1 */,
                double *total) {
   const int64_t nparts = (n + GEARO_PART - 1) / GEARO_PART;
@@ -260,10 +264,10 @@ int gearo_scan(const float *prio, int64_t n, float *cdf, double *l1 /* nparts+1 
     const int64_t lo = p * GEARO_PART;
     const int64_t valid = (n - lo < GEARO_PART) ? (n - lo) : GEARO_PART;
     for (int64_t i = 0; i < valid; ++i)
-      if (!(prio[lo + i] >= 0.0f)) bad = 1;
-    scan_partition(prio + lo, valid, buf);
+      if (signbit(prio[lo + i]) || isnan(prio[lo + i])) bad = 1;
+    const float agg = scan_partition(prio + lo, valid, buf);
     memcpy(cdf + lo, buf, (size_t)valid * sizeof(float));
-    acc = acc + (double)buf[valid - 1];
+    acc = acc + (double)agg;
     l1[p + 1] = acc;
   }
   *total = acc;

@@ -279,12 +279,12 @@ def np_scan(prio: np.ndarray):
     o = off[..., None] + s                                 # [P,W,32,4,4]
     o = o.reshape(nparts, PART).astype(np.float32)
     cdf = np.maximum.accumulate(o, axis=1)
-    last_idx = np.minimum(np.arange(1, nparts + 1) * PART, n) - 1
     flat = cdf.reshape(-1)
+    agg = X[:, BLOCKS - 1] + I[:, BLOCKS - 1, 31]          # block totals in sequence
     l1 = np.zeros(nparts + 1, np.float64)
     acc = 0.0
     for p in range(nparts):
-        acc = acc + float(flat[last_idx[p]])
+        acc = acc + float(agg[p])
         l1[p + 1] = acc
     return flat[:n].copy(), l1, float(acc)
 
