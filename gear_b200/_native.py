@@ -100,6 +100,8 @@ _SIGS = {
     "gearb_sampler_destroy": (C.c_int, [vp]),
     "gearb_sampler_scan": (C.c_int, [vp, vp, vp]),
     "gearb_sampler_scan_totals": (C.c_int, [vp, vp, vp]),
+    "gearb_sampler_scan_partitions": (C.c_int, [vp, vp, C.c_int, vp]),
+    "gearb_sampler_scan_level1": (C.c_int, [vp, vp]),
     "gearb_sampler_update": (C.c_int, [vp, vp, vp, vp, i64, vp]),
     "gearb_sampler_search": (C.c_int, [vp, vp, i64, C.c_int, vp, vp]),
     "gearb_sampler_sample_gather": (C.c_int, [vp, vp, vp, i64, C.c_int, vp, i64, pi32, C.c_int, C.POINTER(vp),

@@ -350,6 +350,18 @@ class PrioritySampler:
              _stream(stream))
         self._lazy_source = None if store else priorities      # keeps the array alive
 
+    def scan_partitions(self, priorities: torch.Tensor, store: bool = True, stream=None) -> None:
+        """First launch of a scan alone: one aggregate per partition (and, with store, the level-2
+        table).  scan_level1() must follow before the table is used."""
+        if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
+            raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
+        call("gearb_sampler_scan_partitions", self._h, _ptr(priorities), int(bool(store)), _stream(stream))
+        self._lazy_source = None if store else priorities
+
+    def scan_level1(self, stream=None) -> None:
+        """Second launch of a scan alone: the partition offsets from the aggregates."""
+        call("gearb_sampler_scan_level1", self._h, _stream(stream))
+
     def update(self, priorities: torch.Tensor, idx: torch.Tensor, values: torch.Tensor, stream=None) -> None:
         """priorities[idx] = values, then rescan only the touched partitions (after a scan())."""
         if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:

@@ -613,6 +613,20 @@ int gearb_sampler_destroy(gearb_sampler *s) {
   return GEARB_OK;
 }
 
+int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int store, void *stream) {
+  GEARB_REQUIRE(s, "sampler_scan_partitions: null sampler");
+  int rc = launch_scan(priorities, s->n, store ? s->cdf : nullptr, s->l1, s->scratch, s->scratch_bytes, s->status,
+                       0, as_stream(stream), 0, /*level1=*/false);
+  if (rc == GEARB_OK) s->lazy_prio = store ? nullptr : priorities;
+  return rc;
+}
+
+int gearb_sampler_scan_level1(gearb_sampler *s, void *stream) {
+  GEARB_REQUIRE(s, "sampler_scan_level1: null sampler");
+  return launch_level1(scan_aggregate_words(s->scratch, s->n), s->nparts, s->l1, nullptr, s->status,
+                       as_stream(stream));
+}
+
 int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan_totals: null sampler");
   int rc = launch_scan(priorities, s->n, nullptr, s->l1, s->scratch, s->scratch_bytes, s->status, 0,

@@ -372,7 +372,8 @@ int64_t scan_scratch_bytes(int64_t n) {
 }
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
-                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, int64_t layout_n) {
+                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, int64_t layout_n,
+                bool level1) {
   GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
   GEARB_REQUIRE(prio && l1 && scratch && status, "scan: null pointer argument");  // cdf may be null
   GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
@@ -424,14 +425,14 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.nbig = static_cast<unsigned>((nparts - tail) / a.group);
   a.ngroups = static_cast<unsigned>(a.nbig + (nparts - static_cast<int64_t>(a.nbig) * a.group));
 
-  a.inline_level1 = nparts <= 1024;
+  a.inline_level1 = level1 && nparts <= 1024;
   int64_t grid = resident;
   if (grid > a.ngroups) grid = a.ngroups;
   if (a.cdf) scan_kernel<true><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
   else scan_kernel<false><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
   GEARB_CUDA(cudaGetLastError());
   // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
-  return a.inline_level1 ? GEARB_OK : launch_level1(a.aggw, nparts, l1, nullptr, status, stream);
+  return (a.inline_level1 || !level1) ? GEARB_OK : launch_level1(a.aggw, nparts, l1, nullptr, status, stream);
 }
 
 // ---------------------------------------------------------------------------------------

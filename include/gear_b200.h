@@ -216,6 +216,13 @@ int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
  * last such call.  gearb_sampler_search and gearb_sampler_pull need the stored table and
  * return GEARB_ERR_STATE until the next gearb_sampler_scan.                                */
 int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream);
+/* The two launches of a scan, separately, for callers that want to put something between
+ * them (an event, work of their own): first the pass over the priorities that leaves one
+ * aggregate per partition (store != 0: and the level-2 table), then the small launch that
+ * turns the aggregates into l1.  Together they equal gearb_sampler_scan (store != 0) or
+ * gearb_sampler_scan_totals (store == 0).                                                */
+int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int store, void *stream);
+int gearb_sampler_scan_level1(gearb_sampler *s, void *stream);
 /* Incremental update after a gearb_sampler_scan of the same array: priorities[idx[i]] =
  * values[i] for i < m (idx, values: device arrays), then only the partitions that were touched
  * are rescanned and the partition offsets rebuilt.  The table afterwards is bit-identical to a

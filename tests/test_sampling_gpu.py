@@ -162,6 +162,20 @@ def test_fill_integer_kinds_match_oracle_philox(O):
     np.testing.assert_allclose(f.cpu().numpy(), O.synth_lognormal(15, 0, 4000), rtol=1e-5)
 
 
+def test_scan_in_two_launches_equals_one_call(O):
+    n = 9 * 4096 + 5
+    p = O.synth_lognormal(91, 0, n)
+    ocdf, ol1, ototal, _ = O.scan(p)
+    s = core.PrioritySampler(n)
+    for store in (True, False):
+        s.scan_partitions(dev(p), store=store)
+        s.scan_level1()
+        tot, st = s.result()
+        assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal and st[0] == 0
+        if store:
+            assert np.array_equal(s.cdf.cpu().numpy(), ocdf)
+
+
 def test_totals_only_scan_gives_the_same_level1(O):
     for n in [1, 4095, 4097, 37 * 4096 + 11, 1 << 22]:
         p = O.synth_lognormal(77, n, n)
