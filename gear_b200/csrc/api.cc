@@ -624,7 +624,7 @@ int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int
 int gearb_sampler_scan_level1(gearb_sampler *s, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan_level1: null sampler");
   return launch_level1(scan_aggregate_words(s->scratch, s->n), s->nparts, s->l1, nullptr, s->status,
-                       as_stream(stream));
+                       as_stream(stream), static_cast<ScanHeader *>(s->scratch), true);
 }
 
 int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream) {
@@ -647,7 +647,8 @@ int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx
   GEARB_REQUIRE(s, "sampler_update: null sampler");
   GEARB_REQUIRE(!s->lazy_prio || s->lazy_prio == priorities,
                 "sampler_update: not the array the table was built from");
-  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1, scan_aggregate_words(s->scratch, s->n), s->upd, idx,
+  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1, scan_aggregate_words(s->scratch, s->n),
+                       static_cast<ScanHeader *>(s->scratch), s->upd, idx,
                        values, m, s->status, as_stream(stream));
 }
 

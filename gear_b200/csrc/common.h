@@ -41,7 +41,7 @@ struct ScanHeader {
   unsigned int ticket;  // next ticket (group of partitions) to hand out
   unsigned int done;    // CTAs that have finished
   unsigned int epoch;   // launch counter; state words of other epochs read as "none"
-  unsigned int pad[61];  // pad[0]: flags of the running launch
+  unsigned int pad[61];  // pad[1..24]: words shared with the level-1 launch (level1.cu)
 };
 static_assert(sizeof(ScanHeader) == 256, "header is one 256-byte block");
 
@@ -57,9 +57,9 @@ int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int
                        cudaStream_t stream);
 float *scan_aggregate_words(void *scratch, int64_t layout_n);
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
-                  cudaStream_t stream);
+                  cudaStream_t stream, ScanHeader *hdr, bool have_range);
 int64_t update_scratch_bytes(int64_t n);
-int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, void *upd,
+int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, ScanHeader *hdr, void *upd,
                   const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream);
 int launch_search(const float *cdf, const double *l1, int64_t n, const double *u, int64_t b,
                   int flags, int64_t *out, int32_t *status, cudaStream_t stream);

@@ -2,9 +2,9 @@
 //
 // The integer route of level1.cuh costs about 70 instructions per aggregate, and one SM needs
 // 25 us for config 3's 24,415 aggregates -- a third of the scan it follows.  Eight CTAs of one
-// cluster each take an eighth of the array; what they must tell each other (the exponent
-// range, the sums of the ranks before, whether anything was inexact) travels through
-// distributed shared memory between three cluster barriers.  The kernel is launched with
+// cluster each take an eighth of the array.  The exponent range comes with the aggregates (the
+// scan leaves it in its header); the sums of the ranks before a rank travel through eight words
+// of that header behind ONE cluster barrier; the last rank to finish does the clean-up.  The kernel is launched with
 // programmatic stream serialisation behind the scan, and lets the kernel behind it start early
 // in the same way.
 #include <cooperative_groups.h>
@@ -20,16 +20,24 @@ namespace {
 constexpr int kClusterCtas = 8;
 constexpr int kClusterThreads = 512;
 
+// Words of the scan header (common.h: ScanHeader::pad) that this kernel and the scan share.
+constexpr int kPadEminInv = 1;  // max over non-zero aggregates of 256 - exponent (0: none seen)
+constexpr int kPadEmax = 2;     // max exponent
+constexpr int kPadBad = 3;      // some rank met a prefix sum that does not fit a float64
+constexpr int kPadDone = 4;     // ranks that have finished
+constexpr int kPadTotals = 9;   // 8 x 64-bit: the sum of every rank's share (8-byte aligned in the header)
+
 struct Shared {
   unsigned long long warp_tot[32];
   unsigned warp_emin[32], warp_emax[32];
-  unsigned long long total;  // this CTA's sum, read by the ranks after it
-  unsigned emin, emax;       // this CTA's exponent range, read by every rank
-  int bad;                   // this CTA met a prefix sum that does not fit a float64
+  unsigned emin, emax;
 };
 
+// have_range: the scan that produced the aggregates also left their exponent range in the
+// header; otherwise (aggregates touched by an incremental update) the cluster finds it first.
 __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterThreads)
-    level1_cluster_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status) {
+    level1_cluster_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status,
+                          ScanHeader *hdr, int have_range) {
   extern __shared__ float4 tile4[];  // level1::kTile floats
   __shared__ Shared sh;
   float *tile = reinterpret_cast<float *>(tile4);
@@ -37,6 +45,7 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
   const unsigned rank = cluster.block_rank();
   const unsigned kAll = 0xffffffffu;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kClusterThreads / 32;
+  unsigned long long *totals = reinterpret_cast<unsigned long long *>(&hdr->pad[kPadTotals]);
 
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the aggregates come from the kernel before
@@ -48,34 +57,40 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
   const unsigned run = ((count + kClusterThreads - 1) / kClusterThreads) | 1u;
   const unsigned lo = min(count, tid * run), hi = min(count, lo + run);
 
-  // ---- exponent range of the non-zero aggregates, over the whole cluster
+  // ---- exponent range of the non-zero aggregates, over the whole table
   unsigned emin = 0xffffffffu, emax = 0u;
+  if (have_range) {
+    const unsigned inv = __ldcg(&hdr->pad[kPadEminInv]);
+    emax = __ldcg(&hdr->pad[kPadEmax]);
+    emin = inv ? 256u - inv : 0xffffffffu;
+  } else {
 #pragma unroll 4
-  for (unsigned q = lo; q < hi; ++q) level1::note_exponent(__float_as_uint(tile[q]), emin, emax);
-  emin = __reduce_min_sync(kAll, emin);
-  emax = __reduce_max_sync(kAll, emax);
-  if (lane == 0) {
-    sh.warp_emin[warp] = emin;
-    sh.warp_emax[warp] = emax;
-  }
-  __syncthreads();
-  if (tid == 0) {
-    unsigned a = 0xffffffffu, b = 0u;
-    for (int w = 0; w < nwarps; ++w) {
-      a = min(a, sh.warp_emin[w]);
-      b = max(b, sh.warp_emax[w]);
+    for (unsigned q = lo; q < hi; ++q) level1::note_exponent(__float_as_uint(tile[q]), emin, emax);
+    emin = __reduce_min_sync(kAll, emin);
+    emax = __reduce_max_sync(kAll, emax);
+    if (lane == 0) {
+      sh.warp_emin[warp] = emin;
+      sh.warp_emax[warp] = emax;
     }
-    sh.emin = a;
-    sh.emax = b;
-    sh.bad = 0;
-  }
-  cluster.sync();
-  emin = 0xffffffffu;
-  emax = 0u;
-  for (unsigned r = 0; r < kClusterCtas; ++r) {
-    const Shared *peer = cluster.map_shared_rank(&sh, r);
-    emin = min(emin, peer->emin);
-    emax = max(emax, peer->emax);
+    __syncthreads();
+    if (tid == 0) {
+      unsigned a = 0xffffffffu, b = 0u;
+      for (int w = 0; w < nwarps; ++w) {
+        a = min(a, sh.warp_emin[w]);
+        b = max(b, sh.warp_emax[w]);
+      }
+      sh.emin = a;
+      sh.emax = b;
+    }
+    cluster.sync();
+    emin = 0xffffffffu;
+    emax = 0u;
+    for (unsigned r = 0; r < kClusterCtas; ++r) {
+      const Shared *peer = cluster.map_shared_rank(&sh, r);
+      emin = min(emin, peer->emin);
+      emax = max(emax, peer->emax);
+    }
+    cluster.sync();  // nobody's shared memory is read by a peer after this point
   }
   if (emax == 0u) emin = 1u;  // all zero
   const bool wide = level1::too_wide(emin, emax, nparts);  // the same verdict in every thread of the cluster
@@ -105,16 +120,16 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
       if (lane >= d) w += o;
     }
     const unsigned long long before = __shfl_up_sync(kAll, w, 1);
-    if (lane == 31) sh.total = w;  // lanes past the last warp hold zeros: this is the share's sum
+    if (lane == 31) __stcg(&totals[rank], w);  // lanes past the last warp hold zeros: the share's sum
     sh.warp_tot[lane] = lane == 0 ? 0ull : before;  // exclusive: the warps before this one
   }
-  cluster.sync();
+  cluster.sync();  // every rank's sum is in global memory (the barrier orders it for the cluster)
 
   // ---- offsets out: the ranks before this one, the warps before this one, the lanes before this one
   bool inexact = false;
   if (!wide) {
     unsigned long long acc = 0ull;
-    for (unsigned r = 0; r < rank; ++r) acc += cluster.map_shared_rank(&sh, r)->total;
+    for (unsigned r = 0; r < rank; ++r) acc += __ldcg(&totals[r]);
     const unsigned long long up = __shfl_up_sync(kAll, incl, 1);
     acc += sh.warp_tot[warp] + (lane == 0 ? 0ull : up);
 #pragma unroll 4
@@ -125,33 +140,44 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
     }
     if (rank == 0 && tid == 0) __stcg(&l1[0], 0.0);
   }
-  if (inexact) atomicOr(&sh.bad, 1);
-  cluster.sync();
-  bool redo = wide;
-  for (unsigned r = 0; r < kClusterCtas; ++r) redo |= cluster.map_shared_rank(&sh, r)->bad != 0;
-  cluster.sync();  // nobody leaves while a peer may still read its shared memory
-  if (rank == 0 && tid == 0) {
-    if (redo) level1::in_order(agg, nparts, l1, status);
-    if (clear_word) *clear_word = 0u;
+  // ---- last rank out: the in-order repeat if anyone needs it, and the header's words back to zero
+  if (__syncthreads_or(inexact) && tid == 0) atomicOr(&hdr->pad[kPadBad], 1u);
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(&hdr->pad[kPadDone], 1u) == kClusterCtas - 1) {
+      __threadfence();
+      if (wide || atomicOr(&hdr->pad[kPadBad], 0u)) level1::in_order(agg, nparts, l1, status);
+      hdr->pad[kPadEminInv] = 0u;
+      hdr->pad[kPadEmax] = 0u;
+      hdr->pad[kPadBad] = 0u;
+      hdr->pad[kPadDone] = 0u;
+      if (clear_word) *clear_word = 0u;
+    }
   }
 }
 
 // One CTA, any size: the tiles are walked in sequence (level1::build).
 __global__ void __launch_bounds__(1024)
-    level1_single_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status) {
+    level1_single_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status,
+                         ScanHeader *hdr) {
   extern __shared__ float4 tile4[];
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   level1::build(agg, nparts, l1, status, reinterpret_cast<float *>(tile4));
-  if (threadIdx.x == 0 && clear_word) *clear_word = 0u;
+  if (threadIdx.x == 0) {
+    hdr->pad[kPadEminInv] = 0u;  // left by the scan, not used here
+    hdr->pad[kPadEmax] = 0u;
+    if (clear_word) *clear_word = 0u;
+  }
 }
 
 }  // namespace
 
 // l1 from the aggregates of `nparts` partitions; `clear_word`, when given, is zeroed at the end
-// (the incremental update's list counter).
+// (the incremental update's list counter).  hdr: the header of the scratch block the aggregates
+// live in; have_range: the scan that wrote them left their exponent range there.
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, ScanHeader *hdr, bool have_range) {
   constexpr int kTileBytes = level1::kTile * sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {
@@ -171,11 +197,12 @@ int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_
   if (nparts <= static_cast<int64_t>(kClusterCtas) * (level1::kTile - 4)) {
     cfg.gridDim = dim3(kClusterCtas);
     cfg.blockDim = dim3(kClusterThreads);
-    GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_cluster_kernel, agg, np, l1, clear_word, status));
+    GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_cluster_kernel, agg, np, l1, clear_word, status, hdr,
+                                  static_cast<int>(have_range)));
   } else {
     cfg.gridDim = dim3(1);
     cfg.blockDim = dim3(1024);
-    GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_single_kernel, agg, np, l1, clear_word, status));
+    GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_single_kernel, agg, np, l1, clear_word, status, hdr));
   }
   return GEARB_OK;
 }

@@ -199,8 +199,10 @@ __device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
 }
 
 // One partition's aggregate to its word in global memory (read back by the last CTA).
-__device__ __forceinline__ void hand_over(const ScanArgs &a, int part, float agg) {
+// The exponent range of the aggregates is collected on the way for the level-1 launch.
+__device__ __forceinline__ void hand_over(const ScanArgs &a, int part, float agg, unsigned &emin, unsigned &emax) {
   a.aggw[part] = agg;
+  level1::note_exponent(__float_as_uint(agg), emin, emax);
 }
 
 // ----------------------------------------------------------------- compute warps
@@ -212,6 +214,7 @@ __device__ __forceinline__ void hand_over(const ScanArgs &a, int part, float agg
 template <bool kStore>
 __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
   unsigned bits = 0;  // OR of the bit patterns seen: the sign bit ends up set if a priority was bad
+  unsigned emin = 0xffffffffu, emax = 0u;  // exponent range of the aggregates this CTA produced (warp 7, lane 0)
   float *xs = sm.xs[warp];
   for (unsigned it = 0;; ++it) {
     const unsigned s = it % kStages;
@@ -246,7 +249,7 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
         float X = 0.f;
 #pragma unroll
         for (int w = 0; w < kComputeWarps; ++w) X = __fadd_rn(X, sm.wt[buf][w]);
-        hand_over(a, part, X);
+        hand_over(a, part, X, emin, emax);
       }
       continue;  // wt[buf] is next written two rounds on, behind the next round's barrier
     }
@@ -264,7 +267,7 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
     float X = 0.f;
     for (int w = 0; w < warp; ++w) X = __fadd_rn(X, sm.wt[buf][w]);
     // the last warp also knows the partition's aggregate X(8): hand it over
-    if (warp == kComputeWarps - 1 && lane == 0) hand_over(a, part, __fadd_rn(X, g.total));
+    if (warp == kComputeWarps - 1 && lane == 0) hand_over(a, part, __fadd_rn(X, g.total), emin, emax);
 
     // ---- second pass: values, then the running maximum block by block
     tree::block_values(X, g, xs, lane, sv, top, false, e0, a.n);
@@ -296,6 +299,10 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
   }
   if (__any_sync(kFull, (bits >> 31) != 0) && lane == 0)
     atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_BAD_PRIORITY);
+  if (warp == kComputeWarps - 1 && lane == 0 && emax != 0u && !a.inline_level1) {
+    atomicMax(&a.hdr->pad[1], 256u - emin);  // the level-1 launch reads and clears these (level1.cu)
+    atomicMax(&a.hdr->pad[2], emax);
+  }
 }
 
 // Last CTA out: the header is re-armed for the next launch.  For a small table the last CTA
@@ -432,7 +439,8 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   else scan_kernel<false><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
   GEARB_CUDA(cudaGetLastError());
   // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
-  return (a.inline_level1 || !level1) ? GEARB_OK : launch_level1(a.aggw, nparts, l1, nullptr, status, stream);
+  return (a.inline_level1 || !level1) ? GEARB_OK
+                                       : launch_level1(a.aggw, nparts, l1, nullptr, status, stream, a.hdr, true);
 }
 
 // ---------------------------------------------------------------------------------------

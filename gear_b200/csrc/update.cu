@@ -116,7 +116,7 @@ int64_t update_scratch_bytes(int64_t n) {
   return ((nparts * 4 + 255) & ~int64_t(255)) * 2 + 256;
 }
 
-int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, void *upd,
+int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, ScanHeader *hdr, void *upd,
                   const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream) {
   GEARB_REQUIRE(n > 0 && m >= 0, "update: bad sizes");
   if (m == 0) return GEARB_OK;
@@ -136,7 +136,7 @@ int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, v
   GEARB_CUDA(cudaGetLastError());
   // l1 from all aggregates (level1.cu); the list of touched partitions is cleared for the next call
   {
-    int rc = launch_level1(aggw, nparts, l1, count, status, stream);
+    int rc = launch_level1(aggw, nparts, l1, count, status, stream, hdr, false);
     if (rc != GEARB_OK) return rc;
   }
   return GEARB_OK;
