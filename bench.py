@@ -232,33 +232,45 @@ def run_ours_single(args):
     torch.cuda.synchronize()
     upd_ms = e3[0].elapsed_time(e3[1]) / K
 
-    # ---- end to end through the C ABI with host buffers (pinned): variates in, batch out
+    # ---- end to end through the public API with host buffers (pinned): variates in, batch out.
+    #      Two batches in flight: the copy-out of a batch overlaps the sampling of the next
+    #      (gear_b200.pipeline.HostBatchPipeline); `serial` is the same with one batch at a time.
+    from gear_b200.pipeline import HostBatchPipeline
     u_host = torch.empty(nbatches * B, dtype=torch.float64).pin_memory()
     u_host.copy_(u_dev.cpu())
-    u_stage = torch.empty(B, dtype=torch.float64, device=dev)
-    out_host = [torch.empty(B * L * r, dtype=torch.uint8).pin_memory() for r in rows]
-    flat_host = torch.empty(B, dtype=torch.int64).pin_memory()
-
-    def e2e_step(i):
-        u_stage.copy_(u_host[(i % nbatches) * B:(i % nbatches + 1) * B], non_blocking=True)
-        sampler.scan(prio, store=False)
-        sampler.sample_gather(handler, u_stage, cols, dsts, scale=True, zero_fill=True, out_flat=flat)
-        for h, d in zip(out_host, dsts):
-            h.copy_(d, non_blocking=True)
-        flat_host.copy_(flat, non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the caller owns the batch when the call returns
-
     Ke = max(10, min(K, 400))
-    for i in range(3):
-        e2e_step(i)
-    torch.cuda.synchronize()
-    w0 = time.perf_counter()
-    for i in range(Ke):
-        e2e_step(i)
-    torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - w0) / Ke
+
+    def e2e_run(depth):
+        pipe = HostBatchPipeline(sampler, handler, cols, B, depth=depth)
+        ub = lambda i: u_host[(i % nbatches) * B:(i % nbatches + 1) * B]
+        for i in range(4):
+            pipe.submit(prio, ub(i))
+            if i >= depth - 1:
+                pipe.next()
+        pipe.drain()
+        torch.cuda.synchronize()
+        w0 = time.perf_counter()
+        for i in range(Ke):
+            pipe.submit(prio, ub(i))
+            if i >= depth - 1:
+                pipe.next()                     # the caller holds a complete batch in host memory here
+        pipe.drain()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - w0) / Ke, pipe
+
+    serial_s, _ = e2e_run(1)
+    e2e_s, pipe = e2e_run(2)
     e2e = {"value": B * L / e2e_s, "unit": UNIT, "h2d_bytes_per_step": B * 8,
-           "d2h_bytes_per_step": gathered + B * 8, "ms_per_step": e2e_s * 1e3, "steps": Ke}
+           "d2h_bytes_per_step": gathered + B * 8, "ms_per_step": e2e_s * 1e3, "steps": Ke,
+           "batches_in_flight": 2,
+           "serial": {"value": B * L / serial_s, "ms_per_step": serial_s * 1e3, "batches_in_flight": 1}}
+    # the last pipelined batch, in host memory, against the device-side result of the same variates
+    hc, hf = pipe._host_cols[(Ke - 1) % 2], pipe._host_flat[(Ke - 1) % 2]
+    sampler.scan(prio, store=False)
+    sampler.sample_gather(handler, batch(Ke - 1), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
+    torch.cuda.synchronize()
+    e2e["matches_device_result"] = bool(torch.equal(hf, flat.cpu()) and all(
+        torch.equal(h, d.cpu()) for h, d in zip(hc, dsts)))
 
     # ---- parity of one batch against the CPU oracle + CPU baseline (bounded sample)
     core.fill(prio, N.FILL_F32_LOGNORMAL, seed=0x6EA20103)      # undo the incremental mode's updates

@@ -307,8 +307,8 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
           const int blk = warp + h * kWarps;
 #pragma unroll
           for (int k = 0; k < 4; ++k) x[k] = pv4[(blk * 4 + k) * 32 + lane];
-          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bits);
-          if (lane == 0) blk_total[blk] = gq.total;
+          const float total = tree::block_total(x, xs, lane, bits);
+          if (lane == 0) blk_total[blk] = total;
         }
         __syncthreads();
         // second pass: values, written back over the priorities; block maxima

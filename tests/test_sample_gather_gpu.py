@@ -164,3 +164,37 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
                 want.reshape(B, L * r)[m] = part.reshape(len(m), L * r)
             assert np.array_equal(dsts[c].cpu().numpy(), want), (trial, c)
     assert shards[0][3].result()[1][0] == 0
+
+
+def test_host_batch_pipeline_delivers_the_same_batches(O):
+    from gear_b200.pipeline import HostBatchPipeline
+    rows, T, cap, B, L = [156, 24, 4, 4, 1], 200, 64, 96, 16
+    t, img = build(O, rows, T, cap, seed=77)
+    h = core.StorageHandler(t)
+    cols = list(range(len(rows)))
+    h.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * len(rows))
+    n = cap * T
+    prio = O.synth_lognormal(78, 0, n)
+    dprio = dev(prio)
+    s = core.PrioritySampler(n)
+    ocdf, ol1, _, _ = O.scan(prio)
+    pipe = HostBatchPipeline(s, h, cols, B, depth=2)
+    us = [torch.from_numpy(O.synth_u01(80 + i, 0, B)).pin_memory() for i in range(5)]
+    got = []
+    for i, u in enumerate(us):
+        pipe.submit(dprio, u)
+        if i >= 1:
+            hc, hf = pipe.next()
+            got.append(([c.clone() for c in hc], hf.clone()))
+    while len(got) < len(us):
+        hc, hf = pipe.next()
+        got.append(([c.clone() for c in hc], hf.clone()))
+    with pytest.raises(core.GearError):
+        pipe.next()
+    for u, (hc, hf) in zip(us, got):
+        want_flat = O.search(ocdf, ol1, u.numpy(), scale=True)
+        assert np.array_equal(hf.numpy(), want_flat)
+        oi, ot, ol = O.decode(want_flat, T)
+        for c, r in enumerate(rows):
+            want = O.fused_subcopy(img, oi, ot, ol, t.trajectory_stride, t.accu[c], T, r, 0, L, False)
+            assert np.array_equal(hc[c].numpy(), want)
