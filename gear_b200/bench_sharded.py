@@ -102,8 +102,7 @@ def run(args):
         scan_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(Ki)]
         for i in range(Ki):
             scan_ev[i][0].record()
-            replay.scan_for_step()
-            scan_ev[i][1].record()
+            replay.scan_for_step(scan_ev[i][1].record)   # second event right behind scan_kernel, before level 1
             step(i, False)
         barrier()
         ms = torch.tensor([e0.elapsed_time(e1) / K, sum(a.elapsed_time(c) for a, c in scan_ev) / Ki],
@@ -120,13 +119,14 @@ def run(args):
         solo_u = [x[rank::world].contiguous() for x in batches_dev]
         replay = ShardedReplay(handler, sampler, cols, 0, 1, None, max_global_batch=b)
         replay.enable_pull(double_buffer=True, ring=False)
-        replay.scan_for_step = lambda: replay.pull_scan(prio)
+        replay.scan_for_step = lambda mid: replay.pull_scan(prio, between=mid)
         solo_ms, _, _ = timed(lambda i, rescan: replay.step_pull(prio, solo_u[i % nb], rescan=rescan), False)
         replay.disable_pull()
         replay = full
 
     # mode 1: owners search + gather into send regions, one grouped NCCL all-to-all per step
-    replay.scan_for_step = lambda: replay.scan(prio)
+    replay.scan_for_step = lambda mid: (replay.sampler.scan_partitions(prio, store=True), mid(),
+                                        replay.sampler.scan_level1())
     a2a_ms, a2a_scan_ms, clk_a2a = timed(
         lambda i, rescan: replay.step_sorted(prio, batches[i % nb], batches_dev[i % nb], rescan=rescan),
         sample_clocks=False)
@@ -135,7 +135,7 @@ def run(args):
     # mode 2: no exchange step -- requesters read the owners' HBM in place over NVLink
     ring = os.environ.get("GEAR_BENCH_PULL_RING", "1") != "0"      # tuning knob; rings are the default
     replay.enable_pull(double_buffer=True, ring=ring)
-    replay.scan_for_step = lambda: replay.pull_scan(prio)
+    replay.scan_for_step = lambda mid: replay.pull_scan(prio, between=mid)
     pull_ms, pull_scan_ms, clk = timed(
         lambda i, rescan: replay.step_pull(prio, batches_dev[i % nb], rescan=rescan), sample_clocks=True)
     parity = sharded_parity(replay, table, handler, prio, batches[0], rank, world, dev, T, rows, L, b, "pull")
@@ -188,7 +188,7 @@ def run(args):
                 "note": "each GPU alone on its own shard with the same per-GPU batch, max over ranks"},
             "gathered_gb_s": 2 * gathered * world / (ms_step * 1e-3) / 1e9,
             "exchanged_bytes_per_step_per_gpu": int(gathered * (world - 1) / world),
-            "roofline": {"kernel": "scan_kernel<true> + level1_cluster_kernel, timed together", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "roofline": {"kernel": "scan_kernel<true>", "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
                          "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms},
             "cpu_baseline": None,

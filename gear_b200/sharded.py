@@ -312,10 +312,17 @@ class ShardedReplay:
             core.ipc_close(p)
         self._pull_mapped = []
 
-    def pull_scan(self, priorities) -> None:
-        """Rebuild this shard's cumulative table into the buffer the next step_pull(rescan=False) reads."""
+    def pull_scan(self, priorities, between=None) -> None:
+        """Rebuild this shard's cumulative table into the buffer the next step_pull(rescan=False) reads.
+        between: called between the scan's two launches (a benchmark records an event there)."""
         self._pull_k += 1
-        self._pull_samplers[self._pull_k % len(self._pull_samplers)].scan(priorities)
+        sm = self._pull_samplers[self._pull_k % len(self._pull_samplers)]
+        if between is None:
+            sm.scan(priorities)
+        else:
+            sm.scan_partitions(priorities, store=True)
+            between()
+            sm.scan_level1()
 
     def step_pull(self, priorities, u01_sorted_dev, rescan: bool = True):
         """One global batch without an exchange step: nothing on the host depends on device
