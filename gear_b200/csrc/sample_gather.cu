@@ -167,6 +167,9 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
   }
   __syncthreads();
 
+  // A scan launched right behind this kernel may start while it runs (it only reads the
+  // priorities and writes its own scratch; it waits for this grid before it lets level 1 go).
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // Everything this kernel reads may have been written by the kernel before it in the stream.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 

@@ -355,6 +355,11 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
   else loader_warp(sm, a, lane);
 
   __syncthreads();
+  // The totals-only instance may have been started while the kernel before it in the stream was
+  // still running (programmatic stream serialisation): it only read the priorities and wrote its
+  // own scratch so far.  What follows it (level 1) overwrites l1, which that kernel may be reading,
+  // so this grid must not complete before that one has.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // Bulk copies still in flight into this CTA's shared memory (only after an abort) must land
   // before the CTA retires.
   if (sm.abort && tid == 0) {
@@ -435,9 +440,24 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.inline_level1 = level1 && nparts <= 1024;
   int64_t grid = resident;
   if (grid > a.ngroups) grid = a.ngroups;
-  if (a.cdf) scan_kernel<true><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
-  else scan_kernel<false><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
-  GEARB_CUDA(cudaGetLastError());
+  if (a.cdf) {
+    scan_kernel<true><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
+    GEARB_CUDA(cudaGetLastError());
+  } else {
+    // May overlap the end of the kernel before it (see the kernel's last lines): the storing
+    // instance may not, it overwrites the table that kernel may be searching.
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GEARB_CUDA(cudaLaunchKernelEx(&cfg, scan_kernel<false>, a));
+  }
   // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
   return (a.inline_level1 || !level1) ? GEARB_OK
                                        : launch_level1(a.aggw, nparts, l1, nullptr, status, stream, a.hdr, true);
