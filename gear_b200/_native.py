@@ -29,6 +29,7 @@ PAD_INACTIVE, PAD_HEAD, PAD_TAIL = 0, 1, 2
 MAX_COLUMNS = 16
 MAX_SHARDS = 16
 IPC_HANDLE_BYTES = 64
+MAILBOX_BYTES = 2 * MAX_SHARDS * 16
 SEARCH_SCALE = 1
 
 DT_F32, DT_F64, DT_I64, DT_F16 = range(4)
@@ -113,6 +114,12 @@ _SIGS = {
     "gearb_ipc_close": (C.c_int, [vp]),
     "gearb_sampler_pull": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), vp, i64,
                                      pi32, C.c_int, C.POINTER(vp), C.c_int, C.c_int, vp, vp, vp, vp]),
+    "gearb_device_alloc": (C.c_int, [i64, C.POINTER(vp)]),
+    "gearb_device_free": (C.c_int, [vp]),
+    "gearb_sampler_publish_total": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(vp), u64, vp]),
+    "gearb_sampler_pull_mailbox": (C.c_int, [vp, vp, C.c_int, C.c_int, vp, u64, C.POINTER(vp), C.POINTER(vp),
+                                             C.POINTER(vp), vp, i64, pi32, C.c_int, C.POINTER(vp), C.c_int, C.c_int,
+                                             vp, vp, vp, vp]),
     "gearb_sampler_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp)]),
     "gearb_sampler_result": (C.c_int, [vp, vp, C.POINTER(f64), pi32]),
     "gearb_comm_unique_id": (C.c_int, [C.c_char_p]),

@@ -134,7 +134,7 @@ def run(args):
 
     # mode 2: no exchange step -- requesters read the owners' HBM in place over NVLink
     ring = os.environ.get("GEAR_BENCH_PULL_RING", "1") != "0"      # tuning knob; rings are the default
-    replay.enable_pull(double_buffer=True, ring=ring)
+    replay.enable_pull(double_buffer=True, ring=ring, mailbox=os.environ.get("GEAR_BENCH_PULL_MAILBOX", "1") != "0")
     replay.scan_for_step = lambda mid: replay.pull_scan(prio, between=mid)
     pull_ms, pull_scan_ms, clk = timed(
         lambda i, rescan: replay.step_pull(prio, batches_dev[i % nb], rescan=rescan), sample_clocks=True)
@@ -176,8 +176,8 @@ def run(args):
                        "batch_per_gpu": b, "global_batch": Bg, "segment_length": L, "priorities_per_gpu": n_local,
                        "table_bytes_per_gpu": table.nbytes, "parallelism": f"trajectory-id shards x{world}",
                        "l2": "inputs larger than L2 (128 MB of priorities re-read every step per GPU)",
-                       "step": "scan + all-gather of shard totals + one launch that routes, searches and gathers "
-                               "from the owners' HBM over NVLink (no exchange step)"},
+                       "step": "scan + level 1 + shard totals written into every rank's mailbox + one launch that "
+                               "routes, searches and gathers from the owners' HBM over NVLink (no collective)"},
             "exchange_modes": {
                 "pull_over_nvlink": {"ms_per_step": pull_ms, "value": Bg * L / (pull_ms * 1e-3), "parity": parity},
                 "nccl_alltoall": {"ms_per_step": a2a_ms, "value": Bg * L / (a2a_ms * 1e-3), "parity": parity_a2a,

@@ -20,7 +20,7 @@ from ._native import GearError, call, lib
 __all__ = [
     "GearError", "SubscribePattern", "TrajectoryTable", "StorageHandler", "Indexset",
     "PrioritySampler", "scan", "search", "sample_uniform", "decode", "fill", "vcopy", "copy",
-    "init", "device_count", "ipc_export", "ipc_open", "ipc_close",
+    "init", "device_count", "ipc_export", "ipc_open", "ipc_close", "DeviceBuffer",
 ]
 
 
@@ -423,17 +423,21 @@ class PrioritySampler:
              tables: Sequence[int], variates: torch.Tensor, columns: Sequence[int], dsts: Sequence[torch.Tensor],
              zero_fill: bool = True, ring: bool = False, out_flat: Optional[torch.Tensor] = None,
              out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None, stream=None,
-             self_shard: int = -1) -> None:
+             self_shard: int = -1, mailbox: int = 0, epoch: int = 0) -> None:
         """This rank's slice of a global batch, read in place from `len(tables)` equal shards.
 
         totals: float64 CUDA tensor, one total priority per shard.  cdfs / l1s / tables: device
         addresses (ints) of every shard's tables, valid on the current device -- this process's
         own allocations or mappings from ipc_open().  variates are U[0,1) of the global draw.
-        self_shard: the shard in this GPU's own memory (its large requests skip the ring)."""
+        self_shard: the shard in this GPU's own memory (its large requests skip the ring).
+        mailbox / epoch: instead of `totals`, take them from this rank's mailbox (device address) once
+        every rank's publish_total() of this epoch has arrived there."""
         w = len(tables)
-        if not (len(cdfs) == len(l1s) == w) or totals.dtype != torch.float64 or not totals.is_cuda \
-                or totals.numel() < w:
-            raise GearError(N.ERR_INVALID, "pull: one cdf, l1, table and float64 CUDA total per shard")
+        if len(cdfs) != w or len(l1s) != w:
+            raise GearError(N.ERR_INVALID, "pull: one cdf, l1 and table per shard")
+        if not mailbox and (totals is None or totals.dtype != torch.float64 or not totals.is_cuda
+                            or totals.numel() < w):
+            raise GearError(N.ERR_INVALID, "pull: a float64 CUDA total per shard (or a mailbox) is required")
         if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
             raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
         b = variates.numel()
@@ -451,10 +455,24 @@ class PrioritySampler:
                 raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
         nc = len(columns)
         arr = lambda v: (C.c_void_p * w)(*[int(x) for x in v])
+        if mailbox:
+            call("gearb_sampler_pull_mailbox", self._h, handler._h, w, int(self_shard), C.c_void_p(int(mailbox)),
+                 C.c_uint64(int(epoch)), arr(cdfs), arr(l1s), arr(tables), _ptr(variates), b,
+                 (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
+                 (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)), int(bool(ring)),
+                 _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _stream(stream))
+            return
         call("gearb_sampler_pull", self._h, handler._h, w, int(self_shard), _ptr(totals), arr(cdfs), arr(l1s), arr(tables),
              _ptr(variates), b, (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
              (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)), int(bool(ring)),
              _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _stream(stream))
+
+    def publish_total(self, world: int, rank: int, mailboxes: Sequence[int], epoch: int, stream=None) -> None:
+        """This shard's total, then `epoch`, into every rank's mailbox (device addresses valid on this
+        device: the own one and the peers' as mapped by ipc_open)."""
+        arr = (C.c_void_p * int(world))(*[int(x) for x in mailboxes])
+        call("gearb_sampler_publish_total", self._h, int(world), int(rank), arr, C.c_uint64(int(epoch)),
+             _stream(stream))
 
     def result(self, stream=None):
         """(total, status words) after synchronising the stream."""
@@ -537,3 +555,26 @@ def ipc_open(handle: bytes) -> int:
 
 def ipc_close(device_ptr: int) -> None:
     call("gearb_ipc_close", C.c_void_p(int(device_ptr)))
+
+
+class DeviceBuffer:
+    """Zero-initialised device memory from the library's own allocator: unlike a tensor of a
+    caching allocator it starts at the beginning of its allocation, so ipc_export() can hand it
+    to other processes."""
+
+    def __init__(self, nbytes: int):
+        self.nbytes = int(nbytes)
+        p = C.c_void_p(0)
+        call("gearb_device_alloc", self.nbytes, C.byref(p))
+        self.ptr = p.value
+
+    def free(self) -> None:
+        if self.ptr:
+            call("gearb_device_free", C.c_void_p(self.ptr))
+            self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

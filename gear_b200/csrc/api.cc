@@ -716,6 +716,47 @@ int gearb_ipc_close(void *device_ptr) {
   return GEARB_OK;
 }
 
+int gearb_device_alloc(int64_t bytes, void **ptr) {
+  GEARB_REQUIRE(ptr && bytes > 0, "device_alloc: bad argument");
+  cudaError_t e = cudaMalloc(ptr, static_cast<size_t>(bytes));
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(GEARB_ERR_NOMEM, "cudaMalloc(%lld bytes) failed: %s", (long long)bytes, cudaGetErrorString(e));
+  }
+  GEARB_CUDA(cudaMemset(*ptr, 0, static_cast<size_t>(bytes)));
+  return GEARB_OK;
+}
+
+int gearb_device_free(void *ptr) {
+  if (ptr) GEARB_CUDA(cudaFree(ptr));
+  return GEARB_OK;
+}
+
+int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
+                                void *stream) {
+  GEARB_REQUIRE(s, "publish_total: null sampler");
+  return launch_publish_total(s->l1 + s->nparts, world, rank, mailboxes, epoch, as_stream(stream));
+}
+
+int gearb_sampler_pull_mailbox(gearb_sampler *s, gearb_handler *h, int world, int self, const void *mailbox,
+                               uint64_t epoch, const void *const *cdf, const void *const *l1,
+                               const void *const *table, const double *variates, int64_t b, const int32_t *columns,
+                               int ncols, void *const *dst, int zero_fill, int ring, int64_t *out_flat,
+                               int64_t *out_idx, int64_t *out_ts, void *stream) {
+  GEARB_REQUIRE(s && mailbox, "pull: null sampler or mailbox");
+  if (s->lazy_prio) return fail(GEARB_ERR_STATE, "pull: the table was built without its level-2 entries");
+  GatherParams p;
+  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
+  if (rc != GEARB_OK) return rc;
+  GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
+                "pull: %lld priorities but a shard holds only %lld steps", (long long)s->n,
+                (long long)(h->table->capacity * h->table->T));
+  GEARB_REQUIRE(h->table->hbm, "pull: the shards must be in device memory");
+  if (p.stage_bytes == 0) p.ring = ring ? 1 : 0;
+  return launch_pull(p, world, self, nullptr, cdf, l1, table, s->n, variates, out_flat, out_idx, out_ts,
+                     as_stream(stream), mailbox, epoch);
+}
+
 int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, int self, const double *totals,
                        const void *const *cdf, const void *const *l1, const void *const *table,
                        const double *variates, int64_t b, const int32_t *columns, int ncols,

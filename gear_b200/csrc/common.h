@@ -107,7 +107,10 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
                          const float *lazy_prio = nullptr);
 int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,
                 const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
-                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream);
+                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream,
+                const void *mailbox = nullptr, unsigned long long epoch = 0);
+int launch_publish_total(const double *total, int world, int rank, void *const *mailboxes,
+                         unsigned long long epoch, cudaStream_t stream);
 int launch_vcopy(const uint8_t *src, uint8_t *dst, const int64_t *src_off,
                  const int64_t *dst_off, const int64_t *lengths, int64_t fixed_length,
                  int64_t n, int64_t max_length, cudaStream_t stream);

@@ -126,6 +126,10 @@ struct PeerArgs {
   int world;             // 0: not sharded
   int self;              // the shard that lives in this GPU's own memory, or -1
   const double *totals;  // float64[world], total priority of every shard (device memory)
+  // When the totals arrive in a mailbox that the peers write directly (publish_kernel), the words
+  // they set to the step's epoch AFTER their total; null: `totals` is complete at launch.
+  const unsigned long long *epochs;
+  unsigned long long epoch;
   const float *cdf[GEARB_MAX_SHARDS];
   const double *l1[GEARB_MAX_SHARDS];
   const uint8_t *table[GEARB_MAX_SHARDS];
@@ -173,6 +177,36 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
   // Everything this kernel reads may have been written by the kernel before it in the stream.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
+  if (kPeers && peers.epochs) {
+    // The shard totals are written into this GPU's mailbox by the peers themselves: wait (with a
+    // limit) until every rank's word carries this step's epoch; its total was written before it.
+    if (warp == 0) {
+      bool ok = true;
+      if (lane < peers.world) {
+        unsigned polls = 0;
+        for (;;) {
+          unsigned long long seen;
+          asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(peers.epochs + lane) : "memory");
+          if (seen >= peers.epoch) break;
+          if (++polls > kWaitLimit) {
+            ok = false;
+            break;
+          }
+          __nanosleep(200);
+        }
+      }
+      if (!__all_sync(kFull, ok) && lane == 0) masks[0][0] = 0xdeadu;
+      else if (lane == 0) masks[0][0] = 0u;
+    }
+    __syncthreads();
+    const bool late = masks[0][0] == 0xdeadu;
+    __syncthreads();  // masks is reused by the search
+    if (late) {  // a peer never published: report, touch nothing
+      if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
+      return;
+    }
+  }
+
   for (int64_t g = blockIdx.x; g < P.n; g += gridDim.x) {
     // ---- which shard: sharded tables route the request by the shard totals first
     const float *cdf = a.cdf;
@@ -184,7 +218,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
       // In-order float64 prefix of the shard totals, as the host router computes it
       // (route() in gear_b200/sharded.py): shard j owns prefix[j] <= v < prefix[j+1].
       double gtotal = 0.0;
-      for (int j = 0; j < peers.world; ++j) gtotal = __dadd_rn(gtotal, __ldg(peers.totals + j));
+      for (int j = 0; j < peers.world; ++j) gtotal = __dadd_rn(gtotal, __ldcg(peers.totals + j));
       v = __dmul_rn(v, gtotal);
       if (!(v >= 0.0)) v = 0.0;
       if (!(v < gtotal)) v = __longlong_as_double(__double_as_longlong(gtotal) - 1);
@@ -192,7 +226,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
       owner = peers.world - 1;
       for (int j = 0; j < peers.world; ++j) {
         before = acc;
-        acc = __dadd_rn(before, __ldg(peers.totals + j));
+        acc = __dadd_rn(before, __ldcg(peers.totals + j));
         if (acc > v) {
           owner = j;
           break;
@@ -587,17 +621,69 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
   return launch_any(p, a, peers, stream);
 }
 
+namespace {
+struct Mailboxes {
+  void *box[GEARB_MAX_SHARDS];
+};
+// One rank's total into slot (epoch & 1) of every rank's mailbox, then the epoch: lane j serves rank j.
+__global__ void publish_kernel(const double *total, Mailboxes m, int world, int rank, unsigned long long epoch) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the total comes from the level-1 launch before
+  const int j = threadIdx.x;
+  if (j >= world) return;
+  const unsigned slot = static_cast<unsigned>(epoch & 1u);
+  char *box = static_cast<char *>(m.box[j]);
+  double *tot = reinterpret_cast<double *>(box) + slot * GEARB_MAX_SHARDS + rank;
+  unsigned long long *ep =
+      reinterpret_cast<unsigned long long *>(box + 2 * GEARB_MAX_SHARDS * 8) + slot * GEARB_MAX_SHARDS + rank;
+  const double t = __ldcg(total);
+  asm volatile("st.relaxed.sys.global.f64 [%0], %1;" ::"l"(tot), "d"(t) : "memory");
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(ep), "l"(epoch) : "memory");
+}
+}  // namespace
+
+int launch_publish_total(const double *total, int world, int rank, void *const *mailboxes,
+                         unsigned long long epoch, cudaStream_t stream) {
+  GEARB_REQUIRE(world >= 1 && world <= GEARB_MAX_SHARDS && rank >= 0 && rank < world, "publish: bad rank or world");
+  GEARB_REQUIRE(total && mailboxes && epoch > 0, "publish: null argument or epoch 0");
+  Mailboxes m = {};
+  for (int j = 0; j < world; ++j) {
+    GEARB_REQUIRE(mailboxes[j], "publish: null mailbox for rank %d", j);
+    m.box[j] = mailboxes[j];
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, publish_kernel, total, m, world, rank, epoch));
+  return GEARB_OK;
+}
+
 int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,
                 const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
-                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream) {
+                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream, const void *mailbox,
+                unsigned long long epoch) {
   GEARB_REQUIRE(n > 0, "pull: the priority table is empty");
   GEARB_REQUIRE(world >= 1 && world <= GEARB_MAX_SHARDS, "pull: %d shards, at most %d", world, GEARB_MAX_SHARDS);
   if (p.n == 0) return GEARB_OK;
-  GEARB_REQUIRE(totals && peer_cdf && peer_l1 && peer_table && u, "pull: null pointer argument");
+  GEARB_REQUIRE((totals || mailbox) && peer_cdf && peer_l1 && peer_table && u, "pull: null pointer argument");
   PeerArgs peers = {};
   peers.world = world;
   peers.self = self;
   peers.totals = totals;
+  if (mailbox) {  // totals and epoch words of the step's slot in this rank's mailbox
+    GEARB_REQUIRE(epoch > 0, "pull: epoch 0 with a mailbox");
+    const char *box = static_cast<const char *>(mailbox);
+    const unsigned slot = static_cast<unsigned>(epoch & 1u);
+    peers.totals = reinterpret_cast<const double *>(box) + slot * GEARB_MAX_SHARDS;
+    peers.epochs = reinterpret_cast<const unsigned long long *>(box + 2 * GEARB_MAX_SHARDS * 8) + slot * GEARB_MAX_SHARDS;
+    peers.epoch = epoch;
+  }
   for (int j = 0; j < world; ++j) {
     GEARB_REQUIRE(peer_cdf[j] && peer_l1[j] && peer_table[j], "pull: null pointer for shard %d", j);
     peers.cdf[j] = static_cast<const float *>(peer_cdf[j]);

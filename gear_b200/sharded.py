@@ -259,8 +259,12 @@ class ShardedReplay:
         return [r[: b * s] for r, s in zip(self.recv, self.slots)], gflat
 
     # -- exchange-free mode: requesters read the owners' memory in place ---------------------
-    def enable_pull(self, double_buffer: bool = True, ring: bool = False) -> None:
+    def enable_pull(self, double_buffer: bool = True, ring: bool = False, mailbox: bool = True) -> None:
         """Map every peer's shard into this process (collective: every rank calls it once).
+
+        mailbox: the shard totals travel without a collective -- every rank writes its total and
+        the step's number straight into every rank's mailbox, and the pull launch waits (with a
+        limit) until all of them have arrived; needs double_buffer.  Otherwise an NCCL all-gather.
 
         double_buffer: alternate between two cumulative tables so that the totals' all-gather is
         the only synchronisation of a step; otherwise one table and a second (8-byte) collective
@@ -273,7 +277,9 @@ class ShardedReplay:
         self._pull_ring = bool(ring)
         self._pull_samplers = [self.sampler] + ([core.PrioritySampler(self.n_local)] if double_buffer else [])
         self._pull_k = -1
-        own = [self.handler.table.device_ptr]
+        self._pull_box = core.DeviceBuffer(self.N.MAILBOX_BYTES) if (mailbox and double_buffer) else None
+        self._pull_epoch = 0
+        own = [self.handler.table.device_ptr] + ([self._pull_box.ptr] if self._pull_box else [])
         for sm in self._pull_samplers:
             own += [sm.cdf_ptr, sm.l1_ptr]
         nh = len(own)
@@ -297,8 +303,10 @@ class ShardedReplay:
                 self._pull_mapped += row
                 ptrs.append(row)
         self._pull_tables = [row[0] for row in ptrs]
-        self._pull_cdfs = [[row[1 + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
-        self._pull_l1s = [[row[2 + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
+        o = 2 if self._pull_box else 1
+        self._pull_boxes = [row[1] for row in ptrs] if self._pull_box else None
+        self._pull_cdfs = [[row[o + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
+        self._pull_l1s = [[row[o + 1 + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
         self._pull_fence = torch.zeros(1, dtype=torch.float32, device=self.dev)
 
     def disable_pull(self) -> None:
@@ -311,6 +319,12 @@ class ShardedReplay:
         for p in self._pull_mapped:
             core.ipc_close(p)
         self._pull_mapped = []
+        if getattr(self, "_pull_box", None) is not None:
+            if self.world > 1:
+                self.comm.allreduce(self._pull_fence)      # every rank has unmapped this mailbox
+                self.torch.cuda.synchronize()
+            self._pull_box.free()
+            self._pull_box = None
 
     def pull_scan(self, priorities, between=None) -> None:
         """Rebuild this shard's cumulative table into the buffer the next step_pull(rescan=False) reads.
@@ -338,6 +352,16 @@ class ShardedReplay:
             self.pull_scan(priorities)
         k = self._pull_k % nbuf
         sm = self._pull_samplers[k]
+        mine_slice = slice(self.rank * b, (self.rank + 1) * b)
+        if self._pull_box is not None:
+            # totals through the mailboxes: no collective, no host involvement
+            self._pull_epoch += 1
+            sm.publish_total(self.world, self.rank, self._pull_boxes, self._pull_epoch)
+            sm.pull(self.handler, None, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables,
+                    u01_sorted_dev[mine_slice], self.columns, self.recv, zero_fill=True, ring=self._pull_ring,
+                    out_flat=self.recv_flat, self_shard=self.rank, mailbox=self._pull_box.ptr,
+                    epoch=self._pull_epoch)
+            return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]
         nparts = (self.n_local + self.N.PART - 1) // self.N.PART
         mine = sm.l1[nparts:nparts + 1]
         if self.world == 1:
@@ -345,7 +369,7 @@ class ShardedReplay:
         else:
             self.comm.allgather(mine, self.totals_dev)   # every shard's scan is complete once this lands
         sm.pull(self.handler, self.totals_dev, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables,
-                u01_sorted_dev[self.rank * b:(self.rank + 1) * b], self.columns, self.recv, zero_fill=True,
+                u01_sorted_dev[mine_slice], self.columns, self.recv, zero_fill=True,
                 ring=self._pull_ring, out_flat=self.recv_flat, self_shard=self.rank)
         if nbuf == 1 and self.world > 1:
             self.comm.allreduce(self._pull_fence)        # the next scan must not overtake the peers' reads

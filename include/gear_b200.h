@@ -318,6 +318,26 @@ int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, int self, 
                        void *const *dst, int zero_fill, int ring, int64_t *out_flat, int64_t *out_idx,
                        int64_t *out_ts, void *stream);
 
+/* The all-gather of the shard totals without a collective: every rank writes its total
+ * straight into every rank's MAILBOX (a zero-initialised device allocation of
+ * GEARB_MAILBOX_BYTES per rank, e.g. from gearb_device_alloc, exported to the peers with
+ * gearb_ipc_export) followed by the step's epoch; the pull launch waits, with a limit, until
+ * all `world` epoch words of its own mailbox have reached the epoch (GEARB_ST_SCAN_ABORTED if
+ * one never does).  Epochs count steps from 1; slot epoch & 1 of the mailbox is used, so a
+ * rank may be one step ahead of its peers but not two -- which the waiting itself ensures.
+ * No counterpart in the reference (its totals never leave rank 0, gear/sampler/global_sampler.py:105-152). */
+#define GEARB_MAILBOX_BYTES (2 * GEARB_MAX_SHARDS * 16)
+int gearb_device_alloc(int64_t bytes, void **ptr); /* cudaMalloc, zeroed */
+int gearb_device_free(void *ptr);
+int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
+                                void *stream);
+/* gearb_sampler_pull with the totals taken from this rank's mailbox at `epoch`. */
+int gearb_sampler_pull_mailbox(gearb_sampler *s, gearb_handler *h, int world, int self, const void *mailbox,
+                               uint64_t epoch, const void *const *cdf, const void *const *l1,
+                               const void *const *table, const double *variates, int64_t b,
+                               const int32_t *columns, int ncols, void *const *dst, int zero_fill, int ring,
+                               int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, void *stream);
+
 /* ======================= synthetic data ================================= */
 /* Device-side Philox4x32-10 fills for benchmark tables that are too large to
  * stage through the host.  kind selects the distribution.                   */

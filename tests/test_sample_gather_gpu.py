@@ -139,10 +139,24 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
             totals_used = totals
         dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=DEV) for r in rows]
         oflat = torch.empty(B, dtype=torch.int64, device=DEV); oidx = torch.empty_like(oflat); ots = torch.empty_like(oflat)
-        shards[0][3].pull(h, dev(totals_used), [sh[3].cdf_ptr for sh in shards], [sh[3].l1_ptr for sh in shards],
-                          [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
-                          out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1))
-        torch.cuda.synchronize()
+        if trial == 0:
+            # totals through a mailbox, as separate processes would exchange them: every shard's
+            # sampler writes its own total and the epoch, the pull launch waits for all of them
+            box = core.DeviceBuffer(N.MAILBOX_BYTES)
+            for epoch in (1, 2, 3):                  # both slots, and a slot's second use
+                for j, sh in enumerate(shards):
+                    sh[3].publish_total(W, j, [box.ptr] * W, epoch)
+                shards[0][3].pull(h, None, [sh[3].cdf_ptr for sh in shards], [sh[3].l1_ptr for sh in shards],
+                                  [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
+                                  out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1),
+                                  mailbox=box.ptr, epoch=epoch)
+            torch.cuda.synchronize()
+            box.free()
+        else:
+            shards[0][3].pull(h, dev(totals_used), [sh[3].cdf_ptr for sh in shards], [sh[3].l1_ptr for sh in shards],
+                              [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
+                              out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1))
+            torch.cuda.synchronize()
         owner, residual, _ = route(totals_used, np.resize(u, B + (-B) % W), W)   # padded to a multiple of W
         owner, residual = owner[:B], residual[:B]
         want_flat = np.empty(B, np.int64)
