@@ -5,8 +5,8 @@
 // cluster each take an eighth of the array.  The exponent range comes with the aggregates (the
 // scan leaves it in its header); the sums of the ranks before a rank travel through eight words
 // of that header behind ONE cluster barrier; the last rank to finish does the clean-up.  The kernel is launched with
-// programmatic stream serialisation behind the scan, and lets the kernel behind it start early
-// in the same way.
+// programmatic stream serialisation behind the scan, and lets the kernel behind it be scheduled
+// once it has read everything it needs.
 #include <cooperative_groups.h>
 
 #include "common.h"
@@ -47,7 +47,6 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kClusterThreads / 32;
   unsigned long long *totals = reinterpret_cast<unsigned long long *>(&hdr->pad[kPadTotals]);
 
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the aggregates come from the kernel before
 
   // this rank's share: a multiple of four aggregates, so that its 16-byte copies stay aligned
@@ -153,6 +152,11 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
       hdr->pad[kPadDone] = 0u;
       if (clear_word) *clear_word = 0u;
     }
+    // Everything this launch reads has been read (by the last rank too, had it to repeat the sum
+    // in order): the launch behind it may be scheduled.  If that is the next scan of the same
+    // table it overwrites the aggregates; it touches the header's exponent-range words only
+    // after this whole grid has completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   }
 }
 
@@ -161,8 +165,7 @@ __global__ void __launch_bounds__(1024)
     level1_single_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status,
                          ScanHeader *hdr) {
   extern __shared__ float4 tile4[];
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // dependents start when this grid is done
   level1::build(agg, nparts, l1, status, reinterpret_cast<float *>(tile4));
   if (threadIdx.x == 0) {
     hdr->pad[kPadEminInv] = 0u;  // left by the scan, not used here

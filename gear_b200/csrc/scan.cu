@@ -132,6 +132,7 @@ struct __align__(128) Smem {
   float wm[2][kComputeWarps];      // block maxima
   alignas(16) float xs[kComputeWarps][128];    // per-warp exchange area: one float per chunk of the warp's block
   volatile unsigned abort;         // a bounded wait ran out somewhere in this CTA
+  unsigned emin, emax;             // exponent range of the aggregates this CTA produced
 };
 
 __device__ __forceinline__ void raise_abort(Smem &sm, const ScanArgs &a) {
@@ -299,9 +300,9 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
   }
   if (__any_sync(kFull, (bits >> 31) != 0) && lane == 0)
     atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_BAD_PRIORITY);
-  if (warp == kComputeWarps - 1 && lane == 0 && emax != 0u && !a.inline_level1) {
-    atomicMax(&a.hdr->pad[1], 256u - emin);  // the level-1 launch reads and clears these (level1.cu)
-    atomicMax(&a.hdr->pad[2], emax);
+  if (warp == kComputeWarps - 1 && lane == 0) {  // published at the very end of the kernel
+    sm.emin = emin;
+    sm.emax = emax;
   }
 }
 
@@ -346,6 +347,8 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
       mbar_init(&sm.empty[s], kComputeWarps);
     }
     sm.abort = 0;
+    sm.emin = 0xffffffffu;
+    sm.emax = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -360,6 +363,13 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
   // own scratch so far.  What follows it (level 1) overwrites l1, which that kernel may be reading,
   // so this grid must not complete before that one has.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Only now, with everything before this launch complete (a level-1 launch of an earlier scan
+  // clears these words at its end), the exponent range goes to the header for the level-1
+  // launch behind this one (level1.cu).
+  if (tid == 0 && sm.emax != 0u && !a.inline_level1) {
+    atomicMax(&a.hdr->pad[1], 256u - sm.emin);
+    atomicMax(&a.hdr->pad[2], sm.emax);
+  }
   // Bulk copies still in flight into this CTA's shared memory (only after an abort) must land
   // before the CTA retires.
   if (sm.abort && tid == 0) {

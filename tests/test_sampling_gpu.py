@@ -239,3 +239,23 @@ def test_incremental_update_inexact_level1_and_bad_index(O):
     _, st = s.result()
     assert st[0] & N.ST_BAD_REQUEST
     assert np.array_equal(dp.cpu().numpy(), p)
+
+
+def test_back_to_back_scans_of_one_sampler(O):
+    # A totals-only scan may start while the launch before it in the stream is still finishing;
+    # with nothing in between, that launch is the previous scan's level-1 launch.  Every scan must
+    # still leave exactly its own table and no spurious status.
+    n = 1500 * 4096 + 77                      # more than 1024 partitions: level 1 is its own launch
+    ps = [O.synth_lognormal(10 + i, 0, n) for i in range(3)]
+    ps[1][::3] *= 1e-3
+    dps = [dev(p) for p in ps]
+    want = O.scan(ps[2])
+    s = core.PrioritySampler(n)
+    for rep in range(5):
+        for store in (False, True):
+            for i in range(3):
+                s.scan(dps[i], store=store)
+            tot, st = s.result()
+            assert np.array_equal(s.l1.cpu().numpy(), want[1]) and tot == want[2] and st[0] == 0
+            if store:
+                assert np.array_equal(s.cdf.cpu().numpy(), want[0])
