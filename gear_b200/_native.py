@@ -101,6 +101,7 @@ _SIGS = {
     "gearb_sampler_destroy": (C.c_int, [vp]),
     "gearb_sampler_scan": (C.c_int, [vp, vp, vp]),
     "gearb_sampler_scan_totals": (C.c_int, [vp, vp, vp]),
+    "gearb_sampler_scan_alternate": (C.c_int, [vp, vp, vp]),
     "gearb_sampler_scan_partitions": (C.c_int, [vp, vp, C.c_int, vp]),
     "gearb_sampler_scan_level1": (C.c_int, [vp, vp]),
     "gearb_sampler_update": (C.c_int, [vp, vp, vp, vp, i64, vp]),

@@ -339,15 +339,18 @@ class PrioritySampler:
         call("gearb_sampler_buffers", self._h, C.byref(c), C.byref(l), C.byref(s))
         self.cdf_ptr, self.l1_ptr, self.status_ptr = c.value, l.value, s.value
 
-    def scan(self, priorities: torch.Tensor, stream=None, store: bool = True) -> None:
+    def scan(self, priorities: torch.Tensor, stream=None, store: bool = True, alternate: bool = False) -> None:
         """Build the two-level table.  store=False keeps only the partition offsets and the total
         (half the memory traffic); sample_gather then rebuilds the partition each request falls
         into from `priorities`, which must stay unchanged (and alive) until then.  search() and
-        pull() need store=True."""
+        pull() need store=True.  alternate=True (with store): this is one of two samplers used in
+        turn and the launch before this call in the stream reads only the other one's tables, so
+        the scan may start while that launch is finishing."""
         if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
             raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
-        call("gearb_sampler_scan" if store else "gearb_sampler_scan_totals", self._h, _ptr(priorities),
-             _stream(stream))
+        name = "gearb_sampler_scan_totals" if not store else ("gearb_sampler_scan_alternate" if alternate
+                                                             else "gearb_sampler_scan")
+        call(name, self._h, _ptr(priorities), _stream(stream))
         self._lazy_source = None if store else priorities      # keeps the array alive
 
     def scan_partitions(self, priorities: torch.Tensor, store: bool = True, stream=None) -> None:

@@ -635,6 +635,13 @@ int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *s
   return rc;
 }
 
+int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void *stream) {
+  GEARB_REQUIRE(s, "sampler_scan_alternate: null sampler");
+  s->lazy_prio = nullptr;
+  return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
+                     as_stream(stream), 0, true, /*overlap_previous=*/true);
+}
+
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan: null sampler");
   s->lazy_prio = nullptr;

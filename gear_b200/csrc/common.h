@@ -48,10 +48,11 @@ static_assert(sizeof(ScanHeader) == 256, "header is one 256-byte block");
 int64_t scan_scratch_bytes(int64_t n);
 // fresh != 0: scratch contents are unknown, clear them first (one memset).
 // level1 == false: only the partitions' aggregates (and the cdf) are produced; the caller
-// follows up with launch_level1 on scan_aggregate_words(scratch).
+// follows up with launch_level1 on scan_aggregate_words(scratch).  overlap_previous: the storing
+// scan may start while the kernel before it in the stream finishes (that kernel must not read cdf).
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream,
-                int64_t layout_n = 0, bool level1 = true);
+                int64_t layout_n = 0, bool level1 = true, bool overlap_previous = false);
 int64_t static_scan_max_n();
 int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
                        cudaStream_t stream);

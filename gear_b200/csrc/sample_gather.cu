@@ -172,8 +172,10 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
   __syncthreads();
 
   // A scan launched right behind this kernel may start while it runs (it only reads the
-  // priorities and writes its own scratch; it waits for this grid before it lets level 1 go).
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // priorities and writes its own scratch or the OTHER of two alternating tables; it waits for
+  // this grid before it lets level 1 go).  With peers, not before they are known to have finished
+  // their previous step (further down): they may still be reading that other table.
+  if (!(kPeers && peers.epochs)) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // Everything this kernel reads may have been written by the kernel before it in the stream.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -205,6 +207,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
       if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
       return;
     }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // every peer is past its previous step
   }
 
   for (int64_t g = blockIdx.x; g < P.n; g += gridDim.x) {

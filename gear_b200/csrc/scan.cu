@@ -358,9 +358,9 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
   else loader_warp(sm, a, lane);
 
   __syncthreads();
-  // The totals-only instance may have been started while the kernel before it in the stream was
-  // still running (programmatic stream serialisation): it only read the priorities and wrote its
-  // own scratch so far.  What follows it (level 1) overwrites l1, which that kernel may be reading,
+  // This grid may have been started while the kernel before it in the stream was still running
+  // (programmatic stream serialisation): it only read the priorities and wrote its own scratch
+  // (and, if the caller allowed that for the storing instance, its own level-2 table) so far.  What follows it (level 1) overwrites l1, which that kernel may be reading,
   // so this grid must not complete before that one has.
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // Only now, with everything before this launch complete (a level-1 launch of an earlier scan
@@ -395,7 +395,7 @@ int64_t scan_scratch_bytes(int64_t n) {
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, int64_t layout_n,
-                bool level1) {
+                bool level1, bool overlap_previous) {
   GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
   GEARB_REQUIRE(prio && l1 && scratch && status, "scan: null pointer argument");  // cdf may be null
   GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
@@ -450,12 +450,10 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.inline_level1 = level1 && nparts <= 1024;
   int64_t grid = resident;
   if (grid > a.ngroups) grid = a.ngroups;
-  if (a.cdf) {
-    scan_kernel<true><<<static_cast<unsigned>(grid), kThreads, smem_bytes, stream>>>(a);
-    GEARB_CUDA(cudaGetLastError());
-  } else {
-    // May overlap the end of the kernel before it (see the kernel's last lines): the storing
-    // instance may not, it overwrites the table that kernel may be searching.
+  {
+    // The totals-only instance may overlap the end of the kernel before it (see the kernel's last
+    // lines); the storing instance only when the caller says that kernel does not read the table
+    // being overwritten.
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(kThreads);
@@ -465,8 +463,9 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    GEARB_CUDA(cudaLaunchKernelEx(&cfg, scan_kernel<false>, a));
+    cfg.numAttrs = (a.cdf == nullptr || overlap_previous) ? 1 : 0;
+    if (a.cdf) GEARB_CUDA(cudaLaunchKernelEx(&cfg, scan_kernel<true>, a));
+    else GEARB_CUDA(cudaLaunchKernelEx(&cfg, scan_kernel<false>, a));
   }
   // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
   return (a.inline_level1 || !level1) ? GEARB_OK

@@ -332,7 +332,8 @@ class ShardedReplay:
         self._pull_k += 1
         sm = self._pull_samplers[self._pull_k % len(self._pull_samplers)]
         if between is None:
-            sm.scan(priorities)
+            # with two tables in turn, the launch before this one (the previous pull) reads the other
+            sm.scan(priorities, alternate=len(self._pull_samplers) == 2)
         else:
             sm.scan_partitions(priorities, store=True)
             between()

@@ -221,6 +221,10 @@ int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *s
  * aggregate per partition (store != 0: and the level-2 table), then the small launch that
  * turns the aggregates into l1.  Together they equal gearb_sampler_scan (store != 0) or
  * gearb_sampler_scan_totals (store == 0).                                                */
+/* gearb_sampler_scan for one of two samplers that are used in turn: the launch may start while
+ * the launch before it in the stream is still finishing, which is only correct when that launch
+ * does not read THIS sampler's tables (it reads the other one's).  It still completes after it. */
+int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void *stream);
 int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int store, void *stream);
 int gearb_sampler_scan_level1(gearb_sampler *s, void *stream);
 /* Incremental update after a gearb_sampler_scan of the same array: priorities[idx[i]] =
