@@ -672,7 +672,7 @@ def main():
         return run_zero_copy(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1 and args.workload != "c5":
         return run_ours_single(args)
-    from gear_b200 import bench_sharded
+    import bench_sharded
     return bench_sharded.run(args)
 
 

@@ -24,10 +24,10 @@ def run(args):
     import torch
     import torch.distributed as dist
 
-    from . import _native as N
-    from . import core
-    from .comm import Communicator
-    from .sharded import ShardedReplay
+    from gear_b200 import _native as N
+    from gear_b200 import core
+    from gear_b200.comm import Communicator
+    from gear_b200.sharded import ShardedReplay
 
     import bench as B  # the top-level script: shared constants and helpers
 
@@ -208,7 +208,7 @@ def sharded_parity(replay, table, handler, prio, u_sorted, rank, world, dev, T, 
     pull mode additionally every byte of the slice against the all-to-all mode's result."""
     import torch
     import torch.distributed as dist
-    from .sharded import plan_sorted
+    from gear_b200.sharded import plan_sorted
     n_local = prio.numel()
     cross = None
     if mode == "pull":
@@ -253,7 +253,7 @@ def sharded_parity(replay, table, handler, prio, u_sorted, rank, world, dev, T, 
         # totals summed in rank order, then the owner-local search.  (It coincides with one table
         # over the concatenated priorities only when a shard holds a whole number of partitions.)
         from oracle import oracle as O
-        from .sharded import route
+        from gear_b200.sharded import route
         scans = [O.scan_mt(p.cpu().numpy(), os.cpu_count() or 1) for p in allp]
         totals = np.array([sc[2] for sc in scans])
         owner, residual, _ = route(totals, u_sorted, world)
