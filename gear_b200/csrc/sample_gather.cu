@@ -32,6 +32,9 @@ constexpr unsigned kFull = 0xffffffffu;
 constexpr int kRingSlots = 3;            // per-warp ring of bulk copies for large requests
 constexpr int kRingSlotBytes = 4096 + 128;  // one 4 KiB piece plus the 16-byte blocks around a misaligned one
 constexpr unsigned kWaitLimit = 1u << 20;  // mbarrier polls before a staged copy is declared lost
+// Polls of a peer's epoch word before the peer is declared absent: about four seconds, far beyond the
+// skew between ranks of one job (host jitter included), short enough to come back from a dead peer.
+constexpr unsigned kPeerWaitLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_addr(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -190,11 +193,11 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
           unsigned long long seen;
           asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(peers.epochs + lane) : "memory");
           if (seen >= peers.epoch) break;
-          if (++polls > kWaitLimit) {
+          if (++polls > kPeerWaitLimit) {
             ok = false;
             break;
           }
-          __nanosleep(200);
+          __nanosleep(polls < 4096u ? 100 : 1000);
         }
       }
       if (!__all_sync(kFull, ok) && lane == 0) masks[0][0] = 0xdeadu;
