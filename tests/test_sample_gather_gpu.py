@@ -212,3 +212,34 @@ def test_host_batch_pipeline_delivers_the_same_batches(O):
         for c, r in enumerate(rows):
             want = O.fused_subcopy(img, oi, ot, ol, t.trajectory_stride, t.accu[c], T, r, 0, L, False)
             assert np.array_equal(hc[c].numpy(), want)
+
+
+def test_pull_gives_up_when_a_peer_never_publishes(O):
+    # The wait on the peers' epoch words is bounded: with one shard's total missing the launch
+    # comes back with GEARB_ST_SCAN_ABORTED, writes nothing, and the context stays usable.
+    rows, T, cap, L, W, B = [64, 4], 50, 40, 4, 3, 32
+    n = cap * T
+    shards = []
+    for j in range(W):
+        t, img = build(O, rows, T, cap, seed=90 + j)
+        s = core.PrioritySampler(n)
+        s.scan(dev(O.synth_lognormal(95 + j, 0, n)))
+        shards.append((t, s))
+    h = core.StorageHandler(shards[0][0])
+    cols = [0, 1]
+    h.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * 2)
+    u = dev(np.sort(O.synth_u01(99, 0, B)))
+    dsts = [torch.full((B * L * r,), 0x77, dtype=torch.uint8, device=DEV) for r in rows]
+    box = core.DeviceBuffer(N.MAILBOX_BYTES)
+    args = ([sh[1].cdf_ptr for sh in shards], [sh[1].l1_ptr for sh in shards], [sh[0].device_ptr for sh in shards])
+    for j in (0, 2):                                   # shard 1 stays silent
+        shards[j][1].publish_total(W, j, [box.ptr] * W, 1)
+    shards[0][1].pull(h, None, *args, u, cols, dsts, mailbox=box.ptr, epoch=1)
+    _, st = shards[0][1].result()
+    assert st[0] & N.ST_SCAN_ABORTED
+    assert all(bool((d == 0x77).all()) for d in dsts)  # nothing was written
+    shards[1][1].publish_total(W, 1, [box.ptr] * W, 1)
+    shards[0][1].pull(h, None, *args, u, cols, dsts, mailbox=box.ptr, epoch=1)
+    torch.cuda.synchronize()
+    assert not all(bool((d == 0x77).all()) for d in dsts)
+    box.free()
