@@ -4,9 +4,9 @@
 // (src/cuda/one_dim_prefix_sum.cu:125-273, src/cuda/one_dim_sum.cu:22-99).
 // The reference kernel is unfinished and has no caller; what is kept from it is
 // the shape of the addition tree (four values per thread in sequence, :40-49; a
-// Hillis-Steele shuffle scan over the lanes of a warp, :23-28; a second scan
-// pass over warp totals, :192-201; partition descriptors with a status word for the
-// look-back, one_dim_prefix_sum.cuh:5-10).
+// Hillis-Steele shuffle scan over the lanes of a warp, :23-28; a second pass over
+// warp totals, :192-201).  Its partition descriptors with a status word for a
+// look-back (one_dim_prefix_sum.cuh:5-10) are not used: see level 1 below.
 //
 // Level 2 (cdf): each 4096-entry partition is scanned on its own, in float32, with the
 // fixed tree written out in scan_tree.cuh (chunks of 4 in sequence, groups of 4 chunk totals
