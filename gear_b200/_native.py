@@ -15,7 +15,6 @@ LIB_PATH = Path(os.environ.get("GEAR_B200_LIB", PKG / "lib" / "libgear_b200.so")
 OK = 0
 ERR_INVALID, ERR_CUDA, ERR_NOMEM, ERR_STATE, ERR_TIMEOUT, ERR_NCCL, ERR_UNSUPPORTED = range(1, 8)
 
-ST_LOOKBACK_TIMEOUT = 0x1
 ST_L1_RESUMMED = 0x2
 ST_BAD_PRIORITY = 0x4
 ST_BAD_REQUEST = 0x8
@@ -109,7 +108,15 @@ _SIGS = {
     "gearb_sampler_sample_gather": (C.c_int, [vp, vp, vp, i64, C.c_int, vp, i64, pi32, C.c_int, C.POINTER(vp),
                                               C.c_int, vp, vp, vp, vp, vp]),
     "gearb_sampler_sample_gather_affine": (C.c_int, [vp, vp, vp, i64, f64, f64, vp, i64, pi32, C.c_int,
-                                                     C.POINTER(vp), C.c_int, vp, vp, vp, vp, vp]),
+                                                     C.POINTER(vp), C.c_int, vp, vp, vp, vp, i64, C.c_int, i64,
+                                                     pi64, vp]),
+    "gearb_sampler_select_slot": (C.c_int, [vp, C.c_int]),
+    "gearb_sampler_block_totals": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(C.c_int)]),
+    "gearb_sampler_clear_status": (C.c_int, [vp, vp]),
+    "gearb_mailbox_bytes": (i64, [i64]),
+    "gearb_mailbox_l1_offset": (i64, [i64, u64, C.c_int]),
+    "gearb_sampler_publish": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(vp), u64, C.c_int, vp]),
+    "gearb_sampler_pull_ex": (C.c_int, [vp, vp, vp, vp]),
     "gearb_ipc_export": (C.c_int, [vp, vp]),
     "gearb_ipc_open": (C.c_int, [vp, C.POINTER(vp)]),
     "gearb_ipc_close": (C.c_int, [vp]),
@@ -154,6 +161,15 @@ def check(code: int) -> None:
 
 def call(name: str, *args):
     check(getattr(lib, name)(*args))
+
+
+class PullArgs(C.Structure):
+    """gearb_pull_args of include/gear_b200.h."""
+    _fields_ = [("world", C.c_int), ("self", C.c_int), ("totals", vp), ("mailbox", vp), ("epoch", u64),
+                ("cdf", C.POINTER(vp)), ("prio", C.POINTER(vp)), ("blk", C.POINTER(vp)), ("l1", C.POINTER(vp)),
+                ("table", C.POINTER(vp)), ("variates", vp), ("b", i64), ("variate_stride", i64),
+                ("columns", pi32), ("ncols", C.c_int), ("dst", C.POINTER(vp)), ("zero_fill", C.c_int),
+                ("ring", C.c_int), ("out_flat", vp), ("out_idx", vp), ("out_ts", vp)]
 
 
 def declared_symbols() -> list[str]:

@@ -90,6 +90,21 @@ class Communicator:
         call("gearb_comm_alltoallv", self._h, nb, (C.c_void_p * nb)(*[t.data_ptr() for t in send]), p(so), p(sb),
              (C.c_void_p * nb)(*[t.data_ptr() for t in recv]), p(ro), p(rb), _stream())
 
+    def connect_all(self) -> None:
+        """One small message between every pair of ranks (collective).  NCCL builds the connection
+        of a pair on its first send/recv, which takes milliseconds; after this call no later
+        all-to-all pays for that, whichever pairs it happens to use."""
+        W = self.world
+        if W <= 1:
+            return
+        s = torch.zeros(W * 16, dtype=torch.uint8, device="cuda")
+        r = torch.empty(W * 16, dtype=torch.uint8, device="cuda")
+        ones = np.ones(W, np.int64)
+        first = np.arange(W, dtype=np.int64)
+        for _ in range(2):
+            self.alltoallv([s], [r], [16], first, ones, first, ones)
+        torch.cuda.current_stream().synchronize()
+
     def close(self) -> None:
         if self._h:
             lib.gearb_comm_destroy(self._h)

@@ -390,10 +390,14 @@ class PrioritySampler:
                       zero_fill: bool = True, out_flat: Optional[torch.Tensor] = None,
                       out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None,
                       out_len: Optional[torch.Tensor] = None, stream=None,
-                      affine: Optional[tuple] = None) -> None:
+                      affine: Optional[tuple] = None, flat_offset: int = 0,
+                      slot_map: Optional[tuple] = None, dst_requests: Optional[int] = None) -> None:
         """Search every variate, decode it to (trajectory, timestep, length) and gather the
         listed columns of the handler's table, all in one launch.  affine=(mul, sub): the
-        variates belong to a global draw over several shards and become u*mul - sub first."""
+        variates belong to a global draw over several shards and become u*mul - sub first;
+        flat_offset is then added to out_flat, and slot_map=(mod, lo, base) sends the request at
+        position q = lo + i of the global batch to slot base[q % mod] + q // mod of the
+        destinations (dst_requests: how many slots they must hold, default one per variate)."""
         if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
             raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
         b = variates.numel()
@@ -402,19 +406,23 @@ class PrioritySampler:
         for c, d in zip(columns, dsts):
             p = handler.patterns.get(int(c))
             if p is not None:
-                need = b * p.length * handler.table.row_bytes[int(c)]
+                need = (b if dst_requests is None else int(dst_requests)) * p.length * handler.table.row_bytes[int(c)]
                 if not d.is_cuda or not d.is_contiguous() or d.numel() * d.element_size() < need:
                     raise GearError(N.ERR_INVALID,
                                     f"destination of column {c} must be a contiguous CUDA tensor of >= {need} bytes")
         for name, t in (("out_flat", out_flat), ("out_idx", out_idx), ("out_ts", out_ts), ("out_len", out_len)):
-            if t is not None and (t.dtype != torch.int64 or not t.is_cuda or t.numel() < b):
+            if t is not None and (t.dtype != torch.int64 or not t.is_cuda
+                                  or t.numel() < (b if dst_requests is None else int(dst_requests))):
                 raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
         nc = len(columns)
         if affine is not None:
+            mod, lo, base = (1, 0, None) if slot_map is None else slot_map
+            base_arr = None if base is None else (C.c_int64 * int(mod))(*[int(x) for x in base])
             call("gearb_sampler_sample_gather_affine", self._h, handler._h, _ptr(variates), b, float(affine[0]),
                  float(affine[1]), _ptr(lengths), int(index_offset), (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
                  (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)),
-                 _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _ptr(out_len), _stream(stream))
+                 _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _ptr(out_len), int(flat_offset), int(mod), int(lo),
+                 base_arr, _stream(stream))
             return
         call("gearb_sampler_sample_gather", self._h, handler._h, _ptr(variates), b,
              N.SEARCH_SCALE if scale else 0, _ptr(lengths), int(index_offset),
@@ -422,11 +430,13 @@ class PrioritySampler:
              (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)),
              _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _ptr(out_len), _stream(stream))
 
-    def pull(self, handler: "StorageHandler", totals: torch.Tensor, cdfs: Sequence[int], l1s: Sequence[int],
-             tables: Sequence[int], variates: torch.Tensor, columns: Sequence[int], dsts: Sequence[torch.Tensor],
-             zero_fill: bool = True, ring: bool = False, out_flat: Optional[torch.Tensor] = None,
-             out_idx: Optional[torch.Tensor] = None, out_ts: Optional[torch.Tensor] = None, stream=None,
-             self_shard: int = -1, mailbox: int = 0, epoch: int = 0) -> None:
+    def pull(self, handler: "StorageHandler", totals: Optional[torch.Tensor], cdfs: Optional[Sequence[int]],
+             l1s: Sequence[int], tables: Sequence[int], variates: torch.Tensor, columns: Sequence[int],
+             dsts: Sequence[torch.Tensor], zero_fill: bool = True, ring: bool = False,
+             out_flat: Optional[torch.Tensor] = None, out_idx: Optional[torch.Tensor] = None,
+             out_ts: Optional[torch.Tensor] = None, stream=None, self_shard: int = -1, mailbox: int = 0,
+             epoch: int = 0, prios: Optional[Sequence[int]] = None, blks: Optional[Sequence[int]] = None,
+             count: Optional[int] = None, variate_stride: int = 1) -> None:
         """This rank's slice of a global batch, read in place from `len(tables)` equal shards.
 
         totals: float64 CUDA tensor, one total priority per shard.  cdfs / l1s / tables: device
@@ -434,16 +444,23 @@ class PrioritySampler:
         own allocations or mappings from ipc_open().  variates are U[0,1) of the global draw.
         self_shard: the shard in this GPU's own memory (its large requests skip the ring).
         mailbox / epoch: instead of `totals`, take them from this rank's mailbox (device address) once
-        every rank's publish_total() of this epoch has arrived there."""
+        every rank's publish() of this epoch has arrived there.
+        cdfs=None with prios / blks: the shards keep no level-2 table (scan(store=False)); the launch
+        rebuilds what each request needs from the owner's priorities and block totals.
+        count / variate_stride: request g (of `count`) uses variates[g * variate_stride]."""
         w = len(tables)
-        if len(cdfs) != w or len(l1s) != w:
-            raise GearError(N.ERR_INVALID, "pull: one cdf, l1 and table per shard")
+        lazy = cdfs is None
+        if len(l1s) != w or (not lazy and len(cdfs) != w) or (lazy and (prios is None or len(prios) != w)):
+            raise GearError(N.ERR_INVALID, "pull: one level-2 table (or priority array), l1 and table per shard")
         if not mailbox and (totals is None or totals.dtype != torch.float64 or not totals.is_cuda
                             or totals.numel() < w):
             raise GearError(N.ERR_INVALID, "pull: a float64 CUDA total per shard (or a mailbox) is required")
         if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
             raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
-        b = variates.numel()
+        stride = int(variate_stride)
+        b = variates.numel() if count is None else int(count)
+        if stride < 1 or (b > 0 and (b - 1) * stride >= variates.numel()):
+            raise GearError(N.ERR_INVALID, "pull: count and variate_stride run past the variates")
         if len(dsts) != len(columns):
             raise GearError(N.ERR_INVALID, "one destination per column is required")
         for c, d in zip(columns, dsts):
@@ -457,31 +474,59 @@ class PrioritySampler:
             if t is not None and (t.dtype != torch.int64 or not t.is_cuda or t.numel() < b):
                 raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
         nc = len(columns)
-        arr = lambda v: (C.c_void_p * w)(*[int(x) for x in v])
-        if mailbox:
-            call("gearb_sampler_pull_mailbox", self._h, handler._h, w, int(self_shard), C.c_void_p(int(mailbox)),
-                 C.c_uint64(int(epoch)), arr(cdfs), arr(l1s), arr(tables), _ptr(variates), b,
-                 (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
-                 (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)), int(bool(ring)),
-                 _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _stream(stream))
-            return
-        call("gearb_sampler_pull", self._h, handler._h, w, int(self_shard), _ptr(totals), arr(cdfs), arr(l1s), arr(tables),
-             _ptr(variates), b, (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
-             (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)), int(bool(ring)),
-             _ptr(out_flat), _ptr(out_idx), _ptr(out_ts), _stream(stream))
+        arr = lambda v: None if v is None else (C.c_void_p * w)(*[int(x) for x in v])
+        a = N.PullArgs()
+        a.world, a.self = w, int(self_shard)
+        a.totals = None if mailbox else totals.data_ptr()
+        a.mailbox, a.epoch = (int(mailbox) or None), int(epoch)
+        keep = [arr(cdfs), arr(prios if lazy else None), arr(blks if lazy else None), arr(l1s), arr(tables),
+                (C.c_int32 * nc)(*[int(c) for c in columns]), (C.c_void_p * nc)(*[d.data_ptr() for d in dsts])]
+        a.cdf = keep[0] if keep[0] is not None else C.POINTER(C.c_void_p)()
+        a.prio = keep[1] if keep[1] is not None else C.POINTER(C.c_void_p)()
+        a.blk = keep[2] if keep[2] is not None else C.POINTER(C.c_void_p)()
+        a.l1, a.table = keep[3], keep[4]
+        a.variates, a.b, a.variate_stride = variates.data_ptr(), b, stride
+        a.columns, a.ncols, a.dst = keep[5], nc, keep[6]
+        a.zero_fill, a.ring = int(bool(zero_fill)), int(bool(ring))
+        a.out_flat = None if out_flat is None else out_flat.data_ptr()
+        a.out_idx = None if out_idx is None else out_idx.data_ptr()
+        a.out_ts = None if out_ts is None else out_ts.data_ptr()
+        call("gearb_sampler_pull_ex", self._h, handler._h, C.byref(a), _stream(stream))
+
+    def publish(self, world: int, rank: int, mailboxes: Sequence[int], epoch: int, copy_l1: bool = False,
+                stream=None) -> None:
+        """This shard's total, then `epoch`, into every rank's mailbox (device addresses valid on this
+        device: the own one and the peers' as mapped by ipc_open); with copy_l1 the level-1 table goes
+        into the other ranks' mailboxes first (they must then be mailbox_bytes(n) large)."""
+        arr = (C.c_void_p * int(world))(*[int(x) for x in mailboxes])
+        call("gearb_sampler_publish", self._h, int(world), int(rank), arr, C.c_uint64(int(epoch)),
+             int(bool(copy_l1)), _stream(stream))
 
     def publish_total(self, world: int, rank: int, mailboxes: Sequence[int], epoch: int, stream=None) -> None:
-        """This shard's total, then `epoch`, into every rank's mailbox (device addresses valid on this
-        device: the own one and the peers' as mapped by ipc_open)."""
-        arr = (C.c_void_p * int(world))(*[int(x) for x in mailboxes])
-        call("gearb_sampler_publish_total", self._h, int(world), int(rank), arr, C.c_uint64(int(epoch)),
-             _stream(stream))
+        self.publish(world, rank, mailboxes, epoch, False, stream)
+
+    def select_slot(self, slot: int) -> None:
+        """Which of the two block-total buffers the NEXT scan writes (ranks of a pull agree on epoch & 1)."""
+        call("gearb_sampler_select_slot", self._h, int(slot))
+
+    def block_totals(self):
+        """(address of buffer 0, address of buffer 1, slot written by the last scan)."""
+        a, b, cur = C.c_void_p(0), C.c_void_p(0), C.c_int(0)
+        call("gearb_sampler_block_totals", self._h, C.byref(a), C.byref(b), C.byref(cur))
+        return a.value, b.value, cur.value
+
+    def clear_status(self, stream=None) -> None:
+        """Zero the status words (they accumulate across launches)."""
+        call("gearb_sampler_clear_status", self._h, _stream(stream))
 
     def result(self, stream=None):
-        """(total, status words) after synchronising the stream."""
+        """(total, status words) after synchronising the stream.  ST_SCAN_ABORTED in status[0] means a
+        bounded wait on the device ran out (the C call returns GEARB_ERR_TIMEOUT then)."""
         total = C.c_double(0.0)
         st = (C.c_int32 * N.STATUS_WORDS)()
-        call("gearb_sampler_result", self._h, _stream(stream), C.byref(total), st)
+        rc = lib.gearb_sampler_result(self._h, _stream(stream), C.byref(total), st)
+        if rc not in (N.OK, N.ERR_TIMEOUT):     # a timed-out device wait is reported through the status words
+            N.check(rc)
         return total.value, list(st)
 
     @property
@@ -540,6 +585,16 @@ def copy(src_ptr: int, dst: torch.Tensor, src_off: torch.Tensor, dst_off: torch.
          _dev_i64(dst_off, "dst_offsets"), n, int(length), _stream(stream))
 
 
+def mailbox_bytes(n: int = 0) -> int:
+    """Size of a mailbox: the header alone (n = 0), or with room for the peers' level-1 copies."""
+    return int(lib.gearb_mailbox_bytes(int(n)))
+
+
+def mailbox_l1_offset(n: int, epoch: int, shard: int) -> int:
+    """Byte offset, inside a mailbox_bytes(n) mailbox, of shard's level-1 copy for that epoch."""
+    return int(lib.gearb_mailbox_l1_offset(int(n), C.c_uint64(int(epoch)), int(shard)))
+
+
 def ipc_export(device_ptr: int) -> bytes:
     """64-byte handle of a device allocation of this process, for the other ranks of the box."""
     buf = C.create_string_buffer(N.IPC_HANDLE_BYTES)
@@ -570,6 +625,10 @@ class DeviceBuffer:
         p = C.c_void_p(0)
         call("gearb_device_alloc", self.nbytes, C.byref(p))
         self.ptr = p.value
+
+    def view(self, dtype: torch.dtype) -> torch.Tensor:
+        """The whole buffer as a tensor of `dtype` (the buffer must outlive the tensor)."""
+        return device_view(self.ptr, self.nbytes // torch.empty(0, dtype=dtype).element_size(), dtype)
 
     def free(self) -> None:
         if self.ptr:

@@ -50,6 +50,27 @@ int sm_count() {
   return n;
 }
 
+int per_device_once(int slot, int (*setup)(int *value), int *value) {
+  constexpr int kMaxDevices = 64;
+  static std::mutex mu;
+  static bool done[kOnceSlots][kMaxDevices] = {};
+  static int vals[kOnceSlots][kMaxDevices] = {};
+  int dev = 0;
+  GEARB_CUDA(cudaGetDevice(&dev));
+  GEARB_REQUIRE(slot >= 0 && slot < kOnceSlots && dev >= 0 && dev < kMaxDevices,
+                "device ordinal %d not supported", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[slot][dev]) {
+    int v = 0;
+    const int rc = setup(&v);
+    if (rc != GEARB_OK) return rc;
+    vals[slot][dev] = v;
+    done[slot][dev] = true;
+  }
+  if (value) *value = vals[slot][dev];
+  return GEARB_OK;
+}
+
 static bool have_cuda_device() {
   static int state = -1;
   if (state < 0) {
@@ -189,6 +210,17 @@ struct gearb_sampler {
   void *upd = nullptr;  // dirty flags + list of touched partitions for incremental updates
   int32_t *status = nullptr;
   const float *lazy_prio = nullptr;  // set by scan_totals: level 2 is rebuilt from these on demand
+  // Block totals (eight per partition) of the last scan and of the one before it: a scan writes
+  // the buffer the previous one did not, so a scan that starts while a sampling launch is still
+  // reading (this GPU's, or a peer's in the pull mode) never overwrites what that launch reads.
+  float *blk[2] = {nullptr, nullptr};
+  int slot = 0;        // buffer the last scan wrote
+  int next_slot = -1;  // chosen by the caller for the next scan, or -1: the other one
+  int take_slot() {
+    slot = next_slot >= 0 ? next_slot : (slot ^ 1);
+    next_slot = -1;
+    return slot;
+  }
 };
 
 extern "C" {
@@ -590,6 +622,8 @@ int gearb_sampler_create(int64_t n, gearb_sampler **out) {
   if (e == cudaSuccess) e = cudaMalloc(&s->scratch, static_cast<size_t>(s->scratch_bytes));
   if (e == cudaSuccess) e = cudaMalloc(&s->upd, static_cast<size_t>(update_scratch_bytes(n)));
   if (e == cudaSuccess) e = cudaMemset(s->upd, 0, static_cast<size_t>(update_scratch_bytes(n)));
+  if (e == cudaSuccess) e = cudaMalloc(&s->blk[0], static_cast<size_t>(round_up(s->nparts * 32, 256)));
+  if (e == cudaSuccess) e = cudaMalloc(&s->blk[1], static_cast<size_t>(round_up(s->nparts * 32, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
   if (e == cudaSuccess) e = cudaMemset(s->scratch, 0, static_cast<size_t>(s->scratch_bytes));
   if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
@@ -608,6 +642,8 @@ int gearb_sampler_destroy(gearb_sampler *s) {
   if (s->l1) (void)cudaFree(s->l1);
   if (s->scratch) (void)cudaFree(s->scratch);
   if (s->upd) (void)cudaFree(s->upd);
+  if (s->blk[0]) (void)cudaFree(s->blk[0]);
+  if (s->blk[1]) (void)cudaFree(s->blk[1]);
   if (s->status) (void)cudaFree(s->status);
   delete s;
   return GEARB_OK;
@@ -616,21 +652,21 @@ int gearb_sampler_destroy(gearb_sampler *s) {
 int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int store, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan_partitions: null sampler");
   int rc = launch_scan(priorities, s->n, store ? s->cdf : nullptr, s->l1, s->scratch, s->scratch_bytes, s->status,
-                       0, as_stream(stream), 0, /*level1=*/false);
+                       0, as_stream(stream), /*level1=*/false, false, s->blk[s->take_slot()]);
   if (rc == GEARB_OK) s->lazy_prio = store ? nullptr : priorities;
   return rc;
 }
 
 int gearb_sampler_scan_level1(gearb_sampler *s, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan_level1: null sampler");
-  return launch_level1(scan_aggregate_words(s->scratch, s->n), s->nparts, s->l1, nullptr, s->status,
+  return launch_level1(scan_aggregate_words(s->scratch), s->nparts, s->l1, nullptr, s->status,
                        as_stream(stream), static_cast<ScanHeader *>(s->scratch), true);
 }
 
 int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan_totals: null sampler");
   int rc = launch_scan(priorities, s->n, nullptr, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
-                       as_stream(stream));
+                       as_stream(stream), true, false, s->blk[s->take_slot()]);
   if (rc == GEARB_OK) s->lazy_prio = priorities;
   return rc;
 }
@@ -639,14 +675,14 @@ int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void
   GEARB_REQUIRE(s, "sampler_scan_alternate: null sampler");
   s->lazy_prio = nullptr;
   return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
-                     as_stream(stream), 0, true, /*overlap_previous=*/true);
+                     as_stream(stream), true, /*overlap_previous=*/true, s->blk[s->take_slot()]);
 }
 
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) {
   GEARB_REQUIRE(s, "sampler_scan: null sampler");
   s->lazy_prio = nullptr;
   return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
-                     as_stream(stream));
+                     as_stream(stream), true, false, s->blk[s->take_slot()]);
 }
 
 int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx, const float *values, int64_t m,
@@ -654,8 +690,8 @@ int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx
   GEARB_REQUIRE(s, "sampler_update: null sampler");
   GEARB_REQUIRE(!s->lazy_prio || s->lazy_prio == priorities,
                 "sampler_update: not the array the table was built from");
-  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1, scan_aggregate_words(s->scratch, s->n),
-                       static_cast<ScanHeader *>(s->scratch), s->upd, idx,
+  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1, scan_aggregate_words(s->scratch),
+                       s->blk[s->slot], static_cast<ScanHeader *>(s->scratch), s->upd, idx,
                        values, m, s->status, as_stream(stream));
 }
 
@@ -671,16 +707,26 @@ int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const
                                        double mul, double sub, const int64_t *lengths, int64_t index_offset,
                                        const int32_t *columns, int ncols, void *const *dst, int zero_fill,
                                        int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
+                                       int64_t flat_offset, int slot_mod, int64_t slot_lo, const int64_t *slot_base,
                                        void *stream) {
   GEARB_REQUIRE(s, "sample_gather: null sampler");
+  GEARB_REQUIRE(slot_mod <= GEARB_MAX_SHARDS && (slot_mod <= 1 || slot_base), "sample_gather: bad slot map");
   GatherParams p;
   int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
   if (rc != GEARB_OK) return rc;
+  if (slot_mod > 1) {
+    p.slot_mod = slot_mod;
+    p.slot_lo = slot_lo;
+    for (int q = 0; q < slot_mod; ++q) p.slot_base[q] = slot_base[q];
+  }
   GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
                 (long long)(h->table->capacity * h->table->T));
+  DrawLayout lay;
+  lay.flat_offset = flat_offset;
   return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, GEARB_SEARCH_AFFINE, lengths, index_offset,
-                              out_flat, out_idx, out_ts, out_len, as_stream(stream), mul, sub, s->lazy_prio);
+                              out_flat, out_idx, out_ts, out_len, as_stream(stream), mul, sub, s->lazy_prio,
+                              s->blk[s->slot], lay);
 }
 
 int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double *variates, int64_t b,
@@ -697,7 +743,8 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
                 (long long)(h->table->capacity * h->table->T));
   return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, flags, lengths, index_offset, out_flat,
-                              out_idx, out_ts, out_len, as_stream(stream), 1.0, 0.0, s->lazy_prio);
+                              out_idx, out_ts, out_len, as_stream(stream), 1.0, 0.0, s->lazy_prio,
+                              s->blk[s->slot]);
 }
 
 int gearb_ipc_export(const void *device_ptr, void *handle64) {
@@ -739,10 +786,45 @@ int gearb_device_free(void *ptr) {
   return GEARB_OK;
 }
 
+int64_t gearb_mailbox_bytes(int64_t n) {
+  return n > 0 ? GEARB_MAILBOX_BYTES + 2 * GEARB_MAX_SHARDS * mailbox_l1_stride(n) : GEARB_MAILBOX_BYTES;
+}
+
+int64_t gearb_mailbox_l1_offset(int64_t n, uint64_t epoch, int shard) {
+  if (n <= 0 || shard < 0 || shard >= GEARB_MAX_SHARDS) return -1;
+  return GEARB_MAILBOX_BYTES +
+         (static_cast<int64_t>(epoch & 1u) * GEARB_MAX_SHARDS + shard) * mailbox_l1_stride(n);
+}
+
+int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
+                          int copy_l1, void *stream) {
+  GEARB_REQUIRE(s, "publish: null sampler");
+  unsigned *counter = &static_cast<ScanHeader *>(s->scratch)->pad[30];
+  return launch_publish(s->l1, s->nparts, world, rank, mailboxes, epoch, copy_l1, counter, as_stream(stream));
+}
+
 int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
                                 void *stream) {
-  GEARB_REQUIRE(s, "publish_total: null sampler");
-  return launch_publish_total(s->l1 + s->nparts, world, rank, mailboxes, epoch, as_stream(stream));
+  return gearb_sampler_publish(s, world, rank, mailboxes, epoch, 0, stream);
+}
+
+int gearb_sampler_pull_ex(gearb_sampler *s, gearb_handler *h, const gearb_pull_args *a, void *stream) {
+  GEARB_REQUIRE(s && a, "pull: null sampler or arguments");
+  GEARB_REQUIRE(a->cdf || a->prio, "pull: neither level-2 tables nor priorities were given");
+  GEARB_REQUIRE(a->totals || a->mailbox, "pull: neither totals nor a mailbox were given");
+  GatherParams p;
+  int rc = build_gather_params(h, a->columns, a->ncols, a->b, a->dst, a->zero_fill, s->status, p, 4096);
+  if (rc != GEARB_OK) return rc;
+  GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
+                "pull: %lld priorities but a shard holds only %lld steps", (long long)s->n,
+                (long long)(h->table->capacity * h->table->T));
+  GEARB_REQUIRE(h->table->hbm, "pull: the shards must be in device memory");
+  if (p.stage_bytes == 0) p.ring = a->ring ? 1 : 0;
+  DrawLayout lay;
+  lay.u_stride = a->variate_stride > 0 ? a->variate_stride : 1;
+  return launch_pull(p, a->world, a->self, a->mailbox ? nullptr : a->totals, a->cdf, a->cdf ? nullptr : a->prio,
+                     a->cdf ? nullptr : a->blk, a->l1, a->table, s->n, a->variates, a->out_flat, a->out_idx,
+                     a->out_ts, as_stream(stream), a->mailbox, a->epoch, lay);
 }
 
 int gearb_sampler_pull_mailbox(gearb_sampler *s, gearb_handler *h, int world, int self, const void *mailbox,
@@ -750,18 +832,12 @@ int gearb_sampler_pull_mailbox(gearb_sampler *s, gearb_handler *h, int world, in
                                const void *const *table, const double *variates, int64_t b, const int32_t *columns,
                                int ncols, void *const *dst, int zero_fill, int ring, int64_t *out_flat,
                                int64_t *out_idx, int64_t *out_ts, void *stream) {
-  GEARB_REQUIRE(s && mailbox, "pull: null sampler or mailbox");
-  if (s->lazy_prio) return fail(GEARB_ERR_STATE, "pull: the table was built without its level-2 entries");
-  GatherParams p;
-  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
-  if (rc != GEARB_OK) return rc;
-  GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
-                "pull: %lld priorities but a shard holds only %lld steps", (long long)s->n,
-                (long long)(h->table->capacity * h->table->T));
-  GEARB_REQUIRE(h->table->hbm, "pull: the shards must be in device memory");
-  if (p.stage_bytes == 0) p.ring = ring ? 1 : 0;
-  return launch_pull(p, world, self, nullptr, cdf, l1, table, s->n, variates, out_flat, out_idx, out_ts,
-                     as_stream(stream), mailbox, epoch);
+  GEARB_REQUIRE(mailbox && cdf, "pull: null mailbox or level-2 tables");
+  gearb_pull_args a = {};
+  a.world = world; a.self = self; a.mailbox = mailbox; a.epoch = epoch; a.cdf = cdf; a.l1 = l1; a.table = table;
+  a.variates = variates; a.b = b; a.variate_stride = 1; a.columns = columns; a.ncols = ncols; a.dst = dst;
+  a.zero_fill = zero_fill; a.ring = ring; a.out_flat = out_flat; a.out_idx = out_idx; a.out_ts = out_ts;
+  return gearb_sampler_pull_ex(s, h, &a, stream);
 }
 
 int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, int self, const double *totals,
@@ -769,18 +845,32 @@ int gearb_sampler_pull(gearb_sampler *s, gearb_handler *h, int world, int self, 
                        const double *variates, int64_t b, const int32_t *columns, int ncols,
                        void *const *dst, int zero_fill, int ring, int64_t *out_flat, int64_t *out_idx,
                        int64_t *out_ts, void *stream) {
-  GEARB_REQUIRE(s, "pull: null sampler");
-  if (s->lazy_prio) return fail(GEARB_ERR_STATE, "pull: the table was built without its level-2 entries");
-  GatherParams p;
-  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
-  if (rc != GEARB_OK) return rc;
-  GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
-                "pull: %lld priorities but a shard holds only %lld steps", (long long)s->n,
-                (long long)(h->table->capacity * h->table->T));
-  GEARB_REQUIRE(h->table->hbm, "pull: the shards must be in device memory");
-  if (p.stage_bytes == 0) p.ring = ring ? 1 : 0;
-  return launch_pull(p, world, self, totals, cdf, l1, table, s->n, variates, out_flat, out_idx, out_ts,
-                     as_stream(stream));
+  GEARB_REQUIRE(totals && cdf, "pull: null totals or level-2 tables");
+  gearb_pull_args a = {};
+  a.world = world; a.self = self; a.totals = totals; a.cdf = cdf; a.l1 = l1; a.table = table;
+  a.variates = variates; a.b = b; a.variate_stride = 1; a.columns = columns; a.ncols = ncols; a.dst = dst;
+  a.zero_fill = zero_fill; a.ring = ring; a.out_flat = out_flat; a.out_idx = out_idx; a.out_ts = out_ts;
+  return gearb_sampler_pull_ex(s, h, &a, stream);
+}
+
+int gearb_sampler_select_slot(gearb_sampler *s, int slot) {
+  GEARB_REQUIRE(s && (slot == 0 || slot == 1), "sampler_select_slot: slot must be 0 or 1");
+  s->next_slot = slot;
+  return GEARB_OK;
+}
+
+int gearb_sampler_block_totals(const gearb_sampler *s, float **slot0, float **slot1, int *current) {
+  GEARB_REQUIRE(s, "sampler_block_totals: null sampler");
+  if (slot0) *slot0 = s->blk[0];
+  if (slot1) *slot1 = s->blk[1];
+  if (current) *current = s->slot;
+  return GEARB_OK;
+}
+
+int gearb_sampler_clear_status(gearb_sampler *s, void *stream) {
+  GEARB_REQUIRE(s, "sampler_clear_status: null sampler");
+  GEARB_CUDA(cudaMemsetAsync(s->status, 0, sizeof(int32_t) * GEARB_STATUS_WORDS, as_stream(stream)));
+  return GEARB_OK;
 }
 
 int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status) {
@@ -796,9 +886,12 @@ int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t 
   GEARB_CUDA(cudaStreamSynchronize(as_stream(stream)));
   if (total)
     GEARB_CUDA(cudaMemcpy(total, s->l1 + s->nparts, sizeof(double), cudaMemcpyDeviceToHost));
-  if (status)
-    GEARB_CUDA(cudaMemcpy(status, s->status, sizeof(int32_t) * GEARB_STATUS_WORDS,
-                          cudaMemcpyDeviceToHost));
+  int32_t st[GEARB_STATUS_WORDS];
+  GEARB_CUDA(cudaMemcpy(st, s->status, sizeof(st), cudaMemcpyDeviceToHost));
+  if (status) std::memcpy(status, st, sizeof(st));
+  if (st[0] & GEARB_ST_SCAN_ABORTED)
+    return fail(GEARB_ERR_TIMEOUT, "a bounded wait on the device ran out (status 0x%x): the tables and the last "
+                "batch are not valid; gearb_sampler_clear_status re-arms the status word", st[0]);
   return GEARB_OK;
 }
 

@@ -35,12 +35,18 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Runs `setup` the first time it is called with `slot` on the current device (function
+// attributes and occupancy figures are per device) and hands back the int it produced then.
+// Thread-safe; slots are small integers, one per call site.
+enum { kOnceScan = 0, kOnceLevel1 = 1, kOnceSampleGather = 2, kOnceSmallScan = 3, kOnceSlots = 8 };
+int per_device_once(int slot, int (*setup)(int *value), int *value);
+
 // ---- scan ------------------------------------------------------------------
 // First block of the scan scratch (the rest is laid out in scan.cu).
 struct ScanHeader {
   unsigned int ticket;  // next ticket (group of partitions) to hand out
   unsigned int done;    // CTAs that have finished
-  unsigned int epoch;   // launch counter; state words of other epochs read as "none"
+  unsigned int aborted; // a bounded wait of the launch in flight ran out; cleared by its last CTA
   unsigned int pad[61];  // pad[1..24]: words shared with the level-1 launch (level1.cu)
 };
 static_assert(sizeof(ScanHeader) == 256, "header is one 256-byte block");
@@ -52,16 +58,16 @@ int64_t scan_scratch_bytes(int64_t n);
 // scan may start while the kernel before it in the stream finishes (that kernel must not read cdf).
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream,
-                int64_t layout_n = 0, bool level1 = true, bool overlap_previous = false);
+                bool level1 = true, bool overlap_previous = false, float *blkw = nullptr);
 int64_t static_scan_max_n();
 int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
                        cudaStream_t stream);
-float *scan_aggregate_words(void *scratch, int64_t layout_n);
+float *scan_aggregate_words(void *scratch);
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
                   cudaStream_t stream, ScanHeader *hdr, bool have_range);
 int64_t update_scratch_bytes(int64_t n);
-int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, ScanHeader *hdr, void *upd,
-                  const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream);
+int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, float *blkw, ScanHeader *hdr,
+                  void *upd, const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream);
 int launch_search(const float *cdf, const double *l1, int64_t n, const double *u, int64_t b,
                   int flags, int64_t *out, int32_t *status, cudaStream_t stream);
 int launch_uniform(int64_t n, const double *u01, int64_t b, int64_t *out, cudaStream_t stream);
@@ -97,21 +103,42 @@ struct GatherParams {
   int32_t zero_fill;
   int32_t stage_bytes;  // > 0: a request's columns fit this much shared memory and the table is in HBM
   int32_t ring;         // 1: larger requests stream through per-warp rings of bulk copies
+  // Where request g of a launch lands in the destinations: slot g, or, with slot_mod > 1, slot
+  // slot_base[(slot_lo + g) % slot_mod] + (slot_lo + g) / slot_mod -- an owner that serves a run
+  // [slot_lo, slot_lo + n) of a global batch whose requests are dealt round-robin to slot_mod
+  // requesters groups them by requester that way (sample_gather only).
+  int32_t slot_mod;
+  int64_t slot_lo;
+  int64_t slot_base[GEARB_MAX_SHARDS];
   GatherColumn cols[GEARB_MAX_COLUMNS];
 };
 
+// How the sampling kernels address their variates and number their results.
+struct DrawLayout {
+  int64_t u_stride = 1;     // request g reads variate u[g * u_stride]
+  int64_t flat_offset = 0;  // added to every flat step index written to out_flat
+};
+
 int launch_gather(const GatherParams &p, cudaStream_t stream);
+// lazy_prio / lazy_blk: the table was built without its level-2 entries; the kernel rebuilds what a
+// request needs from the priorities and the per-block totals the scan left (8 floats per partition).
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
                          cudaStream_t stream, double mul = 1.0, double sub = 0.0,
-                         const float *lazy_prio = nullptr);
+                         const float *lazy_prio = nullptr, const float *lazy_blk = nullptr,
+                         const DrawLayout &lay = DrawLayout());
+// Per shard: either its stored level-2 table (peer_cdf) or its priorities and block totals
+// (peer_prio, peer_blk; peer_cdf null).  peer_l1 may point at local copies of the peers' level 1.
 int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,
-                const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
-                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream,
-                const void *mailbox = nullptr, unsigned long long epoch = 0);
-int launch_publish_total(const double *total, int world, int rank, void *const *mailboxes,
-                         unsigned long long epoch, cudaStream_t stream);
+                const void *const *peer_prio, const void *const *peer_blk, const void *const *peer_l1,
+                const void *const *peer_table, int64_t n, const double *u, int64_t *out_flat, int64_t *out_idx,
+                int64_t *out_ts, cudaStream_t stream, const void *mailbox, unsigned long long epoch,
+                const DrawLayout &lay);
+// Mailbox layout (one per rank, GEARB_MAILBOX_BYTES of header, then optional level-1 copies).
+int64_t mailbox_l1_stride(int64_t n);
+int launch_publish(const double *l1, int64_t nparts, int world, int rank, void *const *mailboxes,
+                   unsigned long long epoch, int copy_l1, unsigned *counter, cudaStream_t stream);
 int launch_vcopy(const uint8_t *src, uint8_t *dst, const int64_t *src_off,
                  const int64_t *dst_off, const int64_t *lengths, int64_t fixed_length,
                  int64_t n, int64_t max_length, cudaStream_t stream);

@@ -182,11 +182,13 @@ __global__ void __launch_bounds__(1024)
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
                   cudaStream_t stream, ScanHeader *hdr, bool have_range) {
   constexpr int kTileBytes = level1::kTile * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    GEARB_CUDA(cudaFuncSetAttribute(level1_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes));
-    GEARB_CUDA(cudaFuncSetAttribute(level1_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes));
-    attr_set = true;
+  {
+    int rc = per_device_once(kOnceLevel1, [](int *) -> int {  // function attributes are per device
+      GEARB_CUDA(cudaFuncSetAttribute(level1_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes));
+      GEARB_CUDA(cudaFuncSetAttribute(level1_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTileBytes));
+      return GEARB_OK;
+    }, nullptr);
+    if (rc != GEARB_OK) return rc;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.dynamicSmemBytes = kTileBytes;

@@ -113,11 +113,14 @@ __device__ __forceinline__ int resolve(Range &r, int64_t step, bool gt0, bool gt
 struct SampleArgs {
   const float *cdf;   // level-2 table, or null when it is rebuilt from `prio` on the fly
   const float *prio;  // the priorities the level-1 table was built from (only when cdf is null)
+  const float *blk;   // with prio: the eight block totals of every partition, as the scan left them (or null)
   const double *l1;
   const double *u;
   const int64_t *lengths;  // per-trajectory lengths or null
   int64_t *out_flat, *out_idx, *out_ts, *out_len;  // each may be null
   int64_t n, nparts, index_offset;
+  int64_t u_stride;     // request g reads u[g * u_stride]
+  int64_t flat_offset;  // added to out_flat
   int flags;
   double mul, sub;  // GEARB_SEARCH_AFFINE: variate -> variate * mul - sub (global draw -> this shard)
 };
@@ -133,8 +136,10 @@ struct PeerArgs {
   // they set to the step's epoch AFTER their total; null: `totals` is complete at launch.
   const unsigned long long *epochs;
   unsigned long long epoch;
-  const float *cdf[GEARB_MAX_SHARDS];
-  const double *l1[GEARB_MAX_SHARDS];
+  const float *cdf[GEARB_MAX_SHARDS];   // stored level-2 tables (instances without kLazy)
+  const float *prio[GEARB_MAX_SHARDS];  // priorities and block totals (instances with kLazy)
+  const float *blk[GEARB_MAX_SHARDS];
+  const double *l1[GEARB_MAX_SHARDS];   // the owner's level 1, or a copy of it in this GPU's memory
   const uint8_t *table[GEARB_MAX_SHARDS];
 };
 
@@ -144,13 +149,33 @@ enum { kStaged = 0, kRing = 1, kDirect = 2 };
 
 constexpr int kLazyBytes = GEARB_PART * 4 + kWarps * 512;  // a partition of priorities + exchange areas
 
-// kLazy: there is no stored level-2 table.  The CTA fetches the chosen partition's 4096
-// priorities (one 16 KiB bulk copy), rebuilds the partition's entries with the scan's own
-// addition tree, and searches them in shared memory.  The scan then only has to read the
-// priorities (4 bytes each) instead of reading them and writing a table (8 bytes each).
+// Cumulative tables that another GPU rewrites every step are read past the L1 cache (a line that
+// an earlier kernel left there would be stale); a table of this GPU is read-only while the kernel
+// runs, and the non-coherent path is the cheaper one.
+template <bool kRemote, typename T>
+__device__ __forceinline__ T ldt(const T *p) {
+  if constexpr (kRemote) return __ldcg(p);
+  else return __ldg(p);
+}
+
+// Destination slot of request g of this launch (GatherParams::slot_*).
+__device__ __forceinline__ int64_t dst_slot(const GatherParams &P, int64_t g) {
+  if (P.slot_mod <= 1) return g;
+  const int64_t q = P.slot_lo + g;
+  return P.slot_base[q % P.slot_mod] + q / P.slot_mod;
+}
+
+// kLazy: there is no stored level-2 table.  The scan left the eight block totals of every
+// partition; they say which 512-value block holds the request's entry, and one warp rebuilds
+// that block with the scan's own addition tree (2 KiB of priorities straight into registers).
+// A variate so close to a block boundary that rounding could put the entry on either side of it
+// (within 2^-17 of the partition's aggregate; the tree's sums of one set of terms differ by at
+// most 42 ulp), or in a ragged last partition, takes the long way: the whole partition (one
+// 16 KiB bulk copy) rebuilt in shared memory and searched.  Both ways give the stored table's
+// answer bit for bit.
 template <bool kPeers, int kPath, bool kLazy>
 __global__ void __launch_bounds__(kThreads, kPath == kStaged ? 7 : (kPath == kRing ? 4 : 5))
-sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
+sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ SampleArgs a,
                      const __grid_constant__ PeerArgs peers) {
   extern __shared__ __align__(128) uint8_t stage[];  // P.stage_bytes of staging area
   __shared__ unsigned masks[2][2 * kWarps];
@@ -160,6 +185,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
   __shared__ float blk_total[8], blk_max[8];
   __shared__ int warp_best[kWarps];
   __shared__ float warp_lo[kWarps];
+  __shared__ int fast_j;
   unsigned ring_it = 0;  // pieces this warp has pushed through its ring so far
   bool ring_dead = false;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -174,27 +200,38 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
   }
   __syncthreads();
 
-  // A scan launched right behind this kernel may start while it runs (it only reads the
-  // priorities and writes its own scratch or the OTHER of two alternating tables; it waits for
-  // this grid before it lets level 1 go).  With peers, not before they are known to have finished
-  // their previous step (further down): they may still be reading that other table.
-  if (!(kPeers && peers.epochs)) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   // Everything this kernel reads may have been written by the kernel before it in the stream.
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // A scan launched right behind this kernel may start while it runs (it only reads the
+  // priorities and writes its own scratch, the block totals of the OTHER parity, or the other of
+  // two alternating tables; it waits for this grid before it lets level 1 go).  The trigger comes
+  // after the wait, so whatever starts early behind this kernel finds everything before this
+  // kernel complete.  With peers, not before they are known to have finished their previous step
+  // (further down): they may still be reading what that scan overwrites.
+  if (!(kPeers && peers.epochs)) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (kPeers && peers.epochs) {
     // The shard totals are written into this GPU's mailbox by the peers themselves: wait (with a
     // limit) until every rank's word carries this step's epoch; its total was written before it.
+    // A CTA whose wait runs out leaves the epoch in status word 2, and every CTA looks there
+    // first: giving up costs the launch one wait, not one per wave of CTAs.
     if (warp == 0) {
       bool ok = true;
+      const unsigned ep32 = static_cast<unsigned>(peers.epoch);
+      unsigned *gave_up = P.status ? reinterpret_cast<unsigned *>(P.status) + 2 : nullptr;
       if (lane < peers.world) {
         unsigned polls = 0;
         for (;;) {
           unsigned long long seen;
           asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(peers.epochs + lane) : "memory");
           if (seen >= peers.epoch) break;
+          if ((polls & 63u) == 0u && gave_up && __ldcg(gave_up) == ep32) {
+            ok = false;
+            break;
+          }
           if (++polls > kPeerWaitLimit) {
             ok = false;
+            if (gave_up) atomicExch(gave_up, ep32);
             break;
           }
           __nanosleep(polls < 4096u ? 100 : 1000);
@@ -210,15 +247,24 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
       if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
       return;
     }
+    // What the peers wrote before their epoch word is read below through ordinary loads and
+    // through bulk copies (the asynchronous proxy): order both behind the acquire above.
+    asm volatile("fence.proxy.async;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // every peer is past its previous step
   }
 
-  for (int64_t g = blockIdx.x; g < P.n; g += gridDim.x) {
+  for (int64_t it = blockIdx.x; it < P.n; it += gridDim.x) {
+    // Sharded: the two ends of the (ascending) slice first, where the requests for other shards
+    // are when slices are contiguous -- they take longest and should not start last.
+    const int64_t g = kPeers ? ((it & 1) ? P.n - 1 - (it >> 1) : (it >> 1)) : it;
+    const int64_t gd = dst_slot(P, g);
     // ---- which shard: sharded tables route the request by the shard totals first
     const float *cdf = a.cdf;
+    const float *prio = a.prio;
+    const float *blk = a.blk;
     const double *l1 = a.l1;
     const uint8_t *table = P.table;
-    double v = __ldg(a.u + g);
+    double v = __ldg(a.u + g * a.u_stride);
     int owner = 0;
     if (kPeers) {
       // In-order float64 prefix of the shard totals, as the host router computes it
@@ -240,6 +286,8 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
       }
       v = __dsub_rn(v, before);
       cdf = peers.cdf[owner];
+      prio = peers.prio[owner];
+      blk = peers.blk[owner];
       l1 = peers.l1[owner];
       table = peers.table[owner];
     }
@@ -248,8 +296,8 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
     Range r1{0, a.nparts - 1, 0};
     int64_t q0, q1, step;
     probe_positions(r1, q0, q1, step);
-    double p0 = __ldg(l1 + 1 + q0), p1 = __ldg(l1 + 1 + q1);
-    const double total = __ldg(l1 + a.nparts);
+    double p0 = ldt<kPeers>(l1 + 1 + q0), p1 = ldt<kPeers>(l1 + 1 + q1);
+    const double total = ldt<kPeers>(l1 + a.nparts);
     int64_t flat;
     if (!(total > 0.0)) {
       flat = a.n - 1;  // nothing selectable: defined as the last index
@@ -268,8 +316,8 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
         resolve(r1, step, p0 > v, p1 > v, masks, round);
         if (step == 1 || r1.lo >= r1.hi) break;
         probe_positions(r1, q0, q1, step);
-        p0 = __ldg(l1 + 1 + q0);
-        p1 = __ldg(l1 + 1 + q1);
+        p0 = ldt<kPeers>(l1 + 1 + q0);
+        p1 = ldt<kPeers>(l1 + 1 + q1);
       }
       const int64_t p = r1.hi;
 
@@ -280,9 +328,9 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
         const float *cp = cdf + base;
         Range r2{0, valid - 1, 0};
         probe_positions(r2, q0, q1, step);
-        float c0 = __ldg(cp + q0), c1 = __ldg(cp + q1);
-        const double off = __ldg(l1 + p);
-        const float last = __ldg(cp + valid - 1);
+        float c0 = ldt<kPeers>(cp + q0), c1 = ldt<kPeers>(cp + q1);
+        const double off = ldt<kPeers>(l1 + p);
+        const float last = ldt<kPeers>(cp + valid - 1);
         float r = __double2float_rn(__dsub_rn(v, off));
         if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
         int first;
@@ -294,8 +342,8 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
           first = resolve(r2, step, c0 > r, c1 > r, masks, round);
           if (step == 1 || r2.lo >= r2.hi) break;
           probe_positions(r2, q0, q1, step);
-          c0 = __ldg(cp + q0);
-          c1 = __ldg(cp + q1);
+          c0 = ldt<kPeers>(cp + q0);
+          c1 = ldt<kPeers>(cp + q1);
         }
         const int64_t j = r2.hi;
         flat = base + j;
@@ -307,10 +355,10 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
           if (step == 1) {
             hi_v = vals[first];
             if (first > 0) lo_v = vals[first - 1];
-            else if (j > 0) lo_v = __ldg(cp + j - 1);
+            else if (j > 0) lo_v = ldt<kPeers>(cp + j - 1);
           } else {
-            hi_v = __ldg(cp + j);
-            if (j > 0) lo_v = __ldg(cp + j - 1);
+            hi_v = ldt<kPeers>(cp + j);
+            if (j > 0) lo_v = ldt<kPeers>(cp + j - 1);
           }
           const bool near = (__uint_as_float(__float_as_uint(r) + 1u) >= hi_v) || (j > 0 && r == lo_v);
           if (near) atomicAdd(P.status + 1, 1);
@@ -320,100 +368,181 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
         float *pv = reinterpret_cast<float *>(stage);
         float4 *pv4 = reinterpret_cast<float4 *>(stage);
         float *xs = pv + GEARB_PART + warp * 128;
-        const float *src = a.prio + base;
-        if (valid == GEARB_PART) {
-          if (threadIdx.x == 0) {
-            mbar_arrive_expect_tx(&stage_bar, GEARB_PART * 4);
-            bulk_load(pv, src, GEARB_PART * 4, &stage_bar);
+        const float *src = prio + base;
+        const double off = ldt<kPeers>(l1 + p);
+        const float r_raw = __double2float_rn(__dsub_rn(v, off));
+
+        // -- the short way: the block totals say which block holds the entry
+        bool fast = false;
+        int wsel = 0;
+        float Xsel = 0.f;
+        if (blk != nullptr && valid == GEARB_PART) {
+          const float4 b0 = ldt<kPeers>(reinterpret_cast<const float4 *>(blk + p * 8));
+          const float4 b1 = ldt<kPeers>(reinterpret_cast<const float4 *>(blk + p * 8) + 1);
+          float X[9];
+          X[0] = 0.f;
+          X[1] = __fadd_rn(X[0], b0.x); X[2] = __fadd_rn(X[1], b0.y);
+          X[3] = __fadd_rn(X[2], b0.z); X[4] = __fadd_rn(X[3], b0.w);
+          X[5] = __fadd_rn(X[4], b1.x); X[6] = __fadd_rn(X[5], b1.y);
+          X[7] = __fadd_rn(X[6], b1.z); X[8] = __fadd_rn(X[7], b1.w);
+          const float delta = X[8] * 7.62939453125e-06f;  // 2^-17 of the aggregate: 128 ulp or more
+          int w = 8;
+#pragma unroll
+          for (int k = 7; k >= 0; --k)
+            if (X[k + 1] > r_raw) w = k;
+          if (w < 8) {
+            float Xlo = 0.f, Xhi = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              if (k == w) {
+                Xlo = X[k];
+                Xhi = X[k + 1];
+              }
+            // every value of the blocks before w lies below r, and block w has one above it
+            fast = (w == 0 || r_raw > Xlo + delta) && (r_raw < Xhi - delta);
+            wsel = w;
+            Xsel = Xlo;
           }
-        } else {  // the ragged last partition: by hand, zeros past the end
-          for (int e = threadIdx.x; e < GEARB_PART; e += kThreads) pv[e] = e < valid ? __ldg(src + e) : 0.f;
+        }
+        int j = -1;
+        if (fast) {
+          if (warp == 0) {
+            const float4 *src4 = reinterpret_cast<const float4 *>(src + wsel * tree::kBlockValues);
+            float4 x[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) x[k] = ldt<kPeers>(src4 + k * 32 + lane);
+            unsigned bits = 0;  // ignored: the scan has already reported bad priorities
+            float sv[4][4], top[4];
+            const tree::Group gq = tree::block_sums(x, xs, lane, sv, bits);
+            tree::block_values(Xsel, gq, xs, lane, sv, top, false, base + wsel * tree::kBlockValues, a.n);
+            int best = tree::kBlockValues;
+#pragma unroll
+            for (int k = 3; k >= 0; --k)
+#pragma unroll
+              for (int q = 3; q >= 0; --q)
+                if (sv[k][q] > r_raw) best = (k * 32 + lane) * 4 + q;
+            best = __reduce_min_sync(kFull, best);
+            // the entry itself (it exceeds everything before it) and the largest value before it in the
+            // block; the blocks before this one stay below r by the margin, so they cannot tie with it
+            float hi_v = 0.f, inner = 0.f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int e = (k * 32 + lane) * 4 + q;
+                if (e == best) hi_v = sv[k][q];
+                if (e < best) inner = fmaxf(inner, sv[k][q]);
+              }
+            hi_v = __uint_as_float(__reduce_max_sync(kFull, __float_as_uint(hi_v)));
+            inner = __uint_as_float(__reduce_max_sync(kFull, __float_as_uint(inner)));
+            if (lane == 0) {
+              fast_j = best < tree::kBlockValues ? wsel * tree::kBlockValues + best : -1;
+              if (P.status && best < tree::kBlockValues) {
+                const bool near =
+                    (__uint_as_float(__float_as_uint(r_raw) + 1u) >= hi_v) || (best > 0 && r_raw == inner);
+                if (near) atomicAdd(P.status + 1, 1);
+              }
+            }
+          }
           __syncthreads();
-          if (threadIdx.x == 0) mbar_arrive(&stage_bar);
+          j = fast_j;
+          __syncthreads();  // fast_j and warp 0's exchange area are free again
         }
-        const double off = __ldg(l1 + p);
-        unsigned polls = 0;
-        bool ok;
-        while (!(ok = mbar_try_wait(&stage_bar, stage_parity)))
-          if (++polls > kWaitLimit) break;
-        stage_parity ^= 1u;
-        if (__syncthreads_or(!ok)) {
-          if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
-          break;
-        }
-        unsigned bits = 0;  // ignored: the scan has already reported bad priorities
-        float sv[4][4], top[4];
-        float4 x[4];
-        // first pass: block totals (warp w: blocks w and w + 4)
+        if (j < 0) {
+          // -- the long way: the whole partition
+          if (valid == GEARB_PART) {
+            if (threadIdx.x == 0) {
+              mbar_arrive_expect_tx(&stage_bar, GEARB_PART * 4);
+              bulk_load(pv, src, GEARB_PART * 4, &stage_bar);
+            }
+          } else {  // the ragged last partition: by hand, zeros past the end
+            for (int e = threadIdx.x; e < GEARB_PART; e += kThreads) pv[e] = e < valid ? ldt<kPeers>(src + e) : 0.f;
+            __syncthreads();
+            if (threadIdx.x == 0) mbar_arrive(&stage_bar);
+          }
+          unsigned polls = 0;
+          bool ok;
+          while (!(ok = mbar_try_wait(&stage_bar, stage_parity)))
+            if (++polls > kWaitLimit) break;
+          stage_parity ^= 1u;
+          if (__syncthreads_or(!ok)) {
+            if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
+            break;
+          }
+          unsigned bits = 0;  // ignored: the scan has already reported bad priorities
+          float sv[4][4], top[4];
+          float4 x[4];
+          // first pass: block totals (warp w: blocks w and w + 4)
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          const int blk = warp + h * kWarps;
+          for (int h = 0; h < 2; ++h) {
+            const int b = warp + h * kWarps;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) x[k] = pv4[(blk * 4 + k) * 32 + lane];
-          const float total = tree::block_total(x, xs, lane, bits);
-          if (lane == 0) blk_total[blk] = total;
-        }
-        __syncthreads();
-        // second pass: values, written back over the priorities; block maxima
+            for (int k = 0; k < 4; ++k) x[k] = pv4[(b * 4 + k) * 32 + lane];
+            const float bt = tree::block_total(x, xs, lane, bits);
+            if (lane == 0) blk_total[b] = bt;
+          }
+          __syncthreads();
+          // second pass: values, written back over the priorities; block maxima
 #pragma unroll 1
-        for (int h = 0; h < 2; ++h) {
-          const int blk = warp + h * kWarps;
+          for (int h = 0; h < 2; ++h) {
+            const int b = warp + h * kWarps;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) x[k] = pv4[(blk * 4 + k) * 32 + lane];
-          const tree::Group gq = tree::block_sums(x, xs, lane, sv, bits);
-          float X = 0.f;
-          for (int w = 0; w < blk; ++w) X = __fadd_rn(X, blk_total[w]);
-          tree::block_values(X, gq, xs, lane, sv, top, false, base + blk * tree::kBlockValues, a.n);
+            for (int k = 0; k < 4; ++k) x[k] = pv4[(b * 4 + k) * 32 + lane];
+            const tree::Group gq = tree::block_sums(x, xs, lane, sv, bits);
+            float X = 0.f;
+            for (int w = 0; w < b; ++w) X = __fadd_rn(X, blk_total[w]);
+            tree::block_values(X, gq, xs, lane, sv, top, false, base + b * tree::kBlockValues, a.n);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            pv4[(blk * 4 + k) * 32 + lane] = make_float4(sv[k][0], sv[k][1], sv[k][2], sv[k][3]);
-          const float m = tree::block_max(top);
-          if (lane == 0) blk_max[blk] = m;
-        }
-        __syncthreads();
-        float last = 0.f;
+            for (int k = 0; k < 4; ++k)
+              pv4[(b * 4 + k) * 32 + lane] = make_float4(sv[k][0], sv[k][1], sv[k][2], sv[k][3]);
+            const float m = tree::block_max(top);
+            if (lane == 0) blk_max[b] = m;
+          }
+          __syncthreads();
+          float last = 0.f;
 #pragma unroll
-        for (int w = 0; w < 8; ++w) last = fmaxf(last, blk_max[w]);
-        float r = __double2float_rn(__dsub_rn(v, off));
-        if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
-        // The stored table would be the running maximum of these values; its first entry above r
-        // is the first VALUE above r, because the maximum passes r exactly where a value does.
-        int best = GEARB_PART;
+          for (int w = 0; w < 8; ++w) last = fmaxf(last, blk_max[w]);
+          float r = r_raw;
+          if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
+          // The stored table would be the running maximum of these values; its first entry above r
+          // is the first VALUE above r, because the maximum passes r exactly where a value does.
+          int best = GEARB_PART;
 #pragma unroll 8
-        for (int i = GEARB_PART / kThreads - 1; i >= 0; --i) {
-          const int e = i * kThreads + threadIdx.x;
-          if (pv[e] > r) best = e;
-        }
-        best = __reduce_min_sync(kFull, best);
-        if (lane == 0) warp_best[warp] = best;
-        __syncthreads();
-        int j = warp_best[0];
-#pragma unroll
-        for (int w = 1; w < kWarps; ++w) j = min(j, warp_best[w]);
-        if (j >= valid) j = static_cast<int>(valid) - 1;  // cannot happen while r < last; keeps the index in range
-        flat = base + j;
-        if (P.status) {
-          // ---- variates within one ulp of a boundary of the chosen entry: the entry itself is
-          // value j (it exceeds everything before it); its predecessor is the largest value before j
-          float lo = 0.f;
-#pragma unroll 8
-          for (int i = 0; i < GEARB_PART / kThreads; ++i) {
+          for (int i = GEARB_PART / kThreads - 1; i >= 0; --i) {
             const int e = i * kThreads + threadIdx.x;
-            if (e < j) lo = fmaxf(lo, pv[e]);
+            if (pv[e] > r) best = e;
           }
-#pragma unroll
-          for (int d = 16; d > 0; d >>= 1) lo = fmaxf(lo, __shfl_xor_sync(kFull, lo, d));
-          if (lane == 0) warp_lo[warp] = lo;
+          best = __reduce_min_sync(kFull, best);
+          if (lane == 0) warp_best[warp] = best;
           __syncthreads();
-          if (threadIdx.x == 0) {
-            float lo_v = 0.f;
-            for (int w = 0; w < kWarps; ++w) lo_v = fmaxf(lo_v, warp_lo[w]);
-            const float hi_v = pv[j];
-            const bool near = (__uint_as_float(__float_as_uint(r) + 1u) >= hi_v) || (j > 0 && r == lo_v);
-            if (near) atomicAdd(P.status + 1, 1);
+          j = warp_best[0];
+#pragma unroll
+          for (int w = 1; w < kWarps; ++w) j = min(j, warp_best[w]);
+          if (j >= valid) j = static_cast<int>(valid) - 1;  // cannot happen while r < last; keeps the index in range
+          if (P.status) {
+            // ---- variates within one ulp of a boundary of the chosen entry: the entry itself is
+            // value j (it exceeds everything before it); its predecessor is the largest value before j
+            float lo = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < GEARB_PART / kThreads; ++i) {
+              const int e = i * kThreads + threadIdx.x;
+              if (e < j) lo = fmaxf(lo, pv[e]);
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) lo = fmaxf(lo, __shfl_xor_sync(kFull, lo, d));
+            if (lane == 0) warp_lo[warp] = lo;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+              float lo_v = 0.f;
+              for (int w = 0; w < kWarps; ++w) lo_v = fmaxf(lo_v, warp_lo[w]);
+              const float hi_v = pv[j];
+              const bool near = (__uint_as_float(__float_as_uint(r) + 1u) >= hi_v) || (j > 0 && r == lo_v);
+              if (near) atomicAdd(P.status + 1, 1);
+            }
           }
+          __syncthreads();  // the partition's values are dead: the gather may reuse the area
         }
-        __syncthreads();  // the partition's values are dead: the gather may reuse the area
+        flat = base + j;
       }
     }
 
@@ -431,10 +560,10 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
     const int64_t len = a.lengths ? __ldg(a.lengths + t) : P.T;
     if (threadIdx.x == 0) {
       // sharded: global ids, shard `owner` holds steps [owner*n, (owner+1)*n)
-      if (a.out_flat) a.out_flat[g] = flat + (kPeers ? owner * a.n : 0);
-      if (a.out_idx) a.out_idx[g] = t + a.index_offset + (kPeers ? owner * P.capacity : 0);
-      if (a.out_ts) a.out_ts[g] = ts;
-      if (a.out_len) a.out_len[g] = len;
+      if (a.out_flat) a.out_flat[gd] = flat + a.flat_offset + (kPeers ? owner * a.n : 0);
+      if (a.out_idx) a.out_idx[gd] = t + a.index_offset + (kPeers ? owner * P.capacity : 0);
+      if (a.out_ts) a.out_ts[gd] = ts;
+      if (a.out_len) a.out_len[gd] = len;
     }
 
     // ---- gather
@@ -482,7 +611,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
         unsigned ignore = 0;
         dev::clip_segment(P, col, t, ts, len, start, bytes, ignore);
         const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start, table));
-        dev::copy_piece<true>(P, col, q - col.chunk_first, g, stage + col.stage_off + (src & 15u), bytes, lane);
+        dev::copy_piece<true>(P, col, q - col.chunk_first, gd, stage + col.stage_off + (src & 15u), bytes, lane);
       }
       __syncthreads();  // the staging area is free for the next request
     } else if (kPath == kRing && !(kPeers && owner == peers.self)) {
@@ -501,7 +630,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
         const GatherColumn &col = P.cols[c];
         int64_t start, bytes;
         dev::clip_segment(P, col, t, ts, len, start, bytes, flags);
-        pi = dev::piece_info(P, col, q - col.chunk_first, g, bytes);
+        pi = dev::piece_info(P, col, q - col.chunk_first, gd, bytes);
         src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start, table)) + static_cast<uintptr_t>(pi.seg_off);
       };
       auto issue = [&](int k) {  // lane 0
@@ -522,7 +651,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
         for (int k = 0; k < kRingSlots && k < npieces; ++k) issue(k);
       bool lost = false;
       for (int k = 0; k < npieces; ++k) {
-        const unsigned it = ring_it + k, s_ = it % kRingSlots, parity = (it / kRingSlots) & 1u;
+        const unsigned itr = ring_it + k, s_ = itr % kRingSlots, parity = (itr / kRingSlots) & 1u;
         unsigned polls = 0;
         bool ok;
         while (!(ok = mbar_try_wait(&ring_bar[warp][s_], parity)))
@@ -551,7 +680,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
       // Direct: the request's pieces, column by column, dealt to the four warps.
       for (int q = warp; q < P.chunks_per_request; q += kWarps) {
         const int c = dev::column_of_piece(P, q);
-        dev::gather_piece(P, P.cols[c], q - P.cols[c].chunk_first, g, t, ts, len, lane, flags, table);
+        dev::gather_piece(P, P.cols[c], q - P.cols[c].chunk_first, gd, t, ts, len, lane, flags, table);
       }
     }
   }
@@ -561,6 +690,19 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const SampleArgs a,
 }  // namespace
 
 namespace {
+using Kernel = void (*)(const GatherParams, const SampleArgs, const PeerArgs);
+// [peers][lazy][path]
+const Kernel kInstances[2][2][3] = {
+    {{sample_gather_kernel<false, kStaged, false>, sample_gather_kernel<false, kRing, false>,
+      sample_gather_kernel<false, kDirect, false>},
+     {sample_gather_kernel<false, kStaged, true>, sample_gather_kernel<false, kRing, true>,
+      sample_gather_kernel<false, kDirect, true>}},
+    {{sample_gather_kernel<true, kStaged, false>, sample_gather_kernel<true, kRing, false>,
+      sample_gather_kernel<true, kDirect, false>},
+     {sample_gather_kernel<true, kStaged, true>, sample_gather_kernel<true, kRing, true>,
+      sample_gather_kernel<true, kDirect, true>}}};
+constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kRingSlots * kRingSlotBytes;
+
 int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers, cudaStream_t stream) {
   int64_t grid = p.n;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
@@ -569,29 +711,18 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
   cfg.blockDim = dim3(kThreads);
-  constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kRingSlots * kRingSlotBytes;
-  using Kernel = void (*)(const GatherParams, const SampleArgs, const PeerArgs);
-  // [peers][lazy][path]; a sharded table read in place always has its stored level-2 tables
-  static const Kernel table[2][2][3] = {
-      {{sample_gather_kernel<false, kStaged, false>, sample_gather_kernel<false, kRing, false>,
-        sample_gather_kernel<false, kDirect, false>},
-       {sample_gather_kernel<false, kStaged, true>, sample_gather_kernel<false, kRing, true>,
-        sample_gather_kernel<false, kDirect, true>}},
-      {{sample_gather_kernel<true, kStaged, false>, sample_gather_kernel<true, kRing, false>,
-        sample_gather_kernel<true, kDirect, false>},
-       {nullptr, nullptr, nullptr}}};
-  static bool attr_set = false;
-  if (!attr_set) {
-    for (int pe = 0; pe < 2; ++pe)
-      for (int lz = 0; lz < 2; ++lz)
-        if (table[pe][lz][kRing])
-          GEARB_CUDA(cudaFuncSetAttribute(table[pe][lz][kRing], cudaFuncAttributeMaxDynamicSharedMemorySize,
+  {
+    int rc = per_device_once(kOnceSampleGather, [](int *) -> int {  // function attributes are per device
+      for (int pe = 0; pe < 2; ++pe)
+        for (int lz = 0; lz < 2; ++lz)
+          GEARB_CUDA(cudaFuncSetAttribute(kInstances[pe][lz][kRing], cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(kRingBytes)));
-    attr_set = true;
+      return GEARB_OK;
+    }, nullptr);
+    if (rc != GEARB_OK) return rc;
   }
   const int path = p.stage_bytes > 0 ? kStaged : (p.ring ? kRing : kDirect);
   const bool lazy = a.cdf == nullptr;
-  GEARB_REQUIRE(!(lazy && peers.world > 0), "pull: the shards need their stored level-2 tables");
   size_t smem = path == kStaged ? static_cast<size_t>(p.stage_bytes) : (path == kRing ? kRingBytes : 0);
   if (lazy && smem < static_cast<size_t>(kLazyBytes)) smem = kLazyBytes;
   cfg.dynamicSmemBytes = smem;
@@ -601,7 +732,7 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  GEARB_CUDA(cudaLaunchKernelEx(&cfg, table[peers.world > 0][lazy][path], p, a, peers));
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, kInstances[peers.world > 0][lazy][path], p, a, peers));
   return GEARB_OK;
 }
 }  // namespace
@@ -609,17 +740,21 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
-                         cudaStream_t stream, double mul, double sub, const float *lazy_prio) {
+                         cudaStream_t stream, double mul, double sub, const float *lazy_prio,
+                         const float *lazy_blk, const DrawLayout &lay) {
   GEARB_REQUIRE(n > 0, "sample_gather: the priority table is empty");
   if (p.n == 0) return GEARB_OK;
   GEARB_REQUIRE((cdf || lazy_prio) && l1 && u, "sample_gather: null pointer argument");
   GEARB_REQUIRE(!lazy_prio || (reinterpret_cast<uintptr_t>(lazy_prio) & 15) == 0,
                 "sample_gather: the priorities must be 16-byte aligned");
-  SampleArgs a;
-  a.cdf = lazy_prio ? nullptr : cdf; a.prio = lazy_prio; a.l1 = l1; a.u = u; a.lengths = lengths;
+  SampleArgs a = {};
+  a.cdf = lazy_prio ? nullptr : cdf; a.prio = lazy_prio; a.blk = lazy_prio ? lazy_blk : nullptr;
+  a.l1 = l1; a.u = u; a.lengths = lengths;
   a.out_flat = out_flat; a.out_idx = out_idx; a.out_ts = out_ts; a.out_len = out_len;
   a.n = n; a.nparts = (n + GEARB_PART - 1) / GEARB_PART;
   a.index_offset = index_offset;
+  a.u_stride = lay.u_stride;
+  a.flat_offset = lay.flat_offset;
   a.flags = flags;
   a.mul = mul;
   a.sub = sub;
@@ -631,53 +766,101 @@ namespace {
 struct Mailboxes {
   void *box[GEARB_MAX_SHARDS];
 };
-// One rank's total into slot (epoch & 1) of every rank's mailbox, then the epoch: lane j serves rank j.
-__global__ void publish_kernel(const double *total, Mailboxes m, int world, int rank, unsigned long long epoch) {
+constexpr int kPublishThreads = 256;
+// One rank's level 1 (optionally) and total into every rank's mailbox, then the epoch.
+//   header of a mailbox:   totals[2 slots][GEARB_MAX_SHARDS] f64 | epochs[2][GEARB_MAX_SHARDS] u64
+//   behind the header:     level-1 copies [2 slots][GEARB_MAX_SHARDS] of l1_stride bytes each
+// Slot epoch & 1 is used.  With copy_l1 the CTAs first spread this rank's level 1 over the other
+// ranks' mailboxes with ordinary stores; the last CTA to finish (a counter in this rank's own
+// memory) then writes the total and, with release semantics at system scope, the epoch word the
+// pull launches of the other ranks wait for.
+__global__ void __launch_bounds__(kPublishThreads)
+    publish_kernel(const double *l1, unsigned nparts, Mailboxes m, int world, int rank, unsigned long long epoch,
+                   int copy_l1, long long l1_stride, unsigned *counter) {
+  __shared__ int is_last;
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // level 1 comes from the launch before
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // the total comes from the level-1 launch before
+  const unsigned slot = static_cast<unsigned>(epoch & 1u);
+  if (copy_l1) {
+    const unsigned count = nparts + 1u;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x) {
+      const double v = __ldcg(l1 + i);
+      for (int j = 0; j < world; ++j) {
+        if (j == rank) continue;
+        double *dst = reinterpret_cast<double *>(static_cast<char *>(m.box[j]) + GEARB_MAILBOX_BYTES +
+                                                 (static_cast<long long>(slot) * GEARB_MAX_SHARDS + rank) * l1_stride);
+        dst[i] = v;
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      is_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+      __threadfence_system();
+    }
+    __syncthreads();
+    if (!is_last) return;
+    if (threadIdx.x == 0) *counter = 0u;
+  } else if (blockIdx.x != 0) {
+    return;
+  }
   const int j = threadIdx.x;
   if (j >= world) return;
-  const unsigned slot = static_cast<unsigned>(epoch & 1u);
   char *box = static_cast<char *>(m.box[j]);
   double *tot = reinterpret_cast<double *>(box) + slot * GEARB_MAX_SHARDS + rank;
   unsigned long long *ep =
       reinterpret_cast<unsigned long long *>(box + 2 * GEARB_MAX_SHARDS * 8) + slot * GEARB_MAX_SHARDS + rank;
-  const double t = __ldcg(total);
+  const double t = __ldcg(l1 + nparts);
   asm volatile("st.relaxed.sys.global.f64 [%0], %1;" ::"l"(tot), "d"(t) : "memory");
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(ep), "l"(epoch) : "memory");
 }
 }  // namespace
 
-int launch_publish_total(const double *total, int world, int rank, void *const *mailboxes,
-                         unsigned long long epoch, cudaStream_t stream) {
+int64_t mailbox_l1_stride(int64_t n) {
+  const int64_t nparts = (n + GEARB_PART - 1) / GEARB_PART;
+  return ((nparts + 1) * 8 + 255) & ~int64_t(255);
+}
+
+int launch_publish(const double *l1, int64_t nparts, int world, int rank, void *const *mailboxes,
+                   unsigned long long epoch, int copy_l1, unsigned *counter, cudaStream_t stream) {
   GEARB_REQUIRE(world >= 1 && world <= GEARB_MAX_SHARDS && rank >= 0 && rank < world, "publish: bad rank or world");
-  GEARB_REQUIRE(total && mailboxes && epoch > 0, "publish: null argument or epoch 0");
+  GEARB_REQUIRE(l1 && mailboxes && epoch > 0, "publish: null argument or epoch 0");
+  GEARB_REQUIRE(!copy_l1 || counter, "publish: the level-1 copy needs a counter word");
   Mailboxes m = {};
   for (int j = 0; j < world; ++j) {
     GEARB_REQUIRE(mailboxes[j], "publish: null mailbox for rank %d", j);
     m.box[j] = mailboxes[j];
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(1);
-  cfg.blockDim = dim3(32);
+  int64_t grid = 1;
+  if (copy_l1 && world > 1) {
+    grid = (nparts + 1 + kPublishThreads - 1) / kPublishThreads;
+    if (grid > 32) grid = 32;
+  }
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kPublishThreads);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  GEARB_CUDA(cudaLaunchKernelEx(&cfg, publish_kernel, total, m, world, rank, epoch));
+  const long long stride = mailbox_l1_stride(nparts * GEARB_PART);
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, publish_kernel, l1, static_cast<unsigned>(nparts), m, world, rank, epoch,
+                                (copy_l1 && world > 1) ? 1 : 0, stride, counter));
   return GEARB_OK;
 }
 
 int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,
-                const void *const *peer_l1, const void *const *peer_table, int64_t n, const double *u,
-                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, cudaStream_t stream, const void *mailbox,
-                unsigned long long epoch) {
+                const void *const *peer_prio, const void *const *peer_blk, const void *const *peer_l1,
+                const void *const *peer_table, int64_t n, const double *u, int64_t *out_flat, int64_t *out_idx,
+                int64_t *out_ts, cudaStream_t stream, const void *mailbox, unsigned long long epoch,
+                const DrawLayout &lay) {
   GEARB_REQUIRE(n > 0, "pull: the priority table is empty");
   GEARB_REQUIRE(world >= 1 && world <= GEARB_MAX_SHARDS, "pull: %d shards, at most %d", world, GEARB_MAX_SHARDS);
   if (p.n == 0) return GEARB_OK;
-  GEARB_REQUIRE((totals || mailbox) && peer_cdf && peer_l1 && peer_table && u, "pull: null pointer argument");
+  GEARB_REQUIRE((totals || mailbox) && (peer_cdf || peer_prio) && peer_l1 && peer_table && u,
+                "pull: null pointer argument");
   PeerArgs peers = {};
   peers.world = world;
   peers.self = self;
@@ -690,16 +873,29 @@ int launch_pull(const GatherParams &p, int world, int self, const double *totals
     peers.epochs = reinterpret_cast<const unsigned long long *>(box + 2 * GEARB_MAX_SHARDS * 8) + slot * GEARB_MAX_SHARDS;
     peers.epoch = epoch;
   }
+  const bool lazy = peer_cdf == nullptr;
   for (int j = 0; j < world; ++j) {
-    GEARB_REQUIRE(peer_cdf[j] && peer_l1[j] && peer_table[j], "pull: null pointer for shard %d", j);
-    peers.cdf[j] = static_cast<const float *>(peer_cdf[j]);
+    GEARB_REQUIRE(peer_l1[j] && peer_table[j], "pull: null pointer for shard %d", j);
+    if (lazy) {
+      GEARB_REQUIRE(peer_prio[j], "pull: null priorities for shard %d", j);
+      GEARB_REQUIRE((reinterpret_cast<uintptr_t>(peer_prio[j]) & 15) == 0, "pull: priorities must be 16-byte aligned");
+      peers.prio[j] = static_cast<const float *>(peer_prio[j]);
+      peers.blk[j] = peer_blk ? static_cast<const float *>(peer_blk[j]) : nullptr;
+    } else {
+      GEARB_REQUIRE(peer_cdf[j], "pull: null level-2 table for shard %d", j);
+      peers.cdf[j] = static_cast<const float *>(peer_cdf[j]);
+    }
     peers.l1[j] = static_cast<const double *>(peer_l1[j]);
     peers.table[j] = static_cast<const uint8_t *>(peer_table[j]);
   }
   SampleArgs a = {};
-  a.cdf = peers.cdf[0]; a.prio = nullptr; a.l1 = peers.l1[0]; a.u = u;
+  a.cdf = lazy ? nullptr : peers.cdf[0];
+  a.prio = lazy ? peers.prio[0] : nullptr;
+  a.l1 = peers.l1[0]; a.u = u;
   a.out_flat = out_flat; a.out_idx = out_idx; a.out_ts = out_ts;
   a.n = n; a.nparts = (n + GEARB_PART - 1) / GEARB_PART;
+  a.u_stride = lay.u_stride;
+  a.flat_offset = lay.flat_offset;
   a.mul = 1.0;
   return launch_any(p, a, peers, stream);
 }

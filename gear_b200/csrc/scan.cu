@@ -114,6 +114,7 @@ struct ScanArgs {
   double *l1;
   ScanHeader *hdr;
   float *aggw;               // per partition: its aggregate
+  float *blkw;               // per partition: its eight block totals (or null: not wanted)
   int32_t *status;
   int64_t n;
   unsigned nparts;
@@ -135,9 +136,13 @@ struct __align__(128) Smem {
   unsigned emin, emax;             // exponent range of the aggregates this CTA produced
 };
 
+// The status word is the caller's and accumulates; the header's word belongs to this launch
+// alone (its last CTA reads and clears it), so an abort of an earlier launch -- or one that
+// another kernel reported through the same status word -- does not make this one skip level 1.
 __device__ __forceinline__ void raise_abort(Smem &sm, const ScanArgs &a) {
   sm.abort = 1u;
   atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_SCAN_ABORTED);
+  atomicExch(&a.hdr->aborted, 1u);
 }
 
 // ------------------------------------------------------------------ loader warp
@@ -205,6 +210,14 @@ __device__ __forceinline__ void hand_over(const ScanArgs &a, int part, float agg
   a.aggw[part] = agg;
   level1::note_exponent(__float_as_uint(agg), emin, emax);
 }
+// The partition's eight block totals, for a sampling kernel that rebuilds single blocks of the
+// level-2 table from the priorities (sample_gather.cu).
+__device__ __forceinline__ void hand_over_blocks(const ScanArgs &a, int part, const float *wt) {
+  if (a.blkw == nullptr) return;
+  float4 *dst = reinterpret_cast<float4 *>(a.blkw + static_cast<int64_t>(part) * kComputeWarps);
+  dst[0] = make_float4(wt[0], wt[1], wt[2], wt[3]);
+  dst[1] = make_float4(wt[4], wt[5], wt[6], wt[7]);
+}
 
 // ----------------------------------------------------------------- compute warps
 // Warp w scans block w (512 values) of the staged partition.  Lane l holds chunk 32k + l of
@@ -251,6 +264,7 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
 #pragma unroll
         for (int w = 0; w < kComputeWarps; ++w) X = __fadd_rn(X, sm.wt[buf][w]);
         hand_over(a, part, X, emin, emax);
+        hand_over_blocks(a, part, sm.wt[buf]);
       }
       continue;  // wt[buf] is next written two rounds on, behind the next round's barrier
     }
@@ -268,7 +282,10 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
     float X = 0.f;
     for (int w = 0; w < warp; ++w) X = __fadd_rn(X, sm.wt[buf][w]);
     // the last warp also knows the partition's aggregate X(8): hand it over
-    if (warp == kComputeWarps - 1 && lane == 0) hand_over(a, part, __fadd_rn(X, g.total), emin, emax);
+    if (warp == kComputeWarps - 1 && lane == 0) {
+      hand_over(a, part, __fadd_rn(X, g.total), emin, emax);
+      hand_over_blocks(a, part, sm.wt[buf]);
+    }
 
     // ---- second pass: values, then the running maximum block by block
     tree::block_values(X, g, xs, lane, sv, top, false, e0, a.n);
@@ -318,16 +335,18 @@ __device__ void finish_launch(Smem &sm, const ScanArgs &a, int tid) {
   }
   __syncthreads();
   if (!is_last) return;
+  // after an abort of THIS launch some aggregates are stale and copies may still land in the
+  // ring: leave l1 alone (every CTA raised its flag before it counted itself done)
+  const unsigned aborted = __ldcg(&a.hdr->aborted);
   if (a.inline_level1) {
     static_assert(sizeof(sm.stage) >= level1::kTile * sizeof(float), "the ring doubles as level 1's tile");
-    // after an abort some aggregates are stale and copies may still land in the ring: leave l1 alone
-    const unsigned aborted = atomicOr(reinterpret_cast<unsigned *>(a.status), 0u) & GEARB_ST_SCAN_ABORTED;
     if (!aborted) level1::build(a.aggw, a.nparts, a.l1, a.status, reinterpret_cast<float *>(sm.stage));
     __syncthreads();
   }
   if (tid == 0) {
     a.hdr->ticket = 0u;
     a.hdr->done = 0u;
+    a.hdr->aborted = 0u;
     __threadfence();
   }
 }
@@ -339,7 +358,11 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // A kernel launched behind this one with programmatic stream serialisation may be scheduled
   // as this grid drains; it still waits (griddepcontrol.wait) for this grid to complete.
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // Not when the last CTA builds level 1 itself: then nothing between two scans of one sampler
+  // is guaranteed to outlast the first (the level-1 launch of a larger table is), and a second
+  // scan that started early would share the header's ticket and CTA counters with it.  Without
+  // the instruction the launch behind this one starts when this grid has completed.
+  if (!a.inline_level1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -384,6 +407,7 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
 }
 
 inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
+constexpr size_t kSmemBytes = sizeof(Smem) + 128;
 
 }  // namespace
 
@@ -394,8 +418,8 @@ int64_t scan_scratch_bytes(int64_t n) {
 }
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
-                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, int64_t layout_n,
-                bool level1, bool overlap_previous) {
+                int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, bool level1,
+                bool overlap_previous, float *blkw) {
   GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
   GEARB_REQUIRE(prio && l1 && scratch && status, "scan: null pointer argument");  // cdf may be null
   GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
@@ -409,7 +433,6 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   GEARB_REQUIRE(scratch_bytes >= scan_scratch_bytes(n), "scan: scratch too small (%lld < %lld)",
                 (long long)scratch_bytes, (long long)scan_scratch_bytes(n));
   char *sc = static_cast<char *>(scratch);
-  (void)layout_n;  // the aggregate words start right behind the header whatever the size
   if (fresh) {
     // the header's ticket and CTA counters must start at zero
     GEARB_CUDA(cudaMemsetAsync(sc, 0, sizeof(ScanHeader), stream));
@@ -421,24 +444,29 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.l1 = l1;
   a.hdr = reinterpret_cast<ScanHeader *>(sc);
   a.aggw = reinterpret_cast<float *>(sc + sizeof(ScanHeader));
+  a.blkw = blkw;
   a.status = status;
   a.n = n;
   a.nparts = static_cast<unsigned>(nparts);
 
-  const size_t smem_bytes = sizeof(Smem) + 128;
-  static int ctas_by_instance[2] = {0, 0};  // [storing?]
-  if (ctas_by_instance[0] == 0) {
-    GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem_bytes)));
-    GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem_bytes)));
-    int v = 0;
-    GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, scan_kernel<true>, kThreads, smem_bytes));
-    ctas_by_instance[1] = v > 0 ? v : 1;
-    GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&v, scan_kernel<false>, kThreads, smem_bytes));
-    ctas_by_instance[0] = v > 0 ? v : 1;
+  // Function attributes and occupancy belong to a device: set up once per device, not per process.
+  int packed = 0;  // resident CTAs per SM: storing instance in the high half, totals-only in the low
+  {
+    int rc = per_device_once(kOnceScan, [](int *value) -> int {
+      GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kSmemBytes)));
+      GEARB_CUDA(cudaFuncSetAttribute(scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kSmemBytes)));
+      int st = 0, tot = 0;
+      GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&st, scan_kernel<true>, kThreads, kSmemBytes));
+      GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&tot, scan_kernel<false>, kThreads, kSmemBytes));
+      *value = ((st > 0 ? st : 1) << 16) | (tot > 0 ? tot : 1);
+      return GEARB_OK;
+    }, &packed);
+    if (rc != GEARB_OK) return rc;
   }
-  const int ctas_per_sm = ctas_by_instance[cdf != nullptr];
+  const size_t smem_bytes = kSmemBytes;
+  const int ctas_per_sm = cdf != nullptr ? (packed >> 16) : (packed & 0xffff);
   const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
   // Group partitions per ticket only when there is enough work to keep every CTA busy.
   a.group = nparts >= resident * kGroupMax * 2 ? kGroupMax : (nparts >= resident * 4 ? 2 : 1);
@@ -488,7 +516,7 @@ static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScra
 int64_t static_scan_max_n() { return kStaticMaxN; }
 
 // Where a scratch block keeps its per-partition aggregate words.
-float *scan_aggregate_words(void *scratch, int64_t) {
+float *scan_aggregate_words(void *scratch) {
   return reinterpret_cast<float *>(static_cast<char *>(scratch) + sizeof(ScanHeader));
 }
 
@@ -520,7 +548,7 @@ int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int
   }
   // The array starts zeroed when the module is loaded and every launch leaves its header
   // re-armed (ticket and CTA counter back at zero), so nothing has to be cleared between calls.
-  return launch_scan(prio, n, cdf, l1, scratch, kStaticScratchBytes, status, /*fresh=*/0, stream, kStaticMaxN);
+  return launch_scan(prio, n, cdf, l1, scratch, kStaticScratchBytes, status, /*fresh=*/0, stream);
 }
 
 }  // namespace gearb

@@ -48,7 +48,7 @@ __global__ void mark_kernel(float *prio, int64_t n, const int64_t *idx, const fl
 // Same tree as the compute warps of scan_kernel (scan_tree.cuh): warp w scans block w.
 // cdf == nullptr: the table is kept without its level-2 entries, only the aggregate is redone.
 __global__ void __launch_bounds__(kThreads) rescan_kernel(const float *prio, int64_t n, float *cdf,
-                                                          float *aggw, const unsigned *list,
+                                                          float *aggw, float *blkw, const unsigned *list,
                                                           const unsigned *count, unsigned *dirty) {
   __shared__ float wt[kWarps], wm[kWarps];
   __shared__ __align__(16) float xs_all[kWarps][128];
@@ -75,7 +75,10 @@ __global__ void __launch_bounds__(kThreads) rescan_kernel(const float *prio, int
       }
     }
     const tree::Group g = tree::block_sums(x, xs, lane, sv, bits);
-    if (lane == 0) wt[warp] = g.total;
+    if (lane == 0) {
+      wt[warp] = g.total;
+      if (blkw) blkw[static_cast<int64_t>(p) * kWarps + warp] = g.total;  // the partition's block totals follow it
+    }
     __syncthreads();
     float X = 0.f;
     for (int w = 0; w < warp; ++w) X = __fadd_rn(X, wt[w]);
@@ -116,8 +119,8 @@ int64_t update_scratch_bytes(int64_t n) {
   return ((nparts * 4 + 255) & ~int64_t(255)) * 2 + 256;
 }
 
-int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, ScanHeader *hdr, void *upd,
-                  const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream) {
+int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, float *blkw, ScanHeader *hdr,
+                  void *upd, const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream) {
   GEARB_REQUIRE(n > 0 && m >= 0, "update: bad sizes");
   if (m == 0) return GEARB_OK;
   GEARB_REQUIRE(prio && l1 && aggw && upd && idx && val && status, "update: null pointer argument");  // cdf may be null
@@ -132,7 +135,7 @@ int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, S
   int64_t grid = m < nparts ? m : nparts;  // at most that many partitions are listed
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   if (grid > cap) grid = cap;
-  rescan_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(prio, n, cdf, aggw, list, count, dirty);
+  rescan_kernel<<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(prio, n, cdf, aggw, blkw, list, count, dirty);
   GEARB_CUDA(cudaGetLastError());
   // l1 from all aggregates (level1.cu); the list of touched partitions is cleared for the next call
   {

@@ -37,7 +37,7 @@ from typing import Optional, Sequence
 
 import numpy as np
 
-__all__ = ["route", "exchange_plan", "plan_sorted", "Plan", "ShardedReplay"]
+__all__ = ["route", "exchange_plan", "plan_sorted", "plan_layout", "Plan", "ShardedReplay"]
 
 
 def route(totals: np.ndarray, u01_sorted: np.ndarray, world: int):
@@ -70,6 +70,18 @@ def route(totals: np.ndarray, u01_sorted: np.ndarray, world: int):
     residual = np.where(residual < totals[owner], residual, top)
     requester = (np.arange(B) // (B // world)).astype(np.int32)
     return owner, residual, requester
+
+
+def requester_of(B: int, world: int, layout: str = "contiguous") -> np.ndarray:
+    """Which rank consumes each position of the sorted global batch: contiguous slices (the
+    reference's partition, gear/loader/offline_loader.py:127-131) or dealt round-robin
+    ("scattered": rank r takes positions r, r + world, ...; its slice is still ascending, but
+    its requests spread over all shards instead of clustering on its own)."""
+    if layout == "contiguous":
+        return (np.arange(B) // (B // world)).astype(np.int32)
+    if layout == "scattered":
+        return (np.arange(B) % world).astype(np.int32)
+    raise ValueError(f"unknown slice layout {layout!r}")
 
 
 @dataclass
@@ -138,20 +150,79 @@ def plan_sorted(totals: np.ndarray, u01_sorted: np.ndarray, rank: int, world: in
     return Plan(np.arange(lo, hi), send_count, send_first, recv_count, recv_first, slice_owner), total, prefix
 
 
+def _owner_bounds(totals: np.ndarray, u01_sorted: np.ndarray, world: int):
+    """Cut points of the ascending batch between owners, the global total and the shard prefix."""
+    totals = np.asarray(totals, np.float64)
+    u = np.asarray(u01_sorted, np.float64)
+    B = len(u)
+    prefix = np.zeros(world + 1, np.float64)
+    acc = 0.0
+    for j in range(world):
+        acc = acc + float(totals[j])
+        prefix[j + 1] = acc
+    total = prefix[world]
+    v = u * total
+    v = np.where(v >= 0.0, v, 0.0)
+    v = np.where(v < total, v, np.nextafter(total, 0.0))
+    cut = np.searchsorted(v, prefix[1:world], side="left")
+    bounds = np.concatenate([[0], cut, [B]]).astype(np.int64)
+    for j in range(world - 1, 0, -1):            # a trailing shard without mass owns nothing
+        if totals[j] > 0.0:
+            break
+        bounds[j] = B
+    return bounds, total, prefix
+
+
+def plan_layout(totals: np.ndarray, u01_sorted: np.ndarray, rank: int, world: int, layout: str = "contiguous"):
+    """plan_sorted for either slice layout.  Returns (plan, total, prefix, slot_map) where slot_map
+    is None (contiguous: an owner's answers are already grouped by requester) or (world, lo, base):
+    the owner's request at position q of the batch goes to slot base[q % world] + q // world of its
+    send regions, which groups them by requester in the order of the requester's slice."""
+    if layout == "contiguous":
+        plan, total, prefix = plan_sorted(totals, u01_sorted, rank, world)
+        return plan, total, prefix, None
+    if layout != "scattered":
+        raise ValueError(f"unknown slice layout {layout!r}")
+    B = len(u01_sorted)
+    if B % world:
+        raise ValueError(f"global batch {B} is not a multiple of the world size {world}")
+    bounds, total, prefix = _owner_bounds(totals, u01_sorted, world)
+
+    def dealt(a: int, b_: int, q: int):
+        """Positions g in [a, b_) with g % world == q: (how many, slot of the first in q's slice)."""
+        g0 = a + ((q - a) % world)
+        return max(0, -(-(b_ - g0) // world)), g0 // world
+
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    send = [dealt(lo, hi, q) for q in range(world)]
+    send_count = np.array([c for c, _ in send], np.int64)
+    send_first = np.concatenate([[0], np.cumsum(send_count)[:-1]]).astype(np.int64)
+    base = np.array([int(send_first[q]) - send[q][1] for q in range(world)], np.int64)
+    recv = [dealt(int(bounds[j]), int(bounds[j + 1]), rank) for j in range(world)]
+    recv_count = np.array([c for c, _ in recv], np.int64)
+    recv_first = np.concatenate([[0], np.cumsum(recv_count)[:-1]]).astype(np.int64)
+    slice_owner = np.repeat(np.arange(world, dtype=np.int32), recv_count)
+    plan = Plan(np.arange(lo, hi), send_count, send_first, recv_count, recv_first, slice_owner)
+    return plan, total, prefix, (world, lo, base)
+
+
 class ShardedReplay:
     """One rank's shard (table + priorities) plus the exchange.
 
     table/handler/sampler are gear_b200.core objects of the local shard; `comm` is a
-    gear_b200.comm.Communicator (or None when world == 1).
+    gear_b200.comm.Communicator (or None when world == 1).  store: the scans keep the level-2
+    table (8 bytes of traffic per priority); False: only the partition offsets and block totals
+    (4 bytes per priority), and the sampling launches rebuild what each request needs.
     """
 
     def __init__(self, handler, sampler, columns: Sequence[int], rank: int, world: int, comm=None,
-                 max_global_batch: int = 8192):
+                 max_global_batch: int = 8192, store: bool = True):
         import torch
         from . import _native as N
         self.torch, self.N = torch, N
         self.handler, self.sampler, self.columns = handler, sampler, [int(c) for c in columns]
         self.rank, self.world, self.comm = int(rank), int(world), comm
+        self.store = bool(store)
         if world > 1 and comm is None:
             raise ValueError("a communicator is required when world > 1")
         t = handler.table
@@ -170,13 +241,16 @@ class ShardedReplay:
         self.totals_host = torch.empty(world, dtype=torch.float64).pin_memory()
         self.res_host = torch.empty(self.maxB, dtype=torch.float64).pin_memory()
         self.res_dev = torch.empty(self.maxB, dtype=torch.float64, device=dev)
-        self.owner_base = torch.empty(b, dtype=torch.int64, device=dev)
-        self.owner_base_host = torch.empty(b, dtype=torch.int64).pin_memory()
         self.last_plan: Optional[Plan] = None
+        if comm is not None and world > 1:
+            # NCCL sets a pair of ranks up for point-to-point traffic the first time they talk, which
+            # takes milliseconds; which pairs a batch needs depends on the draw, so all pairs are
+            # connected here instead of inside some later step.
+            comm.connect_all()
 
     # -- step pieces (separate so that a benchmark can time them) ---------------------------
     def scan(self, priorities):
-        self.sampler.scan(priorities)
+        self.sampler.scan(priorities, store=self.store)
 
     def gather_totals(self) -> np.ndarray:
         """Shard totals of every rank on the host (one 8-byte-per-rank collective + one sync)."""
@@ -191,12 +265,14 @@ class ShardedReplay:
         torch.cuda.current_stream().synchronize()
         return self.totals_host.numpy().copy()
 
-    def step_sorted(self, priorities, u01_sorted: np.ndarray, u01_sorted_dev, rescan: bool = True):
+    def step_sorted(self, priorities, u01_sorted: np.ndarray, u01_sorted_dev, rescan: bool = True,
+                    layout: str = "contiguous"):
         """One global batch whose ascending variates are already on the device as well
         (u01_sorted_dev: float64 CUDA tensor with the same values).  The owner reads its run of
         the batch in place and maps it into its own table inside the kernel, so the host only
-        does O(world) work per step."""
-        torch = self.torch
+        does O(world) work per step: one synchronisation for the shard totals (the message sizes of
+        the all-to-all depend on them), no other copy in either direction.  layout: how the batch
+        is dealt to the ranks (requester_of)."""
         B = len(u01_sorted)
         if B > self.maxB or B % self.world:
             raise ValueError(f"global batch {B}: at most {self.maxB} and a multiple of {self.world}")
@@ -204,7 +280,7 @@ class ShardedReplay:
         if rescan:
             self.scan(priorities)
         totals = self.gather_totals()
-        plan, total, prefix = plan_sorted(totals, u01_sorted, self.rank, self.world)
+        plan, total, prefix, slot_map = plan_layout(totals, u01_sorted, self.rank, self.world, layout)
         self.last_plan = plan
         m = len(plan.mine)
         direct = self.world == 1
@@ -213,17 +289,16 @@ class ShardedReplay:
         if m:
             lo = int(plan.mine[0])
             self.sampler.sample_gather(self.handler, u01_sorted_dev[lo:lo + m], self.columns, dsts, zero_fill=True,
-                                       out_flat=flat, affine=(total, prefix[self.rank]))
+                                       out_flat=flat, affine=(total, prefix[self.rank]),
+                                       flat_offset=self.rank * self.n_local, slot_map=slot_map)
         if not direct:
             self.comm.alltoallv(self.send + [self.send_flat], self.recv + [self.recv_flat], self.slots + [8],
                                 plan.send_first, plan.send_count, plan.recv_first, plan.recv_count)
-        self.owner_base_host[:b].copy_(torch.from_numpy(plan.slice_owner.astype(np.int64) * self.n_local))
-        self.owner_base[:b].copy_(self.owner_base_host[:b], non_blocking=True)
-        gflat = self.recv_flat[:b] + self.owner_base[:b]
-        return [r[: b * s] for r, s in zip(self.recv, self.slots)], gflat
+        return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]
 
     def step(self, priorities, u01_sorted: np.ndarray, rescan: bool = True):
-        """One global batch.  Returns (column byte tensors of this rank's slice, global step ids)."""
+        """One global batch, routed request by request on the host (contiguous slices).  Returns
+        (column byte tensors of this rank's slice, global step ids)."""
         torch = self.torch
         B = len(u01_sorted)
         if B > self.maxB or B % self.world:
@@ -253,35 +328,52 @@ class ShardedReplay:
             self.comm.alltoallv(bufs_s, bufs_r, sizes, plan.send_first, plan.send_count, plan.recv_first,
                                 plan.recv_count)
         # global step id = owner * steps_per_shard + owner-local index
-        self.owner_base_host[:b].copy_(torch.from_numpy(plan.slice_owner.astype(np.int64) * self.n_local))
-        self.owner_base[:b].copy_(self.owner_base_host[:b], non_blocking=True)
-        gflat = self.recv_flat[:b] + self.owner_base[:b]
-        return [r[: b * s] for r, s in zip(self.recv, self.slots)], gflat
+        owner_base = torch.from_numpy(plan.slice_owner.astype(np.int64) * self.n_local).to(self.dev)
+        return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b] + owner_base
 
     # -- exchange-free mode: requesters read the owners' memory in place ---------------------
-    def enable_pull(self, double_buffer: bool = True, ring: bool = False, mailbox: bool = True) -> None:
+    def enable_pull(self, double_buffer: bool = True, ring: bool = False, mailbox: bool = True,
+                    priorities=None) -> None:
         """Map every peer's shard into this process (collective: every rank calls it once).
+
+        priorities: a gear_b200.core.DeviceBuffer holding this shard's float32 priorities.  Given,
+        the shards keep no level-2 table: every rank scans with the totals-only scan (half the
+        traffic), the peers map each other's priorities and block totals, and each rank's level 1
+        travels into the peers' mailboxes with its total, so a requester searches level 1 in its
+        own memory and fetches one 2 KiB block of the owner's priorities per request.  (A
+        DeviceBuffer because another process can only map a whole allocation from its start.)
+        Needs the mailbox.  While a step is in flight anywhere, no rank may change its priorities.
 
         mailbox: the shard totals travel without a collective -- every rank writes its total and
         the step's number straight into every rank's mailbox, and the pull launch waits (with a
         limit) until all of them have arrived; needs double_buffer.  Otherwise an NCCL all-gather.
 
-        double_buffer: alternate between two cumulative tables so that the totals' all-gather is
-        the only synchronisation of a step; otherwise one table and a second (8-byte) collective
-        closes every step.  ring: stream large requests through bulk-copy rings instead of plain
-        16-byte loads."""
+        double_buffer (stored tables only): alternate between two cumulative tables so that the
+        totals' exchange is the only synchronisation of a step; otherwise one table and a second
+        (8-byte) collective closes every step.  ring: stream large requests through bulk-copy
+        rings instead of plain 16-byte loads."""
         torch = self.torch
         from . import core
         if self.handler.table.device_ptr == 0:
             raise ValueError("pull mode needs the shards in device memory")
+        self._pull_lazy = priorities is not None
+        if self._pull_lazy and not (mailbox and double_buffer):
+            raise ValueError("pull on tables without level-2 entries needs the mailbox")
         self._pull_ring = bool(ring)
-        self._pull_samplers = [self.sampler] + ([core.PrioritySampler(self.n_local)] if double_buffer else [])
+        self._pull_prio = priorities
+        two = double_buffer and not self._pull_lazy
+        self._pull_samplers = [self.sampler] + ([core.PrioritySampler(self.n_local)] if two else [])
         self._pull_k = -1
-        self._pull_box = core.DeviceBuffer(self.N.MAILBOX_BYTES) if (mailbox and double_buffer) else None
+        use_box = mailbox and double_buffer
+        self._pull_box = core.DeviceBuffer(core.mailbox_bytes(self.n_local if self._pull_lazy else 0)) if use_box else None
         self._pull_epoch = 0
         own = [self.handler.table.device_ptr] + ([self._pull_box.ptr] if self._pull_box else [])
-        for sm in self._pull_samplers:
-            own += [sm.cdf_ptr, sm.l1_ptr]
+        if self._pull_lazy:
+            b0, b1, _ = self.sampler.block_totals()
+            own += [priorities.ptr, b0, b1]
+        else:
+            for sm in self._pull_samplers:
+                own += [sm.cdf_ptr, sm.l1_ptr]
         nh = len(own)
         self._pull_mapped = []
         if self.world == 1:
@@ -305,8 +397,13 @@ class ShardedReplay:
         self._pull_tables = [row[0] for row in ptrs]
         o = 2 if self._pull_box else 1
         self._pull_boxes = [row[1] for row in ptrs] if self._pull_box else None
-        self._pull_cdfs = [[row[o + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
-        self._pull_l1s = [[row[o + 1 + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
+        if self._pull_lazy:
+            self._pull_prios = [row[o] for row in ptrs]
+            self._pull_blks = [[row[o + 1] for row in ptrs], [row[o + 2] for row in ptrs]]
+            self._pull_slot = 0
+        else:
+            self._pull_cdfs = [[row[o + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
+            self._pull_l1s = [[row[o + 1 + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
         self._pull_fence = torch.zeros(1, dtype=torch.float32, device=self.dev)
 
     def disable_pull(self) -> None:
@@ -331,15 +428,20 @@ class ShardedReplay:
         between: called between the scan's two launches (a benchmark records an event there)."""
         self._pull_k += 1
         sm = self._pull_samplers[self._pull_k % len(self._pull_samplers)]
+        if self._pull_lazy:
+            # every rank writes the block totals of the step into the same one of its two buffers
+            self._pull_slot = (self._pull_epoch + 1) & 1
+            sm.select_slot(self._pull_slot)
+        store = not self._pull_lazy
         if between is None:
             # with two tables in turn, the launch before this one (the previous pull) reads the other
-            sm.scan(priorities, alternate=len(self._pull_samplers) == 2)
+            sm.scan(priorities, store=store, alternate=store and len(self._pull_samplers) == 2)
         else:
-            sm.scan_partitions(priorities, store=True)
+            sm.scan_partitions(priorities, store=store)
             between()
             sm.scan_level1()
 
-    def step_pull(self, priorities, u01_sorted_dev, rescan: bool = True):
+    def step_pull(self, priorities, u01_sorted_dev, rescan: bool = True, layout: str = "contiguous"):
         """One global batch without an exchange step: nothing on the host depends on device
         results, so consecutive steps queue back to back on the stream.  u01_sorted_dev: the
         batch's ascending U[0,1) variates as a float64 CUDA tensor (the same on every rank).
@@ -353,25 +455,39 @@ class ShardedReplay:
             self.pull_scan(priorities)
         k = self._pull_k % nbuf
         sm = self._pull_samplers[k]
-        mine_slice = slice(self.rank * b, (self.rank + 1) * b)
+        if layout == "contiguous":
+            mine, stride = u01_sorted_dev[self.rank * b:(self.rank + 1) * b], 1
+        elif layout == "scattered":
+            mine, stride = u01_sorted_dev[self.rank:], self.world
+        else:
+            raise ValueError(f"unknown slice layout {layout!r}")
+        out = [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]
+        common = dict(zero_fill=True, ring=self._pull_ring, out_flat=self.recv_flat, self_shard=self.rank,
+                      count=b, variate_stride=stride)
         if self._pull_box is not None:
             # totals through the mailboxes: no collective, no host involvement
             self._pull_epoch += 1
-            sm.publish_total(self.world, self.rank, self._pull_boxes, self._pull_epoch)
-            sm.pull(self.handler, None, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables,
-                    u01_sorted_dev[mine_slice], self.columns, self.recv, zero_fill=True, ring=self._pull_ring,
-                    out_flat=self.recv_flat, self_shard=self.rank, mailbox=self._pull_box.ptr,
-                    epoch=self._pull_epoch)
-            return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]
+            e = self._pull_epoch
+            sm.publish(self.world, self.rank, self._pull_boxes, e, copy_l1=self._pull_lazy)
+            if self._pull_lazy:
+                from . import core
+                l1s = [sm.l1_ptr if j == self.rank else self._pull_box.ptr + core.mailbox_l1_offset(self.n_local, e, j)
+                       for j in range(self.world)]
+                sm.pull(self.handler, None, None, l1s, self._pull_tables, mine, self.columns, self.recv,
+                        mailbox=self._pull_box.ptr, epoch=e, prios=self._pull_prios,
+                        blks=self._pull_blks[self._pull_slot], **common)
+            else:
+                sm.pull(self.handler, None, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables, mine,
+                        self.columns, self.recv, mailbox=self._pull_box.ptr, epoch=e, **common)
+            return out
         nparts = (self.n_local + self.N.PART - 1) // self.N.PART
-        mine = sm.l1[nparts:nparts + 1]
+        tot = sm.l1[nparts:nparts + 1]
         if self.world == 1:
-            self.totals_dev.copy_(mine)
+            self.totals_dev.copy_(tot)
         else:
-            self.comm.allgather(mine, self.totals_dev)   # every shard's scan is complete once this lands
-        sm.pull(self.handler, self.totals_dev, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables,
-                u01_sorted_dev[mine_slice], self.columns, self.recv, zero_fill=True,
-                ring=self._pull_ring, out_flat=self.recv_flat, self_shard=self.rank)
+            self.comm.allgather(tot, self.totals_dev)   # every shard's scan is complete once this lands
+        sm.pull(self.handler, self.totals_dev, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables, mine,
+                self.columns, self.recv, **common)
         if nbuf == 1 and self.world > 1:
             self.comm.allreduce(self._pull_fence)        # the next scan must not overtake the peers' reads
-        return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]
+        return out

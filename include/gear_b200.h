@@ -29,19 +29,21 @@ extern "C" {
 #define GEARB_ERR_CUDA 2        /* CUDA runtime failure (reference: assert(0))   */
 #define GEARB_ERR_NOMEM 3
 #define GEARB_ERR_STATE 4       /* object not connected / pattern not set        */
-#define GEARB_ERR_TIMEOUT 5     /* a bounded device-side wait ran out            */
+#define GEARB_ERR_TIMEOUT 5     /* a bounded device-side wait ran out (gearb_sampler_result) */
 #define GEARB_ERR_NCCL 6        /* NCCL failure (reference: exit())              */
 #define GEARB_ERR_UNSUPPORTED 7
 
 /* Bits of the device status word written by the kernels (status[0]).        */
-#define GEARB_ST_LOOKBACK_TIMEOUT 0x1 /* reserved (raised by an earlier look-back scheme; never set now)  */
 #define GEARB_ST_L1_RESUMMED 0x2      /* scan: a float64 partial sum was inexact; level-1 was rebuilt in order */
 #define GEARB_ST_BAD_PRIORITY 0x4     /* scan: a priority had its sign bit set (negative, -0.0) or was NaN */
 #define GEARB_ST_BAD_REQUEST 0x8      /* gather: trajectory index outside the table, request skipped */
 #define GEARB_ST_LEN_CLAMPED 0x10     /* gather: a length beyond trajectory_length was clamped */
-#define GEARB_ST_SCAN_ABORTED 0x20    /* scan: a bounded wait inside a CTA ran out; cdf and l1 are NOT valid */
+#define GEARB_ST_SCAN_ABORTED 0x20    /* a bounded wait inside a kernel ran out (a lost copy, a peer that never
+                                         published): the tables or the batch of that launch are NOT valid */
 /* status[1] = number of variates that landed within one float32 ulp of a
- * cumulative-priority boundary (search), accumulated until cleared.          */
+ * cumulative-priority boundary (search), accumulated until cleared.
+ * status[2] = low 32 bits of the epoch at which a pull launch last gave up waiting for its peers.
+ * The words accumulate; gearb_sampler_clear_status zeroes them.               */
 #define GEARB_STATUS_WORDS 4
 
 /* ---- constants of the cumulative-priority table ------------------------- */
@@ -216,17 +218,30 @@ int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
  * last such call.  gearb_sampler_search and gearb_sampler_pull need the stored table and
  * return GEARB_ERR_STATE until the next gearb_sampler_scan.                                */
 int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream);
+/* gearb_sampler_scan for one of two samplers that are used in turn: the launch may start while
+ * the launch before it in the stream is still finishing, which is only correct when that launch
+ * does not read THIS sampler's tables (it reads the other one's).  It still completes after it.
+ * Which launches may overlap: gearb_sampler_scan_totals and this call may begin while the launch
+ * directly before them in the stream (a sampling or pull launch, a level-1 launch) is still
+ * running; they never run beside an earlier scan of the same sampler, and a table of at most
+ * 1024 partitions (4,194,304 priorities) is always scanned strictly after everything before it.  */
+int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void *stream);
 /* The two launches of a scan, separately, for callers that want to put something between
  * them (an event, work of their own): first the pass over the priorities that leaves one
  * aggregate per partition (store != 0: and the level-2 table), then the small launch that
  * turns the aggregates into l1.  Together they equal gearb_sampler_scan (store != 0) or
  * gearb_sampler_scan_totals (store == 0).                                                */
-/* gearb_sampler_scan for one of two samplers that are used in turn: the launch may start while
- * the launch before it in the stream is still finishing, which is only correct when that launch
- * does not read THIS sampler's tables (it reads the other one's).  It still completes after it. */
-int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void *stream);
 int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int store, void *stream);
 int gearb_sampler_scan_level1(gearb_sampler *s, void *stream);
+/* Every scan of a sampler also leaves the eight 512-value block totals of each partition, from
+ * which a sampling launch on a table without stored level-2 entries rebuilds only the block a
+ * request falls into.  There are two such buffers and a scan writes the one the previous scan
+ * did not (so that a scan never overwrites what a launch still running -- on this GPU, or on a
+ * peer in the pull mode -- is reading).  select_slot fixes the buffer (0 or 1) of the NEXT scan,
+ * for ranks that must agree on it without talking (pull mode: slot = epoch & 1);
+ * block_totals returns both buffers and the slot the last scan wrote.                     */
+int gearb_sampler_select_slot(gearb_sampler *s, int slot);
+int gearb_sampler_block_totals(const gearb_sampler *s, float **slot0, float **slot1, int *current);
 /* Incremental update after a gearb_sampler_scan of the same array: priorities[idx[i]] =
  * values[i] for i < m (idx, values: device arrays), then only the partitions that were touched
  * are rescanned and the partition offsets rebuilt.  The table afterwards is bit-identical to a
@@ -250,15 +265,25 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
 /* The same for one shard of a sharded table: a variate u of the GLOBAL draw becomes
  * u * mul - sub before the search (mul = total priority of all shards, sub = total of the
  * shards before this one), clamped into this shard's range.  Stands where an owner answers
- * the requests of its peers, CpuTrajectoryStorageHandler::subsend, src/storage/handler.cc:160-193. */
+ * the requests of its peers, CpuTrajectoryStorageHandler::subsend, src/storage/handler.cc:160-193.
+ * flat_offset is added to out_flat (the shard's first global step id).  slot_mod > 1: the b
+ * requests are positions [slot_lo, slot_lo + b) of a global batch that is dealt round-robin to
+ * slot_mod requesters; request at position q then lands in slot slot_base[q % slot_mod] +
+ * q / slot_mod of dst and out_*, which groups an owner's answers by requester.  slot_mod <= 1:
+ * request i lands in slot i.                                                              */
 int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const double *variates,
                                        int64_t b, double mul, double sub, const int64_t *lengths,
                                        int64_t index_offset, const int32_t *columns, int ncols,
                                        void *const *dst, int zero_fill, int64_t *out_flat,
-                                       int64_t *out_idx, int64_t *out_ts, int64_t *out_len, void *stream);
+                                       int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
+                                       int64_t flat_offset, int slot_mod, int64_t slot_lo,
+                                       const int64_t *slot_base, void *stream);
 int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status);
-/* Synchronises `stream`, then returns total and the status words. */
+/* Synchronises `stream`, then returns total and the status words.  When GEARB_ST_SCAN_ABORTED is
+ * set in them the outputs are still filled in and the call returns GEARB_ERR_TIMEOUT.       */
 int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t *status);
+/* Zeroes the sampler's status words on `stream` (they accumulate otherwise).               */
+int gearb_sampler_clear_status(gearb_sampler *s, void *stream);
 
 /* ======================= communication ================================== */
 /* create_nccl_id, src/nccl_comm.cc:4-10: 128 bytes to hand to every rank.       */
@@ -335,6 +360,43 @@ int gearb_device_alloc(int64_t bytes, void **ptr); /* cudaMalloc, zeroed */
 int gearb_device_free(void *ptr);
 int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
                                 void *stream);
+/* A mailbox may also carry copies of the peers' level-1 tables, so that a pull launch searches
+ * level 1 in its own GPU's memory instead of the owner's: gearb_mailbox_bytes(n) is the size of
+ * such a mailbox for shards of n priorities (the header above plus two slots of GEARB_MAX_SHARDS
+ * copies), gearb_mailbox_l1_offset(n, epoch, shard) the byte offset of shard's copy for that
+ * epoch.  gearb_sampler_publish with copy_l1 != 0 writes this rank's level 1 into every other
+ * rank's mailbox before the total and the epoch.                                          */
+int64_t gearb_mailbox_bytes(int64_t n);
+int64_t gearb_mailbox_l1_offset(int64_t n, uint64_t epoch, int shard);
+int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
+                          int copy_l1, void *stream);
+/* The general form of gearb_sampler_pull / gearb_sampler_pull_mailbox.  Per shard either its
+ * stored level-2 table (cdf) or, with cdf == NULL, its priorities and block totals (prio, blk:
+ * the slot of the step, see gearb_sampler_select_slot) -- then the shards may have been scanned
+ * with gearb_sampler_scan_totals, which reads half as much.  l1[j] may point at a copy of shard
+ * j's level 1 in this GPU's memory (a mailbox).  Request g of the launch uses variate
+ * variates[g * variate_stride].  Either totals or mailbox + epoch.                          */
+typedef struct gearb_pull_args {
+  int world, self;
+  const double *totals;
+  const void *mailbox;
+  uint64_t epoch;
+  const void *const *cdf;
+  const void *const *prio;
+  const void *const *blk;
+  const void *const *l1;
+  const void *const *table;
+  const double *variates;
+  int64_t b;
+  int64_t variate_stride;
+  const int32_t *columns;
+  int ncols;
+  void *const *dst;
+  int zero_fill;
+  int ring;
+  int64_t *out_flat, *out_idx, *out_ts;
+} gearb_pull_args;
+int gearb_sampler_pull_ex(gearb_sampler *s, gearb_handler *h, const gearb_pull_args *args, void *stream);
 /* gearb_sampler_pull with the totals taken from this rank's mailbox at `epoch`. */
 int gearb_sampler_pull_mailbox(gearb_sampler *s, gearb_handler *h, int world, int self, const void *mailbox,
                                uint64_t epoch, const void *const *cdf, const void *const *l1,

@@ -49,22 +49,30 @@ def main():
     handler.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * len(rows))
     sampler = core.PrioritySampler(n_local)
     replay = ShardedReplay(handler, sampler, cols, rank, W, comm, max_global_batch=B)
-    dprio = torch.from_numpy(prio).to(dev)
+    pbuf = core.DeviceBuffer(n_local * 4)        # an allocation of its own: the peers map it in the lazy pull mode
+    dprio = pbuf.view(torch.float32)
+    dprio.copy_(torch.from_numpy(prio))
 
     imgs, prios = zip(*[shard_data(r) for r in range(W)])
     gimg, gprio = np.concatenate(imgs), np.concatenate(prios)
     gcdf, gl1, _, _ = O.scan(gprio)
     accu, stride = O.table_layout(rows, T)
-    for trial in range(3):
+    def my_slice(x, layout):
+        return x[rank * b:(rank + 1) * b] if layout == "contiguous" else x[rank::W]
+
+    lazy_replay = ShardedReplay(handler, sampler, cols, rank, W, comm, max_global_batch=B, store=False)
+    for trial in range(6):
         u01 = np.sort(O.synth_u01(300 + trial, 0, B))
-        if trial == 2:
+        layout = "scattered" if trial >= 3 else "contiguous"
+        if trial in (2, 5):
             u01[:] = np.sort(O.synth_u01(400, 0, B) * 0.01)     # every request lands on shard 0
-        if trial == 1:      # the device-resident route: same result by construction
-            outs, gflat = replay.step_sorted(dprio, u01, torch.from_numpy(u01).to(dev))
-        else:
+        if trial == 0:      # routed request by request on the host
             outs, gflat = replay.step(dprio, u01)
+        else:               # the device-resident route: same result by construction; 4, 5: tables without level 2
+            rp = lazy_replay if trial >= 4 else replay
+            outs, gflat = rp.step_sorted(dprio, u01, torch.from_numpy(u01).to(dev), layout=layout)
         torch.cuda.synchronize()
-        want_flat = O.search(gcdf, gl1, u01, scale=True)[rank * b:(rank + 1) * b]
+        want_flat = my_slice(O.search(gcdf, gl1, u01, scale=True), layout)
         assert np.array_equal(gflat.cpu().numpy(), want_flat), (rank, trial)
         gi, gt, gl = O.decode(want_flat, T)
         for c in cols:
@@ -74,17 +82,20 @@ def main():
     # exchange-free mode: the requester reads the owners' memory in place
     small = core.StorageHandler(table)                       # short segments: the staged copy path
     small.set(cols, [core.SubscribePattern(-1, 3, N.PAD_HEAD)] * len(rows))
-    for mode, (double_buffer, ring, hd, off, Lm, head) in enumerate(
-            [(True, False, handler, 0, L, False), (False, True, handler, 0, L, False), (True, False, small, -1, 3, True)]):
+    for mode, (double_buffer, ring, hd, off, Lm, head, lazy) in enumerate(
+            [(True, False, handler, 0, L, False, False), (False, True, handler, 0, L, False, False),
+             (True, False, small, -1, 3, True, False),
+             (True, True, handler, 0, L, False, True), (True, False, small, -1, 3, True, True)]):
         rp = ShardedReplay(hd, sampler, cols, rank, W, comm, max_global_batch=B)
-        rp.enable_pull(double_buffer=double_buffer, ring=ring)
-        for trial in range(4):
+        rp.enable_pull(double_buffer=double_buffer, ring=ring, priorities=pbuf if lazy else None)
+        for trial in range(6):
             u01 = np.sort(O.synth_u01(500 + trial, mode, B))
+            layout = "scattered" if trial >= 4 else "contiguous"
             if trial == 2:
                 u01[:] = np.sort(O.synth_u01(600, mode, B) * 0.01)
-            outs, gflat = rp.step_pull(dprio, torch.from_numpy(u01).to(dev), rescan=(trial != 3))
+            outs, gflat = rp.step_pull(dprio, torch.from_numpy(u01).to(dev), rescan=(trial != 3), layout=layout)
             torch.cuda.synchronize()
-            want_flat = O.search(gcdf, gl1, u01, scale=True)[rank * b:(rank + 1) * b]
+            want_flat = my_slice(O.search(gcdf, gl1, u01, scale=True), layout)
             assert np.array_equal(gflat.cpu().numpy(), want_flat), ("pull", mode, rank, trial)
             gi, gt, gl = O.decode(want_flat, T)
             for c in cols:

@@ -88,3 +88,31 @@ def test_offline_loader_matches_oracle(O, residency, method):
     torch.cuda.synchronize()
     for a, b in zip(fused, two_step):
         assert torch.equal(a, b)
+
+
+def test_weighted_draw_with_replacement_gives_duplicate_rows(O):
+    # The reference's WeightedSampler calls torch.multinomial with its default replacement=False
+    # (gear/sampler/global_sampler.py:170): a batch never holds an index twice, and a batch larger
+    # than the number of candidates with weight raises.  Here the draw is with replacement (it
+    # consumes external variates), so a batch larger than the table is served and some trajectories
+    # appear in several rows; every row, duplicates included, holds that trajectory's bytes.
+    gear.init(0)
+    cap, T, B, L = 8, 30, 32, 6
+    ds = _dataset(O, cap, T, key=7100, residency="hbm")
+    with pytest.raises(RuntimeError):
+        torch.multinomial(ds.weights.float().cuda(), B)            # what the reference's call would do
+    mpu = ModelParallelismUnit(device=torch.device("cuda:0"), dp_rank=0, dp_world_size=1)
+    loader = OfflineLoader(ds, B, mpu, "Weighted", [dict(name="obs", offset=0, length=L, pad="tail")])
+    img = np.array(ds._table._t.host_view(), copy=True)
+    accu, stride = O.table_layout([68, 24, 4, 1], T)
+    tss, data = next(loader)
+    torch.cuda.synchronize()
+    idx = torch.sort(loader._indices[loader._sampler._cache]).values.cpu().numpy()
+    assert len(np.unique(idx)) < B                                  # pigeonhole: 32 draws from 8 trajectories
+    lens = ds.timesteps.numpy()[idx]
+    want = O.fused_subcopy(img, idx, lens, lens, stride, int(accu[0]), T, 68, 0, L, False)
+    got = data[0].cpu().numpy().view(np.uint8).reshape(B, -1)
+    assert np.array_equal(got.reshape(-1), want)
+    for i in range(1, B):
+        if idx[i] == idx[i - 1]:
+            assert np.array_equal(got[i], got[i - 1])

@@ -107,7 +107,8 @@ def test_fused_subset_of_columns_and_offset(O):
     ([156, 24, 4, 4, 1], 200, 40, 64, N.PAD_TAIL, 0, False), # short requests: staged in shared memory
     ([3, 7, 13], 37, 300, 9, N.PAD_HEAD, -4, False),
 ])
-def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ring):
+@pytest.mark.parametrize("lazy", [False, True])   # True: no stored level-2 tables, blocks rebuilt from the owners' priorities
+def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ring, lazy):
     # Three equal shards held by one process stand for three ranks: the kernel routes every
     # request by the shard totals and reads the owner's tables through the pointer arrays.  The
     # expected result is defined shard by shard: route() on the host, then the owner's search.
@@ -115,6 +116,7 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
     W, B = 3, 255
     n = cap * T - 5                     # not a whole number of partitions, and fewer steps than the table
     shards = []
+    dprios = []
     for j in range(W):
         t, img = build(O, rows, T, cap, seed=40 + j)
         prio = O.synth_lognormal(50 + j, 0, n)
@@ -122,8 +124,12 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
         if j == 1:
             prio *= 3.0
         s = core.PrioritySampler(n)
-        s.scan(dev(prio))
+        dprios.append(dev(prio))
+        s.scan(dprios[j], store=not lazy)
         shards.append((t, img, prio, s, O.scan(prio)))
+    cdfs = None if lazy else [sh[3].cdf_ptr for sh in shards]
+    kw = dict(prios=[p.data_ptr() for p in dprios],
+              blks=[sh[3].block_totals()[sh[3].block_totals()[2]] for sh in shards]) if lazy else {}
     h = core.StorageHandler(shards[0][0])
     cols = list(range(len(rows)))
     h.set(cols, [core.SubscribePattern(off, L, pad)] * len(rows))
@@ -142,20 +148,23 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
         if trial == 0:
             # totals through a mailbox, as separate processes would exchange them: every shard's
             # sampler writes its own total and the epoch, the pull launch waits for all of them
-            box = core.DeviceBuffer(N.MAILBOX_BYTES)
+            # (with `lazy`, every shard's level 1 travels into the mailbox too and is searched there)
+            box = core.DeviceBuffer(core.mailbox_bytes(n if lazy else 0))
             for epoch in (1, 2, 3):                  # both slots, and a slot's second use
                 for j, sh in enumerate(shards):
-                    sh[3].publish_total(W, j, [box.ptr] * W, epoch)
-                shards[0][3].pull(h, None, [sh[3].cdf_ptr for sh in shards], [sh[3].l1_ptr for sh in shards],
+                    sh[3].publish(W, j, [box.ptr] * W, epoch, copy_l1=lazy)
+                l1s = [box.ptr + core.mailbox_l1_offset(n, epoch, j) for j in range(W)] if lazy \
+                    else [sh[3].l1_ptr for sh in shards]
+                shards[0][3].pull(h, None, cdfs, l1s,
                                   [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
                                   out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1),
-                                  mailbox=box.ptr, epoch=epoch)
+                                  mailbox=box.ptr, epoch=epoch, **kw)
             torch.cuda.synchronize()
             box.free()
         else:
-            shards[0][3].pull(h, dev(totals_used), [sh[3].cdf_ptr for sh in shards], [sh[3].l1_ptr for sh in shards],
+            shards[0][3].pull(h, dev(totals_used), cdfs, [sh[3].l1_ptr for sh in shards],
                               [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
-                              out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1))
+                              out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1), **kw)
             torch.cuda.synchronize()
         owner, residual, _ = route(totals_used, np.resize(u, B + (-B) % W), W)   # padded to a multiple of W
         owner, residual = owner[:B], residual[:B]
@@ -214,10 +223,43 @@ def test_host_batch_pipeline_delivers_the_same_batches(O):
             assert np.array_equal(hc[c].numpy(), want)
 
 
+def test_pull_with_strided_variates_reads_every_kth(O):
+    # A rank whose slice is every W-th request of the sorted batch passes the whole batch and a stride.
+    rows, T, cap, L, W = [4096, 4], 60, 40, 8, 2
+    n = cap * T
+    shards = []
+    for j in range(W):
+        t, img = build(O, rows, T, cap, seed=70 + j)
+        s = core.PrioritySampler(n)
+        s.scan(dev(O.synth_lognormal(75 + j, 0, n)))
+        shards.append((t, s))
+    h = core.StorageHandler(shards[0][0])
+    h.set([0, 1], [core.SubscribePattern(0, L, N.PAD_TAIL)] * 2)
+    B, k = 90, 3
+    u = dev(np.sort(O.synth_u01(79, 0, B)))
+    totals = torch.stack([sh[1].l1[-1] for sh in shards])
+    args = ([sh[1].cdf_ptr for sh in shards], [sh[1].l1_ptr for sh in shards], [sh[0].device_ptr for sh in shards])
+    full = [torch.empty(B * L * r, dtype=torch.uint8, device=DEV) for r in rows]
+    ffull = torch.empty(B, dtype=torch.int64, device=DEV)
+    shards[0][1].pull(h, totals, *args, u, [0, 1], full, out_flat=ffull)
+    for first in range(k):
+        b = len(range(first, B, k))
+        part = [torch.empty(b * L * r, dtype=torch.uint8, device=DEV) for r in rows]
+        fpart = torch.empty(b, dtype=torch.int64, device=DEV)
+        shards[0][1].pull(h, totals, *args, u[first:], [0, 1], part, out_flat=fpart, count=b, variate_stride=k)
+        torch.cuda.synchronize()
+        assert torch.equal(fpart, ffull[first::k])
+        for c, r in enumerate(rows):
+            assert torch.equal(part[c].view(b, L * r), full[c].view(B, L * r)[first::k])
+
+
 def test_pull_gives_up_when_a_peer_never_publishes(O):
     # The wait on the peers' epoch words is bounded: with one shard's total missing the launch
-    # comes back with GEARB_ST_SCAN_ABORTED, writes nothing, and the context stays usable.
-    rows, T, cap, L, W, B = [64, 4], 50, 40, 4, 3, 32
+    # comes back with GEARB_ST_SCAN_ABORTED, writes nothing, and the context stays usable.  The
+    # batch is larger than the number of CTAs the GPU holds at once: the CTAs of the later waves
+    # see that an earlier one ran out and leave at once, so giving up costs one wait, not several.
+    import time
+    rows, T, cap, L, W, B = [64, 4], 50, 40, 4, 3, 6000
     n = cap * T
     shards = []
     for j in range(W):
@@ -234,12 +276,32 @@ def test_pull_gives_up_when_a_peer_never_publishes(O):
     args = ([sh[1].cdf_ptr for sh in shards], [sh[1].l1_ptr for sh in shards], [sh[0].device_ptr for sh in shards])
     for j in (0, 2):                                   # shard 1 stays silent
         shards[j][1].publish_total(W, j, [box.ptr] * W, 1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
     shards[0][1].pull(h, None, *args, u, cols, dsts, mailbox=box.ptr, epoch=1)
     _, st = shards[0][1].result()
-    assert st[0] & N.ST_SCAN_ABORTED
+    first_wait = time.perf_counter() - t0
+    assert st[0] & N.ST_SCAN_ABORTED and st[2] == 1
     assert all(bool((d == 0x77).all()) for d in dsts)  # nothing was written
+    assert N.lib.gearb_sampler_result(shards[0][1]._h, None, None, None) == N.ERR_TIMEOUT
+    # a second launch at the same epoch finds the give-up mark and returns without waiting again
+    t0 = time.perf_counter()
+    shards[0][1].pull(h, None, *args, u, cols, dsts, mailbox=box.ptr, epoch=1)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 0.5 * first_wait + 0.05
+    assert first_wait < 20.0
+    # the status words accumulate until cleared; a later scan of a small table (whose last CTA
+    # builds level 1 itself) is not put off by the earlier time-out
+    sm = shards[0][1]
+    prio0 = O.synth_lognormal(98, 0, n)
+    sm.scan(dev(prio0))
+    assert np.array_equal(sm.l1.cpu().numpy(), O.scan(prio0)[1])
+    assert sm.result()[1][0] & N.ST_SCAN_ABORTED        # still there: nothing cleared it
+    sm.clear_status()
+    assert sm.result()[1][:3] == [0, 0, 0]
     shards[1][1].publish_total(W, 1, [box.ptr] * W, 1)
     shards[0][1].pull(h, None, *args, u, cols, dsts, mailbox=box.ptr, epoch=1)
     torch.cuda.synchronize()
     assert not all(bool((d == 0x77).all()) for d in dsts)
+    assert sm.result()[1][0] == 0
     box.free()

@@ -259,3 +259,168 @@ def test_back_to_back_scans_of_one_sampler(O):
             assert np.array_equal(s.l1.cpu().numpy(), want[1]) and tot == want[2] and st[0] == 0
             if store:
                 assert np.array_equal(s.cdf.cpu().numpy(), want[0])
+
+
+def test_back_to_back_scans_of_a_small_table_without_host_sync(O):
+    # Tables of at most 1024 partitions have their level 1 built by the scan's last CTA, so nothing
+    # stands between two scans of one sampler in the stream.  They must still not run side by side
+    # (they share the ticket and CTA counters): several scans queued without any host
+    # synchronisation leave exactly the last one's table.
+    n = 37 * 4096 + 11
+    ps = [O.synth_lognormal(300 + i, 0, n) for i in range(4)]
+    ps[2][::2] *= 1e-2
+    dps = [dev(p) for p in ps]
+    want = [O.scan(p) for p in ps]
+    s = core.PrioritySampler(n)
+    for rep in range(6):
+        for store in (False, True):
+            for i in range(4):
+                s.scan(dps[i], store=store)
+                s.scan(dps[(i + 1) % 4], store=store)
+                s.scan(dps[i], store=store)
+            tot, st = s.result()
+            assert np.array_equal(s.l1.cpu().numpy(), want[3][1]) and tot == want[3][2] and st[0] == 0
+            if store:
+                assert np.array_equal(s.cdf.cpu().numpy(), want[3][0])
+
+
+def test_small_table_scan_sample_scan_chain_without_host_sync(O):
+    # scan_totals -> sample_gather -> scan_totals -> ... on a small table, and two small samplers
+    # used in turn with the storing scan that may start early: every batch equals the oracle's.
+    rows, T, cap, B, L = [36, 4, 1], 50, 400, 300, 5
+    t = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
+    t.connect()
+    img = O.philox_u32(5, 3, 0, (t.nbytes + 3) // 4).view(np.uint8)[: t.nbytes].copy()
+    t.write(0, img)
+    h = core.StorageHandler(t)
+    cols = [0, 1, 2]
+    h.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * 3)
+    n = cap * T
+    ps = [O.synth_lognormal(310 + i, 0, n) for i in range(3)]
+    dps = [dev(p) for p in ps]
+    scans = [O.scan(p) for p in ps]
+    us = [O.synth_u01(320 + i, 0, B) for i in range(6)]
+    dus = [dev(u) for u in us]
+    for mode in ("totals", "alternate"):
+        sa, sb = core.PrioritySampler(n), core.PrioritySampler(n)
+        flats = [torch.empty(B, dtype=torch.int64, device=DEV) for _ in range(6)]
+        outs = [[torch.empty(B * L * r, dtype=torch.uint8, device=DEV) for r in rows] for _ in range(6)]
+        for i in range(6):                                  # no host synchronisation inside this loop
+            sm = sa if (mode == "totals" or i % 2 == 0) else sb
+            if mode == "totals":
+                sm.scan(dps[i % 3], store=False)
+            else:
+                sm.scan(dps[i % 3], store=True, alternate=True)
+            sm.sample_gather(h, dus[i], cols, outs[i], scale=True, out_flat=flats[i])
+        torch.cuda.synchronize()
+        for i in range(6):
+            ocdf, ol1, _, _ = scans[i % 3]
+            want = O.search(ocdf, ol1, us[i], scale=True)
+            assert np.array_equal(flats[i].cpu().numpy(), want), (mode, i)
+            oi, ot, ol = O.decode(want, T)
+            for c, r in enumerate(rows):
+                w = O.fused_subcopy(img, oi, ot, ol, t.trajectory_stride, t.accu[c], T, r, 0, L, False)
+                assert np.array_equal(outs[i][c].cpu().numpy(), w), (mode, i, c)
+        assert sa.result()[1][0] == 0 and sb.result()[1][0] == 0
+
+
+def test_lazy_level2_block_boundaries_and_block_totals(O):
+    # A table kept without its level-2 entries is sampled through the block totals the scan leaves
+    # (eight per partition): variates on, next to and far from every block boundary of a few
+    # partitions must give the stored table's index; the block totals themselves must be the
+    # tree's; an incremental update keeps them current.
+    n = 6 * 4096 + 1000
+    p = O.synth_lognormal(330, 0, n)
+    p[4096 * 2: 4096 * 2 + 512] = 0.0          # a block without mass
+    p[4096 * 3 + 100] = 5e4                    # a block dominated by one entry
+    ocdf, ol1, total, _ = O.scan(p)
+    rows, T = [8], 1
+    cap = n
+    t = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
+    t.connect()
+    h = core.StorageHandler(t)
+    h.set([0], [core.SubscribePattern(0, 1, N.PAD_TAIL)])
+    s = core.PrioritySampler(n)
+    dp = dev(p)
+    s.scan(dp, store=False)
+    b0, b1, cur = s.block_totals()
+    nparts = (n + 4095) // 4096
+    blk = core.device_view((b0, b1)[cur], nparts * 8, torch.float32).cpu().numpy().reshape(nparts, 8)
+    # block totals from the oracle's table: the aggregate is their in-order sum
+    agg = np.zeros(nparts, np.float32)
+    for q in range(nparts):
+        x = np.float32(0)
+        for w in range(8):
+            x = np.float32(x + blk[q, w])
+        agg[q] = x
+    assert np.array_equal(np.diff(ol1).astype(np.float64), agg.astype(np.float64))
+    # variates: every block boundary of every partition, a few ulps around it, plus random ones
+    targets = []
+    for q in range(nparts):
+        x = np.float32(0)
+        for w in range(8):
+            x = np.float32(x + blk[q, w])
+            for k in (-40, -3, -1, 0, 1, 3, 40):
+                f = np.float32(x)
+                for _ in range(abs(k)):
+                    f = np.nextafter(f, np.float32(np.inf if k > 0 else -np.inf))
+                targets.append(ol1[q] + float(f))
+    u = np.array(targets + list(O.synth_u01(331, 0, 4000) * total), np.float64)
+    u = u[(u >= 0) & (u < total)]
+    du = dev(u)
+    dst = [torch.empty(len(u) * 8, dtype=torch.uint8, device=DEV)]
+    flat = torch.empty(len(u), dtype=torch.int64, device=DEV)
+    s.sample_gather(h, du, [0], dst, scale=False, out_flat=flat)
+    tot, st = s.result()
+    want, near = O.search(ocdf, ol1, u, want_near=True)
+    assert np.array_equal(flat.cpu().numpy(), want)
+    assert st[0] == 0 and st[1] == int(near.sum())
+    # update: new priorities in a few blocks; the block totals follow, the indices stay exact
+    idx = np.array([5, 4096 * 3 + 100, 4096 * 5 + 600, n - 1], np.int64)
+    val = np.array([9.0, 0.5, 77.0, 3.0], np.float32)
+    p[idx] = val
+    s.update(dp, dev(idx), dev(val))
+    s.clear_status()
+    ocdf, ol1, total, _ = O.scan(p)
+    u2 = O.synth_u01(332, 0, 3000) * total
+    flat2 = torch.empty(len(u2), dtype=torch.int64, device=DEV)
+    dst2 = [torch.empty(len(u2) * 8, dtype=torch.uint8, device=DEV)]
+    s.sample_gather(h, dev(u2), [0], dst2, scale=False, out_flat=flat2)
+    want2, near2 = O.search(ocdf, ol1, u2, want_near=True)
+    tot, st = s.result()
+    assert tot == total and np.array_equal(flat2.cpu().numpy(), want2) and st[1] == int(near2.sum())
+
+
+def test_draw_follows_the_priorities_in_distribution(O):
+    # The reference's runnable weighted draw is torch.multinomial (gear/sampler/global_sampler.py:170):
+    # P(i) = w_i / sum(w).  The bit-level definition of this library's draw is its own, so the law
+    # is pinned statistically: 2,000,000 variates on 3,000 LogNormal weights with zeros, chi-square
+    # against w / sum(w) (threshold: mean + 5 sigma of the chi-square distribution, i.e.
+    # dof + 5 * sqrt(2 * dof); a wrong law -- e.g. uniform -- exceeds it by orders of magnitude),
+    # zero-weight entries never drawn, and the same statistic for torch.multinomial's own counts
+    # with replacement as a yardstick.
+    k, draws = 3000, 2_000_000
+    w = O.synth_lognormal(340, 0, k)
+    w[::7] = 0.0
+    dw = dev(w)
+    cdf, l1, status = core.scan(dw)
+    u = torch.empty(draws, dtype=torch.float64, device=DEV)
+    core.fill(u, N.FILL_U01_F64, seed=341)
+    got = core.search(cdf, l1, u, scale=True)
+    counts = torch.bincount(got, minlength=k).cpu().numpy().astype(np.float64)
+    pr = w.astype(np.float64) / w.astype(np.float64).sum()
+    assert counts[w == 0].sum() == 0
+    m = pr > 0
+    dof = int(m.sum()) - 1
+    limit = dof + 5.0 * np.sqrt(2.0 * dof)
+    chi2 = float((((counts[m] - draws * pr[m]) ** 2) / (draws * pr[m])).sum())
+    assert chi2 < limit, (chi2, limit)
+    ref = torch.multinomial(dw.double(), draws, replacement=True)
+    rc = torch.bincount(ref, minlength=k).cpu().numpy().astype(np.float64)
+    chi2_ref = float((((rc[m] - draws * pr[m]) ** 2) / (draws * pr[m])).sum())
+    assert chi2_ref < limit, (chi2_ref, limit)
+    # and the two empirical laws agree with each other (two-sample chi-square, same threshold)
+    two = float((((counts[m] - rc[m]) ** 2) / (counts[m] + rc[m]).clip(min=1)).sum())
+    assert two < limit, (two, limit)
+    uni = float((((np.full(int(m.sum()), draws / m.sum()) - draws * pr[m]) ** 2) / (draws * pr[m])).sum())
+    assert uni > 100 * limit      # the statistic does tell a wrong law from the right one

@@ -65,6 +65,30 @@ def test_static_scratch_scan_matches_scan_twice_in_a_row():
     assert np.array_equal(cdf_a, cdf_b) and np.array_equal(l1_a, l1_b)
 
 
+def test_static_scratch_scan_with_its_own_level1_launch_and_without_a_table():
+    # Above 1024 partitions level 1 is a launch of its own that reads the exponent range of the
+    # aggregates out of the built-in array's header; and the table argument may be NULL (offsets
+    # and total only).  Both twice in a row, against the entry point with caller-provided scratch.
+    rng = np.random.default_rng(21)
+    for n in (5_000_000 + 3, 1200 * 4096, 5_000_000 + 3):
+        prio = rng.lognormal(0.0, 1.0, n).astype(np.float32)
+        cdf_a, l1_a, st_a, cdf_b, l1_b, st_b = _scan_both(prio)
+        assert np.array_equal(cdf_a, cdf_b) and np.array_equal(l1_a, l1_b)
+        assert st_a[0] == 0 and st_b[0] == 0
+        # totals only: no table written, same offsets
+        d = torch.from_numpy(prio).to(DEV)
+        nparts = (n + N.PART - 1) // N.PART
+        for _ in range(2):
+            l1_c = torch.full((nparts + 1,), -1.0, dtype=torch.float64, device=DEV)
+            st_c = torch.zeros(N.STATUS_WORDS, dtype=torch.int32, device=DEV)
+            N.check(N.lib.gearb_scan_static(_p(d), n, None, _p(l1_c), _p(st_c),
+                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            N.check(N.lib.gearb_scan_static(_p(d), n, None, _p(l1_c), _p(st_c),
+                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            torch.cuda.synchronize()
+            assert np.array_equal(l1_c.cpu().numpy(), l1_a) and st_c.cpu().tolist()[0] == 0
+
+
 def test_static_scratch_scan_refuses_sizes_beyond_its_array():
     limit = N.lib.gearb_scan_static_max_n()
     assert limit == 1 << 28
