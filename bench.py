@@ -39,7 +39,7 @@ UNIT = "timesteps/s"
 C3 = dict(name="hbm_decision_transformer_100Mstep", rows=[156, 24, 4, 4, 1], T=1000, capacity=100_000,
           B=1024, L=64)
 C5 = dict(name="sharded_token_table_32Mstep_per_gpu", rows=[4096, 4, 4], T=1000, capacity=32_000,
-          B_per_rank=1024, L=16)
+          B_global=8192, B_per_rank=1024, L=16)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one scan_kernel launch at n = 100,000,000,
 # from the one-pass ncu capture summarised in profiles/scan_kernel_100M_priorities.md (the part of the

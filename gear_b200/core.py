@@ -395,9 +395,10 @@ class PrioritySampler:
         """Search every variate, decode it to (trajectory, timestep, length) and gather the
         listed columns of the handler's table, all in one launch.  affine=(mul, sub): the
         variates belong to a global draw over several shards and become u*mul - sub first;
-        flat_offset is then added to out_flat, and slot_map=(mod, lo, base) sends the request at
-        position q = lo + i of the global batch to slot base[q % mod] + q // mod of the
-        destinations (dst_requests: how many slots they must hold, default one per variate)."""
+        flat_offset is then added to out_flat, and slot_map=(mod, lo, base) says where the request
+        at position q = lo + i of the global batch lands in the destinations: mod > 1: slot
+        base[q % mod] + q // mod; mod == -1: slot q - base[0] for base[0] <= q < base[1], else
+        base[2] + i (dst_requests: how many slots the destinations must hold, default one per variate)."""
         if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
             raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
         b = variates.numel()
@@ -416,8 +417,8 @@ class PrioritySampler:
                 raise GearError(N.ERR_INVALID, f"{name} must be an int64 CUDA tensor with >= {b} entries")
         nc = len(columns)
         if affine is not None:
-            mod, lo, base = (1, 0, None) if slot_map is None else slot_map
-            base_arr = None if base is None else (C.c_int64 * int(mod))(*[int(x) for x in base])
+            mod, lo, base = (0, 0, None) if slot_map is None else slot_map
+            base_arr = None if base is None else (C.c_int64 * len(base))(*[int(x) for x in base])
             call("gearb_sampler_sample_gather_affine", self._h, handler._h, _ptr(variates), b, float(affine[0]),
                  float(affine[1]), _ptr(lengths), int(index_offset), (C.c_int32 * nc)(*[int(c) for c in columns]), nc,
                  (C.c_void_p * nc)(*[d.data_ptr() for d in dsts]), int(bool(zero_fill)),

@@ -710,14 +710,15 @@ int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const
                                        int64_t flat_offset, int slot_mod, int64_t slot_lo, const int64_t *slot_base,
                                        void *stream) {
   GEARB_REQUIRE(s, "sample_gather: null sampler");
-  GEARB_REQUIRE(slot_mod <= GEARB_MAX_SHARDS && (slot_mod <= 1 || slot_base), "sample_gather: bad slot map");
+  GEARB_REQUIRE(slot_mod >= -1 && slot_mod <= GEARB_MAX_SHARDS && (slot_mod == 0 || slot_mod == 1 || slot_base),
+                "sample_gather: bad slot map");
   GatherParams p;
   int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
   if (rc != GEARB_OK) return rc;
-  if (slot_mod > 1) {
+  if (slot_mod > 1 || slot_mod == -1) {
     p.slot_mod = slot_mod;
     p.slot_lo = slot_lo;
-    for (int q = 0; q < slot_mod; ++q) p.slot_base[q] = slot_base[q];
+    for (int q = 0; q < (slot_mod > 1 ? slot_mod : 3); ++q) p.slot_base[q] = slot_base[q];
   }
   GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,

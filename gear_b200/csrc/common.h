@@ -103,10 +103,13 @@ struct GatherParams {
   int32_t zero_fill;
   int32_t stage_bytes;  // > 0: a request's columns fit this much shared memory and the table is in HBM
   int32_t ring;         // 1: larger requests stream through per-warp rings of bulk copies
-  // Where request g of a launch lands in the destinations: slot g, or, with slot_mod > 1, slot
-  // slot_base[(slot_lo + g) % slot_mod] + (slot_lo + g) / slot_mod -- an owner that serves a run
-  // [slot_lo, slot_lo + n) of a global batch whose requests are dealt round-robin to slot_mod
-  // requesters groups them by requester that way (sample_gather only).
+  // Where request g of a launch lands in the destinations (sample_gather only).  Position
+  // q = slot_lo + g of the global batch goes to
+  //   slot_mod == 0:  slot g;
+  //   slot_mod  > 1:  slot_base[q % slot_mod] + q / slot_mod -- an owner that serves a run of a batch
+  //                   dealt round-robin to slot_mod requesters groups its answers by requester;
+  //   slot_mod == -1: q - slot_base[0] when slot_base[0] <= q < slot_base[1] (the owner's own
+  //                   contiguous slice: straight into its final place), else slot_base[2] + g.
   int32_t slot_mod;
   int64_t slot_lo;
   int64_t slot_base[GEARB_MAX_SHARDS];

@@ -69,6 +69,19 @@ __device__ __forceinline__ void bulk_load(void *dst_smem, const void *src, unsig
       : "memory");
 }
 
+// Build with -DGEARB_SG_TIMING to record, per CTA, the SM clock at the phases of its first
+// request (a tuning aid; the array is read back with gearb_debug_sg_times).
+#ifdef GEARB_SG_TIMING
+__device__ unsigned long long g_sg_times[8192][10];
+#define GEARB_STAMP(i)                                                                         \
+  do {                                                                                         \
+    if (threadIdx.x == 0 && blockIdx.x < 8192 && it == static_cast<int64_t>(blockIdx.x))        \
+      g_sg_times[blockIdx.x][i] = clock64();                                                   \
+  } while (0)
+#else
+#define GEARB_STAMP(i) do { } while (0)
+#endif
+
 struct Range {
   int64_t lo, hi;  // the answer (first index whose entry is greater) lies in [lo, hi]
   int64_t step;
@@ -160,8 +173,9 @@ __device__ __forceinline__ T ldt(const T *p) {
 
 // Destination slot of request g of this launch (GatherParams::slot_*).
 __device__ __forceinline__ int64_t dst_slot(const GatherParams &P, int64_t g) {
-  if (P.slot_mod <= 1) return g;
+  if (P.slot_mod == 0) return g;
   const int64_t q = P.slot_lo + g;
+  if (P.slot_mod < 0) return (q >= P.slot_base[0] && q < P.slot_base[1]) ? q - P.slot_base[0] : P.slot_base[2] + g;
   return P.slot_base[q % P.slot_mod] + q / P.slot_mod;
 }
 
@@ -191,6 +205,17 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned flags = 0, stage_parity = 0;
   int round = 0;
+#ifdef GEARB_SG_TIMING
+  {
+    const int64_t it = blockIdx.x;
+    GEARB_STAMP(0);
+    if (threadIdx.x == 0 && blockIdx.x < 8192) {
+      unsigned long long gt;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt));
+      g_sg_times[blockIdx.x][8] = gt;
+    }
+  }
+#endif
   if (threadIdx.x == 0) {
     mbar_init(&stage_bar, 1);
     for (int w = 0; w < kWarps; ++w)
@@ -254,6 +279,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
   }
 
   for (int64_t it = blockIdx.x; it < P.n; it += gridDim.x) {
+    GEARB_STAMP(1);
     // Sharded: the two ends of the (ascending) slice first, where the requests for other shards
     // are when slices are contiguous -- they take longest and should not start last.
     const int64_t g = kPeers ? ((it & 1) ? P.n - 1 - (it >> 1) : (it >> 1)) : it;
@@ -320,6 +346,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
         p1 = ldt<kPeers>(l1 + 1 + q1);
       }
       const int64_t p = r1.hi;
+      GEARB_STAMP(2);
 
       const int64_t base = p * GEARB_PART;
       const int64_t valid = (a.n - base < GEARB_PART) ? (a.n - base) : GEARB_PART;
@@ -405,6 +432,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
           }
         }
         int j = -1;
+        GEARB_STAMP(3);
         if (fast) {
           if (warp == 0) {
             const float4 *src4 = reinterpret_cast<const float4 *>(src + wsel * tree::kBlockValues);
@@ -545,6 +573,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
         flat = base + j;
       }
     }
+    GEARB_STAMP(4);
 
     // ---- decode
     int64_t t, ts;
@@ -595,11 +624,13 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
           }
         }
       }
+      GEARB_STAMP(5);
       unsigned polls = 0;
       bool ok;
       while (!(ok = mbar_try_wait(&stage_bar, stage_parity)))
         if (++polls > kWaitLimit) break;
       stage_parity ^= 1u;
+      GEARB_STAMP(6);
       if (__syncthreads_or(!ok)) {  // a copy never landed: report, do not touch the staging area
         if (threadIdx.x == 0 && P.status) atomicOr(reinterpret_cast<unsigned *>(P.status), GEARB_ST_SCAN_ABORTED);
         break;
@@ -614,6 +645,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
         dev::copy_piece<true>(P, col, q - col.chunk_first, gd, stage + col.stage_off + (src & 15u), bytes, lane);
       }
       __syncthreads();  // the staging area is free for the next request
+      GEARB_STAMP(7);
     } else if (kPath == kRing && !(kPeers && owner == peers.self)) {
       // Ring: a request too large to stage whole.  Each warp streams its pieces (4 KiB of a
       // slot each) through a private ring of bulk asynchronous copies that runs kRingSlots - 1
@@ -815,6 +847,12 @@ __global__ void __launch_bounds__(kPublishThreads)
   asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(ep), "l"(epoch) : "memory");
 }
 }  // namespace
+
+#ifdef GEARB_SG_TIMING
+extern "C" __attribute__((visibility("default"))) int gearb_debug_sg_times(unsigned long long *out, int rows) {
+  return cudaMemcpyFromSymbol(out, g_sg_times, sizeof(unsigned long long) * 10 * rows) == cudaSuccess ? 0 : 2;
+}
+#endif
 
 int64_t mailbox_l1_stride(int64_t n) {
   const int64_t nparts = (n + GEARB_PART - 1) / GEARB_PART;

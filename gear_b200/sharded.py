@@ -232,11 +232,15 @@ class ShardedReplay:
         dev = torch.device("cuda", torch.cuda.current_device())
         self.dev = dev
         b = self.maxB // world
-        # worst case: every request of the batch is served by this rank
-        self.send = [torch.empty(self.maxB * s, dtype=torch.uint8, device=dev) for s in self.slots]
-        self.send_flat = torch.empty(self.maxB, dtype=torch.int64, device=dev)
-        self.recv = [torch.empty(b * s, dtype=torch.uint8, device=dev) for s in self.slots]
-        self.recv_flat = torch.empty(b, dtype=torch.int64, device=dev)
+        self.b_alloc = b
+        # One buffer per column: this rank's finished slice (b slots), then what it sends away (worst
+        # case: every request of the batch is served by this rank).  An owner's launch writes the
+        # requests of its own slice straight into their final slots and the others behind them.
+        self._both = [torch.empty((b + self.maxB) * s, dtype=torch.uint8, device=dev) for s in self.slots]
+        self._both_flat = torch.empty(b + self.maxB, dtype=torch.int64, device=dev)
+        self.recv = [x[: b * s] for x, s in zip(self._both, self.slots)]
+        self.send = [x[b * s:] for x, s in zip(self._both, self.slots)]
+        self.recv_flat, self.send_flat = self._both_flat[:b], self._both_flat[b:]
         self.totals_dev = torch.empty(world, dtype=torch.float64, device=dev)
         self.totals_host = torch.empty(world, dtype=torch.float64).pin_memory()
         self.res_host = torch.empty(self.maxB, dtype=torch.float64).pin_memory()
@@ -283,17 +287,26 @@ class ShardedReplay:
         plan, total, prefix, slot_map = plan_layout(totals, u01_sorted, self.rank, self.world, layout)
         self.last_plan = plan
         m = len(plan.mine)
-        direct = self.world == 1
-        dsts = self.recv if direct else self.send
-        flat = self.recv_flat if direct else self.send_flat
         if m:
             lo = int(plan.mine[0])
-            self.sampler.sample_gather(self.handler, u01_sorted_dev[lo:lo + m], self.columns, dsts, zero_fill=True,
-                                       out_flat=flat, affine=(total, prefix[self.rank]),
-                                       flat_offset=self.rank * self.n_local, slot_map=slot_map)
-        if not direct:
+            if self.world > 1:
+                # the owner's own requests go straight to their final slots, the others to the send region
+                if slot_map is None:
+                    slot_map = (-1, lo, [self.rank * b, (self.rank + 1) * b, self.b_alloc])
+                else:
+                    mod, lo_, base = slot_map
+                    base = np.asarray(base, np.int64) + self.b_alloc
+                    base[self.rank] = 0
+                    slot_map = (mod, lo_, base)
+            self.sampler.sample_gather(self.handler, u01_sorted_dev[lo:lo + m], self.columns, self._both, zero_fill=True,
+                                       out_flat=self._both_flat, affine=(total, prefix[self.rank]),
+                                       flat_offset=self.rank * self.n_local, slot_map=slot_map,
+                                       dst_requests=self.b_alloc + m)
+        if self.world > 1:
+            sc, rc = plan.send_count.copy(), plan.recv_count.copy()
+            sc[self.rank] = rc[self.rank] = 0          # already in place
             self.comm.alltoallv(self.send + [self.send_flat], self.recv + [self.recv_flat], self.slots + [8],
-                                plan.send_first, plan.send_count, plan.recv_first, plan.recv_count)
+                                plan.send_first, sc, plan.recv_first, rc)
         return [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]
 
     def step(self, priorities, u01_sorted: np.ndarray, rescan: bool = True):
@@ -333,16 +346,20 @@ class ShardedReplay:
 
     # -- exchange-free mode: requesters read the owners' memory in place ---------------------
     def enable_pull(self, double_buffer: bool = True, ring: bool = False, mailbox: bool = True,
-                    priorities=None) -> None:
+                    priorities=None, copy_l1="auto") -> None:
         """Map every peer's shard into this process (collective: every rank calls it once).
 
         priorities: a gear_b200.core.DeviceBuffer holding this shard's float32 priorities.  Given,
         the shards keep no level-2 table: every rank scans with the totals-only scan (half the
         traffic), the peers map each other's priorities and block totals, and each rank's level 1
-        travels into the peers' mailboxes with its total, so a requester searches level 1 in its
-        own memory and fetches one 2 KiB block of the owner's priorities per request.  (A
-        DeviceBuffer because another process can only map a whole allocation from its start.)
-        Needs the mailbox.  While a step is in flight anywhere, no rank may change its priorities.
+        may travel into the peers' mailboxes with its total (copy_l1), so that a requester searches
+        level 1 in its own memory; otherwise it searches the owner's over NVLink.  Either way it
+        fetches one 2 KiB block of the owner's priorities per request.  Measured on two GPUs with
+        4096 requests per rank: copying costs a step whose requests are nearly all local 14 us
+        (181 against 167 us) and saves one with half of them remote 57 us (268 against 325 us), so
+        "auto" copies for the scattered layout only.  (A DeviceBuffer because another
+        process can only map a whole allocation from its start.)  Needs the mailbox.  While a
+        step is in flight anywhere, no rank may change its priorities.
 
         mailbox: the shard totals travel without a collective -- every rank writes its total and
         the step's number straight into every rank's mailbox, and the pull launch waits (with a
@@ -361,16 +378,17 @@ class ShardedReplay:
             raise ValueError("pull on tables without level-2 entries needs the mailbox")
         self._pull_ring = bool(ring)
         self._pull_prio = priorities
+        self._pull_copy_l1 = copy_l1 if self._pull_lazy else False
         two = double_buffer and not self._pull_lazy
         self._pull_samplers = [self.sampler] + ([core.PrioritySampler(self.n_local)] if two else [])
         self._pull_k = -1
         use_box = mailbox and double_buffer
-        self._pull_box = core.DeviceBuffer(core.mailbox_bytes(self.n_local if self._pull_lazy else 0)) if use_box else None
+        self._pull_box = core.DeviceBuffer(core.mailbox_bytes(self.n_local if self._pull_copy_l1 else 0)) if use_box else None
         self._pull_epoch = 0
         own = [self.handler.table.device_ptr] + ([self._pull_box.ptr] if self._pull_box else [])
         if self._pull_lazy:
             b0, b1, _ = self.sampler.block_totals()
-            own += [priorities.ptr, b0, b1]
+            own += [priorities.ptr, b0, b1, self.sampler.l1_ptr]
         else:
             for sm in self._pull_samplers:
                 own += [sm.cdf_ptr, sm.l1_ptr]
@@ -400,6 +418,7 @@ class ShardedReplay:
         if self._pull_lazy:
             self._pull_prios = [row[o] for row in ptrs]
             self._pull_blks = [[row[o + 1] for row in ptrs], [row[o + 2] for row in ptrs]]
+            self._pull_l1_remote = [row[o + 3] for row in ptrs]
             self._pull_slot = 0
         else:
             self._pull_cdfs = [[row[o + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
@@ -441,10 +460,12 @@ class ShardedReplay:
             between()
             sm.scan_level1()
 
-    def step_pull(self, priorities, u01_sorted_dev, rescan: bool = True, layout: str = "contiguous"):
+    def step_pull(self, priorities, u01_sorted_dev, rescan: bool = True, layout: str = "contiguous", out=None):
         """One global batch without an exchange step: nothing on the host depends on device
         results, so consecutive steps queue back to back on the stream.  u01_sorted_dev: the
         batch's ascending U[0,1) variates as a float64 CUDA tensor (the same on every rank).
+        out: (column byte tensors, int64 id tensor) to fill instead of the object's own buffers
+        (a caller that keeps several batches in flight passes a different set per batch).
         Returns (column byte tensors of this rank's slice, global step ids)."""
         B = u01_sorted_dev.numel()
         if B > self.maxB or B % self.world:
@@ -461,24 +482,29 @@ class ShardedReplay:
             mine, stride = u01_sorted_dev[self.rank:], self.world
         else:
             raise ValueError(f"unknown slice layout {layout!r}")
-        out = [r[: b * s] for r, s in zip(self.recv, self.slots)], self.recv_flat[:b]
-        common = dict(zero_fill=True, ring=self._pull_ring, out_flat=self.recv_flat, self_shard=self.rank,
+        recv, recv_flat = (self.recv, self.recv_flat) if out is None else out
+        out = [r[: b * s] for r, s in zip(recv, self.slots)], recv_flat[:b]
+        common = dict(zero_fill=True, ring=self._pull_ring, out_flat=recv_flat, self_shard=self.rank,
                       count=b, variate_stride=stride)
         if self._pull_box is not None:
             # totals through the mailboxes: no collective, no host involvement
             self._pull_epoch += 1
             e = self._pull_epoch
-            sm.publish(self.world, self.rank, self._pull_boxes, e, copy_l1=self._pull_lazy)
+            copy = (layout == "scattered") if self._pull_copy_l1 == "auto" else bool(self._pull_copy_l1)
+            sm.publish(self.world, self.rank, self._pull_boxes, e, copy_l1=copy)
             if self._pull_lazy:
                 from . import core
-                l1s = [sm.l1_ptr if j == self.rank else self._pull_box.ptr + core.mailbox_l1_offset(self.n_local, e, j)
-                       for j in range(self.world)]
-                sm.pull(self.handler, None, None, l1s, self._pull_tables, mine, self.columns, self.recv,
+                if copy:
+                    l1s = [sm.l1_ptr if j == self.rank else self._pull_box.ptr + core.mailbox_l1_offset(self.n_local, e, j)
+                           for j in range(self.world)]
+                else:
+                    l1s = self._pull_l1_remote
+                sm.pull(self.handler, None, None, l1s, self._pull_tables, mine, self.columns, recv,
                         mailbox=self._pull_box.ptr, epoch=e, prios=self._pull_prios,
                         blks=self._pull_blks[self._pull_slot], **common)
             else:
                 sm.pull(self.handler, None, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables, mine,
-                        self.columns, self.recv, mailbox=self._pull_box.ptr, epoch=e, **common)
+                        self.columns, recv, mailbox=self._pull_box.ptr, epoch=e, **common)
             return out
         nparts = (self.n_local + self.N.PART - 1) // self.N.PART
         tot = sm.l1[nparts:nparts + 1]
@@ -487,7 +513,7 @@ class ShardedReplay:
         else:
             self.comm.allgather(tot, self.totals_dev)   # every shard's scan is complete once this lands
         sm.pull(self.handler, self.totals_dev, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables, mine,
-                self.columns, self.recv, **common)
+                self.columns, recv, **common)
         if nbuf == 1 and self.world > 1:
             self.comm.allreduce(self._pull_fence)        # the next scan must not overtake the peers' reads
         return out

@@ -266,11 +266,14 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
  * u * mul - sub before the search (mul = total priority of all shards, sub = total of the
  * shards before this one), clamped into this shard's range.  Stands where an owner answers
  * the requests of its peers, CpuTrajectoryStorageHandler::subsend, src/storage/handler.cc:160-193.
- * flat_offset is added to out_flat (the shard's first global step id).  slot_mod > 1: the b
- * requests are positions [slot_lo, slot_lo + b) of a global batch that is dealt round-robin to
- * slot_mod requesters; request at position q then lands in slot slot_base[q % slot_mod] +
- * q / slot_mod of dst and out_*, which groups an owner's answers by requester.  slot_mod <= 1:
- * request i lands in slot i.                                                              */
+ * flat_offset is added to out_flat (the shard's first global step id).  The b requests are
+ * positions [slot_lo, slot_lo + b) of a global batch.  slot_mod > 1: the batch is dealt
+ * round-robin to slot_mod requesters; the request at position q lands in slot
+ * slot_base[q % slot_mod] + q / slot_mod of dst and out_*, which groups an owner's answers by
+ * requester.  slot_mod == -1: the batch is cut into contiguous slices; positions
+ * slot_base[0] <= q < slot_base[1] (the owner's own slice) land in slot q - slot_base[0], the
+ * others in slot slot_base[2] + i, so that one buffer holds the owner's finished slice followed
+ * by what it sends away.  slot_mod 0 or 1: request i lands in slot i.                     */
 int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const double *variates,
                                        int64_t b, double mul, double sub, const int64_t *lengths,
                                        int64_t index_offset, const int32_t *columns, int ncols,
