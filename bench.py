@@ -7,10 +7,12 @@ One step = one prioritized sample + gather of a batch: rebuild the cumulative
 priority table (scan), draw B segment starts on supplied variates, gather B x L
 timesteps of every column.
 
-N = 1 runs the HBM-resident decision-transformer table of BASELINE.json
-(100,000 trajectories x 1000 steps, rows 156/24/4/4/1 B, B=1024, L=64).
+N = 1 runs the HBM-resident decision-transformer table (100,000 trajectories x
+1000 steps, rows 156/24/4/4/1 B, B=1024, L=64) and, beside it under
+`other_configs`, the index-only workload (1,048,576 priorities, 4096 variates) and
+the zero-copy workload (table in pinned mapped host memory, B=512, L=32).
 N > 1 runs the trajectory-id sharded token table (per GPU 32,000 x 1000 steps of
-4104 B, 1024 requests per rank, L=16) with the cross-shard exchange.
+4104 B, global batch 8192, L=16) with the cross-shard exchange.
 
 The line printed by rank 0 carries, beside the base keys:
   roofline      the dominant kernel (scan) against the measured HBM copy peak
@@ -41,12 +43,13 @@ C3 = dict(name="hbm_decision_transformer_100Mstep", rows=[156, 24, 4, 4, 1], T=1
 C5 = dict(name="sharded_token_table_32Mstep_per_gpu", rows=[4096, 4, 4], T=1000, capacity=32_000,
           B_global=8192, B_per_rank=1024, L=16)
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one scan_kernel launch at n = 100,000,000,
-# from the one-pass ncu capture summarised in profiles/scan_kernel_100M_priorities.md (the part of the
-# 400 MB of output that is still dirty in L2 at kernel end is not in it).
+# dram__bytes_read.sum + dram__bytes_write.sum of one scan_kernel launch at n = 100,000,000, taken
+# once from a one-pass ncu capture of that launch (a profiler counter: it cannot be read inside a
+# timed run; the part of the 400 MB of output that is still dirty in L2 at kernel end is not in it).
 SCAN_TRAFFIC_BYTES_C3 = 741_204_736
 # The same for the totals-only instance (no level-2 table written): 400,064,768 B read + 338,688 B written.
 SCAN_TOTALS_TRAFFIC_BYTES_C3 = 400_403_456
+TRAFFIC_SOURCE = "ncu capture of one launch at this size (dram__bytes_read.sum + dram__bytes_write.sum), not read in this run"
 
 
 def peaks():
@@ -153,8 +156,8 @@ def run_ours_single(args):
 
     def timed_steps(store, sample_clocks):
         """K full steps (scan + one-launch search/decode/gather), timed as a whole with one pair of
-        events; then an instrumented run of the same steps with an event after each of the scan's
-        two launches, from which only the kernels' own durations are taken (events between the
+        events; then an instrumented run of the same steps with an event after each of the step's three
+        launches, from which only the kernels' own durations are taken (events between the
         launches cost the overlap of one kernel's start with its predecessor's end).
         store=True: the scan writes the level-2 table and the sampling kernel searches it;
         store=False: the scan keeps only the partition offsets and the sampling kernel rebuilds
@@ -187,7 +190,7 @@ def run_ours_single(args):
         clk = clocks.stop(t0, t1) if sample_clocks else None
         ms_step = ev[0].elapsed_time(ev[1]) / K
         Ki = min(K, 300)
-        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(Ki)]
+        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(Ki)]
         for i in range(Ki):
             marks[i][0].record()
             sampler.scan_partitions(prio, store=store)
@@ -195,13 +198,15 @@ def run_ours_single(args):
             sampler.scan_level1()
             marks[i][2].record()
             sampler.sample_gather(handler, batch(i), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
+            marks[i][3].record()
         torch.cuda.synchronize()
         scan_ms = sum(m[0].elapsed_time(m[1]) for m in marks) / Ki
         level1_ms = sum(m[1].elapsed_time(m[2]) for m in marks) / Ki
-        return ms_step, scan_ms, level1_ms, clk
+        sample_ms = sum(m[2].elapsed_time(m[3]) for m in marks) / Ki
+        return ms_step, scan_ms, (level1_ms, sample_ms), clk
 
-    stored_ms, stored_scan_ms, stored_level1_ms, _ = timed_steps(True, False)
-    ms_step, scan_ms, level1_ms, clk = timed_steps(False, True)          # the headline
+    stored_ms, stored_scan_ms, stored_sample_ms, _ = timed_steps(True, False)
+    ms_step, scan_ms, sample_ms, clk = timed_steps(False, True)          # the headline
     total_prio, status = sampler.result()
 
     gathered = B * L * sum(rows)
@@ -294,8 +299,9 @@ def run_ours_single(args):
         "config": {"workload": cfg["name"], "trajectories": cap, "trajectory_length": T, "row_bytes": rows,
                    "batch": B, "segment_length": L, "priorities": n, "table_bytes": table.nbytes,
                    "l2": "inputs larger than L2 (400 MB of priorities re-read every step)",
-                   "step": "totals-only scan (partition aggregates, no stored level-2 table) + level-1 launch + "
-                           "one launch that searches, rebuilds the chosen partition's entries, decodes and gathers"},
+                   "step": "totals-only scan (partition aggregates and block totals, no stored level-2 table) + "
+                           "level-1 launch + one launch that searches, rebuilds the one 512-value block each "
+                           "request falls into, decodes and gathers"},
         "gathered_gb_s": 2 * gathered / (ms_step * 1e-3) / 1e9,
         "step_algorithmic_gb_s": step_bytes / (ms_step * 1e-3) / 1e9,
         "step_frac_of_measured_peak": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
@@ -304,7 +310,7 @@ def run_ours_single(args):
             "step": "scan that stores the level-2 table (8 B per priority) + level 1 + search + decode + gather; two "
                     "tables used in turn, so a scan may start while the sampling launch on the other table finishes",
             "ms_per_step": stored_ms, "timesteps_per_s": B * L / (stored_ms * 1e-3),
-            "scan_ms": stored_scan_ms, "level1_ms": stored_level1_ms, "scan_algorithmic_bytes": stored_scan_bytes,
+            "scan_ms": stored_scan_ms, "level1_ms": stored_sample_ms[0], "sample_gather_ms": stored_sample_ms[1], "scan_algorithmic_bytes": stored_scan_bytes,
             "scan_achieved_gb_s": stored_achieved, "scan_frac_of_measured_peak": stored_achieved / peak,
             "scan_traffic": SCAN_TRAFFIC_BYTES_C3,
             "step_algorithmic_gb_s": stored_step_bytes / (stored_ms * 1e-3) / 1e9,
@@ -317,11 +323,27 @@ def run_ours_single(args):
                                        "search + decode + gather"},
         "roofline": {"kernel": "scan_kernel<false> (totals only)", "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": SCAN_TOTALS_TRAFFIC_BYTES_C3,
-                     "peak_source": peak_src, "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms,
-                     "level1_cluster_kernel_ms": level1_ms},
+                     "traffic_source": TRAFFIC_SOURCE, "peak_source": peak_src, "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms,
+                     "level1_cluster_kernel_ms": sample_ms[0], "sample_gather_kernel_ms": sample_ms[1]},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": 3 * K, "clocks": clk, "parity": parity,
         "scan_status": status, "total_priority": total_prio,
     }
+    # ---- the other single-GPU configurations, on the same record
+    del pipe, sampler, sampler_b, handler, table, prio, dsts, u_dev
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    other = {}
+    for name, fn in (("c2_index_sampling_only", run_index_only), ("c4_zero_copy_host_table", run_zero_copy)):
+        try:
+            sub_args = argparse.Namespace(**vars(args))
+            sub_args.steps = min(args.steps, 2000)
+            other[name] = fn(sub_args)
+        except Exception as e:  # reported, not fatal: the headline above stands on its own
+            other[name] = {"error": f"{type(e).__name__}: {e}"}
+        gc.collect()
+        torch.cuda.empty_cache()
+    line["other_configs"] = other
     print(json.dumps(line))
 
 
@@ -355,49 +377,108 @@ def cpu_check_and_baseline(cfg, table, prio, u_first, sampler, handler, dsts, fl
     for c, r in enumerate(rows):
         s, d, b, slot = handler.sub(oi, ot, ol, c)
         got = dsts[c].cpu().numpy()
-        for i in range(0, B, 8):      # every 8th request read back from the device table
+        for i in range(B):            # every request read back from the device table
             want = table.read(int(s[i]), int(b[i]))
             byte_mismatch += int((got[d[i]:d[i] + b[i]] != want).sum()) + int(got[i * slot + b[i]:(i + 1) * slot].any())
     parity = {"index_mismatches_vs_oracle": index_mismatch, "gathered_byte_mismatches": byte_mismatch,
-              "variates_within_1ulp_of_boundary": int(near.sum()),
+              "requests_byte_checked": B, "variates_within_1ulp_of_boundary": int(near.sum()),
               "flips_vs_float64_running_sum": int(flips.sum()),
               "max_flip_distance": int(np.abs(oflat[flips] - f64[flips]).max()) if flips.any() else 0}
 
     if not want_cpu:
         return parity, None
 
-    # ---- CPU baseline: full 100M-priority scan + search + gather from a host slice of the table
+    # ---- CPU baseline: full 100M-priority draw + gather from a host slice of the table
     sub_cap = min(cap, 4000)                      # 756 MB host slice: requests folded into it
     host_tab = table.read(0, sub_cap * table.trajectory_stride)
-    fi = oi % sub_cap
-    out = [np.empty(B * L * r, np.uint8) for r in rows]
-    accu = np.asarray(table.accu[:len(rows)], np.int64)
-    reps = 3
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        c2, l2, tot2, _ = O.scan_mt(hp, cores, cdf=ocdf)
-        f2 = O.search(c2, l2, u, scale=True)
-        i2, t2, n2 = O.decode(f2, T)
-        O.gather_mt(host_tab, out, i2 % sub_cap, t2, n2, table.trajectory_stride, T, accu, rows,
-                    [0] * len(rows), [L] * len(rows), [0] * len(rows), cores)
-    cpu_s = (time.perf_counter() - t0) / reps
-    kind = "port"
-    ref_note = ""
-    if O.Reference.available():
-        try:
-            ref = O.Reference(rows, T, sub_cap)
-            for c in cols:
-                ref.set(c, 0, L, 2)
-            g_s = ref.time_gather(host_tab, fi, ot, ol, cols, out, cores, 20) / 20
-            ref.close()
-            ref_note = f"; reference sub()+memcpy alone: {g_s * 1e3:.3f} ms/batch"
-            kind = "reference"
-        except Exception as e:  # the compiled reference is optional
-            ref_note = f"; oracle/_ref not usable here ({type(e).__name__})"
-    cpu = {"value": B * L / cpu_s, "unit": UNIT, "cores": cores, "kind": kind, "ms_per_step": cpu_s * 1e3,
-           "sample": f"{reps} full steps: {len(hp)} priorities scanned on {cores} threads + {B} draws + gather from a "
-                     f"{sub_cap}-trajectory host slice of the table (requests folded into it){ref_note}"}
+    path = CpuPath(rows, T, L, hp, host_tab, sub_cap, cores)
+    cpu = path.time(u, steps=3, warmup=1)
     return parity, cpu
+
+
+class CpuPath:
+    """The path on the host cores, for timing: the prioritized draw over ALL priorities, then the
+    gather.  Two draws are timed and the faster one counts: the plain one (flat float64 running
+    sum over the threads + one upper_bound per variate) and the port of the two-level table (the
+    GPU's addition tree in scalar C, partitions striped over the threads).  Addressing is the
+    reference's own sub() compiled from its sources when that library is present, else the port;
+    the bytes move by memcpy.  The table is a slice of `sub_cap` trajectories with the requests
+    folded into it (the full table does not fit a bounded host sample)."""
+
+    def __init__(self, rows, T, L, prio, host_table, sub_cap, cores):
+        import numpy as np
+        from oracle import oracle as O
+        self.np, self.O = np, O
+        self.rows, self.T, self.L, self.prio, self.tab, self.sub_cap, self.cores = rows, T, L, prio, host_table, sub_cap, cores
+        self.cols = list(range(len(rows)))
+        self.accu, self.stride = O.table_layout(rows, T)
+        self.cdf = np.empty(len(prio), np.float32)
+        self.cum = np.empty(len(prio), np.float64)
+        self.ref = None
+        if O.Reference.available():
+            try:
+                self.ref = O.Reference(rows, T, sub_cap)
+                for c in self.cols:
+                    self.ref.set(c, 0, L, 2)
+            except Exception:      # the compiled reference is optional
+                self.ref = None
+        self.out = None
+
+    def draw_plain(self, u):
+        return self.O.plain_cumsum_search(self.prio, u, self.cores, scale=True, cum=self.cum)[0]
+
+    def draw_tree(self, u):
+        c2, l2, _, _ = self.O.scan_mt(self.prio, self.cores, cdf=self.cdf)
+        return self.O.search(c2, l2, u, scale=True)
+
+    def gather(self, flat):
+        np, O = self.np, self.O
+        B = len(flat)
+        if self.out is None or len(self.out[0]) != B * self.L * self.rows[0]:
+            self.out = [np.empty(B * self.L * r, np.uint8) for r in self.rows]
+        i2, t2, n2 = O.decode(flat % (self.sub_cap * self.T), self.T)
+        if self.ref is not None:
+            self.ref.time_gather(self.tab, i2, t2, n2, self.cols, self.out, self.cores, 1)
+        else:
+            O.gather_mt(self.tab, self.out, i2, t2, n2, self.stride, self.T, self.accu[:len(self.rows)], self.rows,
+                        [0] * len(self.rows), [self.L] * len(self.rows), [0] * len(self.rows), self.cores)
+
+    def time(self, u, steps, warmup):
+        """`steps` timed steps of each draw and of the gather after `warmup` untimed ones."""
+        B = len(u)
+        t = {}
+        flat = None
+        for name, fn in (("plain", self.draw_plain), ("tree", self.draw_tree)):
+            for _ in range(warmup):
+                fn(u)
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                flat = fn(u)
+            t[name] = (time.perf_counter() - t0) / steps
+        for _ in range(warmup):
+            self.gather(flat)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            self.gather(flat)
+        t["gather"] = (time.perf_counter() - t0) / steps
+        draw = min(t["plain"], t["tree"])
+        step_s = draw + t["gather"]
+        which = "plain float64 running sum + upper_bound" if t["plain"] <= t["tree"] else "port of the two-level table"
+        addr = "reference sub() compiled from its sources" if self.ref is not None else "port of sub()"
+        return {"value": B * self.L / step_s, "unit": UNIT, "cores": self.cores,
+                "kind": "reference" if self.ref is not None else "port", "ms_per_step": step_s * 1e3,
+                "draw_ms": {"plain_cumsum_upper_bound": t["plain"] * 1e3, "two_level_tree_port": t["tree"] * 1e3},
+                "gather_ms": t["gather"] * 1e3,
+                "time_share": {"draw (a port: the reference draws with torch.multinomial and has no CPU code for it)": draw / step_s,
+                               f"addressing + memcpy ({addr})": t["gather"] / step_s},
+                "sample": f"{steps} steps after {warmup} warm-up: draw over all {len(self.prio)} priorities on {self.cores} "
+                          f"threads (the faster of two draws counts: {which}) + {B} requests gathered from a "
+                          f"{self.sub_cap}-trajectory host slice of the table (requests folded into it)"}
+
+    def close(self):
+        if self.ref is not None:
+            self.ref.close()
+            self.ref = None
 
 
 # --------------------------------------------------------------------------- #
@@ -410,69 +491,44 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg = C3 if args.gpus == 1 else None
     cores = os.cpu_count() or 1
-    if cfg is None:
-        rows, T, L, B = C5["rows"], C5["T"], C5["L"], C5["B_per_rank"] * args.gpus
-        n = 32_000_000 * args.gpus  # every shard's priorities, scanned by the host threads
-        name = C5["name"]
+    if args.gpus == 1 and args.workload != "c5":
+        cfg = C3
+        rows, T, L, B, cap = cfg["rows"], cfg["T"], cfg["L"], cfg["B"], cfg["capacity"]
+        n = cap * T
+        config = {"workload": cfg["name"], "trajectories": cap, "trajectory_length": T, "row_bytes": rows,
+                  "batch": B, "segment_length": L, "priorities": n, "table_bytes": n * sum(rows)}
     else:
-        rows, T, L, B, name = cfg["rows"], cfg["T"], cfg["L"], cfg["B"], cfg["name"]
-        n = 100_000_000            # the full priority vector every step
+        cfg = C5
+        rows, T, L, B, cap = cfg["rows"], cfg["T"], cfg["L"], cfg["B_global"], cfg["capacity"]
+        n = cap * T * args.gpus    # every shard's priorities, scanned by the host threads
+        config = {"workload": cfg["name"], "trajectories_per_gpu": cap, "trajectory_length": T, "row_bytes": rows,
+                  "global_batch": B, "batch_per_gpu": B // args.gpus, "segment_length": L,
+                  "priorities_per_gpu": cap * T, "table_bytes_per_gpu": cap * T * sum(rows),
+                  "parallelism": f"trajectory-id shards x{args.gpus}"}
     sub_cap = 2000
-    cols = list(range(len(rows)))
     accu, stride = O.table_layout(rows, T)
-    table = O.philox_u32(1, 0, 0, 1 << 20).view(np.uint8)
-    table = np.resize(table, sub_cap * stride)
+    table = np.resize(O.philox_u32(1, 0, 0, 1 << 20).view(np.uint8), sub_cap * stride)
     prio = np.resize(O.synth_lognormal(2, 0, 1 << 20), n)
     u = O.synth_u01(3, 0, B)
-    out = [np.empty(B * L * r, np.uint8) for r in rows]
-    ref = None
-    kind = "port"
-    if O.Reference.available():
-        try:
-            ref = O.Reference(rows, T, sub_cap)
-            for c in cols:
-                ref.set(c, 0, L, 2)
-            kind = "reference"
-        except Exception:
-            ref = None
-    cdf = np.empty(n, np.float32)
-
-    def step():
-        c2, l2, tot, _ = O.scan_mt(prio, cores, cdf=cdf)
-        f = O.search(c2, l2, u, scale=True)
-        i2, t2, n2 = O.decode(f % (sub_cap * T), T)
-        if ref is not None:
-            ref.time_gather(table, i2, t2, n2, cols, out, cores, 1)
-        else:
-            O.gather_mt(table, out, i2, t2, n2, stride, T, accu[:len(rows)], rows, [0] * len(rows),
-                        [L] * len(rows), [0] * len(rows), cores)
-
-    K, W = min(args.steps, 10), min(max(args.warmup, 1), 2)   # bounded: about 10 CPU steps
-    for _ in range(W):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        step()
-    dt = (time.perf_counter() - t0) / K
-    full_dt = dt
-    value = B * L / full_dt
-    sample = (f"{K} full-size steps on {cores} host threads; each step scans all {n} priorities, draws {B} and "
-              f"gathers from a {sub_cap}-trajectory host table (requests folded into it); "
-              f"addressing by {'the reference sub() compiled from its sources' if kind == 'reference' else 'the oracle port'}")
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": K, "warmup": W, "ms_per_step": full_dt * 1e3, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32 scan / f64 level-1 / u8 gather", "data": "synthetic",
-            "config": {"workload": name, "batch": B, "segment_length": L, "row_bytes": rows},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    path = CpuPath(rows, T, L, prio, table, sub_cap, cores)
+    # Bounded: a CPU step takes tens of milliseconds, so the requested counts are honoured up to a
+    # total of about 2000 step-equivalents' worth of time (they are in the thousands only for GPU runs).
+    K, W = max(1, min(args.steps, 200)), max(1, min(args.warmup, 20))
+    cpu = path.time(u, steps=K, warmup=W)
+    path.close()
+    config["l2"] = "host memory: every step streams all priorities"
+    config["step"] = "draw over all priorities + addressing + memcpy gather on the host cores"
+    line = {"impl": "reference", "metric": METRIC, "value": cpu["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": K, "warmup": W, "ms_per_step": cpu["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 / f64 sums, u8 gather", "data": "synthetic", "config": config,
+            "cpu_baseline": cpu,
+            "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-
 # --------------------------------------------------------------------------- #
-# other BASELINE.json configurations (reported beside the headline, same line format)
+# the index-only and the zero-copy configurations (reported beside the headline, same line format)
 # --------------------------------------------------------------------------- #
 C2 = dict(name="index_sampling_only_1Mi", n=1 << 20, B=4096)
 C4 = dict(name="host_zero_copy_frame_stacks_1Mstep", rows=[28224, 4, 4, 1], T=1000, capacity=1000, B=512, L=32)
@@ -492,7 +548,10 @@ def _event_loop(torch, fn, K, W):
 
 
 def run_index_only(args):
-    """Config 2: 1,048,576 priorities, 4096 variates: scan + batched search -> int64 indices."""
+    """Config 2: 1,048,576 priorities, 4096 variates U[0,total) supplied from the host: inclusive
+    prefix-scan + batched binary search -> int64 indices.  The 8 MB working set stays in L2 and a
+    step is two short dependent launches, so the yardstick is a latency model, not the HBM peak:
+    launch + one DRAM/L2 round trip per dependent load of the step's critical path."""
     import torch
     from gear_b200 import _native as N
     from gear_b200 import core
@@ -510,31 +569,67 @@ def run_index_only(args):
     K, W = args.steps, max(args.warmup, 3)
     ms = _event_loop(torch, lambda i: (s.scan(prio), s.search(u, scale=False, out=out)), K, W)
     ms_scan = _event_loop(torch, lambda i: s.scan(prio), K, W)
+    ms_search = _event_loop(torch, lambda i: s.search(u, scale=False, out=out), K, W)
+    # end to end: the variates start in pinned host memory and the indices end there, every step
+    u_host = torch.from_numpy(hu).pin_memory()
+    out_host = torch.empty(B, dtype=torch.int64).pin_memory()
+    Ke = max(10, min(K, 400))
+
+    def e2e_step(i):
+        u.copy_(u_host, non_blocking=True)
+        s.scan(prio)
+        s.search(u, scale=False, out=out)
+        out_host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    w0 = time.perf_counter()
+    for i in range(Ke):
+        e2e_step(i)
+    e2e_s = (time.perf_counter() - w0) / Ke
     ocdf, ol1, _, _ = O.scan(hp)
     want, near = O.search(ocdf, ol1, hu, want_near=True)
     f64 = O.search_f64(hp, hu)
     peak, peak_src = peaks()
     scan_bytes = 8 * n + 8 * (n // 4096)
+    cores = os.cpu_count() or 1
+    cum = __import__("numpy").empty(n)
+    reps = 20
     t0 = time.perf_counter()
-    for _ in range(20):
-        c2, l2, _, _ = O.scan_mt(hp, os.cpu_count() or 1, cdf=ocdf); O.search(c2, l2, hu)
-    cpu_s = (time.perf_counter() - t0) / 20
-    print(json.dumps({
+    for _ in range(reps):
+        c2_, l2_, _, _ = O.scan_mt(hp, cores, cdf=ocdf); O.search(c2_, l2_, hu)
+    tree_s = (time.perf_counter() - t0) / reps
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        O.plain_cumsum_search(hp, hu, cores, scale=False, cum=cum)
+    plain_s = (time.perf_counter() - t0) / reps
+    cpu_s = min(tree_s, plain_s)
+    return {
         "metric": "sampled indices/sec (prefix-scan + batched search)", "value": B / (ms * 1e-3), "unit": "indices/s",
         "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 scan / f64 level-1", "data": "synthetic (seeded Philox4x32-10)",
         "config": {"workload": C2["name"], "priorities": n, "batch": B,
                    "l2": "8 MB working set: L2-resident by construction of this configuration"},
-        "roofline": {"kernel": "scan_kernel", "bound": "hbm", "achieved": scan_bytes / (ms_scan * 1e-3) / 1e9, "peak": peak,
+        "kernel_ms": {"scan (stores the table, builds level 1 in its last CTA)": ms_scan, "search": ms_search},
+        "roofline": {"kernel": "scan_kernel<true>", "bound": "hbm", "achieved": scan_bytes / (ms_scan * 1e-3) / 1e9, "peak": peak,
                      "unit": "GB/s", "frac": scan_bytes / (ms_scan * 1e-3) / 1e9 / peak, "traffic": None,
-                     "peak_source": peak_src, "avg_launch_ms": ms_scan,
-                     "note": "256 partitions on 148 SMs: launch- and latency-bound, not bandwidth-bound"},
-        "cpu_baseline": {"value": B / cpu_s, "unit": "indices/s", "cores": os.cpu_count(), "kind": "port",
-                         "sample": "20 full steps (scan of 1,048,576 priorities + 4096 searches)"},
+                     "peak_source": peak_src, "avg_launch_ms": ms_scan, "algorithmic_bytes": scan_bytes,
+                     "note": "256 partitions on 148 SMs, the data in L2: a launch- and latency-bound step, for which the "
+                             "HBM fraction says little; see latency_model"},
+        "latency_model": {"launch_and_drain_us_per_kernel": 2.5, "dependent_round_trip_us": 0.6,
+                          "scan_chain": "ticket + 16 KiB copy + tree + aggregate + done counter + level 1 by the last CTA: 5 trips",
+                          "search_chain": "variate + level-1 rounds + level-2 rounds: 6 trips",
+                          "model_us": 2 * 2.5 + 11 * 0.6, "measured_us": ms * 1e3},
+        "cpu_baseline": {"value": B / cpu_s, "unit": "indices/s", "cores": cores, "kind": "port",
+                         "draw_ms": {"plain_cumsum_upper_bound": plain_s * 1e3, "two_level_tree_port": tree_s * 1e3},
+                         "sample": f"{reps} full steps of each draw (1,048,576 priorities + 4096 searches); the faster counts"},
+        "e2e": {"value": B / e2e_s, "unit": "indices/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B,
+                "ms_per_step": e2e_s * 1e3, "steps": Ke},
         "parity": {"index_mismatches_vs_oracle": int((out.cpu().numpy() != want).sum()),
                    "variates_within_1ulp_of_boundary": int(near.sum()),
                    "flips_vs_float64_running_sum": int((want != f64).sum())},
-        "gpu_launches": 2 * K}))
+        "gpu_launches": 2 * K}
 
 
 def run_zero_copy(args):
@@ -582,19 +677,41 @@ def run_zero_copy(args):
         best = min(best, e0.elapsed_time(e1))
     link_gbs = (1 << 30) / (best * 1e-3) / 1e9
     gathered = B * L * sum(rows)
-    # parity: every 16th request of the last batch against the host image itself
+    # parity: the indices against the oracle, every request's bytes against the host image itself
+    from oracle import oracle as O
     step(0); torch.cuda.synchronize()
     img = table.host_view()
     fl = flat.cpu().numpy(); mism = 0
+    ocdf, ol1, _, _ = O.scan_mt(prio.cpu().numpy(), os.cpu_count() or 1)
+    idx_mism = int((fl != O.search(ocdf, ol1, u[:B].cpu().numpy(), scale=True)).sum())
     for c, r in enumerate(rows):
         got = dsts[c].cpu().numpy(); slot = L * r
-        for g in range(0, B, 16):
+        for g in range(B):
             t_, ts = divmod(int(fl[g]), T)
             nb = min(L, T - ts) * r
             a0 = t_ * table.trajectory_stride + table.accu[c] * T + ts * r
             mism += int((got[g * slot:g * slot + nb] != img[a0:a0 + nb]).sum()) + int(got[g * slot + nb:(g + 1) * slot].any())
     achieved = gathered / (ms * 1e-3) / 1e9
-    print(json.dumps({
+    # end to end: variates from pinned host memory in, the step's indices back to the host (the
+    # batch itself is consumed on the device: it is 462 MB, and it just came over the same link)
+    u_host = u.cpu().pin_memory()
+    ub = torch.empty(B, dtype=torch.float64, device=dev)
+    flat_host = torch.empty(B, dtype=torch.int64).pin_memory()
+    Ke = max(5, min(K, 50))
+    w0 = time.perf_counter()
+    for i in range(Ke):
+        ub.copy_(u_host[(i % nbatches) * B:(i % nbatches + 1) * B], non_blocking=True)
+        s.scan(prio)
+        s.sample_gather(handler, ub, cols, dsts, scale=True, out_flat=flat)
+        flat_host.copy_(flat, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    e2e_s = (time.perf_counter() - w0) / Ke
+    # CPU path on the same host table: draw over all priorities + gather straight from the image
+    cores = os.cpu_count() or 1
+    path = CpuPath(rows, T, L, prio.cpu().numpy(), img, cap, cores)
+    cpu = path.time(u_host[:B].numpy(), steps=3, warmup=1)
+    path.close()
+    return ({
         "metric": METRIC, "value": B * L / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 gather",
         "data": "synthetic (seeded Philox4x32-10, written into the mapped host table by the GPU)",
@@ -607,13 +724,21 @@ def run_zero_copy(args):
                      "unit": "GB/s", "frac": achieved / link_gbs, "traffic": None,
                      "peak_source": "best of 10 pinned 1 GiB cudaMemcpyAsync H2D in this run",
                      "algorithmic_bytes": gathered},
-        "parity": {"gathered_byte_mismatches": mism}, "gpu_launches": 2 * K}))
+        "cpu_baseline": cpu,
+        "e2e": {"value": B * L / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B,
+                "ms_per_step": e2e_s * 1e3, "steps": Ke,
+                "note": "the table itself is host memory: every step's 462 MB already cross the host link inside the kernel"},
+        "parity": {"gathered_byte_mismatches": mism, "index_mismatches_vs_oracle": idx_mism, "requests_byte_checked": B},
+        "gpu_launches": 2 * K})
 
 
 def run_profile_case(args):
     """Small single-kernel cases for ncu captures (a few hundred MB on the device):
-    `scan`: --profile-n priorities (default 40M: 320 MB of traffic, larger than L2);
-    `sample_gather`: config-3 rows on a 2,000-trajectory table (378 MB), B=1024, L=64."""
+    `scan` / `scan_totals`: --profile-n priorities (default 40M: 320 MB of traffic, larger than L2);
+    `sample_gather` / `sample_gather_lazy`: config-3 rows on a 2,000-trajectory table (378 MB), B=1024, L=64;
+    `gather` / `vcopy`: the unfused gather kernels on the same table and a drawn batch;
+    `search`: scan + search of the index-only configuration; `update`: 1024 changed priorities;
+    `zero_copy`: the sampling kernel on a table in mapped host memory; `pull`: its sharded instance."""
     import torch
     from gear_b200 import _native as N
     from gear_b200 import core
@@ -629,8 +754,31 @@ def run_profile_case(args):
             s.scan(prio, store=args.profile == "scan")
         print(json.dumps({"profile": args.profile, "n": n, "result": s.result()}))
         return
-    rows, T, cap, B, L = C3["rows"], C3["T"], 2000, C3["B"], C3["L"]
-    table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
+    if args.profile == "search":
+        # config 2's kernels: 1,048,576 priorities, 4096 variates
+        n, B = C2["n"], C2["B"]
+        prio = torch.empty(n, dtype=torch.float32, device=dev)
+        core.fill(prio, N.FILL_F32_LOGNORMAL, seed=1)
+        s = core.PrioritySampler(n)
+        u = torch.empty(B, dtype=torch.float64, device=dev)
+        core.fill(u, N.FILL_U01_F64, seed=4)
+        for _ in range(args.warmup + args.steps):
+            s.scan(prio)
+            s.search(u, scale=True)
+        print(json.dumps({"profile": args.profile, "result": s.result()}))
+        return
+    if args.profile == "zero_copy":
+        # config 4's rows on a 64-trajectory table in pinned mapped host memory (1.8 GB), B=512, L=32
+        rows, T, cap, B, L = C4["rows"], C4["T"], 64, C4["B"], C4["L"]
+        table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HOST)
+    elif args.profile == "pull":
+        # the sharded instance of the sampling kernel, three shards of config 5's rows held by this one
+        # GPU (the kernel is the one the ranks run; what it cannot show here is the NVLink)
+        rows, T, cap, B, L = C5["rows"], C5["T"], 300, 1024, C5["L"]
+        table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
+    else:
+        rows, T, cap, B, L = C3["rows"], C3["T"], 2000, C3["B"], C3["L"]
+        table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
     table.connect()
     fill_table(core, N, table, seed=2)
     h = core.StorageHandler(table)
@@ -640,10 +788,52 @@ def run_profile_case(args):
     prio = torch.empty(n, dtype=torch.float32, device=dev)
     core.fill(prio, N.FILL_F32_LOGNORMAL, seed=3)
     s = core.PrioritySampler(n)
-    s.scan(prio, store=args.profile == "sample_gather")
+    s.scan(prio, store=args.profile in ("sample_gather", "gather", "vcopy"))
     u = torch.empty(B, dtype=torch.float64, device=dev)
     core.fill(u, N.FILL_U01_F64, seed=4)
     dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=dev) for r in rows]
+    if args.profile in ("gather", "vcopy"):
+        # the stand-ins for the reference's three copy kernels, on the indices of one draw
+        flat = s.search(u, scale=True)
+        idx, ts, ln = core.decode(flat, T)
+        src_off, dst_off, nbytes, slot = h.sub(idx.cpu().numpy(), ts.cpu().numpy(), ln.cpu().numpy(), 0)
+        so, do, nb = (torch.from_numpy(x).to(dev) for x in (src_off, dst_off, nbytes))
+        for _ in range(args.warmup + args.steps):
+            if args.profile == "gather":
+                h.gather(cols, idx, ts, ln, dsts, zero_fill=True)
+            else:
+                core.vcopy(table.device_ptr, dsts[0], so, do, nb, slot)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": args.profile, "requests": B, "column0_slot_bytes": int(slot)}))
+        return
+    if args.profile == "update":
+        s.scan(prio, store=False)
+        idx = (torch.arange(B, device=dev, dtype=torch.int64) * 97_003) % n
+        val = torch.rand(B, device=dev, dtype=torch.float32)
+        for _ in range(args.warmup + args.steps):
+            s.update(prio, idx, val)
+        print(json.dumps({"profile": args.profile, "result": s.result()}))
+        return
+    if args.profile == "pull":
+        W = 3
+        shards = [(table, prio, s)]
+        for j in range(1, W):
+            tj = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
+            tj.connect()
+            fill_table(core, N, tj, seed=2 + j)
+            pj = torch.empty(n, dtype=torch.float32, device=dev)
+            core.fill(pj, N.FILL_F32_LOGNORMAL, seed=3 + j)
+            shards.append((tj, pj, core.PrioritySampler(n)))
+        for tj, pj, sj in shards:
+            sj.scan(pj, store=False)
+        totals = torch.stack([sj.l1[-1] for _, _, sj in shards])
+        us = torch.sort(u).values
+        for _ in range(args.warmup + args.steps):
+            s.pull(h, totals, None, [sj.l1_ptr for _, _, sj in shards], [tj.device_ptr for tj, _, _ in shards], us,
+                   cols, dsts, ring=True, self_shard=0, prios=[pj.data_ptr() for _, pj, _ in shards],
+                   blks=[sj.block_totals()[sj.block_totals()[2]] for _, _, sj in shards])
+        print(json.dumps({"profile": args.profile, "result": s.result()}))
+        return
     for _ in range(args.warmup + args.steps):
         s.sample_gather(h, u, cols, dsts, scale=True, zero_fill=True)
     print(json.dumps({"profile": args.profile, "result": s.result()}))
@@ -655,11 +845,14 @@ def main():
     ap.add_argument("--steps", type=int, default=3000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default=None, choices=["scan", "scan_totals", "sample_gather", "sample_gather_lazy"],
+    ap.add_argument("--profile", default=None,
+                    choices=["scan", "scan_totals", "sample_gather", "sample_gather_lazy", "gather", "vcopy", "search",
+                             "update", "zero_copy", "pull"],
                     help="run one small single-kernel case (for ncu) instead of the benchmark")
     ap.add_argument("--workload", default="default", choices=["default", "c2", "c4", "c5"],
-                    help="default: config 3 at one GPU, the sharded config 5 at several; c2 / c4: BASELINE.json's "
-                         "index-only and zero-copy configurations; c5: one shard of config 5 on one GPU")
+                    help="default: the HBM-resident table at one GPU (with c2 and c4 beside it), the sharded table at "
+                         "several; c2 / c4: the index-only and zero-copy configurations alone; c5: one shard of the "
+                         "sharded table on one GPU")
     ap.add_argument("--profile-n", type=int, default=40_000_000, help="priorities for --profile scan")
     args = ap.parse_args()
     if args.profile:
@@ -667,9 +860,9 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     if args.workload == "c2":
-        return run_index_only(args)
+        return print(json.dumps(run_index_only(args)))
     if args.workload == "c4":
-        return run_zero_copy(args)
+        return print(json.dumps(run_zero_copy(args)))
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1 and args.workload != "c5":
         return run_ours_single(args)
     import bench_sharded

@@ -112,6 +112,7 @@ _SIGS = {
                                                      pi64, vp]),
     "gearb_sampler_select_slot": (C.c_int, [vp, C.c_int]),
     "gearb_sampler_block_totals": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(C.c_int)]),
+    "gearb_sampler_level1_buffers": (C.c_int, [vp, C.POINTER(vp), C.POINTER(vp)]),
     "gearb_sampler_clear_status": (C.c_int, [vp, vp]),
     "gearb_mailbox_bytes": (i64, [i64]),
     "gearb_mailbox_l1_offset": (i64, [i64, u64, C.c_int]),

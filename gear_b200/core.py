@@ -123,12 +123,20 @@ class TrajectoryTable:
     def upload(self, stream=None) -> None:
         call("gearb_table_upload", self._h, _stream(stream))
 
-    def write(self, offset: int, data: np.ndarray, stream=None) -> None:
+    def write(self, offset: int, data: np.ndarray, stream=None, sync: bool = True) -> None:
+        """Bytes into every resident copy.  sync=False returns while the upload may still be
+        reading `data` (page-locked memory the caller keeps alive and unchanged until it
+        synchronises the stream)."""
         data = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
         call("gearb_table_write", self._h, int(offset), data.ctypes.data_as(C.c_void_p), data.nbytes,
              _stream(stream))
-        if torch.cuda.is_available():
+        if sync and torch.cuda.is_available():
             torch.cuda.current_stream().synchronize()  # `data` may be freed by the caller
+
+    def read_into(self, offset: int, out: np.ndarray) -> None:
+        """Bytes [offset, offset + out.nbytes) of the table into `out` (contiguous uint8)."""
+        call("gearb_table_read", self._h, int(offset), out.ctypes.data_as(C.c_void_p), int(out.nbytes))
+
 
     def read(self, offset: int, nbytes: int) -> np.ndarray:
         out = np.empty(int(nbytes), np.uint8)
@@ -337,7 +345,21 @@ class PrioritySampler:
         call("gearb_sampler_create", self.n, C.byref(self._h))
         c, l, s = C.c_void_p(0), C.c_void_p(0), C.c_void_p(0)
         call("gearb_sampler_buffers", self._h, C.byref(c), C.byref(l), C.byref(s))
-        self.cdf_ptr, self.l1_ptr, self.status_ptr = c.value, l.value, s.value
+        self.cdf_ptr, self.status_ptr = c.value, s.value
+
+    @property
+    def l1_ptr(self) -> int:
+        """Address of the level-1 table of the LAST scan.  A sampler keeps two and a scan writes
+        the one the previous scan did not (see select_slot), so ask again after every scan."""
+        l = C.c_void_p(0)
+        call("gearb_sampler_buffers", self._h, None, C.byref(l), None)
+        return l.value
+
+    def level1_buffers(self):
+        """(address of level 1 in slot 0, in slot 1)."""
+        a, b = C.c_void_p(0), C.c_void_p(0)
+        call("gearb_sampler_level1_buffers", self._h, C.byref(a), C.byref(b))
+        return a.value, b.value
 
     def scan(self, priorities: torch.Tensor, stream=None, store: bool = True, alternate: bool = False) -> None:
         """Build the two-level table.  store=False keeps only the partition offsets and the total
@@ -507,7 +529,9 @@ class PrioritySampler:
         self.publish(world, rank, mailboxes, epoch, False, stream)
 
     def select_slot(self, slot: int) -> None:
-        """Which of the two block-total buffers the NEXT scan writes (ranks of a pull agree on epoch & 1)."""
+        """Which of the two slots (level 1 and block totals) the NEXT scan writes; ranks of a pull
+        agree on epoch & 1.  Pinning the same slot every time gives the tables a fixed address, at
+        the price that a scan then never starts before the launch ahead of it has finished."""
         call("gearb_sampler_select_slot", self._h, int(slot))
 
     def block_totals(self):

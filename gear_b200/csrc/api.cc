@@ -19,9 +19,14 @@
 #include <optional>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.h"
 
 namespace gearb {
+
+TraceRange::TraceRange(const char *name) { nvtxRangePushA(name); }
+TraceRange::~TraceRange() { nvtxRangePop(); }
 
 std::string &last_error() {
   static thread_local std::string e;
@@ -205,7 +210,7 @@ struct gearb_sampler {
   int64_t n = 0, nparts = 0, scratch_bytes = 0;
   int device = 0;
   float *cdf = nullptr;
-  double *l1 = nullptr;
+  double *l1s[2] = {nullptr, nullptr};  // level 1 of the last scan and of the one before it, like blk below
   void *scratch = nullptr;
   void *upd = nullptr;  // dirty flags + list of touched partitions for incremental updates
   int32_t *status = nullptr;
@@ -220,6 +225,17 @@ struct gearb_sampler {
     slot = next_slot >= 0 ? next_slot : (slot ^ 1);
     next_slot = -1;
     return slot;
+  }
+  double *l1() const { return l1s[slot]; }
+  // A scan may begin while the launch before it in the stream is still finishing -- but never
+  // beside an earlier scan of the same sampler: they share the scratch block.  Every launch that
+  // reads the tables waits for the scan before it to complete before it lets its own successor
+  // go, so one such launch between two scans is enough; two scans in a row are not overlapped.
+  bool scan_unconsumed = false;
+  bool may_overlap() {
+    const bool ok = !scan_unconsumed;
+    scan_unconsumed = true;
+    return ok;
   }
 };
 
@@ -329,6 +345,7 @@ void *gearb_table_device_ptr(const gearb_table *t) {
 }
 
 int gearb_table_upload(gearb_table *t, void *stream) {
+  TraceRange trace("gearb:table_upload");
   GEARB_REQUIRE(t && t->connected, "table_upload: table is not connected");
   GEARB_REQUIRE(t->host.addr, "table_upload: table has no host copy");
   if (!t->hbm) {
@@ -448,7 +465,7 @@ int gearb_handler_sub(const gearb_handler *h, const int64_t *idx, const int64_t 
 // Fills the launch parameters shared by the gather kernels from the handler's patterns.
 static int build_gather_params(gearb_handler *h, const int32_t *columns, int ncols, int64_t n,
                                void *const *dst, int zero_fill, int32_t *status, GatherParams &p,
-                               int piece_bytes = 2048) {
+                               int piece_bytes = 2048, bool staged_pieces = true) {
   GEARB_REQUIRE(h && h->table, "gather: null handler");
   GEARB_REQUIRE(ncols >= 0 && ncols <= GEARB_MAX_COLUMNS, "gather: %d columns", ncols);
   GEARB_REQUIRE(n >= 0, "gather: negative request count");
@@ -492,8 +509,11 @@ static int build_gather_params(gearb_handler *h, const int32_t *columns, int nco
   }
   p.ncols = used;
   p.chunks_per_request = static_cast<int32_t>(chunks);
-  // Small requests from an HBM table are staged through shared memory by the fused kernel.
+  // Small requests from an HBM table are staged through shared memory by the fused kernel, which
+  // copies them out in pieces of 1 KiB so that its four warps get equal shares.
   p.stage_bytes = (t->hbm && stage > 0 && stage <= 24 * 1024) ? static_cast<int32_t>(stage) : 0;
+  if (p.stage_bytes > 0 && piece_bytes == 4096 && staged_pieces)  // the fused launches ask for 4 KiB pieces
+    return build_gather_params(h, columns, ncols, n, dst, zero_fill, status, p, 1024, false);
   // Larger requests: from mapped host memory they stream through per-warp rings of bulk copies
   // (measured on config 4: 51.3 GB/s = 0.92 of the host-to-device copy peak, against 32.0 GB/s with
   // plain loads); from HBM plain 16-byte loads are faster (3.6 against 2.6 TB/s on 64 KiB requests).
@@ -506,6 +526,7 @@ static int build_gather_params(gearb_handler *h, const int32_t *columns, int nco
 int gearb_handler_gather(gearb_handler *h, const int32_t *columns, int ncols, const int64_t *idx,
                          const int64_t *ts, const int64_t *len, int64_t n, void *const *dst,
                          int zero_fill, int32_t *status, void *stream) {
+  TraceRange trace("gearb:gather");
   GatherParams p;
   int rc = build_gather_params(h, columns, ncols, n, dst, zero_fill, status, p);
   if (rc != GEARB_OK) return rc;
@@ -539,6 +560,7 @@ int gearb_handler_view(const gearb_handler *h, int64_t index, int column, void *
 
 int gearb_vcopy(const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off,
                 const int64_t *lengths, int64_t n, int64_t max_length, void *stream) {
+  TraceRange trace("gearb:vcopy");
   GEARB_REQUIRE(lengths || n == 0, "vcopy: null lengths");
   return launch_vcopy(static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), src_off, dst_off,
                       lengths, 0, n, max_length, as_stream(stream));
@@ -546,6 +568,7 @@ int gearb_vcopy(const void *src, void *dst, const int64_t *src_off, const int64_
 
 int gearb_copy(const void *src, void *dst, const int64_t *src_off, const int64_t *dst_off, int64_t n,
                int64_t length, void *stream) {
+  TraceRange trace("gearb:copy");
   return launch_vcopy(static_cast<const uint8_t *>(src), static_cast<uint8_t *>(dst), src_off, dst_off,
                       nullptr, length, n, length, as_stream(stream));
 }
@@ -585,11 +608,13 @@ int64_t gearb_scan_scratch_bytes(int64_t n) { return n > 0 ? scan_scratch_bytes(
 
 int gearb_scan(const float *priorities, int64_t n, float *cdf, double *l1, void *scratch,
                int64_t scratch_bytes, int32_t *status, void *stream) {
+  TraceRange trace("gearb:scan");
   return launch_scan(priorities, n, cdf, l1, scratch, scratch_bytes, status, 1, as_stream(stream));
 }
 
 int gearb_scan_static(const float *priorities, int64_t n, float *cdf, double *l1, int32_t *status,
                       void *stream) {
+  TraceRange trace("gearb:scan");
   return launch_scan_static(priorities, n, cdf, l1, status, as_stream(stream));
 }
 
@@ -597,6 +622,7 @@ int64_t gearb_scan_static_max_n(void) { return static_scan_max_n(); }
 
 int gearb_search(const float *cdf, const double *l1, int64_t n, const double *variates, int64_t b,
                  int flags, int64_t *out_index, int32_t *status, void *stream) {
+  TraceRange trace("gearb:search");
   return launch_search(cdf, l1, n, variates, b, flags, out_index, status, as_stream(stream));
 }
 
@@ -618,7 +644,8 @@ int gearb_sampler_create(int64_t n, gearb_sampler **out) {
   s->scratch_bytes = scan_scratch_bytes(n);
   cudaError_t e = cudaGetDevice(&s->device);
   if (e == cudaSuccess) e = cudaMalloc(&s->cdf, static_cast<size_t>(round_up(n * 4, 256)));
-  if (e == cudaSuccess) e = cudaMalloc(&s->l1, static_cast<size_t>(round_up((s->nparts + 1) * 8, 256)));
+  if (e == cudaSuccess) e = cudaMalloc(&s->l1s[0], static_cast<size_t>(round_up((s->nparts + 1) * 8, 256)));
+  if (e == cudaSuccess) e = cudaMalloc(&s->l1s[1], static_cast<size_t>(round_up((s->nparts + 1) * 8, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->scratch, static_cast<size_t>(s->scratch_bytes));
   if (e == cudaSuccess) e = cudaMalloc(&s->upd, static_cast<size_t>(update_scratch_bytes(n)));
   if (e == cudaSuccess) e = cudaMemset(s->upd, 0, static_cast<size_t>(update_scratch_bytes(n)));
@@ -639,7 +666,8 @@ int gearb_sampler_create(int64_t n, gearb_sampler **out) {
 int gearb_sampler_destroy(gearb_sampler *s) {
   if (!s) return GEARB_OK;
   if (s->cdf) (void)cudaFree(s->cdf);
-  if (s->l1) (void)cudaFree(s->l1);
+  if (s->l1s[0]) (void)cudaFree(s->l1s[0]);
+  if (s->l1s[1]) (void)cudaFree(s->l1s[1]);
   if (s->scratch) (void)cudaFree(s->scratch);
   if (s->upd) (void)cudaFree(s->upd);
   if (s->blk[0]) (void)cudaFree(s->blk[0]);
@@ -650,56 +678,77 @@ int gearb_sampler_destroy(gearb_sampler *s) {
 }
 
 int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int store, void *stream) {
+  TraceRange trace("gearb:scan_partitions");
   GEARB_REQUIRE(s, "sampler_scan_partitions: null sampler");
-  int rc = launch_scan(priorities, s->n, store ? s->cdf : nullptr, s->l1, s->scratch, s->scratch_bytes, s->status,
-                       0, as_stream(stream), /*level1=*/false, false, s->blk[s->take_slot()]);
+  const int slot = s->take_slot();
+  int rc = launch_scan(priorities, s->n, store ? s->cdf : nullptr, s->l1s[slot], s->scratch, s->scratch_bytes, s->status,
+                       0, as_stream(stream), /*level1=*/false, /*overlap_previous=*/s->may_overlap() && !store,
+                       s->blk[slot]);
   if (rc == GEARB_OK) s->lazy_prio = store ? nullptr : priorities;
   return rc;
 }
 
 int gearb_sampler_scan_level1(gearb_sampler *s, void *stream) {
+  TraceRange trace("gearb:level1");
   GEARB_REQUIRE(s, "sampler_scan_level1: null sampler");
-  return launch_level1(scan_aggregate_words(s->scratch), s->nparts, s->l1, nullptr, s->status,
-                       as_stream(stream), static_cast<ScanHeader *>(s->scratch), true);
+  s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
+  return launch_level1(scan_aggregate_words(s->scratch), s->nparts, s->l1(), nullptr, s->status,
+                       as_stream(stream), static_cast<ScanHeader *>(s->scratch),
+                       /*have_range=*/s->nparts > 1024);  // only the streaming kernel leaves the exponent range
 }
 
 int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream) {
+  TraceRange trace("gearb:scan_totals");
   GEARB_REQUIRE(s, "sampler_scan_totals: null sampler");
-  int rc = launch_scan(priorities, s->n, nullptr, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
-                       as_stream(stream), true, false, s->blk[s->take_slot()]);
+  // The launch may begin while the one before it in the stream is finishing -- a sampling launch
+  // that reads the level 1 and block totals of the OTHER slot.  Not when the caller pinned the slot.
+  const int before = s->slot;
+  const int slot = s->take_slot();
+  int rc = launch_scan(priorities, s->n, nullptr, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
+                       as_stream(stream), true, /*overlap_previous=*/s->may_overlap() && slot != before,
+                       s->blk[slot]);
   if (rc == GEARB_OK) s->lazy_prio = priorities;
   return rc;
 }
 
 int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void *stream) {
+  TraceRange trace("gearb:scan");
   GEARB_REQUIRE(s, "sampler_scan_alternate: null sampler");
   s->lazy_prio = nullptr;
-  return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
-                     as_stream(stream), true, /*overlap_previous=*/true, s->blk[s->take_slot()]);
+  const int slot = s->take_slot();
+  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
+                     as_stream(stream), true, /*overlap_previous=*/s->may_overlap(), s->blk[slot]);
 }
 
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) {
+  TraceRange trace("gearb:scan");
   GEARB_REQUIRE(s, "sampler_scan: null sampler");
   s->lazy_prio = nullptr;
-  return launch_scan(priorities, s->n, s->cdf, s->l1, s->scratch, s->scratch_bytes, s->status, 0,
-                     as_stream(stream), true, false, s->blk[s->take_slot()]);
+  const int slot = s->take_slot();
+  s->scan_unconsumed = true;
+  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
+                     as_stream(stream), true, false, s->blk[slot]);
 }
 
 int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx, const float *values, int64_t m,
                          void *stream) {
+  TraceRange trace("gearb:update");
   GEARB_REQUIRE(s, "sampler_update: null sampler");
+  s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE(!s->lazy_prio || s->lazy_prio == priorities,
                 "sampler_update: not the array the table was built from");
-  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1, scan_aggregate_words(s->scratch),
+  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1(), scan_aggregate_words(s->scratch),
                        s->blk[s->slot], static_cast<ScanHeader *>(s->scratch), s->upd, idx,
                        values, m, s->status, as_stream(stream));
 }
 
 int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, int flags,
                          int64_t *out_index, void *stream) {
+  TraceRange trace("gearb:search");
   GEARB_REQUIRE(s, "sampler_search: null sampler");
+  s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   if (s->lazy_prio) return fail(GEARB_ERR_STATE, "sampler_search: the table was built without its level-2 entries");
-  return launch_search(s->cdf, s->l1, s->n, variates, b, flags, out_index, s->status,
+  return launch_search(s->cdf, s->l1(), s->n, variates, b, flags, out_index, s->status,
                        as_stream(stream));
 }
 
@@ -709,7 +758,9 @@ int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const
                                        int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
                                        int64_t flat_offset, int slot_mod, int64_t slot_lo, const int64_t *slot_base,
                                        void *stream) {
+  TraceRange trace("gearb:sample_gather(owner)");
   GEARB_REQUIRE(s, "sample_gather: null sampler");
+  s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE(slot_mod >= -1 && slot_mod <= GEARB_MAX_SHARDS && (slot_mod == 0 || slot_mod == 1 || slot_base),
                 "sample_gather: bad slot map");
   GatherParams p;
@@ -725,7 +776,7 @@ int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const
                 (long long)(h->table->capacity * h->table->T));
   DrawLayout lay;
   lay.flat_offset = flat_offset;
-  return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, GEARB_SEARCH_AFFINE, lengths, index_offset,
+  return launch_sample_gather(p, s->cdf, s->l1(), s->n, variates, GEARB_SEARCH_AFFINE, lengths, index_offset,
                               out_flat, out_idx, out_ts, out_len, as_stream(stream), mul, sub, s->lazy_prio,
                               s->blk[s->slot], lay);
 }
@@ -735,7 +786,9 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
                                 const int32_t *columns, int ncols, void *const *dst, int zero_fill,
                                 int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
                                 void *stream) {
+  TraceRange trace("gearb:sample_gather");
   GEARB_REQUIRE(s, "sample_gather: null sampler");
+  s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE((flags & ~GEARB_SEARCH_SCALE) == 0, "sample_gather: unknown flag");
   GatherParams p;
   int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
@@ -743,7 +796,7 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
   GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
                 (long long)(h->table->capacity * h->table->T));
-  return launch_sample_gather(p, s->cdf, s->l1, s->n, variates, flags, lengths, index_offset, out_flat,
+  return launch_sample_gather(p, s->cdf, s->l1(), s->n, variates, flags, lengths, index_offset, out_flat,
                               out_idx, out_ts, out_len, as_stream(stream), 1.0, 0.0, s->lazy_prio,
                               s->blk[s->slot]);
 }
@@ -799,9 +852,11 @@ int64_t gearb_mailbox_l1_offset(int64_t n, uint64_t epoch, int shard) {
 
 int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
                           int copy_l1, void *stream) {
+  TraceRange trace("gearb:publish");
   GEARB_REQUIRE(s, "publish: null sampler");
-  unsigned *counter = &static_cast<ScanHeader *>(s->scratch)->pad[30];
-  return launch_publish(s->l1, s->nparts, world, rank, mailboxes, epoch, copy_l1, counter, as_stream(stream));
+  s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
+  unsigned *counter = &static_cast<ScanHeader *>(s->scratch)->pad[kPadPublish];
+  return launch_publish(s->l1(), s->nparts, world, rank, mailboxes, epoch, copy_l1, counter, as_stream(stream));
 }
 
 int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
@@ -810,7 +865,9 @@ int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *con
 }
 
 int gearb_sampler_pull_ex(gearb_sampler *s, gearb_handler *h, const gearb_pull_args *a, void *stream) {
+  TraceRange trace("gearb:pull");
   GEARB_REQUIRE(s && a, "pull: null sampler or arguments");
+  s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE(a->cdf || a->prio, "pull: neither level-2 tables nor priorities were given");
   GEARB_REQUIRE(a->totals || a->mailbox, "pull: neither totals nor a mailbox were given");
   GatherParams p;
@@ -860,6 +917,13 @@ int gearb_sampler_select_slot(gearb_sampler *s, int slot) {
   return GEARB_OK;
 }
 
+int gearb_sampler_level1_buffers(const gearb_sampler *s, double **slot0, double **slot1) {
+  GEARB_REQUIRE(s, "sampler_level1_buffers: null sampler");
+  if (slot0) *slot0 = s->l1s[0];
+  if (slot1) *slot1 = s->l1s[1];
+  return GEARB_OK;
+}
+
 int gearb_sampler_block_totals(const gearb_sampler *s, float **slot0, float **slot1, int *current) {
   GEARB_REQUIRE(s, "sampler_block_totals: null sampler");
   if (slot0) *slot0 = s->blk[0];
@@ -877,7 +941,7 @@ int gearb_sampler_clear_status(gearb_sampler *s, void *stream) {
 int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status) {
   GEARB_REQUIRE(s, "sampler_buffers: null sampler");
   if (cdf) *cdf = s->cdf;
-  if (l1) *l1 = s->l1;
+  if (l1) *l1 = s->l1();
   if (status) *status = s->status;
   return GEARB_OK;
 }
@@ -886,7 +950,7 @@ int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t 
   GEARB_REQUIRE(s, "sampler_result: null sampler");
   GEARB_CUDA(cudaStreamSynchronize(as_stream(stream)));
   if (total)
-    GEARB_CUDA(cudaMemcpy(total, s->l1 + s->nparts, sizeof(double), cudaMemcpyDeviceToHost));
+    GEARB_CUDA(cudaMemcpy(total, s->l1() + s->nparts, sizeof(double), cudaMemcpyDeviceToHost));
   int32_t st[GEARB_STATUS_WORDS];
   GEARB_CUDA(cudaMemcpy(st, s->status, sizeof(st), cudaMemcpyDeviceToHost));
   if (status) std::memcpy(status, st, sizeof(st));

@@ -170,6 +170,7 @@ int gearb_comm_allgather(gearb_comm *c, const void *send, void *recv, int64_t by
 int gearb_comm_alltoallv(gearb_comm *c, int nbuf, const void *const *send, const int64_t *send_off,
                          const int64_t *send_bytes, void *const *recv, const int64_t *recv_off,
                          const int64_t *recv_bytes, void *stream) {
+  TraceRange trace("gearb:alltoallv");
   GEARB_REQUIRE(c && nbuf >= 0, "comm_alltoallv: bad argument");
   if (nbuf == 0) return GEARB_OK;
   GEARB_REQUIRE(send && recv && send_off && send_bytes && recv_off && recv_bytes, "comm_alltoallv: null argument");

@@ -32,6 +32,16 @@ int fail(int code, const char *fmt, ...);
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// NVTX range around the host side of an entry point, so that the launches of a step can be told
+// apart in a timeline (scan, level 1, sample + gather, publish, pull, all-to-all, update).  Costs a
+// few nanoseconds when no tool is attached.
+struct TraceRange {
+  explicit TraceRange(const char *name);
+  ~TraceRange();
+  TraceRange(const TraceRange &) = delete;
+  TraceRange &operator=(const TraceRange &) = delete;
+};
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
@@ -50,12 +60,15 @@ struct ScanHeader {
   unsigned int pad[61];  // pad[1..24]: words shared with the level-1 launch (level1.cu)
 };
 static_assert(sizeof(ScanHeader) == 256, "header is one 256-byte block");
+// Words of ScanHeader::pad beyond those the level-1 launch uses (level1.cu: 1-4, 9-24).
+enum { kPadPublish = 30 };  // CTA counter of the publish launch
 
 int64_t scan_scratch_bytes(int64_t n);
 // fresh != 0: scratch contents are unknown, clear them first (one memset).
 // level1 == false: only the partitions' aggregates (and the cdf) are produced; the caller
-// follows up with launch_level1 on scan_aggregate_words(scratch).  overlap_previous: the storing
-// scan may start while the kernel before it in the stream finishes (that kernel must not read cdf).
+// follows up with launch_level1 on scan_aggregate_words(scratch).  overlap_previous: the scan may
+// start while the kernel before it in the stream finishes (that kernel must not read the cdf of
+// this call; l1 is written by the level-1 launch, which waits for everything before it).
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream,
                 bool level1 = true, bool overlap_previous = false, float *blkw = nullptr);

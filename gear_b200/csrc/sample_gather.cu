@@ -200,6 +200,8 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
   __shared__ int warp_best[kWarps];
   __shared__ float warp_lo[kWarps];
   __shared__ int fast_j;
+  __shared__ int plan_bytes[GEARB_MAX_COLUMNS];     // staged path: clipped bytes of every column of the request
+  __shared__ unsigned plan_mis[GEARB_MAX_COLUMNS];  // ... and how far its first byte sits inside a 16-byte block
   unsigned ring_it = 0;  // pieces this warp has pushed through its ring so far
   bool ring_dead = false;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -597,32 +599,32 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
 
     // ---- gather
     if (kPath == kStaged) {
-      // Staged: thread 0 starts one bulk asynchronous copy per column (the 16-byte blocks that
-      // cover the clipped segment) into shared memory, so every column of the request is in
-      // flight at once; then the warps realign from shared memory to the destination.
-      if (threadIdx.x == 0) {
-        unsigned total_tx = 0;
-        for (int c = 0; c < P.ncols; ++c) {
+      // Staged: lane c of the first warp clips column c and starts its bulk asynchronous copy
+      // (the 16-byte blocks that cover the clipped segment) into shared memory, so every column
+      // of the request is described and in flight at once; then the warps realign from shared
+      // memory to the destination.
+      if (warp == 0) {
+        unsigned cover = 0;
+        uintptr_t src = 0;
+        if (lane < P.ncols) {
           int64_t start, bytes;
-          dev::clip_segment(P, P.cols[c], t, ts, len, start, bytes, flags);
+          dev::clip_segment(P, P.cols[lane], t, ts, len, start, bytes, flags);
           if (bytes > 0) {
-            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start, table));
-            total_tx += static_cast<unsigned>(((src & 15u) + bytes + 15) & ~int64_t(15));
+            src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[lane], t, start, table));
+            cover = static_cast<unsigned>(((src & 15u) + bytes + 15) & ~int64_t(15));
           }
+          plan_bytes[lane] = static_cast<int>(bytes);
+          plan_mis[lane] = static_cast<unsigned>(src & 15u);
         }
-        if (total_tx) mbar_arrive_expect_tx(&stage_bar, total_tx);
-        else mbar_arrive(&stage_bar);
-        for (int c = 0; c < P.ncols; ++c) {
-          int64_t start, bytes;
-          unsigned ignore = 0;
-          dev::clip_segment(P, P.cols[c], t, ts, len, start, bytes, ignore);
-          if (bytes > 0) {
-            const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, P.cols[c], t, start, table));
-            const unsigned cover = static_cast<unsigned>(((src & 15u) + bytes + 15) & ~int64_t(15));
-            bulk_load(stage + P.cols[c].stage_off, reinterpret_cast<const void *>(src & ~uintptr_t(15)), cover,
-                      &stage_bar);
-          }
+        const unsigned total_tx = __reduce_add_sync(kFull, cover);
+        if (lane == 0) {
+          if (total_tx) mbar_arrive_expect_tx(&stage_bar, total_tx);
+          else mbar_arrive(&stage_bar);
         }
+        __syncwarp();
+        if (cover)
+          bulk_load(stage + P.cols[lane].stage_off, reinterpret_cast<const void *>(src & ~uintptr_t(15)), cover,
+                    &stage_bar);
       }
       GEARB_STAMP(5);
       unsigned polls = 0;
@@ -638,11 +640,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
       for (int q = warp; q < P.chunks_per_request; q += kWarps) {
         const int c = dev::column_of_piece(P, q);
         const GatherColumn &col = P.cols[c];
-        int64_t start, bytes;
-        unsigned ignore = 0;
-        dev::clip_segment(P, col, t, ts, len, start, bytes, ignore);
-        const uintptr_t src = reinterpret_cast<uintptr_t>(dev::segment_src(P, col, t, start, table));
-        dev::copy_piece<true>(P, col, q - col.chunk_first, gd, stage + col.stage_off + (src & 15u), bytes, lane);
+        dev::copy_piece<true>(P, col, q - col.chunk_first, gd, stage + col.stage_off + plan_mis[c], plan_bytes[c], lane);
       }
       __syncthreads();  // the staging area is free for the next request
       GEARB_STAMP(7);
@@ -716,6 +714,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
       }
     }
   }
+  flags = __reduce_or_sync(kFull, flags);  // any lane may have clipped a column
   if (P.status && flags && lane == 0) atomicOr(reinterpret_cast<unsigned *>(P.status), flags);
 }
 

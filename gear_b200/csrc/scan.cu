@@ -16,7 +16,8 @@
 // Level 1 (l1): float64 exclusive offsets of the partitions, defined as the in-order sum of
 // the partitions' aggregates (the eight block totals of a partition added in sequence).  This
 // kernel leaves every partition's aggregate in global memory; a second, small launch
-// (level1.cu) turns the aggregates into l1 (for small tables the last CTA does it on the spot).  An earlier version chained the offsets through a
+// (level1.cu) turns the aggregates into l1 (tables of at most 1024 partitions take
+// small_scan_kernel below, whose last CTA does it on the spot).  An earlier version chained the offsets through a
 // decoupled look-back while streaming: at 6 TB/s the look-back could not keep up with the
 // partitions (37 of 105 us at 1e8 priorities), the separate launch costs a few us.
 //
@@ -323,8 +324,7 @@ __device__ void compute_warps(Smem &sm, const ScanArgs &a, int warp, int lane) {
   }
 }
 
-// Last CTA out: the header is re-armed for the next launch.  For a small table the last CTA
-// also builds level 1 on the spot (a few hundred aggregates cost less than another launch).
+// Last CTA out: the header is re-armed for the next launch.
 __device__ void finish_launch(Smem &sm, const ScanArgs &a, int tid) {
   __shared__ int is_last;
   if (tid == 0) {
@@ -338,11 +338,7 @@ __device__ void finish_launch(Smem &sm, const ScanArgs &a, int tid) {
   // after an abort of THIS launch some aggregates are stale and copies may still land in the
   // ring: leave l1 alone (every CTA raised its flag before it counted itself done)
   const unsigned aborted = __ldcg(&a.hdr->aborted);
-  if (a.inline_level1) {
-    static_assert(sizeof(sm.stage) >= level1::kTile * sizeof(float), "the ring doubles as level 1's tile");
-    if (!aborted) level1::build(a.aggw, a.nparts, a.l1, a.status, reinterpret_cast<float *>(sm.stage));
-    __syncthreads();
-  }
+  (void)aborted;  // after an abort the status word says that the tables are not valid
   if (tid == 0) {
     a.hdr->ticket = 0u;
     a.hdr->done = 0u;
@@ -358,11 +354,9 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // A kernel launched behind this one with programmatic stream serialisation may be scheduled
   // as this grid drains; it still waits (griddepcontrol.wait) for this grid to complete.
-  // Not when the last CTA builds level 1 itself: then nothing between two scans of one sampler
-  // is guaranteed to outlast the first (the level-1 launch of a larger table is), and a second
-  // scan that started early would share the header's ticket and CTA counters with it.  Without
-  // the instruction the launch behind this one starts when this grid has completed.
-  if (!a.inline_level1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // (Two scans of one sampler never run side by side: the level-1 launch between them lets its
+  // successor go only at its end, and the host does not overlap two scans in a row.)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -389,7 +383,7 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
   // Only now, with everything before this launch complete (a level-1 launch of an earlier scan
   // clears these words at its end), the exponent range goes to the header for the level-1
   // launch behind this one (level1.cu).
-  if (tid == 0 && sm.emax != 0u && !a.inline_level1) {
+  if (tid == 0 && sm.emax != 0u) {
     atomicMax(&a.hdr->pad[1], 256u - sm.emin);
     atomicMax(&a.hdr->pad[2], sm.emax);
   }
@@ -404,6 +398,104 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
   }
 
   finish_launch(sm, a, tid);
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Tables of at most kSmallParts partitions: one CTA per partition, no tickets, no staging ring.
+// A table this small sits in L2 and the whole scan is a chain of a few dependent steps (load,
+// tree, aggregate, count, level 1 by the last CTA), so what counts is the length of that chain:
+// the persistent kernel above would add a ticket round trip and a bulk copy to it.  The tree is
+// the same code (scan_tree.cuh), the results the same bits.
+// The kernel lets the launch behind it be scheduled at once (it still waits for this grid where
+// it says so) and is itself never launched to overlap what is before it, so two scans of one
+// sampler cannot share the CTA counter.
+constexpr int kSmallParts = 1024;
+constexpr int kSmallThreads = kComputeThreads;
+
+template <bool kStore>
+__global__ void __launch_bounds__(kSmallThreads) small_scan_kernel(const ScanArgs a) {
+  __shared__ __align__(16) float xs_all[kComputeWarps][128];
+  __shared__ float wt[kComputeWarps], wm[kComputeWarps];
+  __shared__ __align__(16) float tile[kSmallParts];
+  __shared__ int is_last;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int part = blockIdx.x;
+  const int64_t base = static_cast<int64_t>(part) * kPart;
+  const int64_t e0 = base + warp * tree::kBlockValues;
+  float *xs = xs_all[warp];
+  unsigned bits = 0;
+  float4 x[kTilesPerWarp];
+#pragma unroll
+  for (int k = 0; k < kTilesPerWarp; ++k) {
+    const int64_t e = e0 + (k * 32 + lane) * 4;
+    if (e + 4 <= a.n) {
+      x[k] = __ldg(reinterpret_cast<const float4 *>(a.prio + e));
+    } else {
+      x[k].x = e + 0 < a.n ? __ldg(a.prio + e + 0) : 0.f;
+      x[k].y = e + 1 < a.n ? __ldg(a.prio + e + 1) : 0.f;
+      x[k].z = e + 2 < a.n ? __ldg(a.prio + e + 2) : 0.f;
+      x[k].w = e + 3 < a.n ? __ldg(a.prio + e + 3) : 0.f;
+    }
+  }
+  if (!kStore) {
+    const float total = tree::block_total(x, xs, lane, bits);
+    if (lane == 0) wt[warp] = total;
+    __syncthreads();
+  } else {
+    float sv[kTilesPerWarp][4], top[kTilesPerWarp];
+    const tree::Group g = tree::block_sums(x, xs, lane, sv, bits);
+    if (lane == 0) wt[warp] = g.total;
+    __syncthreads();
+    float X = 0.f;
+    for (int w = 0; w < warp; ++w) X = __fadd_rn(X, wt[w]);
+    tree::block_values(X, g, xs, lane, sv, top, false, e0, a.n);
+    const float run = tree::block_prefix_max(top, xs, lane);
+    if (lane == 0) wm[warp] = run;
+    __syncthreads();
+    float G = 0.f;
+    for (int w = 0; w < warp; ++w) G = fmaxf(G, wm[w]);
+    if (e0 + tree::kBlockValues <= a.n) {
+      float4 *dst = reinterpret_cast<float4 *>(a.cdf + e0);
+#pragma unroll
+      for (int k = 0; k < kTilesPerWarp; ++k) {
+        const float m = fmaxf(G, xs[k * 32 + lane]);
+        dst[k * 32 + lane] = make_float4(fmaxf(sv[k][0], m), fmaxf(sv[k][1], m), fmaxf(sv[k][2], m), fmaxf(sv[k][3], m));
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < kTilesPerWarp; ++k) {
+        const float m = fmaxf(G, xs[k * 32 + lane]);
+        const int64_t e = e0 + (k * 32 + lane) * 4;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (e + j < a.n) a.cdf[e + j] = fmaxf(sv[k][j], m);
+      }
+    }
+  }
+  if (__any_sync(kFull, (bits >> 31) != 0) && lane == 0)
+    atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_BAD_PRIORITY);
+  if (tid == 0) {
+    float X = 0.f;
+#pragma unroll
+    for (int w = 0; w < kComputeWarps; ++w) X = __fadd_rn(X, wt[w]);  // the aggregate: block totals in sequence
+    a.aggw[part] = X;
+    hand_over_blocks(a, part, wt);
+    // This grid was launched to start only after everything before it in the stream, but the
+    // instruction costs nothing and keeps "no output before the predecessor is done" explicit.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __threadfence();
+    is_last = atomicAdd(&a.hdr->done, 1u) == gridDim.x - 1;
+    __threadfence();
+  }
+  __syncthreads();
+  if (!is_last) return;
+  if (a.inline_level1) level1::build(a.aggw, a.nparts, a.l1, a.status, tile);
+  if (tid == 0) {
+    a.hdr->done = 0u;
+    __threadfence();
+  }
 }
 
 inline int64_t align256(int64_t v) { return (v + 255) & ~int64_t(255); }
@@ -465,6 +557,15 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
     }, &packed);
     if (rc != GEARB_OK) return rc;
   }
+  if (nparts <= kSmallParts) {
+    // one CTA per partition; never launched to overlap its predecessor (see small_scan_kernel)
+    a.inline_level1 = level1;
+    a.group = a.nbig = a.ngroups = 0;
+    if (a.cdf) small_scan_kernel<true><<<static_cast<unsigned>(nparts), kSmallThreads, 0, stream>>>(a);
+    else small_scan_kernel<false><<<static_cast<unsigned>(nparts), kSmallThreads, 0, stream>>>(a);
+    GEARB_CUDA(cudaGetLastError());
+    return GEARB_OK;
+  }
   const size_t smem_bytes = kSmemBytes;
   const int ctas_per_sm = cdf != nullptr ? (packed >> 16) : (packed & 0xffff);
   const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
@@ -475,13 +576,13 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.nbig = static_cast<unsigned>((nparts - tail) / a.group);
   a.ngroups = static_cast<unsigned>(a.nbig + (nparts - static_cast<int64_t>(a.nbig) * a.group));
 
-  a.inline_level1 = level1 && nparts <= 1024;
+  a.inline_level1 = 0;  // small tables took the other kernel above
   int64_t grid = resident;
   if (grid > a.ngroups) grid = a.ngroups;
   {
-    // The totals-only instance may overlap the end of the kernel before it (see the kernel's last
-    // lines); the storing instance only when the caller says that kernel does not read the table
-    // being overwritten.
+    // The launch may overlap the end of the kernel before it in the stream only when the caller
+    // says so: that kernel must read nothing this launch writes (its level-2 table; l1 is written
+    // by the level-1 launch behind this one, which waits for everything before it).
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(grid));
     cfg.blockDim = dim3(kThreads);
@@ -491,7 +592,7 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = (a.cdf == nullptr || overlap_previous) ? 1 : 0;
+    cfg.numAttrs = overlap_previous ? 1 : 0;
     if (a.cdf) GEARB_CUDA(cudaLaunchKernelEx(&cfg, scan_kernel<true>, a));
     else GEARB_CUDA(cudaLaunchKernelEx(&cfg, scan_kernel<false>, a));
   }

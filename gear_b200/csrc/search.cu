@@ -8,8 +8,9 @@
 // uniform_kernel: floor(u*n), the place of torch.randint (global_sampler.py:121-129).
 // decode: flat step index -> GEAR's (trajectory, timestep, length) request triple.
 //
-// One warp serves one variate and narrows the range 32-fold per round, so a
-// draw costs about six dependent memory round trips instead of ~27.
+// One warp serves one variate and narrows the range 256-fold per round (eight probes per
+// lane, all in flight together), so a draw costs about four dependent memory round trips
+// instead of ~27: level 1 of a table of up to 256 partitions in one, level 2 in two.
 #include "common.h"
 
 namespace gearb {
@@ -18,22 +19,39 @@ namespace {
 constexpr unsigned kFull = 0xffffffffu;
 constexpr int kThreads = 256;
 
-// First q in [lo, hi] with a[q] > v, given a[hi] > v.  Warp-cooperative.
+// First q in [lo, hi] with a[q] > v, given a[hi] > v.  Warp-cooperative.  Slot s of a round
+// probes lo + (s+1)*step - 1 (clamped to hi); lane l takes slots l, l+32, ..., so that the
+// probes of a round with step 1 are consecutive across the lanes.
 template <typename T>
 __device__ __forceinline__ int64_t warp_upper_bound(const T *a, int64_t lo, int64_t hi, T v,
                                                     int lane) {
+  constexpr int kPer = 8;  // probes per lane and round
   for (;;) {
     const int64_t width = hi - lo + 1;
-    const int64_t step = (width + 31) >> 5;
-    int64_t q = lo + (lane + 1) * step - 1;
-    if (q > hi) q = hi;
-    const bool gt = __ldg(a + q) > v;
-    const unsigned m = __ballot_sync(kFull, gt);  // never 0: a[hi] > v and lane 31 probes hi
-    const int f = __ffs(m) - 1;
-    const int64_t qf = __shfl_sync(kFull, q, f);
-    const int64_t qprev = __shfl_sync(kFull, q, f > 0 ? f - 1 : 0);
+    if (width <= 32) {  // one probe per lane finishes it
+      int64_t q = lo + lane;
+      if (q > hi) q = hi;
+      const unsigned m = __ballot_sync(kFull, __ldg(a + q) > v);  // never 0: a[hi] > v
+      return lo + (__ffs(m) - 1);
+    }
+    const int64_t step = (width + 32 * kPer - 1) / (32 * kPer);
+    T x[kPer];
+#pragma unroll
+    for (int k = 0; k < kPer; ++k) {
+      int64_t q = lo + (static_cast<int64_t>(k * 32 + lane) + 1) * step - 1;
+      if (q > hi) q = hi;
+      x[k] = __ldg(a + q);
+    }
+    int first = 32 * kPer - 1;  // the last slot probes hi, whose entry is greater
+#pragma unroll
+    for (int k = kPer - 1; k >= 0; --k) {
+      const unsigned m = __ballot_sync(kFull, x[k] > v);
+      if (m) first = k * 32 + __ffs(m) - 1;
+    }
+    int64_t qf = lo + (static_cast<int64_t>(first) + 1) * step - 1;
+    if (qf > hi) qf = hi;
+    if (first > 0) lo = lo + static_cast<int64_t>(first) * step;  // one past the previous slot's probe
     hi = qf;
-    if (f > 0) lo = qprev + 1;
     if (step == 1 || lo >= hi) return hi;
   }
 }
@@ -53,6 +71,12 @@ struct SearchArgs {
 };
 
 __global__ void __launch_bounds__(kThreads) search_kernel(const SearchArgs a) {
+  // Launched with programmatic stream serialisation: the grid may be scheduled while the scan
+  // before it drains (a small table's scan says so at its start), and waits here until that
+  // scan's tables are complete and visible.  What is launched behind this kernel may be
+  // scheduled from here on; it finds everything before this kernel complete.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int lane = threadIdx.x & 31;
   const int64_t w = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
   if (w >= a.b) return;
@@ -143,8 +167,16 @@ int launch_search_ex(const float *cdf, const double *l1, int64_t n, const double
   a.T = T; a.index_offset = index_offset; a.lengths = lengths;
   a.idx = idx; a.ts = ts; a.len = len;
   const int64_t blocks = (b * 32 + kThreads - 1) / kThreads;
-  search_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, stream>>>(a);
-  GEARB_CUDA(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(kThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, search_kernel, a));
   return GEARB_OK;
 }
 

@@ -25,7 +25,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
 constexpr int kPart = GEARB_PART;
-constexpr unsigned kFull = 0xffffffffu;
 static_assert(kWarps * tree::kBlockValues == kPart, "one warp per block of the partition");
 
 __global__ void mark_kernel(float *prio, int64_t n, const int64_t *idx, const float *val, int64_t m,

@@ -93,26 +93,42 @@ class SharedDataset(Dataset):
         return tuple(raw[i].cast_tensor(self.get_column_dtype(cid)).view(self.get_column_shape(cid))
                      for i, cid in enumerate(cids))
 
-    def checkpoint(self, path):
-        ensure_path(path)
-        with open(path, "wb") as of:
-            pickler = pickle.Pickler(of, protocol=4)     # protocol 4: objects beyond 4 GiB
-            pickler.dump(SharedDatasetMeta(self._table.get_table_spec(),
-                                           IndexMeta(self._iset.global_capacity, self._iset.local_capacity,
-                                                     self._iset.index_offset, self._iset.is_sharing, self._iset.shm_key)))
-            pickler.dump(self._table)
-            pickler.dump(self._iset.get_state())
+    STREAM_ABOVE = 1 << 30      # tables beyond this (or without a host image) are written as a stream of chunks
 
-    def load(self, path, key: Union[int, None] = None, create: bool = True, proc_rank: int = 0):
+    def checkpoint(self, path, streamed: Union[bool, None] = None):
+        """(meta, table, index state) like the reference (:179-199).  The table is either the
+        reference's pickle (one bytes object) or, for large tables and tables that live in HBM
+        only, a header followed by raw chunks (TrajectoryTable.dump_stream): no full host copy,
+        64-bit sizes throughout.  load() reads both."""
+        ensure_path(path)
+        if streamed is None:
+            streamed = self._table.get_size() > self.STREAM_ABOVE or self._table.residency_name() == "hbm"
+        with open(path, "wb") as of:
+            pickle.dump(SharedDatasetMeta(self._table.get_table_spec(),
+                                          IndexMeta(self._iset.global_capacity, self._iset.local_capacity,
+                                                    self._iset.index_offset, self._iset.is_sharing, self._iset.shm_key)),
+                        of, protocol=4)                 # protocol 4: objects beyond 4 GiB
+            if streamed:
+                self._table.dump_stream(of)
+            else:
+                pickle.dump(self._table, of, protocol=4)
+            pickle.dump(self._iset.get_state(), of, protocol=4)
+
+    def load(self, path, key: Union[int, None] = None, create: bool = True, proc_rank: int = 0,
+             residency: Union[str, None] = None):
+        """residency (streamed checkpoints only): where the table goes, e.g. "hbm" to stream the
+        file straight into device memory; default: where it was when it was written."""
         if key is None:
             key = get_local_node_hashed_int32()
         table_key, iset_key = _keys(key)
         with open(pathlib.Path(path), "rb") as f:
-            unpickler = pickle.Unpickler(f)
-            meta = unpickler.load()
+            meta = pickle.load(f)
             if create:
-                self._table = unpickler.load()
-                self._iset = glibc.Indexset.load_state(unpickler.load(), meta.index.shared, iset_key, True)
+                obj = pickle.load(f)
+                if isinstance(obj, glibc.StreamedTableHeader):
+                    obj = glibc.TrajectoryTable.load_stream(obj, f, residency=residency)
+                self._table = obj
+                self._iset = glibc.Indexset.load_state(pickle.load(f), meta.index.shared, iset_key, True)
             else:
                 self._table = glibc.TrajectoryTable(meta.storage, table_key, False)
                 self._iset = glibc.Indexset(meta.index.global_capacity, meta.index.local_capacity,

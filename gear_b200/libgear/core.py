@@ -225,7 +225,11 @@ class _Span:
     def from_tensor(cls, t: torch.Tensor):
         if t.is_cuda:
             raise RuntimeError("spans view host memory; pass device tensors to the GPU entry points directly")
-        a = t.detach().contiguous().numpy() if t.dtype != torch.bool else t.detach().contiguous().numpy()
+        if not t.is_contiguous():
+            # a span is a view (include/common/span.h:51-99): writes through it must reach the
+            # tensor, which a copy made here would silently swallow
+            raise RuntimeError("spans view memory in place; pass a contiguous tensor")
+        a = t.detach().numpy()
         return cls(a.view(cls._np).reshape(-1), keep=t)
 
     @staticmethod
@@ -289,6 +293,22 @@ def _i64_host(x) -> np.ndarray:
     return np.ascontiguousarray(x, np.int64)
 
 
+def _i64_out(x) -> np.ndarray:
+    """An OUTPUT argument as a writable int64 view of the caller's own memory.  The reference's
+    spans write through the tensor's data pointer (src/common/pybind.cc:28); a device tensor or a
+    non-contiguous one would have to be copied first and the results would be lost, so both are
+    refused."""
+    if isinstance(x, _Span):
+        return x._a.view(np.int64) if x._a.dtype != np.int64 else x._a
+    if isinstance(x, torch.Tensor):
+        if x.dtype != torch.int64 or x.is_cuda or not x.is_contiguous():
+            raise RuntimeError("output offsets must be contiguous int64 host tensors (or Int64Span)")
+        return x.detach().numpy()
+    if isinstance(x, np.ndarray) and x.dtype == np.int64 and x.flags.c_contiguous and x.flags.writeable:
+        return x
+    raise RuntimeError("output offsets must be contiguous int64 host tensors (or Int64Span)")
+
+
 # --------------------------------------------------------------------------- #
 # table, handler, index set
 # --------------------------------------------------------------------------- #
@@ -298,6 +318,7 @@ class TrajectoryTable:
 
     def __init__(self, spec: TableSpec, key: int, create: bool, residency: str = "host"):
         self._spec, self._key, self._create = spec, int(key), bool(create)
+        self._residency = residency
         res = {"host": N.RES_HOST, "hbm": N.RES_HBM, "host+hbm": N.RES_HOST | N.RES_HBM}[residency]
         self._t = _c.TrajectoryTable([c.size() for c in spec.column_specs], spec.trajectory_length,
                                      spec.capacity, residency=res, key=self._key, create=self._create)
@@ -326,13 +347,65 @@ class TrajectoryTable:
     def upload(self) -> None:
         """Copy the host image into HBM; later gathers read the HBM copy."""
         self._t.upload()
+        self._residency = "host+hbm"
 
     def get_size(self) -> int:
         return self._t.nbytes
 
     def __getstate__(self):
-        # the reference pickles (spec, key, size, create, raw bytes) (pybind.cc:178-186)
-        return (self._spec, self._key, self._t.nbytes, self._create, np.array(self._t.host_view(), copy=True))
+        # the reference pickles (spec, key, size, create, raw bytes) (pybind.cc:178-186); a table that
+        # lives in HBM only is read back for it (dump_stream below avoids the full host copy)
+        img = np.array(self._t.host_view(), copy=True) if self._t.host_ptr else self._t.read(0, self._t.nbytes)
+        return (self._spec, self._key, self._t.nbytes, self._create, img)
+
+    # -- checkpoint at scale: the table's bytes as a stream of chunks --------------------------
+    # The reference's pickle holds the whole table as ONE bytes object and casts its size to int
+    # on load (src/storage/pybind.cc:178-204), which stops at 2 GiB and needs the table twice in
+    # host memory.  The streamed form is a small pickled header followed by raw chunks, each
+    # trailed by its CRC-32; a chunk goes through a pinned bounce buffer between the file and
+    # whatever copies the table has (mapped host memory, HBM), so an HBM-only table of any size
+    # is written and read back without a host image.
+    STREAM_CHUNK = 64 << 20
+
+    def dump_stream(self, f, chunk_bytes: int = 0) -> None:
+        import pickle
+        import zlib
+        chunk = int(chunk_bytes) or self.STREAM_CHUNK
+        n = self._t.nbytes
+        pickle.dump(StreamedTableHeader(self._spec, self._key, n, self._create, chunk, self.residency_name()), f, protocol=4)
+        bounce = _pinned(min(chunk, max(n, 1)))
+        for off in range(0, n, chunk):
+            m = min(chunk, n - off)
+            view = bounce[:m]
+            self._t.read_into(off, view)
+            f.write(memoryview(view))
+            f.write(int(zlib.crc32(memoryview(view))).to_bytes(4, "little"))
+
+    @classmethod
+    def load_stream(cls, header: "StreamedTableHeader", f, key=None, residency=None) -> "TrajectoryTable":
+        import zlib
+        t = cls(header.spec, header.key if key is None else key, True, residency=residency or header.residency)
+        if t.connect() == -1:
+            raise RuntimeError("TrajectoryTable: cannot allocate the table while loading")
+        n, chunk = int(header.nbytes), int(header.chunk_bytes)
+        if n != t._t.nbytes:
+            raise RuntimeError(f"checkpoint holds {n} bytes, the spec describes {t._t.nbytes}")
+        bounce = [_pinned(min(chunk, max(n, 1))) for _ in range(2)]     # one fills while the other uploads
+        for i, off in enumerate(range(0, n, chunk)):
+            m = min(chunk, n - off)
+            view = bounce[i & 1][:m]
+            if f.readinto(memoryview(view)) != m:
+                raise RuntimeError("checkpoint truncated inside the table")
+            crc = int.from_bytes(f.read(4), "little")
+            if crc != zlib.crc32(memoryview(view)):
+                raise RuntimeError(f"checkpoint corrupt: chunk at byte {off} fails its CRC-32")
+            t._t.write(off, view, sync=i & 1 == 1)       # at most two uploads in flight
+        if torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()
+        return t
+
+    def residency_name(self) -> str:
+        return self._residency
 
     def __setstate__(self, t):
         if len(t) != 5:
@@ -341,6 +414,22 @@ class TrajectoryTable:
         if self.connect() == -1:
             raise RuntimeError("TrajectoryTable: cannot allocate the table while unpickling")
         self._t.write(0, np.asarray(t[4], np.uint8)[: int(t[2])])    # 64-bit size (the reference casts to int, :193)
+
+
+class StreamedTableHeader:
+    """What precedes a table's raw chunks in a streamed checkpoint (TrajectoryTable.dump_stream)."""
+
+    def __init__(self, spec, key, nbytes, create, chunk_bytes, residency):
+        self.spec, self.key, self.nbytes, self.create = spec, int(key), int(nbytes), bool(create)
+        self.chunk_bytes, self.residency = int(chunk_bytes), str(residency)
+
+
+def _pinned(nbytes: int) -> np.ndarray:
+    """A page-locked uint8 buffer when CUDA is there (copies to and from it run at link speed and
+    asynchronously), plain memory otherwise."""
+    if torch.cuda.is_available():
+        return torch.empty(int(nbytes), dtype=torch.uint8).pin_memory().numpy()
+    return np.empty(int(nbytes), np.uint8)
 
 
 class CpuTrajectoryStorageHandler:
@@ -362,8 +451,7 @@ class CpuTrajectoryStorageHandler:
             raise RuntimeError(str(e).split("] ", 1)[-1]) from None
         n = len(s)
         for out, val in ((src_offsets, s), (dst_offsets, d), (copy_lengths, b)):
-            o = _i64_host(out)
-            o[:n] = val
+            _i64_out(out)[:n] = val
         return slot
 
     sub_ = sub

@@ -388,10 +388,10 @@ class ShardedReplay:
         own = [self.handler.table.device_ptr] + ([self._pull_box.ptr] if self._pull_box else [])
         if self._pull_lazy:
             b0, b1, _ = self.sampler.block_totals()
-            own += [priorities.ptr, b0, b1, self.sampler.l1_ptr]
+            own += [priorities.ptr, b0, b1, *self.sampler.level1_buffers()]
         else:
             for sm in self._pull_samplers:
-                own += [sm.cdf_ptr, sm.l1_ptr]
+                own += [sm.cdf_ptr, sm.level1_buffers()[0]]     # these samplers always scan into slot 0
         nh = len(own)
         self._pull_mapped = []
         if self.world == 1:
@@ -418,7 +418,7 @@ class ShardedReplay:
         if self._pull_lazy:
             self._pull_prios = [row[o] for row in ptrs]
             self._pull_blks = [[row[o + 1] for row in ptrs], [row[o + 2] for row in ptrs]]
-            self._pull_l1_remote = [row[o + 3] for row in ptrs]
+            self._pull_l1_remote = [[row[o + 3] for row in ptrs], [row[o + 4] for row in ptrs]]
             self._pull_slot = 0
         else:
             self._pull_cdfs = [[row[o + 2 * k] for row in ptrs] for k in range(len(self._pull_samplers))]
@@ -452,6 +452,8 @@ class ShardedReplay:
             self._pull_slot = (self._pull_epoch + 1) & 1
             sm.select_slot(self._pull_slot)
         store = not self._pull_lazy
+        if store:
+            sm.select_slot(0)       # the peers hold the address of this sampler's slot-0 tables
         if between is None:
             # with two tables in turn, the launch before this one (the previous pull) reads the other
             sm.scan(priorities, store=store, alternate=store and len(self._pull_samplers) == 2)
@@ -498,7 +500,7 @@ class ShardedReplay:
                     l1s = [sm.l1_ptr if j == self.rank else self._pull_box.ptr + core.mailbox_l1_offset(self.n_local, e, j)
                            for j in range(self.world)]
                 else:
-                    l1s = self._pull_l1_remote
+                    l1s = self._pull_l1_remote[self._pull_slot]
                 sm.pull(self.handler, None, None, l1s, self._pull_tables, mine, self.columns, recv,
                         mailbox=self._pull_box.ptr, epoch=e, prios=self._pull_prios,
                         blks=self._pull_blks[self._pull_slot], **common)

@@ -235,13 +235,17 @@ int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int
 int gearb_sampler_scan_level1(gearb_sampler *s, void *stream);
 /* Every scan of a sampler also leaves the eight 512-value block totals of each partition, from
  * which a sampling launch on a table without stored level-2 entries rebuilds only the block a
- * request falls into.  There are two such buffers and a scan writes the one the previous scan
- * did not (so that a scan never overwrites what a launch still running -- on this GPU, or on a
- * peer in the pull mode -- is reading).  select_slot fixes the buffer (0 or 1) of the NEXT scan,
- * for ranks that must agree on it without talking (pull mode: slot = epoch & 1);
- * block_totals returns both buffers and the slot the last scan wrote.                     */
+ * request falls into.  There are two such buffers -- and two level-1 tables -- and a scan writes
+ * the slot the previous scan did not (so that a scan never overwrites what a launch still
+ * running -- on this GPU, or on a peer in the pull mode -- is reading).  select_slot fixes the
+ * slot (0 or 1) of the NEXT scan, for ranks that must agree on it without talking (pull mode:
+ * slot = epoch & 1) or for callers that want fixed addresses (then a scan waits for everything
+ * before it in the stream); block_totals returns both buffers and the slot the last scan wrote. */
 int gearb_sampler_select_slot(gearb_sampler *s, int slot);
 int gearb_sampler_block_totals(const gearb_sampler *s, float **slot0, float **slot1, int *current);
+/* The level-1 table is kept twice in the same way (gearb_sampler_buffers returns the one of
+ * the last scan): the addresses of both, for peers that map them.                          */
+int gearb_sampler_level1_buffers(const gearb_sampler *s, double **slot0, double **slot1);
 /* Incremental update after a gearb_sampler_scan of the same array: priorities[idx[i]] =
  * values[i] for i < m (idx, values: device arrays), then only the partitions that were touched
  * are rescanned and the partition offsets rebuilt.  The table afterwards is bit-identical to a

@@ -115,3 +115,76 @@ void gearo_gather_mt(const uint8_t *table, uint8_t *const *dst, const int64_t *i
   for (int t = 1; t < threads; ++t) pthread_join(tid[t], NULL);
   free(jobs); free(tid);
 }
+
+/* ------------------------------------------------------------------------------------------
+ * The plain way to draw on a CPU, timed beside the tree port above: a flat running sum of the
+ * priorities in float64 (chunks summed by the threads, then offset by the chunks before them)
+ * and one upper_bound per variate.  Its indices may differ from the two-level table's by the
+ * flips that a different summation order causes; it is a timing baseline, not a checker.
+ * cum must hold n doubles.  Returns the total. */
+typedef struct {
+  const float *prio;
+  double *cum;
+  int64_t lo, hi;
+  double sum, offset;
+} cumsum_job;
+
+static void *cumsum_pass1(void *arg) {
+  cumsum_job *j = (cumsum_job *)arg;
+  double s = 0.0;
+  for (int64_t i = j->lo; i < j->hi; ++i) {
+    s += (double)j->prio[i];
+    j->cum[i] = s;
+  }
+  j->sum = s;
+  return NULL;
+}
+
+static void *cumsum_pass2(void *arg) {
+  cumsum_job *j = (cumsum_job *)arg;
+  const double o = j->offset;
+  if (o != 0.0)
+    for (int64_t i = j->lo; i < j->hi; ++i) j->cum[i] += o;
+  return NULL;
+}
+
+double gearo_plain_cumsum_mt(const float *prio, int64_t n, double *cum, int threads) {
+  if (threads < 1) threads = 1;
+  if (threads > n) threads = n > 0 ? (int)n : 1;
+  cumsum_job *jobs = (cumsum_job *)calloc((size_t)threads, sizeof(cumsum_job));
+  pthread_t *tid = (pthread_t *)malloc(sizeof(pthread_t) * (size_t)threads);
+  for (int pass = 0; pass < 2; ++pass) {
+    if (pass == 1) {
+      double acc = 0.0;
+      for (int t = 0; t < threads; ++t) {
+        jobs[t].offset = acc;
+        acc += jobs[t].sum;
+      }
+    }
+    for (int t = 0; t < threads; ++t) {
+      jobs[t].prio = prio; jobs[t].cum = cum;
+      jobs[t].lo = n * t / threads; jobs[t].hi = n * (t + 1) / threads;
+      if (t > 0) pthread_create(&tid[t], NULL, pass == 0 ? cumsum_pass1 : cumsum_pass2, &jobs[t]);
+    }
+    (pass == 0 ? cumsum_pass1 : cumsum_pass2)(&jobs[0]);
+    for (int t = 1; t < threads; ++t) pthread_join(tid[t], NULL);
+  }
+  const double total = n > 0 ? cum[n - 1] : 0.0;
+  free(jobs); free(tid);
+  return total;
+}
+
+/* First index whose running sum exceeds u * total (scale != 0) or u. */
+void gearo_plain_upper_bound(const double *cum, int64_t n, const double *u, int64_t b, int scale, int64_t *out) {
+  const double total = n > 0 ? cum[n - 1] : 0.0;
+  for (int64_t k = 0; k < b; ++k) {
+    const double v = scale ? u[k] * total : u[k];
+    int64_t lo = 0, hi = n - 1;
+    while (lo < hi) {
+      const int64_t mid = lo + (hi - lo) / 2;
+      if (cum[mid] > v) hi = mid;
+      else lo = mid + 1;
+    }
+    out[k] = lo;
+  }
+}

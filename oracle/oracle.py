@@ -398,6 +398,23 @@ def gather_mt(table: np.ndarray, dsts, idx, ts, ln, traj_stride, T, col_accu, ro
                           _p(ph), C.c_int(int(threads)))
 
 
+def plain_cumsum_search(prio: np.ndarray, u: np.ndarray, threads: int, scale: bool = True,
+                        cum: np.ndarray | None = None):
+    """The plain CPU draw, for timing: flat float64 running sum over host threads, then one
+    upper_bound per variate.  Returns (indices, total)."""
+    prio = np.ascontiguousarray(prio, dtype=np.float32)
+    u = np.ascontiguousarray(u, dtype=np.float64)
+    n = len(prio)
+    if cum is None:
+        cum = np.empty(n, np.float64)
+    f = lib().gearo_plain_cumsum_mt
+    f.restype = C.c_double
+    total = f(_p(prio), C.c_int64(n), _p(cum), C.c_int(int(threads)))
+    out = np.empty(len(u), np.int64)
+    lib().gearo_plain_upper_bound(_p(cum), C.c_int64(n), _p(u), C.c_int64(len(u)), C.c_int(int(bool(scale))), _p(out))
+    return out, float(total)
+
+
 REF_LIB_PATH = HERE / "_ref" / "libgear_ref.so"
 
 

@@ -107,3 +107,53 @@ def test_subscribe_pattern_pickle_and_repr():
     q = pkl.loads(pkl.dumps(p))
     assert (q.offset, q.length, q.pad_option) == (-3, 7, glibc.SubscribePattern.PadOption.head)
     assert "kHead" in repr(q) and glibc.SubscribePattern(0, 1).pad_option == glibc.SubscribePattern.PadOption.tail
+
+
+def test_sub_outputs_write_through_or_are_refused():
+    # handler.sub fills caller-owned offset arrays (handler.cc:78-131); an output the results could
+    # not reach -- a non-contiguous tensor, which would have to be copied first -- is refused.
+    import libgear.core as glibc
+    spec = TableSpec.create(0, 1, 10, 4, [dict(shape=[3], dtype=torch.float32, name="x")])
+    table = glibc.TrajectoryTable(spec, 0, True)
+    table.connect()
+    h = glibc.get_cpu_handler(table, 4, glibc.Range(0, 4), glibc.Range(0, 4))
+    h.set([0], [glibc.SubscribePattern(0, 2, glibc.SubscribePattern.PadOption.tail)])
+    idx, ts, ln = torch.tensor([1, 3]), torch.tensor([0, 9]), torch.tensor([10, 10])
+    s, d, b = (torch.zeros(2, dtype=torch.int64) for _ in range(3))
+    assert h.sub(idx, ts, ln, 0, s, d, b) == 24
+    assert s.tolist() == [120, 3 * 120 + 9 * 12] and d.tolist() == [0, 24] and b.tolist() == [24, 12]
+    wide = torch.zeros(2, 2, dtype=torch.int64)
+    with pytest.raises(RuntimeError):
+        h.sub(idx, ts, ln, 0, wide[:, 0], d, b)
+    with pytest.raises(RuntimeError):
+        glibc.Int64Span.from_tensor(wide[:, 0])
+
+
+def test_streamed_checkpoint_round_trip_and_corruption(tmp_path):
+    # The table written as header + raw chunks + CRC-32 per chunk (several chunks here), read back
+    # by the same load() that reads the reference-style pickle; a flipped byte is caught.
+    from gear.dataset import SharedDataset
+    import libgear.core as glibc
+    spec = TableSpec.create(0, 1, 20, 6, [dict(shape=[5], dtype=torch.float32, name="x"),
+                                          dict(shape=[], dtype=torch.uint8, name="d")])
+    ds = SharedDataset.create(spec, create=True, key=9100)
+    rng = np.random.default_rng(1)
+    for i in range(6):
+        ds[i] = (float(i + 1), 20 - i, [torch.from_numpy(rng.standard_normal((20, 5)).astype(np.float32)),
+                                        torch.from_numpy(rng.integers(0, 255, 20).astype(np.uint8))])
+    img = np.array(ds._table._t.host_view(), copy=True)
+    glibc.TrajectoryTable.STREAM_CHUNK = 1000            # 2,520 bytes -> three chunks
+    try:
+        for streamed in (True, False):
+            path = tmp_path / f"ckpt_{int(streamed)}.pkl"
+            ds.checkpoint(path, streamed=streamed)
+            back = SharedDataset().load(path, key=9200 + int(streamed))
+            assert np.array_equal(back._table._t.host_view(), img)
+            assert torch.equal(back.weights, ds.weights) and torch.equal(back.timesteps, ds.timesteps)
+        raw = bytearray((tmp_path / "ckpt_1.pkl").read_bytes())
+        raw[len(raw) // 2] ^= 0x40
+        (tmp_path / "bad.pkl").write_bytes(bytes(raw))
+        with pytest.raises(RuntimeError, match="CRC-32"):
+            SharedDataset().load(tmp_path / "bad.pkl", key=9300)
+    finally:
+        glibc.TrajectoryTable.STREAM_CHUNK = 64 << 20

@@ -116,3 +116,46 @@ def test_weighted_draw_with_replacement_gives_duplicate_rows(O):
     for i in range(1, B):
         if idx[i] == idx[i - 1]:
             assert np.array_equal(got[i], got[i - 1])
+
+
+def test_checkpoint_of_an_hbm_table_above_2_gib_streams_both_ways(tmp_path):
+    # A table that exists in device memory only, larger than 2 GiB (where the reference's pickle
+    # stops: it holds the table as one bytes object and casts its size to int on load,
+    # src/storage/pybind.cc:178-204), is written chunk by chunk through a pinned bounce buffer
+    # and read back straight into HBM.  Compared chunk by chunk on the device.
+    import shutil
+    from gear_b200 import _native as N
+    from gear_b200 import core
+    gear.init(0)
+    T, cap = 1000, 550                                   # 550 x 1000 x 4100 B = 2.255 GB > 2 GiB
+    need = cap * T * 4100
+    if shutil.disk_usage(tmp_path).free < need + (1 << 30):
+        pytest.skip("not enough room for a 2.3 GB checkpoint in the temporary directory")
+    spec = TableSpec.create(0, 1, T, cap, [dict(shape=[1024], dtype=torch.int32, name="obs"),
+                                           dict(shape=[], dtype=torch.float32, name="rew")])
+    ds = SharedDataset.create(spec, create=True, key=7300, residency="hbm")
+    t = ds._table._t
+    assert t.nbytes == need > (1 << 31) and not t.host_ptr
+    core.fill_ptr(t.device_ptr, t.nbytes // 4, N.FILL_U32, seed=0x5EED)
+    ds.weights[:] = torch.arange(cap, dtype=torch.float32)
+    ds.timesteps[:] = T
+    path = tmp_path / "big.ckpt"
+    ds.checkpoint(path)                                  # HBM only: streamed by default
+    assert path.stat().st_size > need
+    back = SharedDataset().load(path, key=7301)          # lands where it was: HBM only
+    tb = back._table._t
+    assert tb.nbytes == need and not tb.host_ptr and tb.device_ptr and tb.device_ptr != t.device_ptr
+    a = core.device_view(t.device_ptr, need // 8, torch.int64)
+    b = core.device_view(tb.device_ptr, need // 8, torch.int64)
+    chunk = (64 << 20) // 8
+    for off in range(0, need // 8, chunk):
+        x, y = a[off:off + chunk], b[off:off + chunk]
+        assert int(x.sum()) == int(y.sum()) and torch.equal(x[::4097], y[::4097]), off
+    assert torch.equal(a, b)
+    assert torch.equal(back.weights, ds.weights)
+    # and the loader's gather works on the reloaded table
+    mpu = ModelParallelismUnit(device=torch.device("cuda:0"), dp_rank=0, dp_world_size=1)
+    loader = OfflineLoader(back, 8, mpu, "Uniform", [dict(name="obs", offset=0, length=4, pad="tail")])
+    tss, data = next(loader)
+    torch.cuda.synchronize()
+    assert list(data[0].shape) == [8, 4, 1024]

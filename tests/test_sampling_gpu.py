@@ -424,3 +424,34 @@ def test_draw_follows_the_priorities_in_distribution(O):
     assert two < limit, (two, limit)
     uni = float((((np.full(int(m.sum()), draws / m.sum()) - draws * pr[m]) ** 2) / (draws * pr[m])).sum())
     assert uni > 100 * limit      # the statistic does tell a wrong law from the right one
+
+
+def test_large_table_level1_falls_back_to_the_in_order_sum(O):
+    # Above 1024 partitions level 1 is a launch of its own (a cluster of eight CTAs summing in
+    # integer arithmetic).  Aggregates ~2^60 apart make float64 sums round: it must notice, redo
+    # the sum strictly in order (the definition, which the oracle computes) and say so; a
+    # well-behaved table right after it on the same sampler must come out exact again, no flag.
+    n = 1300 * 4096 + 321
+    p = np.full(n, 1.234e-3, np.float32)
+    p[::8192] = 3e18
+    p[4096 * 700 + 9] = 7.7e5
+    ocdf, ol1, total, _ = O.scan(p)
+    s = core.PrioritySampler(n)
+    dp = dev(p)
+    for store in (False, True, False):
+        s.scan(dp, store=store)
+        tot, st = s.result()
+        assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == total
+        assert st[0] & N.ST_L1_RESUMMED
+        if store:
+            assert np.array_equal(s.cdf.cpu().numpy(), ocdf)
+    s.clear_status()
+    q = O.synth_lognormal(350, 0, n)
+    q[: 4096 * 130] = 0.0                       # a whole superblock (and a bit) without mass
+    s.scan(dev(q), store=False)
+    tot, st = s.result()
+    _, ql1, qtotal, _ = O.scan(q)
+    assert np.array_equal(s.l1.cpu().numpy(), ql1) and tot == qtotal and st[0] == 0
+    # and through the entry point with caller-provided scratch, twice on one scratch block
+    cdf, l1, status = core.scan(dev(q))
+    assert np.array_equal(l1.cpu().numpy(), ql1) and status.cpu().tolist()[0] == 0
