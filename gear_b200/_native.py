@@ -140,6 +140,24 @@ _SIGS = {
     "gearb_comm_allreduce_sum": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "gearb_comm_allgather": (C.c_int, [vp, vp, vp, i64, vp]),
     "gearb_comm_alltoallv": (C.c_int, [vp, C.c_int, C.POINTER(vp), pi64, pi64, C.POINTER(vp), pi64, pi64, vp]),
+    "gearb_ingest_server_create": (C.c_int, [C.c_int, C.c_int, i64, i64, C.POINTER(vp)]),
+    "gearb_ingest_server_destroy": (C.c_int, [vp]),
+    "gearb_ingest_server_scan": (C.c_int, [vp, vp, vp, vp, i64, pi64, vp, vp, vp, i64, pi64]),
+    "gearb_ingest_server_update": (C.c_int, [vp, vp, vp, vp, i64]),
+    "gearb_ingest_server_callback": (C.c_int, [vp, vp, i64]),
+    "gearb_ingest_server_weights": (vp, [vp]),
+    "gearb_ingest_server_timesteps": (vp, [vp]),
+    "gearb_ingest_server_free_count": (i64, [vp]),
+    "gearb_ingest_server_get_state": (i64, [vp, vp, i64]),
+    "gearb_ingest_server_set_state": (C.c_int, [vp, vp, i64]),
+    "gearb_ingest_client_create": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(vp)]),
+    "gearb_ingest_client_destroy": (C.c_int, [vp]),
+    "gearb_ingest_client_acquire": (C.c_int, [vp, i64, pi64]),
+    "gearb_ingest_client_wait": (C.c_int, [vp, i64]),
+    "gearb_ingest_client_release": (C.c_int, [vp]),
+    "gearb_ingest_client_step": (i64, [vp]),
+    "gearb_ingest_client_writeback": (i64, [vp, C.c_int, C.c_int, f64]),
+    "gearb_ingest_client_status": (C.c_int, [vp, pi64, C.POINTER(f64)]),
     "gearb_fill": (C.c_int, [vp, i64, C.c_int, u64, u64, f64, f64, vp]),
 }
 

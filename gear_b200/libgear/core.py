@@ -615,3 +615,145 @@ def sum(val_tensor: torch.Tensor, sum_tensor: torch.Tensor, stride: int = 1) -> 
     """core.sum(vals, out, stride) (one_dim_sum.cu:84-99): the total in a fixed order."""
     _, l1, _ = _c.scan(val_tensor)
     sum_tensor.view(-1)[:1].copy_(l1[-1:].to(sum_tensor.dtype))
+
+
+# --------------------------------------------------------------------------- #
+# online path: index server / client (src/index/pybind.cc:53-291)
+# --------------------------------------------------------------------------- #
+class _InferenceRequests:
+    """InferenceRequestArray (include/index/request.h:19-35): count, srcs, idxs, tss."""
+
+    def __init__(self, capacity: int):
+        self.capacity, self.count = int(capacity), 0
+        self.srcs = np.zeros(capacity, np.int32)
+        self.idxs = np.zeros(capacity, np.int64)
+        self.tss = np.zeros(capacity, np.int64)
+
+
+class _WeightUpdates:
+    """WeightUpdateRequestArray (include/index/request.h:37-55): the updates recorded since the
+    last continuous() call, one per index."""
+
+    def __init__(self, capacity: int):
+        self.capacity, self.count = int(capacity), 0
+        self.timesteps = np.zeros(capacity, np.int64)
+        self.weights = np.zeros(capacity, np.float32)
+        self._list = []
+
+    def update(self, index: int, timestep: int, weight: float) -> None:
+        if index not in self._list:
+            self._list.append(int(index))
+            self.count += 1
+        self.timesteps[index] = timestep
+        self.weights[index] = weight
+
+    def continuous(self, idxs, weights) -> int:
+        """request.cc:56-75: idxs[i] = index, idxs[capacity + i] = timestep, weights[i]; clears the list."""
+        n = self.count
+        idxs, weights = _i64_out(idxs), (weights._a if isinstance(weights, _Span) else weights.numpy())
+        if len(idxs) < 2 * n or len(weights) < n:
+            raise RuntimeError("Index output array for continuous weight update array has less space than required")
+        for i, idx in enumerate(self._list):
+            idxs[i] = idx
+            idxs[self.capacity + i] = self.timesteps[idx]
+            weights[i] = self.weights[idx]
+        self._list, self.count = [], 0
+        return n
+
+
+class CachedRequest:
+    """CachedRequest (include/index/request.h:57-63)."""
+
+    def __init__(self, capacity: int):
+        self.capacity = int(capacity)
+        self.iarr = _InferenceRequests(capacity)
+        self.warr = _WeightUpdates(capacity)
+
+
+class SharedMemoryIndexServer:
+    """core.SharedMemoryIndexServer(key, num_clients, index_offset, capacity) (src/index/server.cc)."""
+
+    def __init__(self, key: int, num_clients: int, index_offset: int, capacity: int):
+        from ..ingest import IndexServer
+        self._s = IndexServer(key, num_clients, index_offset, capacity)
+
+    def connect(self) -> int:
+        return 0                                   # the segment is created with the object
+
+    def get_capacity(self) -> int:
+        return self._s.capacity
+
+    def get_num_clients(self) -> int:
+        return self._s.num_clients
+
+    def scan(self, cache: CachedRequest) -> None:
+        ni, nu = self._s.scan()
+        cache.iarr.count = 0
+        for k in range(ni):
+            c = cache.iarr.count
+            cache.iarr.srcs[c], cache.iarr.idxs[c], cache.iarr.tss[c] = self._s.infer_src[k], self._s.infer_idx[k], self._s.infer_ts[k]
+            cache.iarr.count = c + 1
+        off = self._s.index_offset
+        for k in range(nu):
+            cache.warr.update(int(self._s.upd_idx[k]) - off, int(self._s.upd_ts[k]), float(self._s.upd_w[k]))
+        self._pending = nu
+
+    def update(self, cache: CachedRequest) -> None:
+        self._s.update(getattr(self, "_pending", 0))
+        self._pending = 0
+
+    def callback(self, cache: CachedRequest) -> None:
+        self._s.callback(cache.iarr.srcs[: cache.iarr.count])
+        cache.iarr.count = 0
+
+    def get_weights(self) -> torch.Tensor:
+        return torch.from_numpy(self._s.weights)
+
+    def get_timesteps(self) -> torch.Tensor:
+        return torch.from_numpy(self._s.timesteps)
+
+    def __getstate__(self):
+        return (self._s.key, self._s.num_clients, self._s.index_offset, self._s.capacity, self._s.get_state())
+
+    def __setstate__(self, t):
+        self.__init__(t[0], t[1], t[2], t[3])
+        self._s.set_state(t[4])
+
+
+class SharedMemoryIndexClient:
+    """core.SharedMemoryIndexClient(key, client_rank, num_clients) (src/index/client.cc)."""
+
+    def __init__(self, key: int, client_rank: int, num_clients: int):
+        from ..ingest import IndexClient
+        self._c = IndexClient(key, client_rank, num_clients)
+        self.timeout_ms = 60_000
+
+    def connect(self) -> int:
+        return self._c.connect()
+
+    def acquire(self) -> None:
+        self._c.acquire(self.timeout_ms)
+
+    def wait(self) -> None:
+        self._c.wait(self.timeout_ms)
+
+    def release(self) -> None:
+        self._c.release()
+
+    def writeback(self, terminated: bool, alloc_new: bool, weight: float = 0.0) -> int:
+        return self._c.writeback(terminated, alloc_new, weight)
+
+    def step_inc(self) -> int:
+        return self._c.step_inc()
+
+    def get_index(self) -> int:
+        return self._c.get_index()
+
+    def get_timestep(self) -> int:
+        return self._c.get_timestep()
+
+    def get_num_clients(self) -> int:
+        return self._c.num_clients
+
+    def get_status_unsafe(self):
+        return self._c.status()

@@ -411,6 +411,46 @@ int gearb_sampler_pull_mailbox(gearb_sampler *s, gearb_handler *h, int world, in
                                const int32_t *columns, int ncols, void *const *dst, int zero_fill, int ring,
                                int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, void *stream);
 
+/* ======================= online ingestion =============================== */
+/* The hand-off between simulator processes that fill trajectories and the trainer that samples
+ * them: SharedMemoryIndexServer / SharedMemoryIndexClient (src/index/server.cc, src/index/client.cc),
+ * one 64-byte status slot per simulator in a System-V segment (include/index/sim_status.h:7-17)
+ * and a FIFO of free trajectory indices (include/circular_buffer.h).  Host code only; what a scan
+ * reports goes to the device through gearb_sampler_update.  Every wait takes a limit in
+ * milliseconds and comes back with GEARB_ERR_TIMEOUT when it runs out.                      */
+typedef struct gearb_ingest_server gearb_ingest_server;
+typedef struct gearb_ingest_client gearb_ingest_client;
+/* SharedMemoryIndexServer::SharedMemoryIndexServer + connect, server.cc:49-110. */
+int gearb_ingest_server_create(int shm_key, int num_clients, int64_t index_offset, int64_t capacity,
+                               gearb_ingest_server **out);
+int gearb_ingest_server_destroy(gearb_ingest_server *s);
+/* SharedMemoryIndexServer::scan, server.cc:115-170.  infer_*: room for num_clients entries,
+ * upd_*: room for 2 * num_clients; an index appears once among the updates.               */
+int gearb_ingest_server_scan(gearb_ingest_server *s, int32_t *infer_src, int64_t *infer_idx, int64_t *infer_ts,
+                             int64_t infer_cap, int64_t *n_infer, int64_t *upd_idx, int64_t *upd_ts, float *upd_w,
+                             int64_t upd_cap, int64_t *n_upd);
+/* SharedMemoryIndexServer::update / callback, server.cc:172-188. */
+int gearb_ingest_server_update(gearb_ingest_server *s, const int64_t *upd_idx, const int64_t *upd_ts,
+                               const float *upd_w, int64_t n);
+int gearb_ingest_server_callback(gearb_ingest_server *s, const int32_t *srcs, int64_t n);
+/* get_weights / get_timesteps, server.cc:190-192; free entries of the FIFO. */
+float *gearb_ingest_server_weights(gearb_ingest_server *s);
+int64_t *gearb_ingest_server_timesteps(gearb_ingest_server *s);
+int64_t gearb_ingest_server_free_count(const gearb_ingest_server *s);
+/* get_state / set_state, server.cc:196-246, as one byte image; get with buf == NULL returns its size. */
+int64_t gearb_ingest_server_get_state(const gearb_ingest_server *s, void *buf, int64_t cap);
+int gearb_ingest_server_set_state(gearb_ingest_server *s, const void *buf, int64_t bytes);
+/* SharedMemoryIndexClient, src/index/client.cc:9-105.  create attaches the server's segment
+ * (GEARB_ERR_STATE while it does not exist).                                               */
+int gearb_ingest_client_create(int shm_key, int client_rank, int num_clients, gearb_ingest_client **out);
+int gearb_ingest_client_destroy(gearb_ingest_client *c);
+int gearb_ingest_client_acquire(gearb_ingest_client *c, int64_t timeout_ms, int64_t *tindex);
+int gearb_ingest_client_wait(gearb_ingest_client *c, int64_t timeout_ms);
+int gearb_ingest_client_release(gearb_ingest_client *c);
+int64_t gearb_ingest_client_step(gearb_ingest_client *c);
+int64_t gearb_ingest_client_writeback(gearb_ingest_client *c, int terminated, int alloc_new, double weight);
+int gearb_ingest_client_status(const gearb_ingest_client *c, int64_t *out7, double *weight);
+
 /* ======================= synthetic data ================================= */
 /* Device-side Philox4x32-10 fills for benchmark tables that are too large to
  * stage through the host.  kind selects the distribution.                   */

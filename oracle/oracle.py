@@ -105,7 +105,7 @@ def np_philox4x32(seed: int, stream: int, counters: np.ndarray) -> np.ndarray:
 
 
 # --------------------------------------------------------------------------- #
-# Synthetic data with the distributions BASELINE.json's configs name.
+# Synthetic data with the distributions of the benchmark configurations.
 # Float values come from numpy's libm here; the device fill kernels use CUDA's,
 # so host- and device-generated floats are NOT expected to match bit for bit --
 # parity tests either upload host data or read the device table back.
@@ -416,6 +416,80 @@ def plain_cumsum_search(prio: np.ndarray, u: np.ndarray, threads: int, scale: bo
 
 
 REF_LIB_PATH = HERE / "_ref" / "libgear_ref.so"
+
+
+class IngestModel:
+    """The online index protocol as a plain state machine, for small cases: the trainer's scan
+    (src/index/server.cc:115-170), update (172-177, applied per index), callback (179-188) and
+    the simulator's acquire / writeback (src/index/client.cc:30-91) over one status record per
+    simulator (include/index/sim_status.h:7-17) and a FIFO of free indices
+    (include/circular_buffer.h).  Single-threaded: a test drives both sides in a fixed order,
+    so ownership is a plain field."""
+
+    def __init__(self, num_clients: int, index_offset: int, capacity: int):
+        self.m, self.off, self.cap = num_clients, index_offset, capacity
+        self.slots = [dict(owner=0, terminated=0, alloc=0, valid=0, tindex=0, timestep=0, weight=0.0)
+                      for _ in range(num_clients)]
+        self.free = [index_offset + i for i in range(capacity)]
+        self.weights = np.zeros(capacity, np.float32)
+        self.timesteps = np.zeros(capacity, np.int64)
+        self.cl = [dict(fly=False, tindex=0, timestep=0) for _ in range(num_clients)]
+
+    # ---- trainer
+    def scan(self):
+        infer, upd = [], {}
+        for i, q in enumerate(self.slots):
+            if q["owner"] != 1:
+                continue
+            if not q["terminated"]:
+                if q["valid"]:
+                    infer.append((i, q["tindex"], q["timestep"]))
+                continue
+            if q["valid"]:
+                self.free.append(q["tindex"])
+                q["valid"] = 0
+                upd[q["tindex"]] = (q["timestep"], np.float32(q["weight"]))
+            if q["alloc"]:
+                if self.free:
+                    q["tindex"] = self.free.pop(0)
+                    q.update(alloc=0, terminated=0, timestep=0, weight=0.0, valid=1, owner=0)
+                    upd[q["tindex"]] = (0, np.float32(0.0))
+            else:
+                q["owner"] = 0
+        return infer, [(k, v[0], v[1]) for k, v in upd.items()]      # dicts keep first-insertion order
+
+    def update(self, upd):
+        for idx, ts, w in upd:
+            self.weights[idx - self.off] = w
+            self.timesteps[idx - self.off] = ts
+
+    def callback(self, srcs):
+        for i in srcs:
+            self.slots[i]["owner"] = 0
+
+    # ---- simulator i; each returns False where the real client would have to wait
+    def acquire(self, i):
+        q, c = self.slots[i], self.cl[i]
+        if q["owner"] != 0:
+            return False
+        if not q["valid"]:
+            q.update(terminated=1, alloc=1, owner=1)
+            return False
+        c.update(fly=True, tindex=q["tindex"], timestep=0)
+        return True
+
+    def step(self, i):
+        c = self.cl[i]
+        c["timestep"] += 1
+        return c["timestep"] - 1 if c["fly"] else 0
+
+    def writeback(self, i, terminated, alloc_new, weight):
+        q, c = self.slots[i], self.cl[i]
+        if not c["fly"]:
+            return 0
+        q.update(terminated=int(terminated), timestep=c["timestep"], alloc=int(alloc_new), weight=float(weight), owner=1)
+        c["fly"] = not terminated
+        return c["timestep"]
 
 
 class Reference:

@@ -44,7 +44,7 @@ def run_gather(h, cols, idx, ts, ln, zero_fill, fill_byte=0):
 
 @pytest.mark.parametrize("residency", [N.RES_HBM, N.RES_HOST, N.RES_HOST | N.RES_HBM])
 def test_config1_shapes_all_columns(O, residency):
-    # BASELINE config 1 shapes (obs f32[17], act f32[6], rew f32, done u8), fewer trajectories.
+    # config 1 shapes (obs f32[17], act f32[6], rew f32, done u8), fewer trajectories.
     rows, T, cap = [68, 24, 4, 1], 1000, 64
     t, img = make_table(O, rows, T, cap, residency)
     h = core.StorageHandler(t)

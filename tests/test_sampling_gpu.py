@@ -28,7 +28,7 @@ def test_scan_bit_exact(O, n):
 
 
 def test_scan_config2_and_search_bit_exact(O):
-    # BASELINE config 2: 1,048,576 LogNormal(0,1) priorities, 4096 variates U[0,total).
+    # config 2: 1,048,576 LogNormal(0,1) priorities, 4096 variates U[0,total).
     n, b = 1 << 20, 4096
     p = O.synth_lognormal(0x6EA20102, 0, n)
     ocdf, ol1, total, _ = O.scan(p)
