@@ -567,7 +567,10 @@ def run_index_only(args):
     u = torch.from_numpy(hu).to(dev)
     out = torch.empty(B, dtype=torch.int64, device=dev)
     K, W = args.steps, max(args.warmup, 3)
-    ms = _event_loop(torch, lambda i: (s.scan(prio), s.search(u, scale=False, out=out)), K, W)
+    ms = _event_loop(torch, lambda i: s.scan_search(prio, u, scale=False, out=out), K, W)
+    got_fused = out.cpu().numpy().copy()
+    out.zero_()
+    ms_two = _event_loop(torch, lambda i: (s.scan(prio), s.search(u, scale=False, out=out)), K, W)
     ms_scan = _event_loop(torch, lambda i: s.scan(prio), K, W)
     ms_search = _event_loop(torch, lambda i: s.search(u, scale=False, out=out), K, W)
     # end to end: the variates start in pinned host memory and the indices end there, every step
@@ -577,8 +580,7 @@ def run_index_only(args):
 
     def e2e_step(i):
         u.copy_(u_host, non_blocking=True)
-        s.scan(prio)
-        s.search(u, scale=False, out=out)
+        s.scan_search(prio, u, scale=False, out=out)
         out_host.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -611,25 +613,30 @@ def run_index_only(args):
         "vs_baseline": None, "dtype": "f32 scan / f64 level-1", "data": "synthetic (seeded Philox4x32-10)",
         "config": {"workload": C2["name"], "priorities": n, "batch": B,
                    "l2": "8 MB working set: L2-resident by construction of this configuration"},
-        "kernel_ms": {"scan (stores the table, builds level 1 in its last CTA)": ms_scan, "search": ms_search},
+        "kernel_ms": {"scan + search in one cooperative launch (the step)": ms,
+                      "the same as two launches (scan, then search behind it)": ms_two,
+                      "scan alone (stores the table, builds level 1 in its last CTA)": ms_scan, "search alone": ms_search},
         "roofline": {"kernel": "scan_kernel<true>", "bound": "hbm", "achieved": scan_bytes / (ms_scan * 1e-3) / 1e9, "peak": peak,
                      "unit": "GB/s", "frac": scan_bytes / (ms_scan * 1e-3) / 1e9 / peak, "traffic": None,
                      "peak_source": peak_src, "avg_launch_ms": ms_scan, "algorithmic_bytes": scan_bytes,
                      "note": "256 partitions on 148 SMs, the data in L2: a launch- and latency-bound step, for which the "
                              "HBM fraction says little; see latency_model"},
         "latency_model": {"launch_and_drain_us_per_kernel": 2.5, "dependent_round_trip_us": 0.6,
-                          "scan_chain": "ticket + 16 KiB copy + tree + aggregate + done counter + level 1 by the last CTA: 5 trips",
-                          "search_chain": "variate + level-1 rounds + level-2 rounds: 6 trips",
-                          "model_us": 2 * 2.5 + 11 * 0.6, "measured_us": ms * 1e3},
+                          "chain": "partition load, tree (two barriers), store + fence, count in, wait for all CTAs, "
+                                   "aggregates into shared memory, level 1 there, variate, last entry of the partition, "
+                                   "two level-2 rounds, index out: 9 trips",
+                          "model_us": 2.5 + 9 * 0.6 + 1.5, "measured_us": ms * 1e3,
+                          "note": "1.5 us stands for the arithmetic of the tree and of level 1 between the trips"},
         "cpu_baseline": {"value": B / cpu_s, "unit": "indices/s", "cores": cores, "kind": "port",
                          "draw_ms": {"plain_cumsum_upper_bound": plain_s * 1e3, "two_level_tree_port": tree_s * 1e3},
                          "sample": f"{reps} full steps of each draw (1,048,576 priorities + 4096 searches); the faster counts"},
         "e2e": {"value": B / e2e_s, "unit": "indices/s", "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 8 * B,
                 "ms_per_step": e2e_s * 1e3, "steps": Ke},
-        "parity": {"index_mismatches_vs_oracle": int((out.cpu().numpy() != want).sum()),
+        "parity": {"index_mismatches_vs_oracle": int((got_fused != want).sum()),
+                   "index_mismatches_vs_oracle_two_launches": int((out.cpu().numpy() != want).sum()),
                    "variates_within_1ulp_of_boundary": int(near.sum()),
                    "flips_vs_float64_running_sum": int((want != f64).sum())},
-        "gpu_launches": 2 * K}
+        "gpu_launches": K}
 
 
 def run_zero_copy(args):

@@ -105,6 +105,7 @@ _SIGS = {
     "gearb_sampler_scan_level1": (C.c_int, [vp, vp]),
     "gearb_sampler_update": (C.c_int, [vp, vp, vp, vp, i64, vp]),
     "gearb_sampler_search": (C.c_int, [vp, vp, i64, C.c_int, vp, vp]),
+    "gearb_sampler_scan_search": (C.c_int, [vp, vp, vp, i64, C.c_int, vp, vp]),
     "gearb_sampler_sample_gather": (C.c_int, [vp, vp, vp, i64, C.c_int, vp, i64, pi32, C.c_int, C.POINTER(vp),
                                               C.c_int, vp, vp, vp, vp, vp]),
     "gearb_sampler_sample_gather_affine": (C.c_int, [vp, vp, vp, i64, f64, f64, vp, i64, pi32, C.c_int,

@@ -406,6 +406,20 @@ class PrioritySampler:
              N.SEARCH_SCALE if scale else 0, _ptr(out), _stream(stream))
         return out
 
+    def scan_search(self, priorities: torch.Tensor, variates: torch.Tensor, scale: bool = False,
+                    out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """scan(priorities) followed by search(variates), as one launch where the table is small enough."""
+        if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
+            raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
+        if variates.dtype != torch.float64 or not variates.is_cuda or not variates.is_contiguous():
+            raise GearError(N.ERR_INVALID, "variates must be a contiguous float64 CUDA tensor")
+        if out is None:
+            out = torch.empty(variates.numel(), dtype=torch.int64, device=variates.device)
+        self._lazy_source = None
+        call("gearb_sampler_scan_search", self._h, _ptr(priorities), _ptr(variates), variates.numel(),
+             N.SEARCH_SCALE if scale else 0, _ptr(out), _stream(stream))
+        return out
+
     def sample_gather(self, handler: "StorageHandler", variates: torch.Tensor, columns: Sequence[int],
                       dsts: Sequence[torch.Tensor], scale: bool = True,
                       lengths: Optional[torch.Tensor] = None, index_offset: int = 0,

@@ -730,6 +730,24 @@ int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) 
                      as_stream(stream), true, false, s->blk[slot]);
 }
 
+int gearb_sampler_scan_search(gearb_sampler *s, const float *priorities, const double *variates, int64_t b,
+                              int flags, int64_t *out_index, void *stream) {
+  TraceRange trace("gearb:scan_search");
+  GEARB_REQUIRE(s, "sampler_scan_search: null sampler");
+  s->lazy_prio = nullptr;
+  const int slot = s->take_slot();
+  int fused = 0;
+  int rc = launch_scan_search(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status,
+                              s->blk[slot], variates, b, flags, out_index, as_stream(stream), &fused);
+  if (rc != GEARB_OK) return rc;
+  s->scan_unconsumed = false;  // in either form the draw comes after the scan
+  if (fused) return GEARB_OK;
+  rc = launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
+                   as_stream(stream), true, false, s->blk[slot]);
+  if (rc != GEARB_OK) return rc;
+  return launch_search(s->cdf, s->l1s[slot], s->n, variates, b, flags, out_index, s->status, as_stream(stream));
+}
+
 int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx, const float *values, int64_t m,
                          void *stream) {
   TraceRange trace("gearb:update");

@@ -48,7 +48,7 @@ int sm_count();
 // Runs `setup` the first time it is called with `slot` on the current device (function
 // attributes and occupancy figures are per device) and hands back the int it produced then.
 // Thread-safe; slots are small integers, one per call site.
-enum { kOnceScan = 0, kOnceLevel1 = 1, kOnceSampleGather = 2, kOnceSmallScan = 3, kOnceSlots = 8 };
+enum { kOnceScan = 0, kOnceLevel1 = 1, kOnceSampleGather = 2, kOnceSmallScan = 3, kOnceScanSearch = 4, kOnceSlots = 8 };
 int per_device_once(int slot, int (*setup)(int *value), int *value);
 
 // ---- scan ------------------------------------------------------------------
@@ -81,6 +81,11 @@ int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_
 int64_t update_scratch_bytes(int64_t n);
 int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, float *blkw, ScanHeader *hdr,
                   void *upd, const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream);
+// Scan (level-2 table stored, level 1, block totals) and draw in one cooperative launch; *fused = 0
+// and nothing launched when the table has more partitions than CTAs can be resident at once.
+int launch_scan_search(const float *prio, int64_t n, float *cdf, double *l1, void *scratch, int64_t scratch_bytes,
+                       int32_t *status, float *blkw, const double *u, int64_t b, int flags, int64_t *out,
+                       cudaStream_t stream, int *fused);
 int launch_search(const float *cdf, const double *l1, int64_t n, const double *u, int64_t b,
                   int flags, int64_t *out, int32_t *status, cudaStream_t stream);
 int launch_uniform(int64_t n, const double *u01, int64_t b, int64_t *out, cudaStream_t stream);

@@ -63,12 +63,15 @@ __device__ __forceinline__ void note_exponent(unsigned b, unsigned &emin, unsign
 }
 // Strictly in-order float64 sum by one thread: the definition itself, for the rare inputs the
 // integer route cannot take.
-__device__ inline void in_order(const float *agg, unsigned nparts, double *l1, int32_t *status) {
+__device__ inline void in_order(const float *agg, unsigned nparts, double *l1, int32_t *status,
+                                double *mirror = nullptr) {
   double s = 0.0;
-  __stcg(&l1[0], 0.0);
+  if (l1) __stcg(&l1[0], 0.0);
+  if (mirror) mirror[0] = 0.0;
   for (unsigned q = 0; q < nparts; ++q) {
     s = __dadd_rn(s, static_cast<double>(__ldcg(agg + q)));
-    __stcg(&l1[q + 1], s);
+    if (l1) __stcg(&l1[q + 1], s);
+    if (mirror) mirror[q + 1] = s;
   }
   atomicOr(reinterpret_cast<unsigned *>(status), GEARB_ST_L1_RESUMMED);
 }
@@ -92,7 +95,11 @@ __device__ __forceinline__ void load_tile(const float *agg, unsigned first, unsi
 // kTile floats of shared memory, 16-byte aligned, that nothing else uses meanwhile.  Each
 // thread works on a contiguous run of the tile; the run length is odd, which spreads the
 // threads' accesses over all banks.
-__device__ inline void build(const float *agg, unsigned nparts, double *l1, int32_t *status, float *tile) {
+// l1 (global memory) and mirror (nparts + 1 doubles of this CTA's shared memory) each receive
+// the result when not null: a kernel whose CTAs all need level 1 lets every CTA build its own
+// copy in shared memory and one of them write the global one.
+__device__ inline void build(const float *agg, unsigned nparts, double *l1, int32_t *status, float *tile,
+                             double *mirror = nullptr) {
   __shared__ unsigned long long warp_tot[32];
   __shared__ unsigned warp_emin[32], warp_emax[32];
   __shared__ unsigned long long tile_total;
@@ -172,16 +179,21 @@ __device__ inline void build(const float *agg, unsigned nparts, double *l1, int3
         const unsigned b = __float_as_uint(tile[q]);
         if (b << 1) acc += scaled(b, emin);
         const unsigned long long dbits = double_bits(acc, emin, inexact);
-        __stcg(reinterpret_cast<unsigned long long *>(l1) + first + q + 1, dbits);
+        if (l1) __stcg(reinterpret_cast<unsigned long long *>(l1) + first + q + 1, dbits);
+        if (mirror) mirror[first + q + 1] = __longlong_as_double(static_cast<long long>(dbits));
       }
       carry += tile_total;
       __syncthreads();  // warp_tot and the tile are reused
     }
-    if (tid == 0) __stcg(&l1[0], 0.0);
+    if (tid == 0) {
+      if (l1) __stcg(&l1[0], 0.0);
+      if (mirror) mirror[0] = 0.0;
+    }
   }
   if (wide || inexact) atomicOr(&fallback, 1);
   __syncthreads();
-  if (fallback && tid == 0) in_order(agg, nparts, l1, status);
+  if (fallback && tid == 0) in_order(agg, nparts, l1, status, mirror);
+  if (mirror) __syncthreads();
 }
 
 }  // namespace level1

@@ -37,6 +37,7 @@
 
 #include "common.h"
 #include "level1.cuh"
+#include "warp_search.cuh"
 #include "scan_tree.cuh"
 
 namespace gearb {
@@ -413,15 +414,12 @@ __global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const Sc
 constexpr int kSmallParts = 1024;
 constexpr int kSmallThreads = kComputeThreads;
 
+// One partition by one CTA of kSmallThreads threads: warp w scans block w.  On return (after a
+// barrier) wt[] holds the eight block totals; the level-2 entries are stored when kStore.
 template <bool kStore>
-__global__ void __launch_bounds__(kSmallThreads) small_scan_kernel(const ScanArgs a) {
-  __shared__ __align__(16) float xs_all[kComputeWarps][128];
-  __shared__ float wt[kComputeWarps], wm[kComputeWarps];
-  __shared__ __align__(16) float tile[kSmallParts];
-  __shared__ int is_last;
+__device__ __forceinline__ void small_partition(const ScanArgs &a, int part, float (*xs_all)[128], float *wt,
+                                                float *wm) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int part = blockIdx.x;
   const int64_t base = static_cast<int64_t>(part) * kPart;
   const int64_t e0 = base + warp * tree::kBlockValues;
   float *xs = xs_all[warp];
@@ -476,6 +474,18 @@ __global__ void __launch_bounds__(kSmallThreads) small_scan_kernel(const ScanArg
   }
   if (__any_sync(kFull, (bits >> 31) != 0) && lane == 0)
     atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_BAD_PRIORITY);
+}
+
+template <bool kStore>
+__global__ void __launch_bounds__(kSmallThreads) small_scan_kernel(const ScanArgs a) {
+  __shared__ __align__(16) float xs_all[kComputeWarps][128];
+  __shared__ float wt[kComputeWarps], wm[kComputeWarps];
+  __shared__ __align__(16) float tile[kSmallParts];
+  __shared__ int is_last;
+  const int tid = threadIdx.x;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int part = blockIdx.x;
+  small_partition<kStore>(a, part, xs_all, wt, wm);
   if (tid == 0) {
     float X = 0.f;
 #pragma unroll
@@ -495,6 +505,87 @@ __global__ void __launch_bounds__(kSmallThreads) small_scan_kernel(const ScanArg
   if (tid == 0) {
     a.hdr->done = 0u;
     __threadfence();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Scan and draw in ONE launch, for tables small enough that every partition's CTA is resident at
+// once (a cooperative launch guarantees that, and refuses the launch otherwise): the place of
+// "prefix sum, then torch.multinomial" (gear/sampler/global_sampler.py:154-176) when the table
+// changes before every draw.  Two launches cost a second launch latency and a second ramp-up on
+// top of a chain that is only a few memory round trips long; here the chain is
+//   load partition -> tree -> store -> count in -> [all CTAs counted] -> level 1, built by every
+//   CTA into its own shared memory -> level-1 search there -> two rounds into the level-2 table.
+// The wait in the middle has an iteration limit; a CTA that runs into it raises
+// GEARB_ST_SCAN_ABORTED, skips its draws and leaves.  Results are the bits of the two launches.
+struct DrawArgs {
+  const double *u;
+  int64_t *out;
+  int64_t b;
+  int flags;
+};
+
+__global__ void __launch_bounds__(kSmallThreads) small_scan_search_kernel(const ScanArgs a, const DrawArgs d) {
+  __shared__ __align__(16) float xs_all[kComputeWarps][128];
+  __shared__ float wt[kComputeWarps], wm[kComputeWarps];
+  __shared__ __align__(16) float tile[kSmallParts];
+  __shared__ __align__(16) double l1s[kSmallParts + 1];
+  __shared__ int gave_up;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int part = blockIdx.x;
+  small_partition<true>(a, part, xs_all, wt, wm);
+  __syncthreads();  // every thread's level-2 stores before thread 0's fence and count
+  if (tid == 0) {
+    float X = 0.f;
+#pragma unroll
+    for (int w = 0; w < kComputeWarps; ++w) X = __fadd_rn(X, wt[w]);
+    a.aggw[part] = X;
+    hand_over_blocks(a, part, wt);
+    __threadfence();
+    atomicAdd(&a.hdr->done, 1u);
+    unsigned seen = 0, spins = 0;
+    do {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&a.hdr->done) : "memory");
+    } while (seen < gridDim.x && ++spins < (1u << 22));
+    gave_up = seen < gridDim.x;
+    if (gave_up) atomicOr(reinterpret_cast<unsigned *>(a.status), GEARB_ST_SCAN_ABORTED);
+    // The counters are cleared by whoever leaves the wait last: nobody reads `done` after that.
+    if (atomicAdd(&a.hdr->ticket, 1u) == gridDim.x - 1) {
+      a.hdr->done = 0u;
+      a.hdr->ticket = 0u;
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  if (gave_up) return;
+  level1::build(a.aggw, a.nparts, part == 0 ? a.l1 : nullptr, a.status, tile, l1s);
+
+  const double total = l1s[a.nparts];
+  for (int64_t w = static_cast<int64_t>(part) * kComputeWarps + warp; w < d.b;
+       w += static_cast<int64_t>(gridDim.x) * kComputeWarps) {
+    if (!(total > 0.0)) {  // no selectable entry at all: defined as the last index
+      if (lane == 0) d.out[w] = a.n - 1;
+      continue;
+    }
+    double v = __ldg(d.u + w);
+    if (d.flags & GEARB_SEARCH_SCALE) v = __dmul_rn(v, total);
+    if (!(v >= 0.0)) v = 0.0;
+    if (!(v < total)) v = __longlong_as_double(__double_as_longlong(total) - 1);
+    const int64_t p = warp_upper_bound<double>(l1s + 1, 0, static_cast<int64_t>(a.nparts) - 1, v, lane, LoadPlain());
+    const int64_t base = p * kPart;
+    const int64_t valid = (a.n - base < kPart) ? (a.n - base) : kPart;
+    float r = __double2float_rn(__dsub_rn(v, l1s[p]));
+    const float last = __ldcg(a.cdf + base + valid - 1);
+    if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
+    const int64_t j = warp_upper_bound<float>(a.cdf + base, 0, valid - 1, r, lane, LoadL2());
+    if (lane == 0) {
+      const int64_t flat = base + j;
+      d.out[w] = flat;
+      const float hi_b = __ldcg(a.cdf + flat);
+      bool near = __uint_as_float(__float_as_uint(r) + 1u) >= hi_b;
+      if (j > 0 && r == __ldcg(a.cdf + flat - 1)) near = true;
+      if (near) atomicAdd(a.status + 1, 1);
+    }
   }
 }
 
@@ -599,6 +690,61 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
   return (a.inline_level1 || !level1) ? GEARB_OK
                                        : launch_level1(a.aggw, nparts, l1, nullptr, status, stream, a.hdr, true);
+}
+
+int launch_scan_search(const float *prio, int64_t n, float *cdf, double *l1, void *scratch, int64_t scratch_bytes,
+                       int32_t *status, float *blkw, const double *u, int64_t b, int flags, int64_t *out,
+                       cudaStream_t stream, int *fused) {
+  GEARB_REQUIRE(n > 0 && b >= 0, "scan_search: n must be positive and b non-negative");
+  GEARB_REQUIRE(prio && cdf && l1 && scratch && status && fused && (b == 0 || (u && out)),
+                "scan_search: null pointer argument");
+  GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 && (reinterpret_cast<uintptr_t>(cdf) & 15) == 0,
+                "scan_search: priorities and cdf must be 16-byte aligned");
+  GEARB_REQUIRE((flags & ~GEARB_SEARCH_SCALE) == 0, "scan_search: unknown flag");
+  GEARB_REQUIRE(scratch_bytes >= scan_scratch_bytes(n), "scan_search: scratch too small");
+  const int64_t nparts = (n + kPart - 1) / kPart;
+  int resident = 0;  // CTAs of the fused kernel that one device holds at once
+  int rc = per_device_once(kOnceScanSearch, [](int *value) -> int {
+    int per_sm = 0, coop = 0, dev = 0;
+    GEARB_CUDA(cudaGetDevice(&dev));
+    GEARB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+    GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, small_scan_search_kernel, kSmallThreads, 0));
+    *value = coop ? per_sm * sm_count() : 0;
+    return GEARB_OK;
+  }, &resident);
+  if (rc != GEARB_OK) return rc;
+  *fused = nparts <= kSmallParts && nparts <= resident;
+  if (!*fused) return GEARB_OK;
+  char *sc = static_cast<char *>(scratch);
+  ScanArgs a;
+  a.prio = prio;
+  a.cdf = cdf;
+  a.l1 = l1;
+  a.hdr = reinterpret_cast<ScanHeader *>(sc);
+  a.aggw = reinterpret_cast<float *>(sc + sizeof(ScanHeader));
+  a.blkw = blkw;
+  a.status = status;
+  a.n = n;
+  a.nparts = static_cast<unsigned>(nparts);
+  a.group = a.nbig = a.ngroups = 0;
+  a.inline_level1 = 1;
+  DrawArgs d;
+  d.u = u;
+  d.out = out;
+  d.b = b;
+  d.flags = flags;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(nparts));
+  cfg.blockDim = dim3(kSmallThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident together, or the launch fails
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  GEARB_CUDA(cudaLaunchKernelEx(&cfg, small_scan_search_kernel, a, d));
+  return GEARB_OK;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -12,49 +12,13 @@
 // lane, all in flight together), so a draw costs about four dependent memory round trips
 // instead of ~27: level 1 of a table of up to 256 partitions in one, level 2 in two.
 #include "common.h"
+#include "warp_search.cuh"
 
 namespace gearb {
 namespace {
 
 constexpr unsigned kFull = 0xffffffffu;
 constexpr int kThreads = 256;
-
-// First q in [lo, hi] with a[q] > v, given a[hi] > v.  Warp-cooperative.  Slot s of a round
-// probes lo + (s+1)*step - 1 (clamped to hi); lane l takes slots l, l+32, ..., so that the
-// probes of a round with step 1 are consecutive across the lanes.
-template <typename T>
-__device__ __forceinline__ int64_t warp_upper_bound(const T *a, int64_t lo, int64_t hi, T v,
-                                                    int lane) {
-  constexpr int kPer = 8;  // probes per lane and round
-  for (;;) {
-    const int64_t width = hi - lo + 1;
-    if (width <= 32) {  // one probe per lane finishes it
-      int64_t q = lo + lane;
-      if (q > hi) q = hi;
-      const unsigned m = __ballot_sync(kFull, __ldg(a + q) > v);  // never 0: a[hi] > v
-      return lo + (__ffs(m) - 1);
-    }
-    const int64_t step = (width + 32 * kPer - 1) / (32 * kPer);
-    T x[kPer];
-#pragma unroll
-    for (int k = 0; k < kPer; ++k) {
-      int64_t q = lo + (static_cast<int64_t>(k * 32 + lane) + 1) * step - 1;
-      if (q > hi) q = hi;
-      x[k] = __ldg(a + q);
-    }
-    int first = 32 * kPer - 1;  // the last slot probes hi, whose entry is greater
-#pragma unroll
-    for (int k = kPer - 1; k >= 0; --k) {
-      const unsigned m = __ballot_sync(kFull, x[k] > v);
-      if (m) first = k * 32 + __ffs(m) - 1;
-    }
-    int64_t qf = lo + (static_cast<int64_t>(first) + 1) * step - 1;
-    if (qf > hi) qf = hi;
-    if (first > 0) lo = lo + static_cast<int64_t>(first) * step;  // one past the previous slot's probe
-    hi = qf;
-    if (step == 1 || lo >= hi) return hi;
-  }
-}
 
 struct SearchArgs {
   const float *cdf;
@@ -101,7 +65,7 @@ __global__ void __launch_bounds__(kThreads) search_kernel(const SearchArgs a) {
   if (!(v < total)) v = __longlong_as_double(__double_as_longlong(total) - 1);  // next below total
 
   // level 1: partition p with l1[p] <= v < l1[p+1]
-  const int64_t p = warp_upper_bound<double>(a.l1 + 1, 0, a.nparts - 1, v, lane);
+  const int64_t p = warp_upper_bound<double>(a.l1 + 1, 0, a.nparts - 1, v, lane, LoadReadOnly());
   const int64_t base = p * GEARB_PART;
   const int64_t valid = (a.n - base < GEARB_PART) ? (a.n - base) : GEARB_PART;
   float r = __double2float_rn(__dsub_rn(v, __ldg(a.l1 + p)));
@@ -109,7 +73,7 @@ __global__ void __launch_bounds__(kThreads) search_kernel(const SearchArgs a) {
   if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);  // next below last (> 0)
 
   // level 2: first entry of the partition greater than r
-  const int64_t j = warp_upper_bound<float>(a.cdf + base, 0, valid - 1, r, lane);
+  const int64_t j = warp_upper_bound<float>(a.cdf + base, 0, valid - 1, r, lane, LoadReadOnly());
   const int64_t flat = base + j;
 
   if (lane == 0) {

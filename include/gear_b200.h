@@ -246,6 +246,14 @@ int gearb_sampler_block_totals(const gearb_sampler *s, float **slot0, float **sl
 /* The level-1 table is kept twice in the same way (gearb_sampler_buffers returns the one of
  * the last scan): the addresses of both, for peers that map them.                          */
 int gearb_sampler_level1_buffers(const gearb_sampler *s, double **slot0, double **slot1);
+/* Scan, then draw, as one call: the prefix sum and the torch.multinomial call behind it
+ * (gear/sampler/global_sampler.py:154-176) for a table that changes before every draw.  Tables of
+ * up to 1024 partitions whose CTAs fit on the device together take ONE cooperative launch (the
+ * chain is a few memory round trips long; a second launch would double it); larger ones take the
+ * scan's and the search's launches.  Tables, status words and indices are those of
+ * gearb_sampler_scan followed by gearb_sampler_search, bit for bit.                          */
+int gearb_sampler_scan_search(gearb_sampler *s, const float *priorities, const double *variates, int64_t b,
+                              int flags, int64_t *out_index, void *stream);
 /* Incremental update after a gearb_sampler_scan of the same array: priorities[idx[i]] =
  * values[i] for i < m (idx, values: device arrays), then only the partitions that were touched
  * are rescanned and the partition offsets rebuilt.  The table afterwards is bit-identical to a

@@ -455,3 +455,66 @@ def test_large_table_level1_falls_back_to_the_in_order_sum(O):
     # and through the entry point with caller-provided scratch, twice on one scratch block
     cdf, l1, status = core.scan(dev(q))
     assert np.array_equal(l1.cpu().numpy(), ql1) and status.cpu().tolist()[0] == 0
+
+
+@pytest.mark.parametrize("n", [1, 4095, 3 * 4096 + 5, 1 << 20, 592 * 4096, 700 * 4096 + 9])
+def test_scan_and_draw_in_one_call(O, n):
+    # up to 592 partitions (4 CTAs of 63 registers x 256 threads per SM, 148 SMs) the call is one
+    # cooperative launch; above that it is the two launches.  Either way: the bits of scan + search.
+    s = core.PrioritySampler(n)
+    two = core.PrioritySampler(n)
+    rng = np.random.default_rng(n)
+    for rep in range(3):                          # back to back: the launch leaves its counters at zero
+        p = O.synth_lognormal(70 + rep, n, n)
+        if rep == 1:
+            p[:: 3] = 0.0
+        b = [1, 4096, 777][rep]
+        hu = rng.random(b)
+        if b > 2:
+            hu[0], hu[1] = 0.0, np.nextafter(1.0, 0.0)
+        dp, du = dev(p), dev(hu)
+        got = s.scan_search(dp, du, scale=True)
+        tot, st = s.result()
+        ocdf, ol1, ototal, _ = O.scan(p)
+        want, near = O.search(ocdf, ol1, hu, scale=True, want_near=True)
+        assert np.array_equal(got.cpu().numpy(), want)
+        assert np.array_equal(s.cdf.cpu().numpy(), ocdf)
+        assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal
+        assert st[0] == 0 and st[1] == int(near.sum())
+        two.scan(dp)
+        assert np.array_equal(two.search(du, scale=True).cpu().numpy(), want)
+        two.clear_status(); s.clear_status()
+    # the tables it leaves serve the other consumers: a plain search and an incremental update
+    assert np.array_equal(s.search(du, scale=True).cpu().numpy(), want)
+    idx = np.unique(rng.integers(0, n, min(n, 50)).astype(np.int64))
+    val = rng.random(len(idx)).astype(np.float32)
+    p[idx] = val
+    s.update(dp, dev(idx), dev(val))
+    tot, _ = s.result()
+    ocdf, ol1, ototal, _ = O.scan(p)
+    assert np.array_equal(s.cdf.cpu().numpy(), ocdf) and np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal
+
+
+def test_scan_and_draw_edge_tables(O):
+    n = 5 * 4096
+    s = core.PrioritySampler(n)
+    z = torch.zeros(n, dtype=torch.float32, device=DEV)
+    got = s.scan_search(z, dev(np.array([0.0, 0.5, 0.999])), scale=True)
+    assert got.cpu().tolist() == [n - 1] * 3              # nothing selectable: defined as the last index
+    p = np.zeros(n, np.float32); p[4096 * 2 + 17] = 2.0; p[n - 1] = 1.0
+    got = s.scan_search(dev(p), dev(np.array([0.0, 1.999, 2.0, 2.999, 5.0, -1.0])), scale=False)
+    assert got.cpu().tolist() == [4096 * 2 + 17] * 2 + [n - 1] * 3 + [4096 * 2 + 17]
+    bad = p.copy(); bad[5] = -1.0
+    s.scan_search(dev(bad), dev(np.array([0.5])), scale=True)
+    _, st = s.result()
+    assert st[0] & N.ST_BAD_PRIORITY
+    s.clear_status()
+    assert s.scan_search(dev(p), torch.empty(0, dtype=torch.float64, device=DEV)).numel() == 0
+    # inexact level 1 (aggregates 2^70 apart): the in-order float64 sum, as in the separate launches
+    q = np.full(n, 1e-3, np.float32); q[0] = 3e18; q[4096] = 3e18
+    hu = np.random.default_rng(5).random(512)
+    got = s.scan_search(dev(q), dev(hu), scale=True)
+    ocdf, ol1, _, _ = O.scan(q)
+    _, st = s.result()
+    assert np.array_equal(got.cpu().numpy(), O.search(ocdf, ol1, hu, scale=True))
+    assert np.array_equal(s.l1.cpu().numpy(), ol1) and st[0] & N.ST_L1_RESUMMED
