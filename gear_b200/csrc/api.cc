@@ -211,7 +211,8 @@ struct gearb_sampler {
   int device = 0;
   float *cdf = nullptr;
   double *l1s[2] = {nullptr, nullptr};  // level 1 of the last scan and of the one before it, like blk below
-  void *scratch = nullptr;
+  void *scratches[2] = {nullptr, nullptr};  // header + aggregates of the last scan and of the one before it
+  double *sb[2] = {nullptr, nullptr};       // superblock sums, zero except between a scan_totals and its level-1 launch
   void *upd = nullptr;  // dirty flags + list of touched partitions for incremental updates
   int32_t *status = nullptr;
   const float *lazy_prio = nullptr;  // set by scan_totals: level 2 is rebuilt from these on demand
@@ -227,6 +228,20 @@ struct gearb_sampler {
     return slot;
   }
   double *l1() const { return l1s[slot]; }
+  void *scratch() const { return scratches[slot]; }
+  // A totals-only scan of a table of more than 1024 partitions leaves level 1 for later: the
+  // sampling launch behind it finds partitions through the superblock sums, and the level-1
+  // launch goes behind the NEXT scan, beside which it runs (the two work in different slots).
+  // Every other consumer of level 1 has it launched first (settle()).
+  bool l1_owed = false;
+  int owed_slot = 0;
+  cudaStream_t owed_stream = nullptr;  // for the entry points that take no stream
+  int settle(cudaStream_t stream, bool after_next = false) {
+    if (!l1_owed) return GEARB_OK;
+    l1_owed = false;
+    return launch_level1(scan_aggregate_words(scratches[owed_slot]), nparts, l1s[owed_slot], nullptr, status, stream,
+                         static_cast<ScanHeader *>(scratches[owed_slot]), true, sb[owed_slot], after_next);
+  }
   // A scan may begin while the launch before it in the stream is still finishing -- but never
   // beside an earlier scan of the same sampler: they share the scratch block.  Every launch that
   // reads the tables waits for the scan before it to complete before it lets its own successor
@@ -646,13 +661,18 @@ int gearb_sampler_create(int64_t n, gearb_sampler **out) {
   if (e == cudaSuccess) e = cudaMalloc(&s->cdf, static_cast<size_t>(round_up(n * 4, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->l1s[0], static_cast<size_t>(round_up((s->nparts + 1) * 8, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->l1s[1], static_cast<size_t>(round_up((s->nparts + 1) * 8, 256)));
-  if (e == cudaSuccess) e = cudaMalloc(&s->scratch, static_cast<size_t>(s->scratch_bytes));
+  const size_t sb_bytes = static_cast<size_t>(round_up((s->nparts / GEARB_SUPER_PARTS + 1) * 8, 256));
+  for (int k = 0; k < 2; ++k) {
+    if (e == cudaSuccess) e = cudaMalloc(&s->scratches[k], static_cast<size_t>(s->scratch_bytes));
+    if (e == cudaSuccess) e = cudaMemset(s->scratches[k], 0, static_cast<size_t>(s->scratch_bytes));
+    if (e == cudaSuccess) e = cudaMalloc(&s->sb[k], sb_bytes);
+    if (e == cudaSuccess) e = cudaMemset(s->sb[k], 0, sb_bytes);
+  }
   if (e == cudaSuccess) e = cudaMalloc(&s->upd, static_cast<size_t>(update_scratch_bytes(n)));
   if (e == cudaSuccess) e = cudaMemset(s->upd, 0, static_cast<size_t>(update_scratch_bytes(n)));
   if (e == cudaSuccess) e = cudaMalloc(&s->blk[0], static_cast<size_t>(round_up(s->nparts * 32, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->blk[1], static_cast<size_t>(round_up(s->nparts * 32, 256)));
   if (e == cudaSuccess) e = cudaMalloc(&s->status, 256);
-  if (e == cudaSuccess) e = cudaMemset(s->scratch, 0, static_cast<size_t>(s->scratch_bytes));
   if (e == cudaSuccess) e = cudaMemset(s->status, 0, 256);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -668,7 +688,10 @@ int gearb_sampler_destroy(gearb_sampler *s) {
   if (s->cdf) (void)cudaFree(s->cdf);
   if (s->l1s[0]) (void)cudaFree(s->l1s[0]);
   if (s->l1s[1]) (void)cudaFree(s->l1s[1]);
-  if (s->scratch) (void)cudaFree(s->scratch);
+  for (int k = 0; k < 2; ++k) {
+    if (s->scratches[k]) (void)cudaFree(s->scratches[k]);
+    if (s->sb[k]) (void)cudaFree(s->sb[k]);
+  }
   if (s->upd) (void)cudaFree(s->upd);
   if (s->blk[0]) (void)cudaFree(s->blk[0]);
   if (s->blk[1]) (void)cudaFree(s->blk[1]);
@@ -680,8 +703,10 @@ int gearb_sampler_destroy(gearb_sampler *s) {
 int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int store, void *stream) {
   TraceRange trace("gearb:scan_partitions");
   GEARB_REQUIRE(s, "sampler_scan_partitions: null sampler");
+  int rc0 = s->settle(as_stream(stream));
+  if (rc0 != GEARB_OK) return rc0;
   const int slot = s->take_slot();
-  int rc = launch_scan(priorities, s->n, store ? s->cdf : nullptr, s->l1s[slot], s->scratch, s->scratch_bytes, s->status,
+  int rc = launch_scan(priorities, s->n, store ? s->cdf : nullptr, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status,
                        0, as_stream(stream), /*level1=*/false, /*overlap_previous=*/s->may_overlap() && !store,
                        s->blk[slot]);
   if (rc == GEARB_OK) s->lazy_prio = store ? nullptr : priorities;
@@ -691,9 +716,12 @@ int gearb_sampler_scan_partitions(gearb_sampler *s, const float *priorities, int
 int gearb_sampler_scan_level1(gearb_sampler *s, void *stream) {
   TraceRange trace("gearb:level1");
   GEARB_REQUIRE(s, "sampler_scan_level1: null sampler");
+  const bool was_owed_here = s->l1_owed && s->owed_slot == s->slot;
+  int rc0 = s->settle(as_stream(stream));
+  if (rc0 != GEARB_OK || was_owed_here) return rc0;  // that WAS this table's level-1 launch
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
-  return launch_level1(scan_aggregate_words(s->scratch), s->nparts, s->l1(), nullptr, s->status,
-                       as_stream(stream), static_cast<ScanHeader *>(s->scratch),
+  return launch_level1(scan_aggregate_words(s->scratch()), s->nparts, s->l1(), nullptr, s->status,
+                       as_stream(stream), static_cast<ScanHeader *>(s->scratch()),
                        /*have_range=*/s->nparts > 1024);  // only the streaming kernel leaves the exponent range
 }
 
@@ -703,30 +731,54 @@ int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *s
   // The launch may begin while the one before it in the stream is finishing -- a sampling launch
   // that reads the level 1 and block totals of the OTHER slot.  Not when the caller pinned the slot.
   const int before = s->slot;
+  const bool pinned = s->next_slot >= 0;  // the caller chose the slot: peers read its tables, nothing is left owing
   const int slot = s->take_slot();
-  int rc = launch_scan(priorities, s->n, nullptr, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
-                       as_stream(stream), true, /*overlap_previous=*/s->may_overlap() && slot != before,
-                       s->blk[slot]);
-  if (rc == GEARB_OK) s->lazy_prio = priorities;
+  // Level 1 of a large table is left owing (see gearb_sampler::settle): a sampling launch that
+  // follows does without it, everything else has it launched first.
+  const bool owe = !pinned && s->nparts > 1024 && level1_can_follow_next_scan(s->nparts);
+  if (s->l1_owed && s->owed_slot == slot) {  // a pinned slot: the old order, nothing overlaps
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
+  int rc = launch_scan(priorities, s->n, nullptr, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
+                       as_stream(stream), /*level1=*/!owe, /*overlap_previous=*/s->may_overlap() && slot != before,
+                       s->blk[slot], owe ? s->sb[slot] : nullptr);
+  if (rc != GEARB_OK) return rc;
+  s->lazy_prio = priorities;
+  // what the previous scan owes goes behind this one and runs beside it
+  rc = s->settle(as_stream(stream), /*after_next=*/true);
+  if (owe) {
+    s->l1_owed = true;
+    s->owed_slot = slot;
+    s->owed_stream = as_stream(stream);
+  }
   return rc;
 }
 
 int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void *stream) {
   TraceRange trace("gearb:scan");
   GEARB_REQUIRE(s, "sampler_scan_alternate: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->lazy_prio = nullptr;
   const int slot = s->take_slot();
-  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
+  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
                      as_stream(stream), true, /*overlap_previous=*/s->may_overlap(), s->blk[slot]);
 }
 
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) {
   TraceRange trace("gearb:scan");
   GEARB_REQUIRE(s, "sampler_scan: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->lazy_prio = nullptr;
   const int slot = s->take_slot();
   s->scan_unconsumed = true;
-  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
+  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
                      as_stream(stream), true, false, s->blk[slot]);
 }
 
@@ -734,15 +786,19 @@ int gearb_sampler_scan_search(gearb_sampler *s, const float *priorities, const d
                               int flags, int64_t *out_index, void *stream) {
   TraceRange trace("gearb:scan_search");
   GEARB_REQUIRE(s, "sampler_scan_search: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->lazy_prio = nullptr;
   const int slot = s->take_slot();
   int fused = 0;
-  int rc = launch_scan_search(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status,
+  int rc = launch_scan_search(priorities, s->n, s->cdf, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status,
                               s->blk[slot], variates, b, flags, out_index, as_stream(stream), &fused);
   if (rc != GEARB_OK) return rc;
   s->scan_unconsumed = false;  // in either form the draw comes after the scan
   if (fused) return GEARB_OK;
-  rc = launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch, s->scratch_bytes, s->status, 0,
+  rc = launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
                    as_stream(stream), true, false, s->blk[slot]);
   if (rc != GEARB_OK) return rc;
   return launch_search(s->cdf, s->l1s[slot], s->n, variates, b, flags, out_index, s->status, as_stream(stream));
@@ -752,11 +808,15 @@ int gearb_sampler_update(gearb_sampler *s, float *priorities, const int64_t *idx
                          void *stream) {
   TraceRange trace("gearb:update");
   GEARB_REQUIRE(s, "sampler_update: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE(!s->lazy_prio || s->lazy_prio == priorities,
                 "sampler_update: not the array the table was built from");
-  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1(), scan_aggregate_words(s->scratch),
-                       s->blk[s->slot], static_cast<ScanHeader *>(s->scratch), s->upd, idx,
+  return launch_update(priorities, s->n, s->lazy_prio ? nullptr : s->cdf, s->l1(), scan_aggregate_words(s->scratch()),
+                       s->blk[s->slot], static_cast<ScanHeader *>(s->scratch()), s->upd, idx,
                        values, m, s->status, as_stream(stream));
 }
 
@@ -764,6 +824,10 @@ int gearb_sampler_search(gearb_sampler *s, const double *variates, int64_t b, in
                          int64_t *out_index, void *stream) {
   TraceRange trace("gearb:search");
   GEARB_REQUIRE(s, "sampler_search: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   if (s->lazy_prio) return fail(GEARB_ERR_STATE, "sampler_search: the table was built without its level-2 entries");
   return launch_search(s->cdf, s->l1(), s->n, variates, b, flags, out_index, s->status,
@@ -778,6 +842,10 @@ int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const
                                        void *stream) {
   TraceRange trace("gearb:sample_gather(owner)");
   GEARB_REQUIRE(s, "sample_gather: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE(slot_mod >= -1 && slot_mod <= GEARB_MAX_SHARDS && (slot_mod == 0 || slot_mod == 1 || slot_base),
                 "sample_gather: bad slot map");
@@ -814,9 +882,21 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
   GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
                 (long long)(h->table->capacity * h->table->T));
+  // Level 1 still owed for this very table: the launch finds partitions through what the scan
+  // left (the level-1 launch follows the next scan, or the next call that needs the table).
+  Level1Sums sums;
+  const bool from_sums = s->l1_owed && s->owed_slot == s->slot && s->lazy_prio;
+  if (from_sums) {
+    sums.sb = s->sb[s->slot];
+    sums.agg = scan_aggregate_words(s->scratch());
+    sums.range = &static_cast<ScanHeader *>(s->scratch())->pad[1];
+  } else {
+    rc = s->settle(as_stream(stream));
+    if (rc != GEARB_OK) return rc;
+  }
   return launch_sample_gather(p, s->cdf, s->l1(), s->n, variates, flags, lengths, index_offset, out_flat,
                               out_idx, out_ts, out_len, as_stream(stream), 1.0, 0.0, s->lazy_prio,
-                              s->blk[s->slot]);
+                              s->blk[s->slot], DrawLayout(), from_sums ? &sums : nullptr);
 }
 
 int gearb_ipc_export(const void *device_ptr, void *handle64) {
@@ -872,8 +952,12 @@ int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *ma
                           int copy_l1, void *stream) {
   TraceRange trace("gearb:publish");
   GEARB_REQUIRE(s, "publish: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
-  unsigned *counter = &static_cast<ScanHeader *>(s->scratch)->pad[kPadPublish];
+  unsigned *counter = &static_cast<ScanHeader *>(s->scratch())->pad[kPadPublish];
   return launch_publish(s->l1(), s->nparts, world, rank, mailboxes, epoch, copy_l1, counter, as_stream(stream));
 }
 
@@ -885,6 +969,10 @@ int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *con
 int gearb_sampler_pull_ex(gearb_sampler *s, gearb_handler *h, const gearb_pull_args *a, void *stream) {
   TraceRange trace("gearb:pull");
   GEARB_REQUIRE(s && a, "pull: null sampler or arguments");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE(a->cdf || a->prio, "pull: neither level-2 tables nor priorities were given");
   GEARB_REQUIRE(a->totals || a->mailbox, "pull: neither totals nor a mailbox were given");
@@ -956,8 +1044,13 @@ int gearb_sampler_clear_status(gearb_sampler *s, void *stream) {
   return GEARB_OK;
 }
 
-int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int32_t **status) {
-  GEARB_REQUIRE(s, "sampler_buffers: null sampler");
+int gearb_sampler_buffers(const gearb_sampler *cs, float **cdf, double **l1, int32_t **status) {
+  GEARB_REQUIRE(cs, "sampler_buffers: null sampler");
+  gearb_sampler *s = const_cast<gearb_sampler *>(cs);
+  if (l1) {  // whoever asks for the table gets it launched, on the stream of the scan that owes it
+    int rc0 = s->settle(s->owed_stream);
+    if (rc0 != GEARB_OK) return rc0;
+  }
   if (cdf) *cdf = s->cdf;
   if (l1) *l1 = s->l1();
   if (status) *status = s->status;
@@ -966,6 +1059,10 @@ int gearb_sampler_buffers(const gearb_sampler *s, float **cdf, double **l1, int3
 
 int gearb_sampler_result(gearb_sampler *s, void *stream, double *total, int32_t *status) {
   GEARB_REQUIRE(s, "sampler_result: null sampler");
+  {
+    int rc0 = s->settle(as_stream(stream));
+    if (rc0 != GEARB_OK) return rc0;
+  }
   GEARB_CUDA(cudaStreamSynchronize(as_stream(stream)));
   if (total)
     GEARB_CUDA(cudaMemcpy(total, s->l1() + s->nparts, sizeof(double), cudaMemcpyDeviceToHost));

@@ -71,13 +71,24 @@ int64_t scan_scratch_bytes(int64_t n);
 // this call; l1 is written by the level-1 launch, which waits for everything before it).
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream,
-                bool level1 = true, bool overlap_previous = false, float *blkw = nullptr);
+                bool level1 = true, bool overlap_previous = false, float *blkw = nullptr, double *sb = nullptr);
+// sb (tables of more than 1024 partitions): one float64 per GEARB_SUPER_PARTS partitions, zero before
+// the launch, receives the sums of their aggregates; the level-1 launch for this scan gets the
+// same pointer and zeroes the words again at its end.
+#define GEARB_SUPER_PARTS 128
 int64_t static_scan_max_n();
 int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
                        cudaStream_t stream);
 float *scan_aggregate_words(void *scratch);
+// sb: superblock sums to zero at the end (or null).  after_next: the launch sits BEHIND the next
+// scan in the stream instead of in front of it (that scan works in the other scratch block, and
+// began only when the one whose aggregates these are was complete): it starts at once, works
+// beside that scan, and waits for it only before its clean-up -- so whatever follows finds both
+// complete, and nothing that still reads the header words or the sums can be running.
+bool level1_can_follow_next_scan(int64_t nparts);
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
-                  cudaStream_t stream, ScanHeader *hdr, bool have_range);
+                  cudaStream_t stream, ScanHeader *hdr, bool have_range, double *sb = nullptr,
+                  bool after_next = false);
 int64_t update_scratch_bytes(int64_t n);
 int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, float *blkw, ScanHeader *hdr,
                   void *upd, const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream);
@@ -140,7 +151,17 @@ struct DrawLayout {
   int64_t flat_offset = 0;  // added to every flat step index written to out_flat
 };
 
+// What a scan leaves besides level 1, enough to find a variate's partition and its offset
+// before the level-1 table exists: the sums of the aggregates of every GEARB_SUPER_PARTS
+// partitions, the aggregates, and the two header words with their exponent range.
+struct Level1Sums {
+  const double *sb;
+  const float *agg;
+  const unsigned *range;
+};
+
 int launch_gather(const GatherParams &p, cudaStream_t stream);
+// sums (with lazy_prio, local tables): l1 has not been built yet, see Level1Sums.
 // lazy_prio / lazy_blk: the table was built without its level-2 entries; the kernel rebuilds what a
 // request needs from the priorities and the per-block totals the scan left (8 floats per partition).
 int launch_sample_gather(const GatherParams &p, const float *cdf, const double *l1, int64_t n,
@@ -148,7 +169,7 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
                          cudaStream_t stream, double mul = 1.0, double sub = 0.0,
                          const float *lazy_prio = nullptr, const float *lazy_blk = nullptr,
-                         const DrawLayout &lay = DrawLayout());
+                         const DrawLayout &lay = DrawLayout(), const Level1Sums *sums = nullptr);
 // Per shard: either its stored level-2 table (peer_cdf) or its priorities and block totals
 // (peer_prio, peer_blk; peer_cdf null).  peer_l1 may point at local copies of the peers' level 1.
 int launch_pull(const GatherParams &p, int world, int self, const double *totals, const void *const *peer_cdf,

@@ -37,7 +37,7 @@ struct Shared {
 // header; otherwise (aggregates touched by an incremental update) the cluster finds it first.
 __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterThreads)
     level1_cluster_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status,
-                          ScanHeader *hdr, int have_range) {
+                          ScanHeader *hdr, int have_range, double *sb, int after_next) {
   extern __shared__ float4 tile4[];  // level1::kTile floats
   __shared__ Shared sh;
   float *tile = reinterpret_cast<float *>(tile4);
@@ -47,7 +47,11 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = kClusterThreads / 32;
   unsigned long long *totals = reinterpret_cast<unsigned long long *>(&hdr->pad[kPadTotals]);
 
-  asm volatile("griddepcontrol.wait;" ::: "memory");  // the aggregates come from the kernel before
+  // The aggregates come from the kernel before -- or, when this launch sits behind the NEXT scan
+  // (after_next), from a scan that was complete before that one began: then there is nothing to
+  // wait for yet, and what follows this launch may be staged at once (it waits for this grid).
+  if (!after_next) asm volatile("griddepcontrol.wait;" ::: "memory");
+  else asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // this rank's share: a multiple of four aggregates, so that its 16-byte copies stay aligned
   const unsigned per = ((nparts + kClusterCtas - 1) / kClusterCtas + 3u) & ~3u;
@@ -146,6 +150,13 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
     if (atomicAdd(&hdr->pad[kPadDone], 1u) == kClusterCtas - 1) {
       __threadfence();
       if (wide || atomicOr(&hdr->pad[kPadBad], 0u)) level1::in_order(agg, nparts, l1, status);
+      // Behind the next scan: that scan ends only after the sampling launch before it, the one
+      // reader of the exponent range and of the superblock sums besides this launch, has ended.
+      if (after_next) asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (sb) {
+        const unsigned nsb = (nparts + GEARB_SUPER_PARTS - 1) / GEARB_SUPER_PARTS;
+        for (unsigned k = 0; k < nsb; ++k) sb[k] = 0.0;
+      }
       hdr->pad[kPadEminInv] = 0u;
       hdr->pad[kPadEmax] = 0u;
       hdr->pad[kPadBad] = 0u;
@@ -163,10 +174,14 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
 // One CTA, any size: the tiles are walked in sequence (level1::build).
 __global__ void __launch_bounds__(1024)
     level1_single_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status,
-                         ScanHeader *hdr) {
+                         ScanHeader *hdr, double *sb) {
   extern __shared__ float4 tile4[];
   asm volatile("griddepcontrol.wait;" ::: "memory");  // dependents start when this grid is done
   level1::build(agg, nparts, l1, status, reinterpret_cast<float *>(tile4));
+  if (sb) {
+    const unsigned nsb = (nparts + GEARB_SUPER_PARTS - 1) / GEARB_SUPER_PARTS;
+    for (unsigned k = threadIdx.x; k < nsb; k += blockDim.x) sb[k] = 0.0;
+  }
   if (threadIdx.x == 0) {
     hdr->pad[kPadEminInv] = 0u;  // left by the scan, not used here
     hdr->pad[kPadEmax] = 0u;
@@ -179,8 +194,13 @@ __global__ void __launch_bounds__(1024)
 // l1 from the aggregates of `nparts` partitions; `clear_word`, when given, is zeroed at the end
 // (the incremental update's list counter).  hdr: the header of the scratch block the aggregates
 // live in; have_range: the scan that wrote them left their exponent range there.
+bool level1_can_follow_next_scan(int64_t nparts) {
+  return nparts <= static_cast<int64_t>(kClusterCtas) * (level1::kTile - 4);
+}
+
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
-                  cudaStream_t stream, ScanHeader *hdr, bool have_range) {
+                  cudaStream_t stream, ScanHeader *hdr, bool have_range, double *sb, bool after_next) {
+  GEARB_REQUIRE(!after_next || level1_can_follow_next_scan(nparts), "level1: table too large to follow the next scan");
   constexpr int kTileBytes = level1::kTile * sizeof(float);
   {
     int rc = per_device_once(kOnceLevel1, [](int *) -> int {  // function attributes are per device
@@ -202,12 +222,15 @@ int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_
   if (nparts <= static_cast<int64_t>(kClusterCtas) * (level1::kTile - 4)) {
     cfg.gridDim = dim3(kClusterCtas);
     cfg.blockDim = dim3(kClusterThreads);
+    // only the rank's share is staged: a small footprint lets the CTAs sit beside a running scan
+    const unsigned per = ((np + kClusterCtas - 1) / kClusterCtas + 3u) & ~3u;
+    cfg.dynamicSmemBytes = per * 4u < 1024u ? 1024u : per * 4u;
     GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_cluster_kernel, agg, np, l1, clear_word, status, hdr,
-                                  static_cast<int>(have_range)));
+                                  static_cast<int>(have_range), sb, static_cast<int>(after_next)));
   } else {
     cfg.gridDim = dim3(1);
     cfg.blockDim = dim3(1024);
-    GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_single_kernel, agg, np, l1, clear_word, status, hdr));
+    GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_single_kernel, agg, np, l1, clear_word, status, hdr, sb));
   }
   return GEARB_OK;
 }

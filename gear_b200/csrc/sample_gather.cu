@@ -18,6 +18,8 @@
 // The kernel is launched with programmatic stream serialisation: its CTAs may be
 // scheduled while the kernel before it in the stream (normally the scan) drains,
 // and wait in griddepcontrol.wait until that kernel's results are visible.
+#include <cstdlib>
+
 #include "common.h"
 #include "device_copy.cuh"
 #include "scan_tree.cuh"
@@ -136,6 +138,11 @@ struct SampleArgs {
   int64_t flat_offset;  // added to out_flat
   int flags;
   double mul, sub;  // GEARB_SEARCH_AFFINE: variate -> variate * mul - sub (global draw -> this shard)
+  // Level 1 not built yet (its launch follows the next scan): the partition and its offset come
+  // from the superblock sums and the aggregates the scan left (local kLazy instances only).
+  const double *sb;       // null: l1 is valid
+  const float *agg;       // one aggregate per partition
+  const unsigned *range;  // two words: 256 - smallest exponent among the aggregates (0: none), largest exponent
 };
 
 // Sharded table read in place: every request is routed to the shard that owns its variate, and
@@ -187,6 +194,34 @@ __device__ __forceinline__ int64_t dst_slot(const GatherParams &P, int64_t g) {
 // most 42 ulp), or in a ragged last partition, takes the long way: the whole partition (one
 // 16 KiB bulk copy) rebuilt in shared memory and searched.  Both ways give the stored table's
 // answer bit for bit.
+// Superblock sums per thread when level 1 comes from them: tables of up to
+// kThreads * kSuperPerThread superblocks (131,072 partitions) can do without a level-1 table.
+constexpr int kSuperPerThread = 8;
+
+// Exclusive prefix of one float64 per thread over the CTA (kThreads threads) and the CTA's sum.
+// Plain float64 additions: the callers use it where every partial sum is exact.
+__device__ __forceinline__ double cta_exclusive_sum(double x, double &before, int lane, int warp, double *warp_tot,
+                                                    double *total_slot) {
+  double incl = x;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const double o = __shfl_up_sync(kFull, incl, d);
+    if (lane >= d) incl = __dadd_rn(incl, o);
+  }
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  double wbase = 0.0, all = 0.0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    if (w < warp) wbase = __dadd_rn(wbase, warp_tot[w]);
+    all = __dadd_rn(all, warp_tot[w]);
+  }
+  before = __dadd_rn(wbase, __dsub_rn(incl, x));
+  (void)total_slot;
+  __syncthreads();  // warp_tot may be written again
+  return all;
+}
+
 template <bool kPeers, int kPath, bool kLazy>
 __global__ void __launch_bounds__(kThreads, kPath == kStaged ? 7 : (kPath == kRing ? 4 : 5))
 sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ SampleArgs a,
@@ -200,6 +235,9 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
   __shared__ int warp_best[kWarps];
   __shared__ float warp_lo[kWarps];
   __shared__ int fast_j;
+  __shared__ double dsum_warp[kWarps];  // level 1 from the superblock sums: warp totals,
+  __shared__ double dsum_total[1];      // the total (or the offset of the pick),
+  __shared__ int dsum_pick[1];          // and the superblock / partition picked
   __shared__ int plan_bytes[GEARB_MAX_COLUMNS];     // staged path: clipped bytes of every column of the request
   __shared__ unsigned plan_mis[GEARB_MAX_COLUMNS];  // ... and how far its first byte sits inside a 16-byte block
   unsigned ring_it = 0;  // pieces this warp has pushed through its ring so far
@@ -320,12 +358,52 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
       table = peers.table[owner];
     }
 
-    // ---- level 1, first round: the probes and the variate travel together
+    // ---- level 1
     Range r1{0, a.nparts - 1, 0};
-    int64_t q0, q1, step;
-    probe_positions(r1, q0, q1, step);
-    double p0 = ldt<kPeers>(l1 + 1 + q0), p1 = ldt<kPeers>(l1 + 1 + q1);
-    const double total = ldt<kPeers>(l1 + a.nparts);
+    int64_t q0 = 0, q1 = 0, step = 1;
+    double p0 = 0.0, p1 = 0.0, total;
+    const bool from_sums = !kPeers && kLazy && a.sb != nullptr;  // the same in every thread of the grid
+    double sum_before = 0.0;  // from_sums: what lies before this thread's first superblock (later: partition)
+    double sum_run[kSuperPerThread];
+    bool sums_exact = true;
+    if (from_sums) {
+      // Every sum of aggregates is exact in float64 -- and therefore the in-order sum that level 1
+      // is defined as, whatever the order -- when the exponents of the aggregates span little enough.
+      // (the sums are fetched beside the range words that say whether they may be used)
+      const int nsb = static_cast<int>((a.nparts + GEARB_SUPER_PARTS - 1) / GEARB_SUPER_PARTS);
+#pragma unroll
+      for (int k = 0; k < kSuperPerThread; ++k) {
+        const int q = static_cast<int>(threadIdx.x) * kSuperPerThread + k;
+        sum_run[k] = q < nsb ? __ldcg(a.sb + q) : 0.0;
+      }
+      const unsigned inv = __ldcg(a.range), emax = __ldcg(a.range + 1);
+      const unsigned emin = inv ? 256u - inv : 1u;
+      sums_exact = emax == 0u || (emax < 255u && (emax - emin) + 24u + (32u - __clz(static_cast<unsigned>(a.nparts))) <= 53u);
+      if (sums_exact) {
+        double run = 0.0;
+#pragma unroll
+        for (int k = 0; k < kSuperPerThread; ++k) {
+          run = __dadd_rn(run, sum_run[k]);
+          sum_run[k] = run;
+        }
+        total = cta_exclusive_sum(run, sum_before, lane, warp, dsum_warp, dsum_total);
+      } else {
+        if (threadIdx.x == 0) {  // the definition itself, by one thread: rare tables only
+          double acc = 0.0;
+          for (int64_t q = 0; q < a.nparts; ++q) acc = __dadd_rn(acc, static_cast<double>(__ldcg(a.agg + q)));
+          *dsum_total = acc;
+        }
+        __syncthreads();
+        total = *dsum_total;
+        __syncthreads();
+      }
+    } else {
+      // first round: the probes and the variate travel together
+      probe_positions(r1, q0, q1, step);
+      p0 = ldt<kPeers>(l1 + 1 + q0);
+      p1 = ldt<kPeers>(l1 + 1 + q1);
+      total = ldt<kPeers>(l1 + a.nparts);
+    }
     int64_t flat;
     if (!(total > 0.0)) {
       flat = a.n - 1;  // nothing selectable: defined as the last index
@@ -340,12 +418,61 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
       }
       if (!(v >= 0.0)) v = 0.0;
       if (!(v < total)) v = __longlong_as_double(__double_as_longlong(total) - 1);
-      for (;;) {
-        resolve(r1, step, p0 > v, p1 > v, masks, round);
-        if (step == 1 || r1.lo >= r1.hi) break;
-        probe_positions(r1, q0, q1, step);
-        p0 = ldt<kPeers>(l1 + 1 + q0);
-        p1 = ldt<kPeers>(l1 + 1 + q1);
+      double off_sums = 0.0;
+      if (from_sums && sums_exact) {
+        // the superblock whose half-open range of sums holds v (exactly one thread finds it) ...
+#pragma unroll
+        for (int k = 0; k < kSuperPerThread; ++k) {
+          const double lo = __dadd_rn(sum_before, k ? sum_run[k - 1] : 0.0), hi = __dadd_rn(sum_before, sum_run[k]);
+          if (lo <= v && v < hi) {
+            *dsum_pick = static_cast<int>(threadIdx.x) * kSuperPerThread + k;
+            *dsum_total = lo;
+          }
+        }
+        __syncthreads();
+        const int64_t first = static_cast<int64_t>(*dsum_pick) * GEARB_SUPER_PARTS;
+        const double base_sum = *dsum_total;
+        __syncthreads();
+        // ... then the partition inside it, one aggregate per thread
+        static_assert(kThreads == GEARB_SUPER_PARTS, "one partition of a superblock per thread");
+        const int64_t q = first + threadIdx.x;
+        const double x = q < a.nparts ? static_cast<double>(__ldcg(a.agg + q)) : 0.0;
+        double before;
+        cta_exclusive_sum(x, before, lane, warp, dsum_warp, dsum_total);
+        const double lo = __dadd_rn(base_sum, before), hi = __dadd_rn(lo, x);
+        __syncthreads();  // everybody has read the total slot
+        if (lo <= v && v < hi) {
+          *dsum_pick = static_cast<int>(threadIdx.x);
+          *dsum_total = lo;
+        }
+        __syncthreads();
+        r1.hi = first + *dsum_pick;
+        off_sums = *dsum_total;
+        __syncthreads();
+      } else if (from_sums) {
+        if (threadIdx.x == 0) {
+          double acc = 0.0, before = 0.0;
+          int64_t q = 0;
+          for (; q < a.nparts; ++q) {
+            before = acc;
+            acc = __dadd_rn(acc, static_cast<double>(__ldcg(a.agg + q)));
+            if (acc > v) break;
+          }
+          *dsum_pick = static_cast<int>(q < a.nparts ? q : a.nparts - 1);
+          *dsum_total = before;
+        }
+        __syncthreads();
+        r1.hi = *dsum_pick;
+        off_sums = *dsum_total;
+        __syncthreads();
+      } else {
+        for (;;) {
+          resolve(r1, step, p0 > v, p1 > v, masks, round);
+          if (step == 1 || r1.lo >= r1.hi) break;
+          probe_positions(r1, q0, q1, step);
+          p0 = ldt<kPeers>(l1 + 1 + q0);
+          p1 = ldt<kPeers>(l1 + 1 + q1);
+        }
       }
       const int64_t p = r1.hi;
       GEARB_STAMP(2);
@@ -398,7 +525,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
         float4 *pv4 = reinterpret_cast<float4 *>(stage);
         float *xs = pv + GEARB_PART + warp * 128;
         const float *src = prio + base;
-        const double off = ldt<kPeers>(l1 + p);
+        const double off = from_sums ? off_sums : ldt<kPeers>(l1 + p);
         const float r_raw = __double2float_rn(__dsub_rn(v, off));
 
         // -- the short way: the block totals say which block holds the entry
@@ -738,6 +865,14 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
   int64_t grid = p.n;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
   if (grid > cap) grid = cap;
+  // A table whose level 1 is still owed is a table that is rescanned every step: the next scan
+  // starts while this launch runs.  Three CTAs per SM (each striding over the requests) leave
+  // room for two of that scan's three CTAs per SM from the start; the full grid would keep the
+  // scan out until it drains (measured at 1024 requests: 77 us per step against 84).
+  if (a.sb != nullptr && grid > static_cast<int64_t>(sm_count()) * 3) grid = static_cast<int64_t>(sm_count()) * 3;
+#ifdef GEARB_TUNE_ENV  // tuning builds only: a smaller grid (the CTAs stride over the requests)
+  if (const char *e = getenv("GEARB_TUNE_SG_GRID")) grid = atoi(e) > 0 && atoi(e) < grid ? atoi(e) : grid;
+#endif
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -772,8 +907,11 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
                          const double *u, int flags, const int64_t *lengths, int64_t index_offset,
                          int64_t *out_flat, int64_t *out_idx, int64_t *out_ts, int64_t *out_len,
                          cudaStream_t stream, double mul, double sub, const float *lazy_prio,
-                         const float *lazy_blk, const DrawLayout &lay) {
+                         const float *lazy_blk, const DrawLayout &lay, const Level1Sums *sums) {
   GEARB_REQUIRE(n > 0, "sample_gather: the priority table is empty");
+  GEARB_REQUIRE(!sums || (lazy_prio && sums->sb && sums->agg && sums->range &&
+                          (n + GEARB_PART - 1) / GEARB_PART <= int64_t(kThreads) * kSuperPerThread * GEARB_SUPER_PARTS),
+                "sample_gather: level 1 from the scan's sums needs a table built without its level-2 entries");
   if (p.n == 0) return GEARB_OK;
   GEARB_REQUIRE((cdf || lazy_prio) && l1 && u, "sample_gather: null pointer argument");
   GEARB_REQUIRE(!lazy_prio || (reinterpret_cast<uintptr_t>(lazy_prio) & 15) == 0,
@@ -789,6 +927,11 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
   a.flags = flags;
   a.mul = mul;
   a.sub = sub;
+  if (sums) {
+    a.sb = sums->sb;
+    a.agg = sums->agg;
+    a.range = sums->range;
+  }
   PeerArgs peers = {};
   return launch_any(p, a, peers, stream);
 }

@@ -33,6 +33,7 @@
 //
 // HBM traffic: 4 B read + 4 B written per priority, plus ~16 B per partition; the
 // totals-only instance (cdf == nullptr) writes nothing per priority.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.h"
@@ -117,6 +118,7 @@ struct ScanArgs {
   ScanHeader *hdr;
   float *aggw;               // per partition: its aggregate
   float *blkw;               // per partition: its eight block totals (or null: not wanted)
+  double *sb;                // per superblock of kSuperParts partitions: the sum of their aggregates (or null)
   int32_t *status;
   int64_t n;
   unsigned nparts;
@@ -208,8 +210,13 @@ __device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
 
 // One partition's aggregate to its word in global memory (read back by the last CTA).
 // The exponent range of the aggregates is collected on the way for the level-1 launch.
+// With a.sb the aggregate is also added to its superblock's sum: float64 additions in whatever
+// order the CTAs arrive, which is the in-order sum whenever no addition rounds -- the consumer
+// (the sampling kernel's level-1 lookup without a level-1 table) checks the exponent range for
+// that before it trusts the sums.
 __device__ __forceinline__ void hand_over(const ScanArgs &a, int part, float agg, unsigned &emin, unsigned &emax) {
   a.aggw[part] = agg;
+  if (a.sb) atomicAdd(a.sb + (part / GEARB_SUPER_PARTS), static_cast<double>(agg));
   level1::note_exponent(__float_as_uint(agg), emin, emax);
 }
 // The partition's eight block totals, for a sampling kernel that rebuilds single blocks of the
@@ -602,7 +609,7 @@ int64_t scan_scratch_bytes(int64_t n) {
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, bool level1,
-                bool overlap_previous, float *blkw) {
+                bool overlap_previous, float *blkw, double *sb) {
   GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
   GEARB_REQUIRE(prio && l1 && scratch && status, "scan: null pointer argument");  // cdf may be null
   GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
@@ -628,6 +635,7 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   a.hdr = reinterpret_cast<ScanHeader *>(sc);
   a.aggw = reinterpret_cast<float *>(sc + sizeof(ScanHeader));
   a.blkw = blkw;
+  a.sb = nparts > kSmallParts ? sb : nullptr;  // small tables have their level 1 at once
   a.status = status;
   a.n = n;
   a.nparts = static_cast<unsigned>(nparts);
@@ -658,7 +666,10 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
     return GEARB_OK;
   }
   const size_t smem_bytes = kSmemBytes;
-  const int ctas_per_sm = cdf != nullptr ? (packed >> 16) : (packed & 0xffff);
+  int ctas_per_sm = cdf != nullptr ? (packed >> 16) : (packed & 0xffff);
+#ifdef GEARB_TUNE_ENV  // tuning builds only: resident CTAs per SM from the environment
+  if (const char *e = getenv("GEARB_TUNE_SCAN_CTAS")) ctas_per_sm = atoi(e) > 0 && atoi(e) < ctas_per_sm ? atoi(e) : ctas_per_sm;
+#endif
   const int64_t resident = static_cast<int64_t>(sm_count()) * ctas_per_sm;
   // Group partitions per ticket only when there is enough work to keep every CTA busy.
   a.group = nparts >= resident * kGroupMax * 2 ? kGroupMax : (nparts >= resident * 4 ? 2 : 1);
@@ -689,7 +700,7 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   }
   // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
   return (a.inline_level1 || !level1) ? GEARB_OK
-                                       : launch_level1(a.aggw, nparts, l1, nullptr, status, stream, a.hdr, true);
+                                       : launch_level1(a.aggw, nparts, l1, nullptr, status, stream, a.hdr, true, a.sb, false);
 }
 
 int launch_scan_search(const float *prio, int64_t n, float *cdf, double *l1, void *scratch, int64_t scratch_bytes,
@@ -723,6 +734,7 @@ int launch_scan_search(const float *prio, int64_t n, float *cdf, double *l1, voi
   a.hdr = reinterpret_cast<ScanHeader *>(sc);
   a.aggw = reinterpret_cast<float *>(sc + sizeof(ScanHeader));
   a.blkw = blkw;
+  a.sb = nullptr;
   a.status = status;
   a.n = n;
   a.nparts = static_cast<unsigned>(nparts);

@@ -17,7 +17,6 @@
 namespace gearb {
 namespace {
 
-constexpr unsigned kFull = 0xffffffffu;
 constexpr int kThreads = 256;
 
 struct SearchArgs {

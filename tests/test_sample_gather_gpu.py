@@ -305,3 +305,102 @@ def test_pull_gives_up_when_a_peer_never_publishes(O):
     assert not all(bool((d == 0x77).all()) for d in dsts)
     assert sm.result()[1][0] == 0
     box.free()
+
+
+def _check_batch(O, s, h, t, img, rows, T, L, prio, u01, dsts, out_flat):
+    ocdf, ol1, ototal, _ = O.scan(prio)
+    oflat = O.search(ocdf, ol1, u01, scale=True)
+    assert np.array_equal(out_flat.cpu().numpy(), oflat)
+    oi, ot, ol = O.decode(oflat, T)
+    for c, r in enumerate(rows):
+        want = O.fused_subcopy(img, oi, ot, ol, t.trajectory_stride, t.accu[c], T, r, 0, L, False)
+        assert np.array_equal(dsts[c].cpu().numpy(), want), c
+    return ol1, ototal
+
+
+def test_large_table_draws_before_its_level1_exists(O):
+    # More than 1024 partitions and no stored level 2: the scan leaves level 1 owing, the sampling
+    # launch finds partitions through the superblock sums, and the level-1 launch runs behind the
+    # next scan.  Indices, bytes and (whenever it is asked for) level 1 are the oracle's.
+    rows, T, cap, B, L = [8, 4], 1000, 6200, 1024, 16
+    t, img = build(O, rows, T, cap, seed=9)
+    h = core.StorageHandler(t)
+    cols = [0, 1]
+    h.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * 2)
+    n = cap * T
+    rng = np.random.default_rng(3)
+    prios = [O.synth_lognormal(90 + k, n, n) for k in range(3)]
+    prios[1][: 300 * 4096] = 0.0                         # whole superblocks without weight
+    prios[2][::2] = 0.0
+    dps = [dev(p) for p in prios]
+    s = core.PrioritySampler(n)
+    dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=DEV) for r in rows]
+    flat = torch.empty(B, dtype=torch.int64, device=DEV)
+    for step in range(7):                                # scan, draw, scan, draw ...: level 1 always one step behind
+        k = step % 3
+        u01 = rng.random(B)
+        u01[0], u01[1] = 0.0, np.nextafter(1.0, 0.0)
+        s.scan(dps[k], store=False)
+        s.sample_gather(h, dev(u01), cols, dsts, scale=True, out_flat=flat)
+        if step in (2, 5):                               # without a host sync in between on the other steps
+            ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prios[k], u01, dsts, flat)
+            if step == 5:                                # asking for the table has it built
+                tot, st = s.result()
+                assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal and st[0] == 0
+    ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prios[k], u01, dsts, flat)
+    # two draws from one scan; then consumers that need the table itself
+    u2 = rng.random(B)
+    s.sample_gather(h, dev(u2), cols, dsts, scale=True, out_flat=flat)
+    _check_batch(O, s, h, t, img, rows, T, L, prios[k], u2, dsts, flat)
+    idx = np.unique(rng.integers(0, n, 400).astype(np.int64)); val = rng.random(len(idx)).astype(np.float32)
+    prios[k][idx] = val
+    s.update(dps[k], dev(idx), dev(val))
+    s.sample_gather(h, dev(u2), cols, dsts, scale=True, out_flat=flat)
+    ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prios[k], u2, dsts, flat)
+    tot, st = s.result()
+    assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal and st[0] == 0
+    # two scans in a row, a pinned slot, and the two-launch form of a scan
+    s.scan(dps[0], store=False); s.scan(dps[1], store=False)
+    s.sample_gather(h, dev(u2), cols, dsts, scale=True, out_flat=flat)
+    _check_batch(O, s, h, t, img, rows, T, L, prios[1], u2, dsts, flat)
+    for k in (2, 0, 2):
+        s.select_slot(0)
+        s.scan(dps[k], store=False)
+        s.sample_gather(h, dev(u2), cols, dsts, scale=True, out_flat=flat)
+    ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prios[2], u2, dsts, flat)
+    s.scan_partitions(dps[0], store=False); s.scan_level1()
+    s.sample_gather(h, dev(u2), cols, dsts, scale=True, out_flat=flat)
+    ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prios[0], u2, dsts, flat)
+    tot, st = s.result()
+    assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal and st[0] == 0
+    # a stored scan afterwards, and back
+    s.scan(dps[1]); assert np.array_equal(s.search(dev(u2), scale=True).cpu().numpy(), O.search(*O.scan(prios[1])[:2], u2, scale=True))
+    s.scan(dps[2], store=False)
+    s.sample_gather(h, dev(u2), cols, dsts, scale=True, out_flat=flat)
+    _check_batch(O, s, h, t, img, rows, T, L, prios[2], u2, dsts, flat)
+
+
+def test_large_table_with_aggregates_too_far_apart_for_exact_sums(O):
+    # Aggregates 2^30 apart: sums of subsets are no longer exact in float64 in every order, so the
+    # sampling launch adds the aggregates in order itself; the answers stay the oracle's.
+    rows, T, cap, B, L = [4], 1000, 5000, 256, 8
+    t, img = build(O, rows, T, cap, seed=10)
+    h = core.StorageHandler(t)
+    h.set([0], [core.SubscribePattern(0, L, N.PAD_TAIL)])
+    n = cap * T
+    prio = O.synth_lognormal(95, n, n)
+    prio[4096 * 7: 4096 * 9] *= np.float32(2.0 ** 30)
+    prio[4096 * 900: 4096 * 901] *= np.float32(2.0 ** -12)
+    s = core.PrioritySampler(n)
+    dp = dev(prio)
+    dsts = [torch.empty(B * L * 4, dtype=torch.uint8, device=DEV)]
+    flat = torch.empty(B, dtype=torch.int64, device=DEV)
+    rng = np.random.default_rng(4)
+    for step in range(3):
+        u01 = rng.random(B)
+        u01[:64] *= 1e-9                                   # also draws outside the heavy partitions
+        s.scan(dp, store=False)
+        s.sample_gather(h, dev(u01), [0], dsts, scale=True, out_flat=flat)
+        ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prio, u01, dsts, flat)
+    tot, st = s.result()
+    assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal
