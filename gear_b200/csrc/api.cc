@@ -236,6 +236,7 @@ struct gearb_sampler {
   bool l1_owed = false;
   int owed_slot = 0;
   cudaStream_t owed_stream = nullptr;  // for the entry points that take no stream
+  bool drawn_since_scan = false;
   int settle(cudaStream_t stream, bool after_next = false) {
     if (!l1_owed) return GEARB_OK;
     l1_owed = false;
@@ -751,6 +752,7 @@ int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *s
     s->l1_owed = true;
     s->owed_slot = slot;
     s->owed_stream = as_stream(stream);
+    s->drawn_since_scan = false;
   }
   return rc;
 }
@@ -884,8 +886,11 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
                 (long long)(h->table->capacity * h->table->T));
   // Level 1 still owed for this very table: the launch finds partitions through what the scan
   // left (the level-1 launch follows the next scan, or the next call that needs the table).
+  // Only for the first draw after the scan: a second draw from one table says that no scan is
+  // about to follow, so the table is completed and the launch takes its full width again.
   Level1Sums sums;
-  const bool from_sums = s->l1_owed && s->owed_slot == s->slot && s->lazy_prio;
+  const bool from_sums = s->l1_owed && s->owed_slot == s->slot && s->lazy_prio && !s->drawn_since_scan;
+  s->drawn_since_scan = true;
   if (from_sums) {
     sums.sb = s->sb[s->slot];
     sums.agg = scan_aggregate_words(s->scratch());

@@ -50,9 +50,15 @@ constexpr int kThreads = kComputeThreads + 32;  // + loader warp
 constexpr int kTilesPerWarp = 4;
 constexpr int kPart = kComputeWarps * kTilesPerWarp * 128;
 static_assert(kPart == GEARB_PART, "partition size is part of the ABI");
+// Three ring slots and (below) at most three CTAs per SM: 162 KB of the SM's shared memory and
+// two thirds of its registers.  Four slots, or a fourth CTA, move no more bytes per second (144 KB
+// in flight per SM is three times what the latency-bandwidth product asks for), but they leave
+// no room for the sampling launch of the step before, which otherwise runs beside this kernel's
+// first third: with 1024 requests a step of scan + draw takes 73.5 us this way against 76.4.
 #ifndef GEARB_SCAN_STAGES
-#define GEARB_SCAN_STAGES 4
+#define GEARB_SCAN_STAGES 3
 #endif
+constexpr int kMaxCtasPerSm = 3;
 #ifndef GEARB_SCAN_GROUP
 #define GEARB_SCAN_GROUP 4
 #endif
@@ -154,7 +160,7 @@ __device__ void loader_warp(Smem &sm, const ScanArgs &a, int lane) {
   unsigned it = 0;
   bool stop = false;
   // The ticket after the current one is requested before the current one is served, so the
-  // round trip of the atomic is hidden behind four partitions' worth of copies.
+  // round trip of the atomic is hidden behind a group of partitions' worth of copies.
   unsigned ahead = 0;
   if (lane == 0) ahead = atomicAdd(&a.hdr->ticket, 1u);
   while (!stop) {
@@ -356,7 +362,7 @@ __device__ void finish_launch(Smem &sm, const ScanArgs &a, int tid) {
 }
 
 template <bool kStore>
-__global__ void __launch_bounds__(kThreads, kStore ? 3 : 4) scan_kernel(const ScanArgs a) {
+__global__ void __launch_bounds__(kThreads, kMaxCtasPerSm) scan_kernel(const ScanArgs a) {
   extern __shared__ unsigned char smem_raw[];
   Smem &sm = *reinterpret_cast<Smem *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -651,6 +657,8 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
       int st = 0, tot = 0;
       GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&st, scan_kernel<true>, kThreads, kSmemBytes));
       GEARB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&tot, scan_kernel<false>, kThreads, kSmemBytes));
+      st = st > kMaxCtasPerSm ? kMaxCtasPerSm : st;
+      tot = tot > kMaxCtasPerSm ? kMaxCtasPerSm : tot;
       *value = ((st > 0 ? st : 1) << 16) | (tot > 0 ? tot : 1);
       return GEARB_OK;
     }, &packed);
