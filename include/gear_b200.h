@@ -216,7 +216,13 @@ int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
  * `priorities` (16 KiB per request, the scan's own addition tree), with the same result bit
  * for bit.  `priorities` must stay unchanged (except through gearb_sampler_update) until the
  * last such call.  gearb_sampler_search and gearb_sampler_pull need the stored table and
- * return GEARB_ERR_STATE until the next gearb_sampler_scan.                                */
+ * return GEARB_ERR_STATE until the next gearb_sampler_scan.
+ * For a table of more than 1024 partitions the call leaves l1 owing: the first
+ * gearb_sampler_sample_gather behind it finds its partitions through sums the scan left, and
+ * the launch that writes l1 is issued behind the NEXT gearb_sampler_scan_totals (beside which it
+ * runs) or in front of the next call of any other kind on this sampler -- gearb_sampler_result
+ * and gearb_sampler_buffers included, so a caller never sees an incomplete l1.  All calls on one
+ * sampler are expected on one stream.                                                      */
 int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream);
 /* gearb_sampler_scan for one of two samplers that are used in turn: the launch may start while
  * the launch before it in the stream is still finishing, which is only correct when that launch
