@@ -750,7 +750,8 @@ def run_profile_case(args):
     `sample_gather` / `sample_gather_lazy`: config-3 rows on a 2,000-trajectory table (378 MB), B=1024, L=64;
     `gather` / `vcopy`: the unfused gather kernels on the same table and a drawn batch;
     `search`: scan + search of the index-only configuration; `update`: 1024 changed priorities;
-    `zero_copy`: the sampling kernel on a table in mapped host memory; `pull`: its sharded instance."""
+    `zero_copy`: the sampling kernel on a table in mapped host memory; `pull`: its sharded instance;
+    `step_lazy`: scan + draw through the scan's sums + owed level-1 launch on a 6,000-trajectory table (1.1 GB)."""
     import torch
     from gear_b200 import _native as N
     from gear_b200 import core
@@ -779,6 +780,18 @@ def run_profile_case(args):
             s.search(u, scale=True)
         print(json.dumps({"profile": args.profile, "result": s.result()}))
         return
+    if args.profile == "scan_search":
+        # config 2 as one cooperative launch
+        n, B = C2["n"], C2["B"]
+        prio = torch.empty(n, dtype=torch.float32, device=dev)
+        core.fill(prio, N.FILL_F32_LOGNORMAL, seed=1)
+        s = core.PrioritySampler(n)
+        u = torch.empty(B, dtype=torch.float64, device=dev)
+        core.fill(u, N.FILL_U01_F64, seed=4)
+        for _ in range(args.warmup + args.steps):
+            s.scan_search(prio, u, scale=True)
+        print(json.dumps({"profile": args.profile, "result": s.result()}))
+        return
     if args.profile == "zero_copy":
         # config 4's rows on a 64-trajectory table in pinned mapped host memory (1.8 GB), B=512, L=32
         rows, T, cap, B, L = C4["rows"], C4["T"], 64, C4["B"], C4["L"]
@@ -789,7 +802,8 @@ def run_profile_case(args):
         rows, T, cap, B, L = C5["rows"], C5["T"], 300, 1024, C5["L"]
         table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
     else:
-        rows, T, cap, B, L = C3["rows"], C3["T"], 2000, C3["B"], C3["L"]
+        # `step_lazy` needs more than 1024 partitions (level 1 is only owed for such tables): 6,000,000 priorities
+        rows, T, cap, B, L = C3["rows"], C3["T"], (6000 if args.profile == "step_lazy" else 2000), C3["B"], C3["L"]
         table = core.TrajectoryTable(rows, T, cap, residency=N.RES_HBM)
     table.connect()
     fill_table(core, N, table, seed=2)
@@ -846,6 +860,14 @@ def run_profile_case(args):
                    blks=[sj.block_totals()[sj.block_totals()[2]] for _, _, sj in shards])
         print(json.dumps({"profile": args.profile, "result": s.result()}))
         return
+    if args.profile == "step_lazy":
+        # the headline step's three launches: scan, sampling launch that draws through the scan's sums,
+        # and the level-1 launch that follows the next scan
+        for _ in range(args.warmup + args.steps):
+            s.scan(prio, store=False)
+            s.sample_gather(h, u, cols, dsts, scale=True, zero_fill=True)
+        print(json.dumps({"profile": args.profile, "result": s.result()}))
+        return
     for _ in range(args.warmup + args.steps):
         s.sample_gather(h, u, cols, dsts, scale=True, zero_fill=True)
     print(json.dumps({"profile": args.profile, "result": s.result()}))
@@ -859,7 +881,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile", default=None,
                     choices=["scan", "scan_totals", "sample_gather", "sample_gather_lazy", "gather", "vcopy", "search",
-                             "update", "zero_copy", "pull"],
+                             "update", "zero_copy", "pull", "step_lazy", "scan_search"],
                     help="run one small single-kernel case (for ncu) instead of the benchmark")
     ap.add_argument("--workload", default="default", choices=["default", "c2", "c4", "c5"],
                     help="default: the HBM-resident table at one GPU (with c2 and c4 beside it), the sharded table at "

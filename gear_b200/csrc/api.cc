@@ -726,62 +726,52 @@ int gearb_sampler_scan_level1(gearb_sampler *s, void *stream) {
                        /*have_range=*/s->nparts > 1024);  // only the streaming kernel leaves the exponent range
 }
 
-int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream) {
-  TraceRange trace("gearb:scan_totals");
-  GEARB_REQUIRE(s, "sampler_scan_totals: null sampler");
-  // The launch may begin while the one before it in the stream is finishing -- a sampling launch
-  // that reads the level 1 and block totals of the OTHER slot.  Not when the caller pinned the slot.
+// The three whole-table scans.  Level 1 of a table of more than 1024 partitions is left owing
+// (see gearb_sampler::settle): a sampling launch that follows does without it, everything else
+// has it launched first.  Not when the caller pinned the slot: then peers read this table.
+static int scan_whole(gearb_sampler *s, const float *priorities, cudaStream_t stream, bool store, bool may_start_early) {
   const int before = s->slot;
-  const bool pinned = s->next_slot >= 0;  // the caller chose the slot: peers read its tables, nothing is left owing
+  const bool pinned = s->next_slot >= 0;
   const int slot = s->take_slot();
-  // Level 1 of a large table is left owing (see gearb_sampler::settle): a sampling launch that
-  // follows does without it, everything else has it launched first.
   const bool owe = !pinned && s->nparts > 1024 && level1_can_follow_next_scan(s->nparts);
-  if (s->l1_owed && s->owed_slot == slot) {  // a pinned slot: the old order, nothing overlaps
-    int rc0 = s->settle(as_stream(stream));
+  if (s->l1_owed && (s->owed_slot == slot || !owe)) {  // the old order: level 1 in front of this scan
+    int rc0 = s->settle(stream);
     if (rc0 != GEARB_OK) return rc0;
   }
-  int rc = launch_scan(priorities, s->n, nullptr, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
-                       as_stream(stream), /*level1=*/!owe, /*overlap_previous=*/s->may_overlap() && slot != before,
-                       s->blk[slot], owe ? s->sb[slot] : nullptr);
+  const bool overlap = s->may_overlap() && may_start_early && slot != before;
+  int rc = launch_scan(priorities, s->n, store ? s->cdf : nullptr, s->l1s[slot], s->scratch(), s->scratch_bytes,
+                       s->status, 0, stream, /*level1=*/!owe, overlap, s->blk[slot], owe ? s->sb[slot] : nullptr);
   if (rc != GEARB_OK) return rc;
-  s->lazy_prio = priorities;
-  // what the previous scan owes goes behind this one and runs beside it
-  rc = s->settle(as_stream(stream), /*after_next=*/true);
+  s->lazy_prio = store ? nullptr : priorities;
+  rc = s->settle(stream, /*after_next=*/true);  // what the previous scan owes goes behind this one and runs beside it
   if (owe) {
     s->l1_owed = true;
     s->owed_slot = slot;
-    s->owed_stream = as_stream(stream);
+    s->owed_stream = stream;
     s->drawn_since_scan = false;
   }
   return rc;
 }
 
+int gearb_sampler_scan_totals(gearb_sampler *s, const float *priorities, void *stream) {
+  TraceRange trace("gearb:scan_totals");
+  GEARB_REQUIRE(s, "sampler_scan_totals: null sampler");
+  // The launch may begin while the one before it in the stream is finishing -- a sampling launch
+  // that reads the level 1 and block totals of the OTHER slot.
+  return scan_whole(s, priorities, as_stream(stream), /*store=*/false, /*may_start_early=*/true);
+}
+
 int gearb_sampler_scan_alternate(gearb_sampler *s, const float *priorities, void *stream) {
   TraceRange trace("gearb:scan");
   GEARB_REQUIRE(s, "sampler_scan_alternate: null sampler");
-  {
-    int rc0 = s->settle(as_stream(stream));
-    if (rc0 != GEARB_OK) return rc0;
-  }
-  s->lazy_prio = nullptr;
-  const int slot = s->take_slot();
-  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
-                     as_stream(stream), true, /*overlap_previous=*/s->may_overlap(), s->blk[slot]);
+  return scan_whole(s, priorities, as_stream(stream), /*store=*/true, /*may_start_early=*/true);
 }
 
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream) {
   TraceRange trace("gearb:scan");
   GEARB_REQUIRE(s, "sampler_scan: null sampler");
-  {
-    int rc0 = s->settle(as_stream(stream));
-    if (rc0 != GEARB_OK) return rc0;
-  }
-  s->lazy_prio = nullptr;
-  const int slot = s->take_slot();
-  s->scan_unconsumed = true;
-  return launch_scan(priorities, s->n, s->cdf, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
-                     as_stream(stream), true, false, s->blk[slot]);
+  s->scan_unconsumed = true;  // never beside the launch before it: that launch may read this table's level 2
+  return scan_whole(s, priorities, as_stream(stream), /*store=*/true, /*may_start_early=*/false);
 }
 
 int gearb_sampler_scan_search(gearb_sampler *s, const float *priorities, const double *variates, int64_t b,
@@ -889,7 +879,7 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
   // Only for the first draw after the scan: a second draw from one table says that no scan is
   // about to follow, so the table is completed and the launch takes its full width again.
   Level1Sums sums;
-  const bool from_sums = s->l1_owed && s->owed_slot == s->slot && s->lazy_prio && !s->drawn_since_scan;
+  const bool from_sums = s->l1_owed && s->owed_slot == s->slot && !s->drawn_since_scan;
   s->drawn_since_scan = true;
   if (from_sums) {
     sums.sb = s->sb[s->slot];

@@ -362,7 +362,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
     Range r1{0, a.nparts - 1, 0};
     int64_t q0 = 0, q1 = 0, step = 1;
     double p0 = 0.0, p1 = 0.0, total;
-    const bool from_sums = !kPeers && kLazy && a.sb != nullptr;  // the same in every thread of the grid
+    const bool from_sums = !kPeers && a.sb != nullptr;  // the same in every thread of the grid
     double sum_before = 0.0;  // from_sums: what lies before this thread's first superblock (later: partition)
     double sum_run[kSuperPerThread];
     bool sums_exact = true;
@@ -485,7 +485,7 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
         Range r2{0, valid - 1, 0};
         probe_positions(r2, q0, q1, step);
         float c0 = ldt<kPeers>(cp + q0), c1 = ldt<kPeers>(cp + q1);
-        const double off = ldt<kPeers>(l1 + p);
+        const double off = from_sums ? off_sums : ldt<kPeers>(l1 + p);
         const float last = ldt<kPeers>(cp + valid - 1);
         float r = __double2float_rn(__dsub_rn(v, off));
         if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
@@ -870,7 +870,7 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
   // that scan's three (shared memory and registers both), so the scan runs at full width from its
   // start; the full grid would keep it out until this launch drains (measured at 1024 requests:
   // 73.5 us per step against 84).
-  if (a.sb != nullptr && grid > static_cast<int64_t>(sm_count()) * 2) grid = static_cast<int64_t>(sm_count()) * 2;
+  if (a.sb != nullptr && a.prio != nullptr && grid > static_cast<int64_t>(sm_count()) * 2) grid = static_cast<int64_t>(sm_count()) * 2;
 #ifdef GEARB_TUNE_ENV  // tuning builds only: a smaller grid (the CTAs stride over the requests)
   if (const char *e = getenv("GEARB_TUNE_SG_GRID")) grid = atoi(e) > 0 && atoi(e) < grid ? atoi(e) : grid;
 #endif
@@ -910,9 +910,9 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
                          cudaStream_t stream, double mul, double sub, const float *lazy_prio,
                          const float *lazy_blk, const DrawLayout &lay, const Level1Sums *sums) {
   GEARB_REQUIRE(n > 0, "sample_gather: the priority table is empty");
-  GEARB_REQUIRE(!sums || (lazy_prio && sums->sb && sums->agg && sums->range &&
+  GEARB_REQUIRE(!sums || (sums->sb && sums->agg && sums->range &&
                           (n + GEARB_PART - 1) / GEARB_PART <= int64_t(kThreads) * kSuperPerThread * GEARB_SUPER_PARTS),
-                "sample_gather: level 1 from the scan's sums needs a table built without its level-2 entries");
+                "sample_gather: level 1 from the scan's sums: null pointer or too many partitions");
   if (p.n == 0) return GEARB_OK;
   GEARB_REQUIRE((cdf || lazy_prio) && l1 && u, "sample_gather: null pointer argument");
   GEARB_REQUIRE(!lazy_prio || (reinterpret_cast<uintptr_t>(lazy_prio) & 15) == 0,

@@ -546,6 +546,9 @@ __global__ void __launch_bounds__(kSmallThreads) small_scan_search_kernel(const 
   __shared__ int gave_up;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int part = blockIdx.x;
+  // this warp's first variate travels while the partition is scanned
+  const int64_t w_first = static_cast<int64_t>(part) * kComputeWarps + warp;
+  double u_next = w_first < d.b ? __ldg(d.u + w_first) : 0.0;
   small_partition<true>(a, part, xs_all, wt, wm);
   __syncthreads();  // every thread's level-2 stores before thread 0's fence and count
   if (tid == 0) {
@@ -574,13 +577,14 @@ __global__ void __launch_bounds__(kSmallThreads) small_scan_search_kernel(const 
   level1::build(a.aggw, a.nparts, part == 0 ? a.l1 : nullptr, a.status, tile, l1s);
 
   const double total = l1s[a.nparts];
-  for (int64_t w = static_cast<int64_t>(part) * kComputeWarps + warp; w < d.b;
-       w += static_cast<int64_t>(gridDim.x) * kComputeWarps) {
+  const int64_t w_stride = static_cast<int64_t>(gridDim.x) * kComputeWarps;
+  for (int64_t w = w_first; w < d.b; w += w_stride) {
+    double v = u_next;
+    if (w + w_stride < d.b) u_next = __ldg(d.u + w + w_stride);
     if (!(total > 0.0)) {  // no selectable entry at all: defined as the last index
       if (lane == 0) d.out[w] = a.n - 1;
       continue;
     }
-    double v = __ldg(d.u + w);
     if (d.flags & GEARB_SEARCH_SCALE) v = __dmul_rn(v, total);
     if (!(v >= 0.0)) v = 0.0;
     if (!(v < total)) v = __longlong_as_double(__double_as_longlong(total) - 1);
@@ -591,12 +595,14 @@ __global__ void __launch_bounds__(kSmallThreads) small_scan_search_kernel(const 
     const float last = __ldcg(a.cdf + base + valid - 1);
     if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
     const int64_t j = warp_upper_bound<float>(a.cdf + base, 0, valid - 1, r, lane, LoadL2());
+    // the chosen entry and the one before it, fetched side by side (lanes 0 and 1)
+    const int64_t flat = base + j;
+    const float edge = lane < 2 ? __ldcg(a.cdf + (flat - (lane == 1 && j > 0 ? 1 : 0))) : 0.f;
+    const float lo_b = __shfl_sync(kFull, edge, 1);
     if (lane == 0) {
-      const int64_t flat = base + j;
       d.out[w] = flat;
-      const float hi_b = __ldcg(a.cdf + flat);
-      bool near = __uint_as_float(__float_as_uint(r) + 1u) >= hi_b;
-      if (j > 0 && r == __ldcg(a.cdf + flat - 1)) near = true;
+      bool near = __uint_as_float(__float_as_uint(r) + 1u) >= edge;
+      if (j > 0 && r == lo_b) near = true;
       if (near) atomicAdd(a.status + 1, 1);
     }
   }

@@ -404,3 +404,43 @@ def test_large_table_with_aggregates_too_far_apart_for_exact_sums(O):
         ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prio, u01, dsts, flat)
     tot, st = s.result()
     assert np.array_equal(s.l1.cpu().numpy(), ol1) and tot == ototal
+
+
+def test_large_stored_tables_draw_before_their_level1_exists(O):
+    # The same for scans that store level 2: one sampler scanned and drawn from in a loop, and
+    # two samplers used in turn (each one's scan may start under the other's sampling launch).
+    rows, T, cap, B, L = [8, 4], 1000, 5000, 512, 16
+    t, img = build(O, rows, T, cap, seed=11)
+    h = core.StorageHandler(t)
+    cols = [0, 1]
+    h.set(cols, [core.SubscribePattern(0, L, N.PAD_TAIL)] * 2)
+    n = cap * T
+    rng = np.random.default_rng(6)
+    prios = [O.synth_lognormal(96 + k, n, n) for k in range(2)]
+    prios[1][1000 * 4096:] = 0.0
+    dps = [dev(p) for p in prios]
+    dsts = [torch.empty(B * L * r, dtype=torch.uint8, device=DEV) for r in rows]
+    flat = torch.empty(B, dtype=torch.int64, device=DEV)
+    a, b = core.PrioritySampler(n), core.PrioritySampler(n)
+    for step in range(6):
+        k = step % 2
+        u01 = rng.random(B)
+        a.scan(dps[k])
+        a.sample_gather(h, dev(u01), cols, dsts, scale=True, out_flat=flat)
+        if step >= 3:
+            _check_batch(O, a, h, t, img, rows, T, L, prios[k], u01, dsts, flat)
+    ocdf, ol1, ototal, _ = O.scan(prios[k])
+    assert np.array_equal(a.search(dev(u01), scale=True).cpu().numpy(), O.search(ocdf, ol1, u01, scale=True))
+    tot, st = a.result()
+    assert np.array_equal(a.l1.cpu().numpy(), ol1) and np.array_equal(a.cdf.cpu().numpy(), ocdf) and tot == ototal
+    for step in range(8):
+        s, k = (a, b)[step % 2], (step // 2) % 2
+        u01 = rng.random(B)
+        s.scan(dps[k], alternate=True)
+        s.sample_gather(h, dev(u01), cols, dsts, scale=True, out_flat=flat)
+        if step >= 4:
+            ol1, ototal = _check_batch(O, s, h, t, img, rows, T, L, prios[k], u01, dsts, flat)
+    for s in (a, b):
+        tot, st = s.result()
+        assert st[0] == 0
+    assert np.array_equal(b.l1.cpu().numpy(), ol1) and tot == ototal
