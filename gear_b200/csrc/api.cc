@@ -237,6 +237,7 @@ struct gearb_sampler {
   int owed_slot = 0;
   cudaStream_t owed_stream = nullptr;  // for the entry points that take no stream
   bool drawn_since_scan = false;
+  bool last_scan_may_start_early = false;
   int settle(cudaStream_t stream, bool after_next = false) {
     if (!l1_owed) return GEARB_OK;
     l1_owed = false;
@@ -743,6 +744,7 @@ static int scan_whole(gearb_sampler *s, const float *priorities, cudaStream_t st
                        s->status, 0, stream, /*level1=*/!owe, overlap, s->blk[slot], owe ? s->sb[slot] : nullptr);
   if (rc != GEARB_OK) return rc;
   s->lazy_prio = store ? nullptr : priorities;
+  s->last_scan_may_start_early = may_start_early;
   rc = s->settle(stream, /*after_next=*/true);  // what the previous scan owes goes behind this one and runs beside it
   if (owe) {
     s->l1_owed = true;
@@ -885,6 +887,10 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
     sums.sb = s->sb[s->slot];
     sums.agg = scan_aggregate_words(s->scratch());
     sums.range = &static_cast<ScanHeader *>(s->scratch())->pad[1];
+    // the scan expected behind this launch: a totals-only one fits beside two of its CTAs per
+    // SM, a storing one of the other of two tables beside four; a storing scan of THIS table
+    // cannot start before the launch has ended, so the launch keeps its full width
+    sums.ctas_per_sm = s->lazy_prio ? 2 : (s->last_scan_may_start_early ? 4 : 0);
   } else {
     rc = s->settle(as_stream(stream));
     if (rc != GEARB_OK) return rc;

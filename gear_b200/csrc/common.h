@@ -158,6 +158,7 @@ struct Level1Sums {
   const double *sb;
   const float *agg;
   const unsigned *range;
+  int ctas_per_sm;  // > 0: a scan is expected to start under this launch; it leaves room with this many CTAs per SM
 };
 
 int launch_gather(const GatherParams &p, cudaStream_t stream);

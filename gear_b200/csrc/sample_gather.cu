@@ -861,16 +861,17 @@ const Kernel kInstances[2][2][3] = {
       sample_gather_kernel<true, kDirect, true>}}};
 constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kRingSlots * kRingSlotBytes;
 
-int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers, cudaStream_t stream) {
+int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers, cudaStream_t stream, int width = 0) {
   int64_t grid = p.n;
   const int64_t cap = static_cast<int64_t>(sm_count()) * 32;
   if (grid > cap) grid = cap;
   // A table whose level 1 is still owed is a table that is rescanned every step: the next scan
-  // starts while this launch runs.  Two CTAs per SM (each striding over the requests) fit beside
-  // that scan's three (shared memory and registers both), so the scan runs at full width from its
-  // start; the full grid would keep it out until this launch drains (measured at 1024 requests:
-  // 73.5 us per step against 84).
-  if (a.sb != nullptr && a.prio != nullptr && grid > static_cast<int64_t>(sm_count()) * 2) grid = static_cast<int64_t>(sm_count()) * 2;
+  // starts while this launch runs.  With few CTAs per SM (each striding over the requests) this
+  // launch fits beside that scan's CTAs -- shared memory and registers both -- so the scan runs at
+  // full width from its start; the full grid would keep it out until this launch drains.
+  // Measured at 1024 requests and 1e8 priorities: totals-only scans, 2 per SM: 73.5 us per step
+  // against 84; storing scans on two tables in turn, 4 per SM: 139 against 143.
+  if (width > 0 && grid > static_cast<int64_t>(sm_count()) * width) grid = static_cast<int64_t>(sm_count()) * width;
 #ifdef GEARB_TUNE_ENV  // tuning builds only: a smaller grid (the CTAs stride over the requests)
   if (const char *e = getenv("GEARB_TUNE_SG_GRID")) grid = atoi(e) > 0 && atoi(e) < grid ? atoi(e) : grid;
 #endif
@@ -934,7 +935,7 @@ int launch_sample_gather(const GatherParams &p, const float *cdf, const double *
     a.range = sums->range;
   }
   PeerArgs peers = {};
-  return launch_any(p, a, peers, stream);
+  return launch_any(p, a, peers, stream, sums ? sums->ctas_per_sm : 0);
 }
 
 namespace {
