@@ -31,7 +31,13 @@ constexpr int kThreads = 128;
 constexpr int kWarps = kThreads / 32;
 constexpr int kSlots = 2 * kThreads;  // probes per round
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kRingSlots = 3;            // per-warp ring of bulk copies for large requests
+#ifndef GEARB_SG_RING_SLOTS
+#define GEARB_SG_RING_SLOTS 3
+#endif
+#ifndef GEARB_SG_RING_CTAS
+#define GEARB_SG_RING_CTAS 4
+#endif
+constexpr int kRingSlots = GEARB_SG_RING_SLOTS;  // per-warp ring of bulk copies for large requests
 constexpr int kRingSlotBytes = 4096 + 128;  // one 4 KiB piece plus the 16-byte blocks around a misaligned one
 constexpr unsigned kWaitLimit = 1u << 20;  // mbarrier polls before a staged copy is declared lost
 // Polls of a peer's epoch word before the peer is declared absent: about four seconds, far beyond the
@@ -223,7 +229,7 @@ __device__ __forceinline__ double cta_exclusive_sum(double x, double &before, in
 }
 
 template <bool kPeers, int kPath, bool kLazy>
-__global__ void __launch_bounds__(kThreads, kPath == kStaged ? 7 : (kPath == kRing ? 4 : 5))
+__global__ void __launch_bounds__(kThreads, kPath == kStaged ? 7 : (kPath == kRing ? GEARB_SG_RING_CTAS : 5))
 sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_constant__ SampleArgs a,
                      const __grid_constant__ PeerArgs peers) {
   extern __shared__ __align__(128) uint8_t stage[];  // P.stage_bytes of staging area

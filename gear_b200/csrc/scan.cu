@@ -591,14 +591,41 @@ __global__ void __launch_bounds__(kSmallThreads) small_scan_search_kernel(const 
     const int64_t p = warp_upper_bound<double>(l1s + 1, 0, static_cast<int64_t>(a.nparts) - 1, v, lane, LoadPlain());
     const int64_t base = p * kPart;
     const int64_t valid = (a.n - base < kPart) ? (a.n - base) : kPart;
+    // Level 2 in two rounds of loads.  Round 1: 256 probes at a fixed stride, eight per lane, whose
+    // addresses do not depend on the residual -- they travel at once, and the last of them IS
+    // the partition's last entry, which clamps the residual.  Round 2: the <= 16 entries between
+    // two probes plus the one before them, one per lane, which also are the two entries the
+    // boundary check wants.  "First entry greater than r", as warp_upper_bound finds it.
+    const float *cp = a.cdf + base;
+    const int64_t st = (valid + 255) / 256;
+    float x[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      int64_t q = (static_cast<int64_t>(k * 32 + lane) + 1) * st - 1;
+      if (q > valid - 1) q = valid - 1;
+      x[k] = __ldcg(cp + q);
+    }
+    const float last = __shfl_sync(kFull, x[7], 31);  // slot 255 probes the last valid entry
     float r = __double2float_rn(__dsub_rn(v, l1s[p]));
-    const float last = __ldcg(a.cdf + base + valid - 1);
     if (!(r < last)) r = __uint_as_float(__float_as_uint(last) - 1u);
-    const int64_t j = warp_upper_bound<float>(a.cdf + base, 0, valid - 1, r, lane, LoadL2());
-    // the chosen entry and the one before it, fetched side by side (lanes 0 and 1)
+    int first = 255;
+#pragma unroll
+    for (int k = 7; k >= 0; --k) {
+      const unsigned m = __ballot_sync(kFull, x[k] > r);
+      if (m) first = k * 32 + __ffs(m) - 1;
+    }
+    const int64_t lo = static_cast<int64_t>(first) * st;  // one past the previous slot's probe
+    int64_t hi = lo + st - 1;
+    if (hi > valid - 1) hi = valid - 1;
+    const int width = static_cast<int>(hi - lo + 1);  // 1..16
+    const int64_t qe = lo - 1 + lane;                 // lane 0: the entry before the range
+    const float y = (qe >= 0 && lane <= width) ? __ldcg(cp + qe) : 0.f;
+    const unsigned m2 = __ballot_sync(kFull, lane >= 1 && lane <= width && y > r);  // never 0: cp[hi] > r
+    const int pick = __ffs(m2) - 1;
+    const int64_t j = lo + pick - 1;
+    const float edge = __shfl_sync(kFull, y, pick);
+    const float lo_b = __shfl_sync(kFull, y, pick - 1);
     const int64_t flat = base + j;
-    const float edge = lane < 2 ? __ldcg(a.cdf + (flat - (lane == 1 && j > 0 ? 1 : 0))) : 0.f;
-    const float lo_b = __shfl_sync(kFull, edge, 1);
     if (lane == 0) {
       d.out[w] = flat;
       bool near = __uint_as_float(__float_as_uint(r) + 1u) >= edge;
