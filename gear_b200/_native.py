@@ -74,6 +74,7 @@ _SIGS = {
     "gearb_table_host_ptr": (vp, [vp]),
     "gearb_table_device_ptr": (vp, [vp]),
     "gearb_table_upload": (C.c_int, [vp, vp]),
+    "gearb_table_upload_range": (C.c_int, [vp, i64, i64, vp]),
     "gearb_table_write": (C.c_int, [vp, i64, vp, i64, vp]),
     "gearb_table_read": (C.c_int, [vp, i64, vp, i64]),
     "gearb_handler_create": (C.c_int, [vp, i64, i64, i64, i64, i64, C.POINTER(vp)]),

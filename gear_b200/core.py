@@ -123,6 +123,10 @@ class TrajectoryTable:
     def upload(self, stream=None) -> None:
         call("gearb_table_upload", self._h, _stream(stream))
 
+    def upload_range(self, offset: int, nbytes: int, stream=None) -> None:
+        """Bytes [offset, offset + nbytes) of the host copy into the device copy (after upload())."""
+        call("gearb_table_upload_range", self._h, int(offset), int(nbytes), _stream(stream))
+
     def write(self, offset: int, data: np.ndarray, stream=None, sync: bool = True) -> None:
         """Bytes into every resident copy.  sync=False returns while the upload may still be
         reading `data` (page-locked memory the caller keeps alive and unchanged until it

@@ -381,6 +381,18 @@ int gearb_table_upload(gearb_table *t, void *stream) {
   return GEARB_OK;
 }
 
+int gearb_table_upload_range(gearb_table *t, int64_t offset, int64_t bytes, void *stream) {
+  GEARB_REQUIRE(t && t->connected, "table_upload_range: table is not connected");
+  GEARB_REQUIRE(t->host.addr && t->hbm, "table_upload_range: the table needs a host copy and an uploaded device copy");
+  GEARB_REQUIRE(offset >= 0 && bytes >= 0 && offset + bytes <= t->nbytes,
+                "table_upload_range: range [%lld, +%lld) outside the table (%lld bytes)", (long long)offset,
+                (long long)bytes, (long long)t->nbytes);
+  if (bytes == 0) return GEARB_OK;
+  GEARB_CUDA(cudaMemcpyAsync(static_cast<char *>(t->hbm) + offset, static_cast<const char *>(t->host.addr) + offset,
+                             static_cast<size_t>(bytes), cudaMemcpyHostToDevice, as_stream(stream)));
+  return GEARB_OK;
+}
+
 int gearb_table_write(gearb_table *t, int64_t offset, const void *src, int64_t bytes, void *stream) {
   GEARB_REQUIRE(t && t->connected, "table_write: table is not connected");
   GEARB_REQUIRE(offset >= 0 && bytes >= 0 && offset + bytes <= t->nbytes,

@@ -167,10 +167,13 @@ class OnlineIngest:
     server: IndexServer of this shard.  sampler / priorities: a gear_b200.core.PrioritySampler
     over one float32 priority per trajectory of the shard and the CUDA tensor it was scanned from
     (optional: without them only the host arrays are kept).  After every `step()` the device
-    table equals a full scan of the server's weights, bit for bit."""
+    table equals a full scan of the server's weights, bit for bit.  table: a
+    gear_b200.core.TrajectoryTable with a shared-memory host copy, which the simulators write,
+    and an uploaded device copy: every committed trajectory's bytes are copied to the device
+    copy before its weight makes it selectable (same stream, so the order holds on the device)."""
 
-    def __init__(self, server: IndexServer, sampler=None, priorities=None):
-        self.server, self.sampler, self.priorities = server, sampler, priorities
+    def __init__(self, server: IndexServer, sampler=None, priorities=None, table=None):
+        self.server, self.sampler, self.priorities, self.table = server, sampler, priorities, table
         if sampler is not None:
             import torch
             if priorities is None or priorities.numel() != server.capacity or sampler.n != server.capacity:
@@ -189,6 +192,11 @@ class OnlineIngest:
         ni, nu = s.scan()
         if nu:
             s.update(nu)
+            if self.table is not None:
+                stride = self.table.trajectory_stride
+                for k in range(nu):
+                    if s.upd_w[k] > 0.0:          # a finished trajectory (allocations come with weight 0)
+                        self.table.upload_range((int(s.upd_idx[k]) - s.index_offset) * stride, stride)
             if self.sampler is not None:
                 torch = self._torch
                 self._idx_host[:nu] = torch.from_numpy(s.upd_idx[:nu] - s.index_offset)

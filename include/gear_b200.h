@@ -103,6 +103,11 @@ void *gearb_table_device_ptr(const gearb_table *t);
  * HBM-resident table the reference only declares
  * (CudaTrajectoryStorageHandler, include/storage/handler.h:89-102).          */
 int gearb_table_upload(gearb_table *t, void *stream);
+/* One byte range of the host copy into the device copy (after gearb_table_upload): what a
+ * trainer does with a trajectory that a simulator process has finished writing into the
+ * shared-memory side of the table (the reference's trainer reads that memory in place,
+ * src/memory/shared_memory.cc:59-61; a device-resident table has to be told).             */
+int gearb_table_upload_range(gearb_table *t, int64_t offset, int64_t bytes, void *stream);
 /* Byte-range write/read against every resident copy (Uint8Span::copy on a
  * handler view, include/common/span.h:73-79).                                */
 int gearb_table_write(gearb_table *t, int64_t offset, const void *src, int64_t bytes,
