@@ -9,8 +9,9 @@ timesteps of every column.
 
 N = 1 runs the HBM-resident decision-transformer table (100,000 trajectories x
 1000 steps, rows 156/24/4/4/1 B, B=1024, L=64) and, beside it under
-`other_configs`, the index-only workload (1,048,576 priorities, 4096 variates) and
-the zero-copy workload (table in pinned mapped host memory, B=512, L=32).
+`other_configs`, the index-only workload (1,048,576 priorities, 4096 variates),
+the zero-copy workload (table in pinned mapped host memory, B=512, L=32) and the
+sharded workload's whole global batch on this one GPU (the N = 1 point of ITS curve).
 N > 1 runs the trajectory-id sharded token table (per GPU 32,000 x 1000 steps of
 4104 B, global batch 8192, L=16) with the cross-shard exchange.
 
@@ -76,6 +77,9 @@ class ClockSampler:
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
+            deadline = time.time() + 3.0      # nvidia-smi needs a few hundred ms before its first line
+            while not self.rows and time.time() < deadline:
+                time.sleep(0.01)
         except Exception:
             self.proc = None
 
@@ -172,13 +176,22 @@ def run_ours_single(args):
             sm.scan(prio, store=store, alternate=store)
             sm.sample_gather(handler, batch(i), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
 
-        for i in range(max(args.warmup, 3)):
-            one_step(i)
-        torch.cuda.synchronize()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        # The clock sampler starts first and the GPU is brought to its working clocks by 150 ms of the
+        # same steps (untimed, before the warm-up steps proper): a timed region of a few milliseconds
+        # right after an idle GPU would otherwise be measured partly at idle clocks.
         if sample_clocks:
             clocks.start()
-            time.sleep(0.12)
+        t_load = time.time()
+        spin_until = time.perf_counter() + 0.15
+        i_spin = 0
+        while time.perf_counter() < spin_until:
+            one_step(i_spin)
+            i_spin += 1
+            if i_spin % 64 == 0:
+                torch.cuda.synchronize()
+        for i in range(max(args.warmup, 3)):
+            one_step(i)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         torch.cuda.synchronize()
         t0 = time.time()
         ev[0].record()
@@ -187,7 +200,7 @@ def run_ours_single(args):
         ev[1].record()
         torch.cuda.synchronize()
         t1 = time.time()
-        clk = clocks.stop(t0, t1) if sample_clocks else None
+        clk = clocks.stop(t_load, t1) if sample_clocks else None
         ms_step = ev[0].elapsed_time(ev[1]) / K
         Ki = min(K, 300)
         marks = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(Ki)]
@@ -322,6 +335,7 @@ def run_ours_single(args):
         "config": {"workload": cfg["name"], "trajectories": cap, "trajectory_length": T, "row_bytes": rows,
                    "batch": B, "segment_length": L, "priorities": n, "table_bytes": table.nbytes,
                    "l2": "inputs larger than L2 (400 MB of priorities re-read every step)",
+                   "spin_up": "150 ms of untimed steps before the warm-up steps bring the GPU from idle to its working clocks; the clock samples (every 50 ms) cover that stretch and the timed region behind it",
                    "step": "totals-only scan (partition aggregates, block totals and superblock sums, no stored "
                            "level-2 table) + one launch that finds each request's partition through those sums, "
                            "rebuilds the one 512-value block it falls into, decodes and gathers; the level-1 "
@@ -362,7 +376,18 @@ def run_ours_single(args):
     gc.collect()
     torch.cuda.empty_cache()
     other = {}
-    for name, fn in (("c2_index_sampling_only", run_index_only), ("c4_zero_copy_host_table", run_zero_copy)):
+    def run_one_shard(a):
+        # config 5 with its whole global batch on ONE GPU: the N = 1 point of the sharded
+        # configuration's own scaling curve (the lines for N > 1 are that configuration)
+        import bench_sharded
+        a.steps, a.warmup = min(a.steps, 50), min(max(a.warmup, 3), 5)
+        full = bench_sharded.run(a, emit=False)
+        keep = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "config", "global_batch_8192",
+                "global_batch_1024_per_gpu", "small_case_every_byte_vs_oracle", "roofline", "e2e", "parity", "gpu_launches")
+        return {k: full[k] for k in keep if k in full}
+
+    for name, fn in (("c2_index_sampling_only", run_index_only), ("c4_zero_copy_host_table", run_zero_copy),
+                     ("c5_sharded_table_on_one_gpu", run_one_shard)):
         try:
             sub_args = argparse.Namespace(**vars(args))
             sub_args.steps = min(args.steps, 2000)

@@ -92,7 +92,8 @@ def _small_oracle_case(rank, world, comm, dev):
             "both exchange modes x both layouts x 3 batches (one of them entirely on shard 0)"}
 
 
-def run(args):
+def run(args, emit=True):
+    """emit=False (one process, one GPU): return the line instead of printing it."""
     import torch
     import torch.distributed as dist
 
@@ -167,18 +168,26 @@ def run(args):
     K = args.steps
     clocks = B.ClockSampler(local)
 
+    spin_steps = 600      # 100-150 ms of steps on this configuration: the clock samples (every 50 ms) cover them
+
     def timed(step, scan_only, sample_clocks=False):
         """W_ warm-up steps, then K timed ones between one pair of events; then an instrumented run of
         the same steps with events after the scan's first launch, after level 1 and at the end of the
         step (events inside a step cost some overlap between launches, so they stay out of the step
         time).  Returns max over ranks of (ms per step, ms per scan launch, ms from the end of level 1
         to the end of the step -- the publish + pull launches, or the exchange), and the clock record."""
-        for i in range(W_):
-            step(i, True)
-        barrier()
+        # The clock sampler starts first, and 100-150 ms of the same steps (untimed, a fixed count agreed by
+        # all ranks) bring the GPUs from idle to their working clocks before the warm-up steps proper.
         if sample_clocks and rank == 0:
             clocks.start()
-            time.sleep(0.12)
+        barrier()
+        t_load = time.time()
+        for i in range(spin_steps if sample_clocks else 64):
+            step(i, True)
+            if i % 32 == 31:
+                torch.cuda.synchronize()
+        for i in range(W_):
+            step(i, True)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         t0 = time.time()
@@ -188,7 +197,7 @@ def run(args):
         e1.record()
         barrier()
         t1 = time.time()
-        clk = clocks.stop(t0, t1) if (sample_clocks and rank == 0) else None
+        clk = clocks.stop(t_load, t1) if (sample_clocks and rank == 0) else None
         barrier()     # rank 0 spent a moment with the clock sampler: the ranks start the next loop together
         Ki = min(K, 100)
         ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(Ki)]
@@ -384,10 +393,12 @@ def run(args):
                     "d2h_floor": "all ranks copying one slice to pinned host memory at once, nothing else running"},
             "gpu_launches": 4 * K * world, "clocks": clk_main, "parity": head["parity"],
         }
-        print(json.dumps(line))
+        if emit:
+            print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return line if rank == 0 else None
 
 
 _ORACLE_SCANS = {}
