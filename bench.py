@@ -176,13 +176,13 @@ def run_ours_single(args):
             sm.scan(prio, store=store, alternate=store)
             sm.sample_gather(handler, batch(i), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
 
-        # The clock sampler starts first and the GPU is brought to its working clocks by 150 ms of the
+        # The clock sampler starts first and the GPU is brought to its working clocks by 60 ms of the
         # same steps (untimed, before the warm-up steps proper): a timed region of a few milliseconds
         # right after an idle GPU would otherwise be measured partly at idle clocks.
         if sample_clocks:
             clocks.start()
         t_load = time.time()
-        spin_until = time.perf_counter() + 0.15
+        spin_until = time.perf_counter() + 0.06
         i_spin = 0
         while time.perf_counter() < spin_until:
             one_step(i_spin)
@@ -335,7 +335,7 @@ def run_ours_single(args):
         "config": {"workload": cfg["name"], "trajectories": cap, "trajectory_length": T, "row_bytes": rows,
                    "batch": B, "segment_length": L, "priorities": n, "table_bytes": table.nbytes,
                    "l2": "inputs larger than L2 (400 MB of priorities re-read every step)",
-                   "spin_up": "150 ms of untimed steps before the warm-up steps bring the GPU from idle to its working clocks; the clock samples (every 50 ms) cover that stretch and the timed region behind it",
+                   "spin_up": "60 ms of untimed steps before the warm-up steps bring the GPU from idle to its working clocks; the clock samples (every 50 ms) cover that stretch and the timed region behind it",
                    "step": "totals-only scan (partition aggregates, block totals and superblock sums, no stored "
                            "level-2 table) + one launch that finds each request's partition through those sums, "
                            "rebuilds the one 512-value block it falls into, decodes and gathers; the level-1 "

@@ -168,7 +168,7 @@ def run(args, emit=True):
     K = args.steps
     clocks = B.ClockSampler(local)
 
-    spin_steps = 600      # 100-150 ms of steps on this configuration: the clock samples (every 50 ms) cover them
+    spin_steps = 300      # 50-80 ms of steps on this configuration: a clock sample or two (every 50 ms) fall into them
 
     def timed(step, scan_only, sample_clocks=False):
         """W_ warm-up steps, then K timed ones between one pair of events; then an instrumented run of
@@ -176,7 +176,7 @@ def run(args, emit=True):
         step (events inside a step cost some overlap between launches, so they stay out of the step
         time).  Returns max over ranks of (ms per step, ms per scan launch, ms from the end of level 1
         to the end of the step -- the publish + pull launches, or the exchange), and the clock record."""
-        # The clock sampler starts first, and 100-150 ms of the same steps (untimed, a fixed count agreed by
+        # The clock sampler starts first, and 50-80 ms of the same steps (untimed, a fixed count agreed by
         # all ranks) bring the GPUs from idle to their working clocks before the warm-up steps proper.
         if sample_clocks and rank == 0:
             clocks.start()

@@ -324,6 +324,46 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // every peer is past its previous step
   }
 
+  // Level 1 not built yet: the prefix of the superblock sums is the same for every request this
+  // CTA serves, so it is formed once (kept in registers: the sums of this thread's superblocks
+  // and of all before them).
+  const bool from_sums = !kPeers && a.sb != nullptr;  // the same in every thread of the grid
+  double sum_before = 0.0, sums_total = 0.0;
+  double sum_run[kSuperPerThread];
+  bool sums_exact = true;
+  if (from_sums) {
+    // Every sum of aggregates is exact in float64 -- and therefore the in-order sum that level 1
+    // is defined as, whatever the order -- when the exponents of the aggregates span little enough.
+    // (the sums are fetched beside the range words that say whether they may be used)
+    const int nsb = static_cast<int>((a.nparts + GEARB_SUPER_PARTS - 1) / GEARB_SUPER_PARTS);
+#pragma unroll
+    for (int k = 0; k < kSuperPerThread; ++k) {
+      const int q = static_cast<int>(threadIdx.x) * kSuperPerThread + k;
+      sum_run[k] = q < nsb ? __ldcg(a.sb + q) : 0.0;
+    }
+    const unsigned inv = __ldcg(a.range), emax = __ldcg(a.range + 1);
+    const unsigned emin = inv ? 256u - inv : 1u;
+    sums_exact = emax == 0u || (emax < 255u && (emax - emin) + 24u + (32u - __clz(static_cast<unsigned>(a.nparts))) <= 53u);
+    if (sums_exact) {
+      double run = 0.0;
+#pragma unroll
+      for (int k = 0; k < kSuperPerThread; ++k) {
+        run = __dadd_rn(run, sum_run[k]);
+        sum_run[k] = run;
+      }
+      sums_total = cta_exclusive_sum(run, sum_before, lane, warp, dsum_warp, dsum_total);
+    } else {
+      if (threadIdx.x == 0) {  // the definition itself, by one thread: rare tables only
+        double acc = 0.0;
+        for (int64_t q = 0; q < a.nparts; ++q) acc = __dadd_rn(acc, static_cast<double>(__ldcg(a.agg + q)));
+        *dsum_total = acc;
+      }
+      __syncthreads();
+      sums_total = *dsum_total;
+      __syncthreads();
+    }
+  }
+
   for (int64_t it = blockIdx.x; it < P.n; it += gridDim.x) {
     GEARB_STAMP(1);
     // Sharded: the two ends of the (ascending) slice first, where the requests for other shards
@@ -368,41 +408,8 @@ sample_gather_kernel(const __grid_constant__ GatherParams P, const __grid_consta
     Range r1{0, a.nparts - 1, 0};
     int64_t q0 = 0, q1 = 0, step = 1;
     double p0 = 0.0, p1 = 0.0, total;
-    const bool from_sums = !kPeers && a.sb != nullptr;  // the same in every thread of the grid
-    double sum_before = 0.0;  // from_sums: what lies before this thread's first superblock (later: partition)
-    double sum_run[kSuperPerThread];
-    bool sums_exact = true;
     if (from_sums) {
-      // Every sum of aggregates is exact in float64 -- and therefore the in-order sum that level 1
-      // is defined as, whatever the order -- when the exponents of the aggregates span little enough.
-      // (the sums are fetched beside the range words that say whether they may be used)
-      const int nsb = static_cast<int>((a.nparts + GEARB_SUPER_PARTS - 1) / GEARB_SUPER_PARTS);
-#pragma unroll
-      for (int k = 0; k < kSuperPerThread; ++k) {
-        const int q = static_cast<int>(threadIdx.x) * kSuperPerThread + k;
-        sum_run[k] = q < nsb ? __ldcg(a.sb + q) : 0.0;
-      }
-      const unsigned inv = __ldcg(a.range), emax = __ldcg(a.range + 1);
-      const unsigned emin = inv ? 256u - inv : 1u;
-      sums_exact = emax == 0u || (emax < 255u && (emax - emin) + 24u + (32u - __clz(static_cast<unsigned>(a.nparts))) <= 53u);
-      if (sums_exact) {
-        double run = 0.0;
-#pragma unroll
-        for (int k = 0; k < kSuperPerThread; ++k) {
-          run = __dadd_rn(run, sum_run[k]);
-          sum_run[k] = run;
-        }
-        total = cta_exclusive_sum(run, sum_before, lane, warp, dsum_warp, dsum_total);
-      } else {
-        if (threadIdx.x == 0) {  // the definition itself, by one thread: rare tables only
-          double acc = 0.0;
-          for (int64_t q = 0; q < a.nparts; ++q) acc = __dadd_rn(acc, static_cast<double>(__ldcg(a.agg + q)));
-          *dsum_total = acc;
-        }
-        __syncthreads();
-        total = *dsum_total;
-        __syncthreads();
-      }
+      total = sums_total;
     } else {
       // first round: the probes and the variate travel together
       probe_positions(r1, q0, q1, step);
