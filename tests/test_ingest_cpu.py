@@ -254,3 +254,29 @@ def test_libgear_names():
     del srv
     back = pickle.loads(blob)
     assert back.get_weights()[0] == 3.0 and back.get_timesteps()[0] == 2
+
+
+def test_ingestion_code_under_address_and_undefined_behaviour_sanitizers(tmp_path):
+    """The host code of the ingestion path built on its own with -fsanitize=address,undefined and
+    driven through the protocol, its error paths and the state image in a child process."""
+    import shutil
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    gxx = shutil.which("g++")
+    asan = subprocess.run([gxx, "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+    if not gxx or not Path(asan).is_file() or not (cuda_inc / "cuda_runtime.h").is_file():
+        pytest.skip("g++ with libasan and the CUDA headers are needed")
+    so = tmp_path / "libingest_san.so"
+    build = subprocess.run(
+        [gxx, "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined",
+         "-fno-sanitize-recover=undefined", "-shared", "-fPIC", "-I", str(root / "include"), "-I", str(root / "gear_b200" / "csrc"),
+         "-I", str(cuda_inc), str(root / "gear_b200" / "csrc" / "ingest.cc"), str(root / "tests" / "sanitize" / "host_stub.cc"),
+         "-o", str(so), "-lpthread"], capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-2000:]
+    env = dict(os.environ, LD_PRELOAD=asan, ASAN_OPTIONS="detect_leaks=0:abort_on_error=0:exitcode=23")
+    run = subprocess.run([sys.executable, str(root / "tests" / "sanitize" / "drive_ingest.py"), str(so)],
+                         capture_output=True, text=True, env=env, timeout=300)
+    assert run.returncode == 0 and "sanitized run ok" in run.stdout, (run.stdout[-500:], run.stderr[-3000:])
