@@ -384,7 +384,11 @@ def run(args, emit=True):
             "remote_bytes_counted_per_step_per_gpu": main_res["contiguous"]["remote_bytes_counted_per_step_per_gpu"],
             "roofline": {"kernel": "scan_kernel<false> (totals only)", "bound": "hbm", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
-                         "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms},
+                         "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms,
+                         "note": "the launch before every scan is a gather that has just written a batch larger than "
+                                 "L2: while the scan reads its 128 MB, about as many bytes of that batch are still being "
+                                 "written back from L2, so DRAM carries roughly twice the algorithmic bytes (back to "
+                                 "back on a quiet GPU the same scan takes 27 us)"},
             "cpu_baseline": None,
             "e2e": {"value": Bg_main * L / e2e_s, "unit": B.UNIT, "h2d_bytes_per_step": 8 * Bg_main * world,
                     "d2h_bytes_per_step": (gathered + 8 * b) * world, "ms_per_step": e2e_s * 1e3, "steps": Ke,
