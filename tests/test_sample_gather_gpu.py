@@ -444,3 +444,89 @@ def test_large_stored_tables_draw_before_their_level1_exists(O):
         tot, st = s.result()
         assert st[0] == 0
     assert np.array_equal(b.l1.cpu().numpy(), ol1) and tot == ototal
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_random_call_sequences_keep_tables_and_draws_exact(O, seed):
+    # Any order of the sampler's entry points on a table large enough to owe its level 1: every
+    # draw, and the table whenever it is read, equals the oracle's for the priorities of the moment.
+    rows, T, cap, B, L = [8], 500, 11000, 256, 4
+    t, img = build(O, rows, T, cap, seed=20 + seed)
+    h = core.StorageHandler(t)
+    h.set([0], [core.SubscribePattern(0, L, N.PAD_TAIL)])
+    n = cap * T                                           # 5,500,000 priorities: 1343 partitions
+    rng = np.random.default_rng(seed)
+    s = core.PrioritySampler(n)
+    base = [O.synth_lognormal(30 + k, n, n) for k in range(2)]
+    base[1][: n // 3] = 0.0
+    cur = None            # host copy of the priorities the table was last built from
+    dp = None
+    stored = False
+    dsts = [torch.empty(B * L * 8, dtype=torch.uint8, device=DEV)]
+    flat = torch.empty(B, dtype=torch.int64, device=DEV)
+    cache = {}
+
+    def oracle():
+        key = cur.tobytes()[:64] + cur[-8:].tobytes() + bytes([int(cur.sum() * 1000) % 251])
+        if key not in cache:
+            cache.clear()
+            cache[key] = O.scan(cur)
+        return cache[key]
+
+    for op_i in range(45):
+        op = rng.choice(["scan_lazy", "scan_store", "draw", "draw", "search", "update", "result", "pin", "two_launch", "scan_search"])
+        if cur is None and op not in ("scan_lazy", "scan_store", "two_launch"):
+            op = "scan_lazy"
+        if op in ("scan_lazy", "scan_store", "two_launch", "pin"):
+            k = int(rng.integers(0, 2))
+            cur = base[k].copy()
+            dp = dev(cur)
+            stored = op == "scan_store" or (op in ("two_launch", "pin") and bool(rng.integers(0, 2)))
+            if op == "pin":
+                s.select_slot(int(rng.integers(0, 2)))
+            if op == "two_launch":
+                s.scan_partitions(dp, store=stored)
+                s.scan_level1()
+            else:
+                s.scan(dp, store=stored)
+        elif op == "draw":
+            u01 = rng.random(B)
+            s.sample_gather(h, dev(u01), [0], dsts, scale=True, out_flat=flat)
+            ocdf, ol1, ototal, _ = oracle()
+            want = O.search(ocdf, ol1, u01, scale=True)
+            assert np.array_equal(flat.cpu().numpy(), want), (op_i, op)
+            oi, ot, ol = O.decode(want, T)
+            assert np.array_equal(dsts[0].cpu().numpy(),
+                                  O.fused_subcopy(img, oi, ot, ol, t.trajectory_stride, t.accu[0], T, 8, 0, L, False))
+        elif op == "search":
+            u01 = rng.random(B)
+            if stored:
+                got = s.search(dev(u01), scale=True).cpu().numpy()
+                ocdf, ol1, _, _ = oracle()
+                assert np.array_equal(got, O.search(ocdf, ol1, u01, scale=True)), (op_i, op)
+            else:
+                with pytest.raises(core.GearError):
+                    s.search(dev(u01), scale=True)
+        elif op == "update":
+            idx = np.unique(rng.integers(0, n, 300).astype(np.int64)); val = rng.random(len(idx)).astype(np.float32)
+            cur[idx] = val
+            s.update(dp, dev(idx), dev(val))
+        elif op == "scan_search":
+            k = int(rng.integers(0, 2))
+            cur = base[k].copy()
+            dp = dev(cur)
+            stored = True
+            u01 = rng.random(B)
+            got = s.scan_search(dp, dev(u01), scale=True).cpu().numpy()
+            ocdf, ol1, _, _ = oracle()
+            assert np.array_equal(got, O.search(ocdf, ol1, u01, scale=True)), (op_i, op)
+        else:
+            tot, st = s.result()
+            ocdf, ol1, ototal, _ = oracle()
+            # (an update may leave aggregates so far apart that level 1 is summed in order: that is flagged)
+            assert tot == ototal and st[0] & ~N.ST_L1_RESUMMED == 0, (op_i, op)
+            assert np.array_equal(s.l1.cpu().numpy(), ol1)
+            if stored:
+                assert np.array_equal(s.cdf.cpu().numpy(), ocdf)
+    tot, st = s.result()
+    assert tot == oracle()[2] and st[0] & ~N.ST_L1_RESUMMED == 0
