@@ -213,10 +213,26 @@ def run_ours_single(args):
             sampler.sample_gather(handler, batch(i), cols, dsts, scale=True, zero_fill=True, out_flat=flat)
             marks[i][3].record()
         torch.cuda.synchronize()
-        scan_ms = sum(m[0].elapsed_time(m[1]) for m in marks) / Ki
+        scan_ev_ms = sum(m[0].elapsed_time(m[1]) for m in marks) / Ki
         level1_ms = sum(m[1].elapsed_time(m[2]) for m in marks) / Ki
         sample_ms = sum(m[2].elapsed_time(m[3]) for m in marks) / Ki
-        return ms_step, scan_ms, (level1_ms, sample_ms), clk
+        # The scan kernel's own duration: launches of it alone, one behind the other with nothing in
+        # between (strictly serialised: a scan of a sampler never starts beside the one before it), between
+        # one pair of events.  An event on either side of a single launch adds about 5 us that are
+        # not the kernel's (the ncu launch list agrees with this loop to 0.5 us).
+        Kb = max(20, min(K, 200))
+        for _ in range(3):
+            sampler.scan_partitions(prio, store=store)
+        torch.cuda.synchronize()
+        eb = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        eb[0].record()
+        for _ in range(Kb):
+            sampler.scan_partitions(prio, store=store)
+        eb[1].record()
+        torch.cuda.synchronize()
+        sampler.scan_level1()
+        scan_ms = eb[0].elapsed_time(eb[1]) / Kb
+        return ms_step, scan_ms, (level1_ms, sample_ms, scan_ev_ms), clk
 
     stored_ms, stored_scan_ms, stored_sample_ms, _ = timed_steps(True, False)
     ms_step, scan_ms, sample_ms, clk = timed_steps(False, True)          # the headline
@@ -349,7 +365,7 @@ def run_ours_single(args):
             "step": "scan that stores the level-2 table (8 B per priority) + level 1 + search + decode + gather; two "
                     "tables used in turn, so a scan may start while the sampling launch on the other table finishes",
             "ms_per_step": stored_ms, "timesteps_per_s": B * L / (stored_ms * 1e-3),
-            "scan_ms": stored_scan_ms, "level1_ms": stored_sample_ms[0], "sample_gather_ms": stored_sample_ms[1], "scan_algorithmic_bytes": stored_scan_bytes,
+            "scan_ms": stored_scan_ms, "scan_ms_with_an_event_on_either_side": stored_sample_ms[2], "level1_ms": stored_sample_ms[0], "sample_gather_ms": stored_sample_ms[1], "scan_algorithmic_bytes": stored_scan_bytes,
             "scan_achieved_gb_s": stored_achieved, "scan_frac_of_measured_peak": stored_achieved / peak,
             "scan_traffic": SCAN_TRAFFIC_BYTES_C3,
             "step_algorithmic_gb_s": stored_step_bytes / (stored_ms * 1e-3) / 1e9,
@@ -363,6 +379,9 @@ def run_ours_single(args):
         "roofline": {"kernel": "scan_kernel<false> (totals only)", "bound": "hbm", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "traffic": SCAN_TOTALS_TRAFFIC_BYTES_C3,
                      "traffic_source": TRAFFIC_SOURCE, "peak_source": peak_src, "algorithmic_bytes": scan_bytes, "avg_launch_ms": scan_ms,
+                     "avg_launch_ms_how": "launches of the kernel alone, back to back and serialised, between one pair of events",
+                     "avg_launch_ms_with_an_event_on_either_side": sample_ms[2],
+                     "frac_with_an_event_on_either_side": scan_bytes / (sample_ms[2] * 1e-3) / 1e9 / peak,
                      "level1_cluster_kernel_ms": sample_ms[0], "sample_gather_kernel_ms": sample_ms[1],
                      "note": "the three launch times are taken with an event on either side of each launch, one "
                              "after the other; in the step the level-1 launch runs beside the next scan and the "
