@@ -211,7 +211,11 @@ int gearb_decode(const int64_t *flat, int64_t b, int64_t trajectory_length,
                  int64_t *len, void *stream);
 
 /* Sampler object: owns cdf, l1, scratch and a status word on the current
- * device, so that repeated scans need no allocation and no clearing.         */
+ * device, so that repeated scans need no allocation and no clearing.  All calls on one sampler
+ * are expected on one stream.  After any of the three whole-table scans of a table of more than
+ * 1024 partitions, the launch that writes l1 is issued lazily -- behind the next scan, beside
+ * which it runs, or in front of the first call that needs l1 (see gearb_sampler_scan_totals);
+ * the first gearb_sampler_sample_gather behind a scan does not need it.                      */
 int gearb_sampler_create(int64_t n, gearb_sampler **out);
 int gearb_sampler_destroy(gearb_sampler *s);
 int gearb_sampler_scan(gearb_sampler *s, const float *priorities, void *stream);
