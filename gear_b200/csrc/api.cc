@@ -541,7 +541,7 @@ static int build_gather_params(gearb_handler *h, const int32_t *columns, int nco
   // Small requests from an HBM table are staged through shared memory by the fused kernel, which
   // copies them out in pieces of 1 KiB so that its four warps get equal shares.
   p.stage_bytes = (t->hbm && stage > 0 && stage <= 24 * 1024) ? static_cast<int32_t>(stage) : 0;
-  if (p.stage_bytes > 0 && piece_bytes == 4096 && staged_pieces)  // the fused launches ask for 4 KiB pieces
+  if (p.stage_bytes > 0 && piece_bytes == GEARB_SG_PIECE && staged_pieces)  // the fused launches ask for 4 KiB pieces
     return build_gather_params(h, columns, ncols, n, dst, zero_fill, status, p, 1024, false);
   // Larger requests: from mapped host memory they stream through per-warp rings of bulk copies
   // (measured on config 4: 51.3 GB/s = 0.92 of the host-to-device copy peak, against 32.0 GB/s with
@@ -856,7 +856,7 @@ int gearb_sampler_sample_gather_affine(gearb_sampler *s, gearb_handler *h, const
   GEARB_REQUIRE(slot_mod >= -1 && slot_mod <= GEARB_MAX_SHARDS && (slot_mod == 0 || slot_mod == 1 || slot_base),
                 "sample_gather: bad slot map");
   GatherParams p;
-  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
+  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, GEARB_SG_PIECE);
   if (rc != GEARB_OK) return rc;
   if (slot_mod > 1 || slot_mod == -1) {
     p.slot_mod = slot_mod;
@@ -883,7 +883,7 @@ int gearb_sampler_sample_gather(gearb_sampler *s, gearb_handler *h, const double
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   GEARB_REQUIRE((flags & ~GEARB_SEARCH_SCALE) == 0, "sample_gather: unknown flag");
   GatherParams p;
-  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, 4096);
+  int rc = build_gather_params(h, columns, ncols, b, dst, zero_fill, s->status, p, GEARB_SG_PIECE);
   if (rc != GEARB_OK) return rc;
   GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
                 "sample_gather: %lld priorities but the table holds only %lld steps", (long long)s->n,
@@ -990,7 +990,7 @@ int gearb_sampler_pull_ex(gearb_sampler *s, gearb_handler *h, const gearb_pull_a
   GEARB_REQUIRE(a->cdf || a->prio, "pull: neither level-2 tables nor priorities were given");
   GEARB_REQUIRE(a->totals || a->mailbox, "pull: neither totals nor a mailbox were given");
   GatherParams p;
-  int rc = build_gather_params(h, a->columns, a->ncols, a->b, a->dst, a->zero_fill, s->status, p, 4096);
+  int rc = build_gather_params(h, a->columns, a->ncols, a->b, a->dst, a->zero_fill, s->status, p, GEARB_SG_PIECE);
   if (rc != GEARB_OK) return rc;
   GEARB_REQUIRE(s->n <= h->table->capacity * h->table->T,
                 "pull: %lld priorities but a shard holds only %lld steps", (long long)s->n,

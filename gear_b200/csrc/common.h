@@ -76,6 +76,10 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
 // the launch, receives the sums of their aggregates; the level-1 launch for this scan gets the
 // same pointer and zeroes the words again at its end.
 #define GEARB_SUPER_PARTS 128
+// Bytes per piece of a request's column in the fused launches' ring of bulk copies.
+#ifndef GEARB_SG_PIECE
+#define GEARB_SG_PIECE 4096
+#endif
 int64_t static_scan_max_n();
 int launch_scan_static(const float *prio, int64_t n, float *cdf, double *l1, int32_t *status,
                        cudaStream_t stream);

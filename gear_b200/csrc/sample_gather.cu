@@ -38,7 +38,7 @@ constexpr unsigned kFull = 0xffffffffu;
 #define GEARB_SG_RING_CTAS 4
 #endif
 constexpr int kRingSlots = GEARB_SG_RING_SLOTS;  // per-warp ring of bulk copies for large requests
-constexpr int kRingSlotBytes = 4096 + 128;  // one 4 KiB piece plus the 16-byte blocks around a misaligned one
+constexpr int kRingSlotBytes = GEARB_SG_PIECE + 128;  // one piece plus the 16-byte blocks around a misaligned one
 constexpr unsigned kWaitLimit = 1u << 20;  // mbarrier polls before a staged copy is declared lost
 // Polls of a peer's epoch word before the peer is declared absent: about four seconds, far beyond the
 // skew between ranks of one job (host jitter included), short enough to come back from a dead peer.
@@ -897,7 +897,7 @@ int launch_any(const GatherParams &p, const SampleArgs &a, const PeerArgs &peers
       for (int pe = 0; pe < 2; ++pe)
         for (int lz = 0; lz < 2; ++lz)
           GEARB_CUDA(cudaFuncSetAttribute(kInstances[pe][lz][kRing], cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(kRingBytes)));
+                                          static_cast<int>(kRingBytes > static_cast<size_t>(kLazyBytes) ? kRingBytes : kLazyBytes)));
       return GEARB_OK;
     }, nullptr);
     if (rc != GEARB_OK) return rc;
