@@ -30,11 +30,14 @@ __all__ = ["HostBatchPipeline"]
 
 class HostBatchPipeline:
     def __init__(self, sampler: PrioritySampler, handler: StorageHandler, columns: Sequence[int], batch: int,
-                 depth: int = 2, store_table: bool = False):
+                 depth: int = 2, store_table: bool = False, batch_to_host: bool = True):
         if depth < 1:
             raise GearError(N.ERR_INVALID, "depth must be at least 1")
         self.sampler, self.handler, self.columns = sampler, handler, [int(c) for c in columns]
         self.batch, self.depth, self.store_table = int(batch), int(depth), bool(store_table)
+        # batch_to_host=False: the gathered columns stay in device memory for a consumer on the GPU
+        # (what the reference's loader returns); only the drawn step ids travel to the host.
+        self.batch_to_host = bool(batch_to_host)
         t = handler.table
         self.slots = [handler.patterns[c].length * t.row_bytes[c] for c in self.columns]
         dev = torch.device("cuda", torch.cuda.current_device())
@@ -43,7 +46,7 @@ class HostBatchPipeline:
         self._dev_flat = [torch.empty(self.batch, dtype=torch.int64, device=dev) for _ in range(self.depth)]
         self._dev_u = [torch.empty(self.batch, dtype=torch.float64, device=dev) for _ in range(self.depth)]
         self._host_cols = [[torch.empty(self.batch * s, dtype=torch.uint8).pin_memory() for s in self.slots]
-                           for _ in range(self.depth)]
+                           for _ in range(self.depth)] if self.batch_to_host else None
         self._host_flat = [torch.empty(self.batch, dtype=torch.int64).pin_memory() for _ in range(self.depth)]
         self._compute = torch.cuda.current_stream()
         self._copy = torch.cuda.Stream()
@@ -71,20 +74,22 @@ class HostBatchPipeline:
             self._computed[b].record(cs)
         self._copy.wait_event(self._computed[b])
         with torch.cuda.stream(self._copy):
-            for h, d in zip(self._host_cols[b], self._dev_cols[b]):
-                h.copy_(d, non_blocking=True)
+            if self.batch_to_host:
+                for h, d in zip(self._host_cols[b], self._dev_cols[b]):
+                    h.copy_(d, non_blocking=True)
             self._host_flat[b].copy_(self._dev_flat[b], non_blocking=True)
             self._copied[b].record(self._copy)
         self._pending.append(b)
         self._submitted += 1
 
     def next(self):
-        """The oldest batch in flight, complete in pinned host memory: (column byte tensors, flat step ids)."""
+        """The oldest batch in flight, complete: (column byte tensors in pinned host memory -- or, with
+        batch_to_host=False, in device memory -- and the flat step ids in pinned host memory)."""
         if not self._pending:
             raise GearError(N.ERR_STATE, "nothing in flight")
         b = self._pending.popleft()
         self._copied[b].synchronize()
-        return self._host_cols[b], self._host_flat[b]
+        return (self._host_cols[b] if self.batch_to_host else self._dev_cols[b]), self._host_flat[b]
 
     def drain(self) -> None:
         while self._pending:

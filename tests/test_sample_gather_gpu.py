@@ -189,7 +189,8 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
     assert shards[0][3].result()[1][0] == 0
 
 
-def test_host_batch_pipeline_delivers_the_same_batches(O):
+@pytest.mark.parametrize("to_host", [True, False])       # False: the columns stay in device memory, only the ids travel
+def test_host_batch_pipeline_delivers_the_same_batches(O, to_host):
     from gear_b200.pipeline import HostBatchPipeline
     rows, T, cap, B, L = [156, 24, 4, 4, 1], 200, 64, 96, 16
     t, img = build(O, rows, T, cap, seed=77)
@@ -201,17 +202,18 @@ def test_host_batch_pipeline_delivers_the_same_batches(O):
     dprio = dev(prio)
     s = core.PrioritySampler(n)
     ocdf, ol1, _, _ = O.scan(prio)
-    pipe = HostBatchPipeline(s, h, cols, B, depth=2)
+    pipe = HostBatchPipeline(s, h, cols, B, depth=2, batch_to_host=to_host)
     us = [torch.from_numpy(O.synth_u01(80 + i, 0, B)).pin_memory() for i in range(5)]
     got = []
     for i, u in enumerate(us):
         pipe.submit(dprio, u)
         if i >= 1:
             hc, hf = pipe.next()
-            got.append(([c.clone() for c in hc], hf.clone()))
+            assert all(c.is_cuda != to_host for c in hc) and not hf.is_cuda
+            got.append(([c.cpu().clone() for c in hc], hf.clone()))
     while len(got) < len(us):
         hc, hf = pipe.next()
-        got.append(([c.clone() for c in hc], hf.clone()))
+        got.append(([c.cpu().clone() for c in hc], hf.clone()))
     with pytest.raises(core.GearError):
         pipe.next()
     for u, (hc, hf) in zip(us, got):
