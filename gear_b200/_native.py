@@ -119,6 +119,7 @@ _SIGS = {
     "gearb_mailbox_bytes": (i64, [i64]),
     "gearb_mailbox_l1_offset": (i64, [i64, u64, C.c_int]),
     "gearb_sampler_publish": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(vp), u64, C.c_int, vp]),
+    "gearb_sampler_scan_totals_publish": (C.c_int, [vp, vp, C.c_int, C.c_int, C.POINTER(vp), u64, vp]),
     "gearb_sampler_pull_ex": (C.c_int, [vp, vp, vp, vp]),
     "gearb_ipc_export": (C.c_int, [vp, vp]),
     "gearb_ipc_open": (C.c_int, [vp, C.POINTER(vp)]),

@@ -543,6 +543,17 @@ class PrioritySampler:
         call("gearb_sampler_publish", self._h, int(world), int(rank), arr, C.c_uint64(int(epoch)),
              int(bool(copy_l1)), _stream(stream))
 
+    def scan_publish(self, priorities: torch.Tensor, world: int, rank: int, mailboxes: Sequence[int], epoch: int,
+                     stream=None) -> None:
+        """scan(priorities, store=False) and publish(..., copy_l1=False) as one call: for tables of more
+        than 1024 partitions the launch that builds level 1 also writes the mailboxes."""
+        if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
+            raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
+        arr = (C.c_void_p * int(world))(*[int(x) for x in mailboxes])
+        call("gearb_sampler_scan_totals_publish", self._h, _ptr(priorities), int(world), int(rank), arr,
+             C.c_uint64(int(epoch)), _stream(stream))
+        self._lazy_source = priorities
+
     def publish_total(self, world: int, rank: int, mailboxes: Sequence[int], epoch: int, stream=None) -> None:
         self.publish(world, rank, mailboxes, epoch, False, stream)
 

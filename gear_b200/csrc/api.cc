@@ -974,6 +974,38 @@ int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *ma
   return launch_publish(s->l1(), s->nparts, world, rank, mailboxes, epoch, copy_l1, counter, as_stream(stream));
 }
 
+int gearb_sampler_scan_totals_publish(gearb_sampler *s, const float *priorities, int world, int rank,
+                                      void *const *mailboxes, uint64_t epoch, void *stream) {
+  TraceRange trace("gearb:scan_totals+publish");
+  GEARB_REQUIRE(s && mailboxes, "scan_totals_publish: null argument");
+  GEARB_REQUIRE(world >= 1 && world <= GEARB_MAX_SHARDS && rank >= 0 && rank < world && epoch > 0,
+                "scan_totals_publish: bad rank, world or epoch");
+  int rc = s->settle(as_stream(stream));  // peers read this table's level 1: nothing is left owing here
+  if (rc != GEARB_OK) return rc;
+  const int before = s->slot;
+  const int slot = s->take_slot();
+  PublishTail tail;
+  tail.world = world;
+  tail.rank = rank;
+  tail.epoch = epoch;
+  for (int j = 0; j < world; ++j) {
+    GEARB_REQUIRE(mailboxes[j], "scan_totals_publish: null mailbox for rank %d", j);
+    tail.box[j] = mailboxes[j];
+  }
+  // Tables whose level 1 is its own launch let that launch write the mailboxes at its end; the
+  // others (at most 1024 partitions: level 1 by the scan's last CTA) take the publish launch.
+  const bool in_level1 = s->nparts > 1024 && level1_can_follow_next_scan(s->nparts);
+  rc = launch_scan(priorities, s->n, nullptr, s->l1s[slot], s->scratch(), s->scratch_bytes, s->status, 0,
+                   as_stream(stream), true, /*overlap_previous=*/s->may_overlap() && slot != before, s->blk[slot],
+                   nullptr, in_level1 ? &tail : nullptr);
+  if (rc != GEARB_OK) return rc;
+  s->lazy_prio = priorities;
+  s->scan_unconsumed = false;  // the level-1 launch behind the scan waits for it
+  if (in_level1) return GEARB_OK;
+  unsigned *counter = &static_cast<ScanHeader *>(s->scratch())->pad[kPadPublish];
+  return launch_publish(s->l1(), s->nparts, world, rank, mailboxes, epoch, 0, counter, as_stream(stream));
+}
+
 int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
                                 void *stream) {
   return gearb_sampler_publish(s, world, rank, mailboxes, epoch, 0, stream);

@@ -63,6 +63,7 @@ static_assert(sizeof(ScanHeader) == 256, "header is one 256-byte block");
 // Words of ScanHeader::pad beyond those the level-1 launch uses (level1.cu: 1-4, 9-24).
 enum { kPadPublish = 30 };  // CTA counter of the publish launch
 
+struct PublishTail;
 int64_t scan_scratch_bytes(int64_t n);
 // fresh != 0: scratch contents are unknown, clear them first (one memset).
 // level1 == false: only the partitions' aggregates (and the cdf) are produced; the caller
@@ -71,7 +72,8 @@ int64_t scan_scratch_bytes(int64_t n);
 // this call; l1 is written by the level-1 launch, which waits for everything before it).
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream,
-                bool level1 = true, bool overlap_previous = false, float *blkw = nullptr, double *sb = nullptr);
+                bool level1 = true, bool overlap_previous = false, float *blkw = nullptr, double *sb = nullptr,
+                const PublishTail *publish = nullptr);
 // sb (tables of more than 1024 partitions): one float64 per GEARB_SUPER_PARTS partitions, zero before
 // the launch, receives the sums of their aggregates; the level-1 launch for this scan gets the
 // same pointer and zeroes the words again at its end.
@@ -90,9 +92,17 @@ float *scan_aggregate_words(void *scratch);
 // beside that scan, and waits for it only before its clean-up -- so whatever follows finds both
 // complete, and nothing that still reads the header words or the sums can be running.
 bool level1_can_follow_next_scan(int64_t nparts);
+// A rank's total and the step's number into every rank's mailbox, done by the level-1 launch
+// itself at its end (the place of a separate publish launch without a level-1 copy).
+struct PublishTail {
+  void *box[GEARB_MAX_SHARDS];
+  int world = 0;  // 0: nothing to publish
+  int rank = 0;
+  unsigned long long epoch = 0;
+};
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
                   cudaStream_t stream, ScanHeader *hdr, bool have_range, double *sb = nullptr,
-                  bool after_next = false);
+                  bool after_next = false, const PublishTail *publish = nullptr);
 int64_t update_scratch_bytes(int64_t n);
 int launch_update(float *prio, int64_t n, float *cdf, double *l1, float *aggw, float *blkw, ScanHeader *hdr,
                   void *upd, const int64_t *idx, const float *val, int64_t m, int32_t *status, cudaStream_t stream);

@@ -37,7 +37,8 @@ struct Shared {
 // header; otherwise (aggregates touched by an incremental update) the cluster finds it first.
 __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterThreads)
     level1_cluster_kernel(const float *agg, unsigned nparts, double *l1, unsigned *clear_word, int32_t *status,
-                          ScanHeader *hdr, int have_range, double *sb, int after_next) {
+                          ScanHeader *hdr, int have_range, double *sb, int after_next,
+                          const __grid_constant__ PublishTail pub) {
   extern __shared__ float4 tile4[];  // level1::kTile floats
   __shared__ Shared sh;
   float *tile = reinterpret_cast<float *>(tile4);
@@ -162,6 +163,24 @@ __global__ void __cluster_dims__(kClusterCtas, 1, 1) __launch_bounds__(kClusterT
       hdr->pad[kPadBad] = 0u;
       hdr->pad[kPadDone] = 0u;
       if (clear_word) *clear_word = 0u;
+      if (pub.world > 0) {
+        // The table is complete (every rank's fence came before its count above): this shard's
+        // total, then -- behind ONE fence at system scope -- the step's number, into every
+        // rank's mailbox.  The pull launches wait for that number with acquire loads.
+        const unsigned slot = static_cast<unsigned>(pub.epoch & 1u);
+        const double t = __ldcg(l1 + nparts);
+        for (int j = 0; j < pub.world; ++j) {
+          double *tot = reinterpret_cast<double *>(pub.box[j]) + slot * GEARB_MAX_SHARDS + pub.rank;
+          asm volatile("st.relaxed.sys.global.f64 [%0], %1;" ::"l"(tot), "d"(t) : "memory");
+        }
+        __threadfence_system();
+        for (int j = 0; j < pub.world; ++j) {
+          unsigned long long *ep = reinterpret_cast<unsigned long long *>(static_cast<char *>(pub.box[j]) +
+                                                                          2 * GEARB_MAX_SHARDS * 8) +
+                                   slot * GEARB_MAX_SHARDS + pub.rank;
+          asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(ep), "l"(pub.epoch) : "memory");
+        }
+      }
     }
     // Everything this launch reads has been read (by the last rank too, had it to repeat the sum
     // in order): the launch behind it may be scheduled.  If that is the next scan of the same
@@ -199,8 +218,12 @@ bool level1_can_follow_next_scan(int64_t nparts) {
 }
 
 int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_word, int32_t *status,
-                  cudaStream_t stream, ScanHeader *hdr, bool have_range, double *sb, bool after_next) {
+                  cudaStream_t stream, ScanHeader *hdr, bool have_range, double *sb, bool after_next,
+                  const PublishTail *publish) {
   GEARB_REQUIRE(!after_next || level1_can_follow_next_scan(nparts), "level1: table too large to follow the next scan");
+  GEARB_REQUIRE(!publish || (level1_can_follow_next_scan(nparts) && !after_next),
+                "level1: publishing from this launch needs the cluster kernel in its usual place");
+  const PublishTail none = PublishTail();
   constexpr int kTileBytes = level1::kTile * sizeof(float);
   {
     int rc = per_device_once(kOnceLevel1, [](int *) -> int {  // function attributes are per device
@@ -226,7 +249,8 @@ int launch_level1(const float *agg, int64_t nparts, double *l1, unsigned *clear_
     const unsigned per = ((np + kClusterCtas - 1) / kClusterCtas + 3u) & ~3u;
     cfg.dynamicSmemBytes = per * 4u < 1024u ? 1024u : per * 4u;
     GEARB_CUDA(cudaLaunchKernelEx(&cfg, level1_cluster_kernel, agg, np, l1, clear_word, status, hdr,
-                                  static_cast<int>(have_range), sb, static_cast<int>(after_next)));
+                                  static_cast<int>(have_range), sb, static_cast<int>(after_next),
+                                  publish ? *publish : none));
   } else {
     cfg.gridDim = dim3(1);
     cfg.blockDim = dim3(1024);

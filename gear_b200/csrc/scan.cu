@@ -648,7 +648,7 @@ int64_t scan_scratch_bytes(int64_t n) {
 
 int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scratch,
                 int64_t scratch_bytes, int32_t *status, int fresh, cudaStream_t stream, bool level1,
-                bool overlap_previous, float *blkw, double *sb) {
+                bool overlap_previous, float *blkw, double *sb, const PublishTail *publish) {
   GEARB_REQUIRE(n > 0, "scan: n must be positive (got %lld)", (long long)n);
   GEARB_REQUIRE(prio && l1 && scratch && status, "scan: null pointer argument");  // cdf may be null
   GEARB_REQUIRE((reinterpret_cast<uintptr_t>(prio) & 15) == 0 &&
@@ -741,7 +741,7 @@ int launch_scan(const float *prio, int64_t n, float *cdf, double *l1, void *scra
   }
   // level 1 from the aggregates: a second, small launch (level1.cu), unless the last CTA did it
   return (a.inline_level1 || !level1) ? GEARB_OK
-                                       : launch_level1(a.aggw, nparts, l1, nullptr, status, stream, a.hdr, true, a.sb, false);
+                                       : launch_level1(a.aggw, nparts, l1, nullptr, status, stream, a.hdr, true, a.sb, false, publish);
 }
 
 int launch_scan_search(const float *prio, int64_t n, float *cdf, double *l1, void *scratch, int64_t scratch_bytes,

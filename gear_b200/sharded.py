@@ -442,9 +442,11 @@ class ShardedReplay:
             self._pull_box.free()
             self._pull_box = None
 
-    def pull_scan(self, priorities, between=None) -> None:
+    def pull_scan(self, priorities, between=None, publish_epoch=None) -> None:
         """Rebuild this shard's cumulative table into the buffer the next step_pull(rescan=False) reads.
-        between: called between the scan's two launches (a benchmark records an event there)."""
+        between: called between the scan's two launches (a benchmark records an event there).
+        publish_epoch (tables without stored level 2, mailbox, no level-1 copy): the scan's level-1
+        launch also writes this shard's total and that epoch into every rank's mailbox."""
         self._pull_k += 1
         sm = self._pull_samplers[self._pull_k % len(self._pull_samplers)]
         if self._pull_lazy:
@@ -454,7 +456,9 @@ class ShardedReplay:
         store = not self._pull_lazy
         if store:
             sm.select_slot(0)       # the peers hold the address of this sampler's slot-0 tables
-        if between is None:
+        if publish_epoch is not None:
+            sm.scan_publish(priorities, self.world, self.rank, self._pull_boxes, publish_epoch)
+        elif between is None:
             # with two tables in turn, the launch before this one (the previous pull) reads the other
             sm.scan(priorities, store=store, alternate=store and len(self._pull_samplers) == 2)
         else:
@@ -474,8 +478,13 @@ class ShardedReplay:
             raise ValueError(f"global batch {B}: at most {self.maxB} and a multiple of {self.world}")
         b = B // self.world
         nbuf = len(self._pull_samplers)
+        copy = (layout == "scattered") if self._pull_copy_l1 == "auto" else bool(self._pull_copy_l1)
+        # scan and publish in one call where the publish is only the total and the epoch
+        fuse = self._pull_box is not None and self._pull_lazy and not copy
+        published = False
         if rescan or self._pull_k < 0:
-            self.pull_scan(priorities)
+            self.pull_scan(priorities, publish_epoch=self._pull_epoch + 1 if fuse else None)
+            published = fuse
         k = self._pull_k % nbuf
         sm = self._pull_samplers[k]
         if layout == "contiguous":
@@ -492,8 +501,8 @@ class ShardedReplay:
             # totals through the mailboxes: no collective, no host involvement
             self._pull_epoch += 1
             e = self._pull_epoch
-            copy = (layout == "scattered") if self._pull_copy_l1 == "auto" else bool(self._pull_copy_l1)
-            sm.publish(self.world, self.rank, self._pull_boxes, e, copy_l1=copy)
+            if not published:
+                sm.publish(self.world, self.rank, self._pull_boxes, e, copy_l1=copy)
             if self._pull_lazy:
                 from . import core
                 if copy:

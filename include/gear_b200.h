@@ -400,6 +400,11 @@ int64_t gearb_mailbox_bytes(int64_t n);
 int64_t gearb_mailbox_l1_offset(int64_t n, uint64_t epoch, int shard);
 int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
                           int copy_l1, void *stream);
+/* gearb_sampler_scan_totals followed by gearb_sampler_publish (without the level-1 copy) as one
+ * call: for tables of more than 1024 partitions the launch that builds level 1 writes the total
+ * and the epoch into the mailboxes at its end, which saves the publish launch of every step.  */
+int gearb_sampler_scan_totals_publish(gearb_sampler *s, const float *priorities, int world, int rank,
+                                      void *const *mailboxes, uint64_t epoch, void *stream);
 /* The general form of gearb_sampler_pull / gearb_sampler_pull_mailbox.  Per shard either its
  * stored level-2 table (cdf) or, with cdf == NULL, its priorities and block totals (prio, blk:
  * the slot of the step, see gearb_sampler_select_slot) -- then the shards may have been scanned
