@@ -118,6 +118,7 @@ _SIGS = {
     "gearb_sampler_clear_status": (C.c_int, [vp, vp]),
     "gearb_mailbox_bytes": (i64, [i64]),
     "gearb_mailbox_l1_offset": (i64, [i64, u64, C.c_int]),
+    "gearb_mailbox_blk_offset": (i64, [i64, u64, C.c_int]),
     "gearb_sampler_publish": (C.c_int, [vp, C.c_int, C.c_int, C.POINTER(vp), u64, C.c_int, vp]),
     "gearb_sampler_scan_totals_publish": (C.c_int, [vp, vp, C.c_int, C.c_int, C.POINTER(vp), u64, vp]),
     "gearb_sampler_pull_ex": (C.c_int, [vp, vp, vp, vp]),

@@ -649,6 +649,11 @@ def mailbox_l1_offset(n: int, epoch: int, shard: int) -> int:
     return int(lib.gearb_mailbox_l1_offset(int(n), C.c_uint64(int(epoch)), int(shard)))
 
 
+def mailbox_blk_offset(n: int, epoch: int, shard: int) -> int:
+    """Byte offset, inside a mailbox for shards of n priorities, of `shard`'s block-total copy for `epoch`."""
+    return int(lib.gearb_mailbox_blk_offset(int(n), C.c_uint64(int(epoch)), int(shard)))
+
+
 def ipc_export(device_ptr: int) -> bytes:
     """64-byte handle of a device allocation of this process, for the other ranks of the box."""
     buf = C.create_string_buffer(N.IPC_HANDLE_BYTES)

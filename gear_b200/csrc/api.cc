@@ -952,13 +952,18 @@ int gearb_device_free(void *ptr) {
 }
 
 int64_t gearb_mailbox_bytes(int64_t n) {
-  return n > 0 ? GEARB_MAILBOX_BYTES + 2 * GEARB_MAX_SHARDS * mailbox_l1_stride(n) : GEARB_MAILBOX_BYTES;
+  return n > 0 ? mailbox_blk_base(n) + 2 * GEARB_MAX_SHARDS * mailbox_blk_stride(n) : GEARB_MAILBOX_BYTES;
 }
 
 int64_t gearb_mailbox_l1_offset(int64_t n, uint64_t epoch, int shard) {
   if (n <= 0 || shard < 0 || shard >= GEARB_MAX_SHARDS) return -1;
   return GEARB_MAILBOX_BYTES +
          (static_cast<int64_t>(epoch & 1u) * GEARB_MAX_SHARDS + shard) * mailbox_l1_stride(n);
+}
+
+int64_t gearb_mailbox_blk_offset(int64_t n, uint64_t epoch, int shard) {
+  if (n <= 0 || shard < 0 || shard >= GEARB_MAX_SHARDS) return -1;
+  return mailbox_blk_base(n) + (static_cast<int64_t>(epoch & 1u) * GEARB_MAX_SHARDS + shard) * mailbox_blk_stride(n);
 }
 
 int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
@@ -971,7 +976,9 @@ int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *ma
   }
   s->scan_unconsumed = false;  // this launch waits for the scan before it (see may_overlap)
   unsigned *counter = &static_cast<ScanHeader *>(s->scratch())->pad[kPadPublish];
-  return launch_publish(s->l1(), s->nparts, world, rank, mailboxes, epoch, copy_l1, counter, as_stream(stream));
+  // with the level-1 copy, a table without stored level 2 also sends its block totals of this step
+  return launch_publish(s->l1(), s->nparts, world, rank, mailboxes, epoch, copy_l1, counter, as_stream(stream),
+                        (copy_l1 && s->lazy_prio) ? s->blk[s->slot] : nullptr);
 }
 
 int gearb_sampler_scan_totals_publish(gearb_sampler *s, const float *priorities, int world, int rank,

@@ -193,9 +193,14 @@ int launch_pull(const GatherParams &p, int world, int self, const double *totals
                 int64_t *out_ts, cudaStream_t stream, const void *mailbox, unsigned long long epoch,
                 const DrawLayout &lay);
 // Mailbox layout (one per rank, GEARB_MAILBOX_BYTES of header, then optional level-1 copies).
+// behind the level-1 copies: copies of the block totals [2 slots][GEARB_MAX_SHARDS] of blk_stride bytes each
 int64_t mailbox_l1_stride(int64_t n);
+int64_t mailbox_blk_stride(int64_t n);
+int64_t mailbox_blk_base(int64_t n);
+// blk (with copy_l1): the rank's block totals of the step travel with its level 1.
 int launch_publish(const double *l1, int64_t nparts, int world, int rank, void *const *mailboxes,
-                   unsigned long long epoch, int copy_l1, unsigned *counter, cudaStream_t stream);
+                   unsigned long long epoch, int copy_l1, unsigned *counter, cudaStream_t stream,
+                   const float *blk = nullptr);
 int launch_vcopy(const uint8_t *src, uint8_t *dst, const int64_t *src_off,
                  const int64_t *dst_off, const int64_t *lengths, int64_t fixed_length,
                  int64_t n, int64_t max_length, cudaStream_t stream);

@@ -965,7 +965,8 @@ constexpr int kPublishThreads = 256;
 // pull launches of the other ranks wait for.
 __global__ void __launch_bounds__(kPublishThreads)
     publish_kernel(const double *l1, unsigned nparts, Mailboxes m, int world, int rank, unsigned long long epoch,
-                   int copy_l1, long long l1_stride, unsigned *counter) {
+                   int copy_l1, long long l1_stride, unsigned *counter, const float *blk, long long blk_base,
+                   long long blk_stride) {
   __shared__ int is_last;
   asm volatile("griddepcontrol.wait;" ::: "memory");  // level 1 comes from the launch before
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -979,6 +980,18 @@ __global__ void __launch_bounds__(kPublishThreads)
         double *dst = reinterpret_cast<double *>(static_cast<char *>(m.box[j]) + GEARB_MAILBOX_BYTES +
                                                  (static_cast<long long>(slot) * GEARB_MAX_SHARDS + rank) * l1_stride);
         dst[i] = v;
+      }
+    }
+    if (blk) {  // the eight block totals of every partition travel too: 32 bytes per partition, as two float4
+      const unsigned quads = nparts * 2u;
+      for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < quads; i += gridDim.x * blockDim.x) {
+        const float4 v = __ldcg(reinterpret_cast<const float4 *>(blk) + i);
+        for (int j = 0; j < world; ++j) {
+          if (j == rank) continue;
+          float4 *dst = reinterpret_cast<float4 *>(static_cast<char *>(m.box[j]) + blk_base +
+                                                   (static_cast<long long>(slot) * GEARB_MAX_SHARDS + rank) * blk_stride);
+          dst[i] = v;
+        }
       }
     }
     __threadfence_system();
@@ -1015,9 +1028,14 @@ int64_t mailbox_l1_stride(int64_t n) {
   const int64_t nparts = (n + GEARB_PART - 1) / GEARB_PART;
   return ((nparts + 1) * 8 + 255) & ~int64_t(255);
 }
+int64_t mailbox_blk_stride(int64_t n) {
+  const int64_t nparts = (n + GEARB_PART - 1) / GEARB_PART;
+  return (nparts * 32 + 255) & ~int64_t(255);
+}
+int64_t mailbox_blk_base(int64_t n) { return GEARB_MAILBOX_BYTES + 2 * GEARB_MAX_SHARDS * mailbox_l1_stride(n); }
 
 int launch_publish(const double *l1, int64_t nparts, int world, int rank, void *const *mailboxes,
-                   unsigned long long epoch, int copy_l1, unsigned *counter, cudaStream_t stream) {
+                   unsigned long long epoch, int copy_l1, unsigned *counter, cudaStream_t stream, const float *blk) {
   GEARB_REQUIRE(world >= 1 && world <= GEARB_MAX_SHARDS && rank >= 0 && rank < world, "publish: bad rank or world");
   GEARB_REQUIRE(l1 && mailboxes && epoch > 0, "publish: null argument or epoch 0");
   GEARB_REQUIRE(!copy_l1 || counter, "publish: the level-1 copy needs a counter word");
@@ -1029,7 +1047,7 @@ int launch_publish(const double *l1, int64_t nparts, int world, int rank, void *
   cudaLaunchConfig_t cfg = {};
   int64_t grid = 1;
   if (copy_l1 && world > 1) {
-    grid = (nparts + 1 + kPublishThreads - 1) / kPublishThreads;
+    grid = ((blk ? nparts * 2 : nparts + 1) + kPublishThreads - 1) / kPublishThreads;
     if (grid > 32) grid = 32;
   }
   cfg.gridDim = dim3(static_cast<unsigned>(grid));
@@ -1042,7 +1060,10 @@ int launch_publish(const double *l1, int64_t nparts, int world, int rank, void *
   cfg.numAttrs = 1;
   const long long stride = mailbox_l1_stride(nparts * GEARB_PART);
   GEARB_CUDA(cudaLaunchKernelEx(&cfg, publish_kernel, l1, static_cast<unsigned>(nparts), m, world, rank, epoch,
-                                (copy_l1 && world > 1) ? 1 : 0, stride, counter));
+                                (copy_l1 && world > 1) ? 1 : 0, stride, counter,
+                                (copy_l1 && world > 1) ? blk : nullptr,
+                                static_cast<long long>(mailbox_blk_base(nparts * GEARB_PART)),
+                                static_cast<long long>(mailbox_blk_stride(nparts * GEARB_PART))));
   return GEARB_OK;
 }
 

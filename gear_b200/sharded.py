@@ -505,14 +505,18 @@ class ShardedReplay:
                 sm.publish(self.world, self.rank, self._pull_boxes, e, copy_l1=copy)
             if self._pull_lazy:
                 from . import core
+                blks = self._pull_blks[self._pull_slot]
                 if copy:
+                    # level 1 and the block totals of the peers came with their totals: read here, not over NVLink
                     l1s = [sm.l1_ptr if j == self.rank else self._pull_box.ptr + core.mailbox_l1_offset(self.n_local, e, j)
                            for j in range(self.world)]
+                    blks = [blks[j] if j == self.rank else self._pull_box.ptr + core.mailbox_blk_offset(self.n_local, e, j)
+                            for j in range(self.world)]
                 else:
                     l1s = self._pull_l1_remote[self._pull_slot]
                 sm.pull(self.handler, None, None, l1s, self._pull_tables, mine, self.columns, recv,
                         mailbox=self._pull_box.ptr, epoch=e, prios=self._pull_prios,
-                        blks=self._pull_blks[self._pull_slot], **common)
+                        blks=blks, **common)
             else:
                 sm.pull(self.handler, None, self._pull_cdfs[k], self._pull_l1s[k], self._pull_tables, mine,
                         self.columns, recv, mailbox=self._pull_box.ptr, epoch=e, **common)

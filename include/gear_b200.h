@@ -398,6 +398,10 @@ int gearb_sampler_publish_total(gearb_sampler *s, int world, int rank, void *con
  * rank's mailbox before the total and the epoch.                                          */
 int64_t gearb_mailbox_bytes(int64_t n);
 int64_t gearb_mailbox_l1_offset(int64_t n, uint64_t epoch, int shard);
+/* With copy_l1 a sampler scanned by gearb_sampler_scan_totals also sends its block totals (32 bytes
+ * per partition): gearb_mailbox_blk_offset is where shard's copy for that epoch lies, to be passed
+ * as that shard's `blk` to gearb_sampler_pull_ex.  gearb_mailbox_bytes covers both kinds.      */
+int64_t gearb_mailbox_blk_offset(int64_t n, uint64_t epoch, int shard);
 int gearb_sampler_publish(gearb_sampler *s, int world, int rank, void *const *mailboxes, uint64_t epoch,
                           int copy_l1, void *stream);
 /* gearb_sampler_scan_totals followed by gearb_sampler_publish (without the level-1 copy) as one
