@@ -580,8 +580,12 @@ class PrioritySampler:
         than 1024 partitions the launch that builds level 1 also writes the mailboxes."""
         if priorities.dtype != torch.float32 or not priorities.is_cuda or priorities.numel() != self.n:
             raise GearError(N.ERR_INVALID, f"priorities must be float32 CUDA with {self.n} entries")
-        arr = (C.c_void_p * int(world))(*[int(x) for x in mailboxes])
-        call("gearb_sampler_scan_totals_publish", self._h, _ptr(priorities), int(world), int(rank), arr,
+        key = (int(world), tuple(int(x) for x in mailboxes))
+        cached = getattr(self, "_mailbox_arr", None)
+        if cached is None or cached[0] != key:            # marshalled once: this call is made every step
+            cached = (key, (C.c_void_p * int(world))(*key[1]))
+            self._mailbox_arr = cached
+        call("gearb_sampler_scan_totals_publish", self._h, _ptr(priorities), int(world), int(rank), cached[1],
              C.c_uint64(int(epoch)), _stream(stream))
         self._lazy_source = priorities
 
