@@ -129,11 +129,15 @@ __device__ __forceinline__ void block_values(float X, const Group &g, float *xs,
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const float off = xs[k * 32 + lane];
+    // An entry before which its chunk holds only zeros (running sum still 0) counts as 0: it takes
+    // no part in any maximum and so repeats the running maximum before it bit for bit -- the
+    // chunk's offset can be an ulp above the previous chunk's last value, and an entry of weight
+    // zero must never be the first one greater than a variate.
     if (!only_tops || !whole) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) sv[k][j] = __fadd_rn(off, sv[k][j]);
+      for (int j = 0; j < 4; ++j) sv[k][j] = sv[k][j] == 0.f ? 0.f : __fadd_rn(off, sv[k][j]);
     } else {
-      sv[k][3] = __fadd_rn(off, sv[k][3]);
+      sv[k][3] = sv[k][3] == 0.f ? 0.f : __fadd_rn(off, sv[k][3]);
     }
     top[k] = sv[k][3];  // sums of non-negative terms do not decrease inside a chunk
     if (!whole) {       // entries past n take no part in any maximum (and are never stored)

@@ -187,6 +187,13 @@ void gearo_fused_subcopy(const uint8_t *table, uint8_t *dst, const int64_t *idx,
  * inversions a tree-shaped float scan can leave between chunks, so that the
  * stored table is non-decreasing and "first entry greater than r" is well
  * defined for any search order.  Entries past n count as zero.
+ * One exception keeps "a zero priority repeats its predecessor's entry" exact:
+ * inside a chunk that holds for zeros (s_j = s_(j-1)), but a chunk that BEGINS
+ * with zeros would give them the chunk's offset O, which can be an ulp above
+ * the previous chunk's last value (two roundings of the same sum) -- and an
+ * entry of weight zero could then be the first one greater than r.  Entries
+ * with s_j = 0 therefore take no part in the maximum (their value counts as
+ * 0) and so repeat the running maximum before them.
  *
  * Level 1: l1[0]=0, l1[p+1] = l1[p] + (double)aggregate(p), added in partition order in
  * float64, where aggregate(p) = X(8) is the partition's eight block totals added in sequence
@@ -241,7 +248,9 @@ static float scan_partition(const float *x, int64_t valid, float *out) {
         const int e0 = w * GEARO_BLOCK + 16 * q + 4 * i;
         const float off = (i == 0) ? b : b + gprev[e0 / 4];
         for (int j = 0; j < 4; ++j) {
-          const float v = off + s[e0 + j];
+          /* an entry before which its chunk holds only zeros takes no part in the maximum:
+           * it repeats what came before it, bit for bit (see the comment above)           */
+          const float v = (s[e0 + j] == 0.0f) ? 0.0f : off + s[e0 + j];
           if (v > run) run = v;
           out[e0 + j] = run;
         }

@@ -277,6 +277,7 @@ def np_scan(prio: np.ndarray):
     for i in range(1, 4):
         off[..., i] = b + g[..., i - 1]
     o = off[..., None] + s                                 # [P,W,32,4,4]
+    o = np.where(s == 0, np.float32(0), o)                 # a chunk's leading zeros take no part in the maximum
     o = o.reshape(nparts, PART).astype(np.float32)
     cdf = np.maximum.accumulate(o, axis=1)
     flat = cdf.reshape(-1)

@@ -518,3 +518,36 @@ def test_scan_and_draw_edge_tables(O):
     _, st = s.result()
     assert np.array_equal(got.cpu().numpy(), O.search(ocdf, ol1, hu, scale=True))
     assert np.array_equal(s.l1.cpu().numpy(), ol1) and st[0] & N.ST_L1_RESUMMED
+
+
+def test_entries_of_weight_zero_are_never_drawn(O):
+    # A chunk that begins with zeros would give them its offset, which can be an ulp above the
+    # previous chunk's last value; the tree counts such entries as 0 in its running maximum, so
+    # they repeat what came before bit for bit.  Variates aimed exactly at those places.
+    n = 40 * 4096 + 1234
+    rng = np.random.default_rng(11)
+    p = rng.lognormal(0, 1, n).astype(np.float32)
+    p[rng.random(n) < 0.7] = 0.0
+    p[4096 * 3: 4096 * 5] = 0.0                      # whole partitions without weight
+    dp = dev(p)
+    s = core.PrioritySampler(n)
+    s.scan(dp)
+    cdf, l1 = s.cdf.cpu().numpy(), s.l1.cpu().numpy()
+    ocdf, ol1, total, _ = O.scan(p)
+    assert np.array_equal(cdf, ocdf) and np.array_equal(l1, ol1)
+    prev = np.concatenate([[0], cdf[:-1]]); prev[::4096] = 0
+    assert np.array_equal(cdf[p == 0], prev[p == 0])  # a zero priority repeats its predecessor's entry exactly
+    # variates on, just below and just above every entry that precedes an entry of weight zero
+    z = np.nonzero(p == 0)[0]
+    part = z // 4096
+    edge = prev[z].astype(np.float64) + l1[part]
+    u = np.concatenate([edge, np.nextafter(edge, 0), np.nextafter(edge, np.inf), rng.random(500_000) * total])
+    u = np.clip(u, 0, np.nextafter(total, 0))
+    got = s.search(dev(u)).cpu().numpy()
+    assert np.array_equal(got, O.search(ocdf, ol1, u))
+    assert (p[got] > 0).all()
+    # the same through the one-launch scan + draw (a small table) and the draw that rebuilds blocks
+    m = 30 * 4096
+    s2 = core.PrioritySampler(m)
+    got2 = s2.scan_search(dev(p[:m]), dev(rng.random(100_000)), scale=True).cpu().numpy()
+    assert (p[:m][got2] > 0).all()
