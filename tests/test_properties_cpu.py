@@ -90,3 +90,54 @@ def test_sorted_routing_equals_request_by_request_routing(world, per_rank, layou
         assert plan.send_count.sum() == len(want.mine) and plan.recv_count.sum() == per_rank
         seen[want.mine] += 1
     assert np.all(seen == 1)                          # every request has exactly one owner
+
+
+@settings(**SET)
+@given(st.sampled_from([2, 3, 4, 8]), st.integers(1, 30), st.integers(0, 2**31 - 1))
+def test_scattered_slot_map_delivers_every_answer_to_its_place(world, per_rank, seed):
+    """Simulate the all-to-all of the scattered layout with the slot maps alone: every owner writes
+    its answers at base[q % world] + q // world, the regions travel as send_first/send_count say,
+    and each requester must end up with its slice of the batch in order."""
+    rng = np.random.default_rng(seed)
+    B = world * per_rank
+    totals = rng.lognormal(0, 1, world)
+    totals[rng.random(world) < 0.25] = 0.0
+    if totals.sum() == 0:
+        totals[-1] = 2.0
+    u = np.sort(rng.random(B))
+    plans = [sharded.plan_layout(totals, u, r, world, "scattered") for r in range(world)]
+    received = [np.full(per_rank, -1, np.int64) for _ in range(world)]
+    for owner in range(world):
+        plan, _, _, (mod, lo, base) = plans[owner]
+        region = np.full(int(plan.send_count.sum()), -1, np.int64)      # the owner's send regions, by requester
+        for q in plan.mine:                                              # what the owner's launch does per request
+            slot = int(base[q % mod]) + q // mod
+            assert region[slot] == -1
+            region[slot] = q
+        assert np.all(region >= 0)
+        for req in range(world):                                         # what the exchange does per pair
+            c, f = int(plan.send_count[req]), int(plan.send_first[req])
+            rplan = plans[req][0]
+            assert int(rplan.recv_count[owner]) == c
+            dst = int(rplan.recv_first[owner])
+            received[req][dst:dst + c] = region[f:f + c]
+    for req in range(world):
+        assert np.array_equal(received[req], np.arange(req, B, world))   # rank r's slice: positions r, r + world, ...
+
+
+@settings(**SET)
+@given(st.integers(1, 2 * 4096 + 9), st.integers(0, 2**31 - 1))
+def test_any_variate_draws_an_entry_with_weight(n, seed):
+    rng = np.random.default_rng(seed)
+    p = rng.lognormal(0, 3, n).astype(np.float32)
+    p[rng.random(n) < rng.random()] = 0.0
+    if not p.any():
+        p[int(rng.integers(0, n))] = 1.0
+    cdf, l1, total, _ = O.scan(p)
+    wild = np.array([0.0, -1.0, np.nan, np.inf, -np.inf, total, total * 2, np.nextafter(total, 0), 5e-324,
+                     *(rng.random(50) * total), *l1, *np.nextafter(l1, 0), *np.nextafter(l1, np.inf)])
+    got = O.search(cdf, l1, wild)
+    assert np.all((got >= 0) & (got < n)) and np.all(p[got] > 0)
+    assert np.array_equal(got, O.np_search(cdf, l1, wild))
+    flat = O.uniform(rng.random(100), n)
+    assert np.all((flat >= 0) & (flat < n))
