@@ -532,3 +532,52 @@ def test_random_call_sequences_keep_tables_and_draws_exact(O, seed):
                 assert np.array_equal(s.cdf.cpu().numpy(), ocdf)
     tot, st = s.result()
     assert tot == oracle()[2] and st[0] & ~N.ST_L1_RESUMMED == 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_tables_patterns_and_paths(O, seed):
+    # Random row sets (which decide between the staged, the direct and -- for a host table -- the
+    # ring path), offsets of either sign, both paddings, ragged lengths, stored and rebuilt level 2.
+    rng = np.random.default_rng(100 + seed)
+    for trial in range(7):
+        ncols = int(rng.integers(1, 5))
+        big = rng.random() < 0.35
+        rows = [int(rng.integers(1, 700 if big else 90)) for _ in range(ncols)]
+        T = int(rng.integers(8, 120))
+        cap = int(rng.integers(3, 40))
+        L = int(rng.integers(1, min(T, 48) + 1))
+        host = rng.random() < 0.25
+        t = core.TrajectoryTable(rows, T, cap, residency=N.RES_HOST if host else N.RES_HBM)
+        t.connect()
+        img = rng.integers(0, 256, t.nbytes, dtype=np.uint8)
+        t.write(0, img)
+        h = core.StorageHandler(t)
+        cols = list(range(ncols))
+        pats = [core.SubscribePattern(int(rng.integers(-L, L + 1)), L, int(rng.integers(1, 3))) for _ in cols]
+        h.set(cols, pats)
+        n = cap * T
+        prio = rng.lognormal(0, 1.5, n).astype(np.float32)
+        prio[rng.random(n) < 0.4] = 0.0
+        if not prio.any():
+            prio[0] = 1.0
+        lengths = rng.integers(1, T + 1, cap).astype(np.int64)
+        B = int(rng.integers(1, 200))
+        u01 = rng.random(B)
+        store = bool(rng.integers(0, 2))
+        s = core.PrioritySampler(n)
+        s.scan(dev(prio), store=store)
+        dsts = [torch.full((B * L * r,), 0x3C, dtype=torch.uint8, device=DEV) for r in rows]
+        flat = torch.empty(B, dtype=torch.int64, device=DEV)
+        s.sample_gather(h, dev(u01), cols, dsts, scale=True, lengths=dev(lengths), out_flat=flat, zero_fill=True)
+        _, st = s.result()
+        ocdf, ol1, _, _ = O.scan(prio)
+        want = O.search(ocdf, ol1, u01, scale=True)
+        tag = (seed, trial, rows, T, cap, L, host, store, B)
+        assert np.array_equal(flat.cpu().numpy(), want), tag
+        assert st[0] & ~N.ST_L1_RESUMMED == 0, tag
+        oi, ot, ol = O.decode(want, T, lengths=lengths)
+        for c, r in enumerate(rows):
+            exp = O.fused_subcopy(img, oi, ot, ol, t.trajectory_stride, t.accu[c], T, r, pats[c].offset, L,
+                                  pats[c].pad == N.PAD_HEAD)
+            assert np.array_equal(dsts[c].cpu().numpy(), exp), (tag, c)
+        s.close(); h.close(); t.close()
