@@ -371,8 +371,9 @@ def run(args, emit=True):
                        "priorities_per_gpu": n_local, "table_bytes_per_gpu": table.nbytes,
                        "parallelism": f"trajectory-id shards x{world}", "slice_layout": "contiguous (the reference's partition)",
                        "l2": "inputs larger than L2 (128 MB of priorities re-read every step per GPU)",
-                       "step": "totals-only scan + level 1 + level 1 and shard total written into every rank's mailbox + one "
-                               "launch that routes, searches and gathers from the owners' HBM over NVLink (no collective)"},
+                       "step": "totals-only scan + level-1 launch that also writes the shard total and the step's number into "
+                               "every rank's mailbox + one launch that routes, searches and gathers from the owners' HBM "
+                               "over NVLink (no collective)"},
             "efficiency_vs_one_gpu_same_workload": None if solo is None else solo["ms_per_step"] / ms_step,
             "global_batch_8192": main_res,
             "global_batch_1024_per_gpu": results[Bg_side],
@@ -395,7 +396,7 @@ def run(args, emit=True):
                     "batches_in_flight": depth, "matches_device_result": e2e_ok_all,
                     "d2h_floor_ms_per_step": floor_s * 1e3, "frac_of_d2h_floor": floor_s / e2e_s,
                     "d2h_floor": "all ranks copying one slice to pinned host memory at once, nothing else running"},
-            "gpu_launches": 4 * K * world, "clocks": clk_main, "parity": head["parity"],
+            "gpu_launches": 3 * K * world,   # per rank and step: scan, level 1 (which also publishes), pull "clocks": clk_main, "parity": head["parity"],
         }
         if emit:
             print(json.dumps(line))
