@@ -155,10 +155,13 @@ def test_pull_from_several_shards_on_one_device(O, rows, T, cap, L, pad, off, ri
                     sh[3].publish(W, j, [box.ptr] * W, epoch, copy_l1=lazy)
                 l1s = [box.ptr + core.mailbox_l1_offset(n, epoch, j) for j in range(W)] if lazy \
                     else [sh[3].l1_ptr for sh in shards]
+                kw_box = dict(kw)
+                if lazy:                              # ... and so do its block totals
+                    kw_box["blks"] = [box.ptr + core.mailbox_blk_offset(n, epoch, j) for j in range(W)]
                 shards[0][3].pull(h, None, cdfs, l1s,
                                   [sh[0].device_ptr for sh in shards], dev(u), cols, dsts, ring=ring,
                                   out_flat=oflat, out_idx=oidx, out_ts=ots, self_shard=(1 if ring else -1),
-                                  mailbox=box.ptr, epoch=epoch, **kw)
+                                  mailbox=box.ptr, epoch=epoch, **kw_box)
             torch.cuda.synchronize()
             box.free()
         else:
