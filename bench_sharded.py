@@ -396,7 +396,8 @@ def run(args, emit=True):
                     "batches_in_flight": depth, "matches_device_result": e2e_ok_all,
                     "d2h_floor_ms_per_step": floor_s * 1e3, "frac_of_d2h_floor": floor_s / e2e_s,
                     "d2h_floor": "all ranks copying one slice to pinned host memory at once, nothing else running"},
-            "gpu_launches": 3 * K * world,   # per rank and step: scan, level 1 (which also publishes), pull "clocks": clk_main, "parity": head["parity"],
+            # per rank and step: scan, level 1 (which also publishes), pull
+            "gpu_launches": 3 * K * world, "clocks": clk_main, "parity": head["parity"],
         }
         if emit:
             print(json.dumps(line))

@@ -691,6 +691,13 @@ class PreparedPull:
         self._a.epoch = int(epoch)
         call("gearb_sampler_pull_ex", self._sampler._h, self._handler._h, C.byref(self._a), _stream(stream))
 
+    def run_at(self, variates_ptr: int, epoch: int = 0, stream=None) -> None:
+        """run() on variates given by their device address (float64, as many as the plan was prepared
+        for, same stride): for callers that have checked the tensor once and only move inside it."""
+        self._a.variates = int(variates_ptr)
+        self._a.epoch = int(epoch)
+        call("gearb_sampler_pull_ex", self._sampler._h, self._handler._h, C.byref(self._a), _stream(stream))
+
 
 def mailbox_bytes(n: int = 0) -> int:
     """Size of a mailbox: the header alone (n = 0), or with room for the peers' level-1 copies."""
