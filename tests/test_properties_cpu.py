@@ -141,3 +141,59 @@ def test_any_variate_draws_an_entry_with_weight(n, seed):
     assert np.array_equal(got, O.np_search(cdf, l1, wild))
     flat = O.uniform(rng.random(100), n)
     assert np.all((flat >= 0) & (flat < n))
+
+
+@settings(deadline=None, max_examples=25, suppress_health_check=[HealthCheck.too_slow])
+@given(st.integers(1, 5), st.integers(1, 6),
+       st.lists(st.tuples(st.integers(0, 9), st.integers(0, 4), st.booleans(), st.booleans(),
+                          st.floats(0.1, 10.0, allow_nan=False)), min_size=1, max_size=150))
+def test_index_protocol_equals_its_state_machine(m, cap, actions):
+    """Any interleaving of simulator and trainer actions: the shared-memory index server and its
+    clients report and hold what the plain state machine does."""
+    import os
+    from gear_b200 import _native as N
+    from gear_b200._native import GearError
+    from gear_b200.ingest import IndexClient, IndexServer
+    key = 0x4B000000 + (os.getpid() % 50000) * 16 + 3
+    srv = IndexServer(key, m, 7, cap)
+    cls = [IndexClient(key, i, m) for i in range(m)]
+    try:
+        assert all(c.connect() == 0 for c in cls)
+        model = O.IngestModel(m, 7, cap)
+        pending = []
+        for kind, who, term, alloc, w in actions:
+            i = who % m
+            if kind < 3:
+                try:
+                    got = cls[i].acquire(0)
+                    assert model.acquire(i) and got == model.cl[i]["tindex"]
+                except GearError as e:
+                    assert e.code == N.ERR_TIMEOUT and not model.acquire(i)
+            elif kind < 5:
+                if model.cl[i]["fly"] and model.slots[i]["owner"] == 0:
+                    assert cls[i].step_inc() == model.step(i)
+            elif kind < 7:
+                if model.cl[i]["fly"] and model.slots[i]["owner"] == 0:
+                    assert cls[i].writeback(term, alloc, w) == model.writeback(i, term, alloc, w)
+            elif kind < 9:
+                ni, nu = srv.scan()
+                infer, upd = model.scan()
+                assert [(int(srv.infer_src[k]), int(srv.infer_idx[k]), int(srv.infer_ts[k])) for k in range(ni)] == infer
+                assert [(int(srv.upd_idx[k]), int(srv.upd_ts[k]), np.float32(srv.upd_w[k])) for k in range(nu)] == upd
+                srv.update(nu)
+                model.update(upd)
+                pending += [s for s, _, _ in infer]
+            else:
+                srv.callback(np.array(pending, np.int32))
+                model.callback(pending)
+                pending = []
+            assert srv.free_count == len(model.free)
+            np.testing.assert_array_equal(srv.weights, model.weights)
+            np.testing.assert_array_equal(srv.timesteps, model.timesteps)
+            # a trajectory is held by at most one simulator, and a held one is not in the free list
+            held = [c_["tindex"] for c_, q in zip(model.cl, model.slots) if c_["fly"]]
+            assert len(set(held)) == len(held) and not (set(held) & set(model.free))
+    finally:
+        for c in cls:
+            c.close()
+        srv.close()
